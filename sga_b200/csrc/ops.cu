@@ -1,0 +1,442 @@
+// Bandwidth-bound model ops in bf16 with fp32 math: RMSNorm (also per-head
+// QK-norm) forward / backward, rotary embedding, SwiGLU, fused softmax
+// cross-entropy (loss and logit gradient in one kernel), embedding gather and
+// its scatter-add backward into the fp32 main-grad buffer.
+//
+// These stand where the reference's external stack calls TransformerEngine /
+// Apex fused ops (examples/llama3/train_1b_adamw.yaml:89-107); none of that
+// source is part of the reference tree.
+#include "common.cuh"
+
+namespace sga {
+
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(p[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 u;
+  __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) p[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return u;
+}
+
+// ---------------------------------------------------------------- RMSNorm
+// One warp per row of H elements (H % 8 == 0). y = x * rstd * w.
+// Rows may be strided (row_stride elements) so the kernel also serves the
+// per-head QK-norm on a slice of the fused QKV activation.
+__global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                                          const __nv_bfloat16* __restrict__ w,
+                                                          __nv_bfloat16* __restrict__ y, float* __restrict__ rstd,
+                                                          long long rows, int H, long long x_stride,
+                                                          long long y_stride, int rows_per_group,
+                                                          long long group_stride_x, long long group_stride_y,
+                                                          float eps) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  // row -> (group, r): address = group * group_stride + r * stride
+  const long long grp = row / rows_per_group, r = row % rows_per_group;
+  const __nv_bfloat16* xr = x + grp * group_stride_x + r * x_stride;
+  __nv_bfloat16* yr = y + grp * group_stride_y + r * y_stride;
+  const int nch = H >> 3;
+  float ss = 0.f;
+  for (int c = lane; c < nch; c += 32) {
+    float f[8];
+    unpack8(*reinterpret_cast<const uint4*>(xr + c * 8), f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+  }
+  ss = warp_sum(ss);
+  const float rs = rsqrtf(ss / (float)H + eps);
+  if (lane == 0 && rstd) rstd[row] = rs;
+  for (int c = lane; c < nch; c += 32) {
+    float f[8], g[8];
+    unpack8(*reinterpret_cast<const uint4*>(xr + c * 8), f);
+    unpack8(*reinterpret_cast<const uint4*>(w + c * 8), g);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = f[i] * rs * g[i];
+    *reinterpret_cast<uint4*>(yr + c * 8) = pack8(f);
+  }
+}
+
+// dx = rstd * (dy*w - xhat * mean(dy*w*xhat)); dw partial per CTA.
+// Each warp walks rows (strided by total warps); lanes own column chunks.
+template <int NCH>  // chunks of 8 columns per lane: H <= NCH * 256
+__global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                                          const __nv_bfloat16* __restrict__ w,
+                                                          const __nv_bfloat16* __restrict__ dy,
+                                                          const float* __restrict__ rstd,
+                                                          __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_part,
+                                                          long long rows, int H, long long x_stride,
+                                                          long long dy_stride, long long dx_stride,
+                                                          int rows_per_group, long long gsx, long long gsdy,
+                                                          long long gsdx, int accumulate_dx) {
+  extern __shared__ float sdw[];  // [H]
+  const int lane = threadIdx.x & 31;
+  const int nch = H >> 3;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) sdw[i] = 0.f;
+  __syncthreads();
+  float dwacc[NCH][8];
+#pragma unroll
+  for (int j = 0; j < NCH; ++j)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dwacc[j][i] = 0.f;
+  const long long warps = (long long)gridDim.x * (blockDim.x >> 5);
+  for (long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows; row += warps) {
+    const long long grp = row / rows_per_group, r = row % rows_per_group;
+    const __nv_bfloat16* xr = x + grp * gsx + r * x_stride;
+    const __nv_bfloat16* dyr = dy + grp * gsdy + r * dy_stride;
+    __nv_bfloat16* dxr = dx + grp * gsdx + r * dx_stride;
+    const float rs = rstd[row];
+    float dot = 0.f;
+    float xh[NCH][8], gw[NCH][8];
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) {
+      const int c = lane + 32 * j;
+      if (c < nch) {
+        float fx[8], fw[8], fd[8];
+        unpack8(*reinterpret_cast<const uint4*>(xr + c * 8), fx);
+        unpack8(*reinterpret_cast<const uint4*>(w + c * 8), fw);
+        unpack8(*reinterpret_cast<const uint4*>(dyr + c * 8), fd);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          xh[j][i] = fx[i] * rs;
+          gw[j][i] = fd[i] * fw[i];
+          dot += gw[j][i] * xh[j][i];
+          dwacc[j][i] += fd[i] * xh[j][i];
+        }
+      }
+    }
+    dot = warp_sum(dot) / (float)H;
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) {
+      const int c = lane + 32 * j;
+      if (c < nch) {
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = rs * (gw[j][i] - xh[j][i] * dot);
+        if (accumulate_dx) {
+          float prev[8];
+          unpack8(*reinterpret_cast<const uint4*>(dxr + c * 8), prev);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] += prev[i];
+        }
+        *reinterpret_cast<uint4*>(dxr + c * 8) = pack8(o);
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < NCH; ++j) {
+    const int c = lane + 32 * j;
+    if (c < nch) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) atomicAdd(&sdw[c * 8 + i], dwacc[j][i]);
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < H; i += blockDim.x) dw_part[(long long)blockIdx.x * H + i] = sdw[i];
+}
+
+// out[i] (+)= sum_b part[b][i]  (fixed order)
+__global__ void colsum_kernel(const float* __restrict__ part, int nb, int H, float* __restrict__ out, int accumulate) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= H) return;
+  float s = 0.f;
+  for (int b = 0; b < nb; ++b) s += part[(long long)b * H + i];
+  out[i] = accumulate ? out[i] + s : s;
+}
+
+// ------------------------------------------------------------------- RoPE
+// In place on rows of [T, nheads, hd] embedded in a wider activation
+// (row pitch `pitch` elements, heads start at column `col0`). Pairs are
+// (i, i + hd/2). cos/sin: [S, hd/2] fp32. sign = +1 forward, -1 backward.
+__global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const float* __restrict__ cs, const float* __restrict__ sn,
+                            long long T, int S, int nheads, int hd, long long pitch, int col0, float sign) {
+  const int half = hd >> 1;
+  const long long total = T * nheads * half;
+  const long long gstride = (long long)gridDim.x * blockDim.x;
+  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += gstride) {
+    const int i = (int)(e % half);
+    const long long th = e / half;
+    const int h = (int)(th % nheads);
+    const long long t = th / nheads;
+    const int pos = (int)(t % S);
+    __nv_bfloat16* p = x + t * pitch + col0 + (long long)h * hd;
+    const float a = __bfloat162float(p[i]), b = __bfloat162float(p[i + half]);
+    const float c = cs[pos * half + i], s = sn[pos * half + i] * sign;
+    p[i] = __float2bfloat16_rn(a * c - b * s);
+    p[i + half] = __float2bfloat16_rn(b * c + a * s);
+  }
+}
+
+// ----------------------------------------------------------------- SwiGLU
+// in: [T, 2F] = gate | up ; out: [T, F] = silu(gate) * up
+__global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, long long T,
+                                  int F) {
+  const long long total = T * (F >> 3);
+  const long long gstride = (long long)gridDim.x * blockDim.x;
+  const int fc = F >> 3;
+  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += gstride) {
+    const long long t = e / fc;
+    const int c = (int)(e % fc);
+    float g[8], u[8];
+    unpack8(*reinterpret_cast<const uint4*>(in + t * 2 * F + c * 8), g);
+    unpack8(*reinterpret_cast<const uint4*>(in + t * 2 * F + F + c * 8), u);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) g[i] = g[i] / (1.f + __expf(-g[i])) * u[i];
+    *reinterpret_cast<uint4*>(out + t * F + c * 8) = pack8(g);
+  }
+}
+// din: [T, 2F] from dout [T, F] and the saved input.
+__global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bfloat16* __restrict__ dout,
+                                  __nv_bfloat16* __restrict__ din, long long T, int F) {
+  const long long total = T * (F >> 3);
+  const long long gstride = (long long)gridDim.x * blockDim.x;
+  const int fc = F >> 3;
+  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += gstride) {
+    const long long t = e / fc;
+    const int c = (int)(e % fc);
+    float g[8], u[8], d[8], dg[8], du[8];
+    unpack8(*reinterpret_cast<const uint4*>(in + t * 2 * F + c * 8), g);
+    unpack8(*reinterpret_cast<const uint4*>(in + t * 2 * F + F + c * 8), u);
+    unpack8(*reinterpret_cast<const uint4*>(dout + t * F + c * 8), d);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float sg = 1.f / (1.f + __expf(-g[i]));
+      const float silu = g[i] * sg;
+      du[i] = d[i] * silu;
+      dg[i] = d[i] * u[i] * (sg * (1.f + g[i] * (1.f - sg)));
+    }
+    *reinterpret_cast<uint4*>(din + t * 2 * F + c * 8) = pack8(dg);
+    *reinterpret_cast<uint4*>(din + t * 2 * F + F + c * 8) = pack8(du);
+  }
+}
+
+// ---------------------------------------------------------- cross-entropy
+// One CTA per row. loss[t] = logsumexp(z) - z[target]; logits are replaced in
+// place by (softmax - onehot) * grad_scale (the gradient of mean loss).
+__global__ void __launch_bounds__(1024) ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits,
+                                                          const long long* __restrict__ targets,
+                                                          float* __restrict__ loss, int V, long long pitch,
+                                                          float grad_scale, int write_grad) {
+  __shared__ float red[32];
+  __shared__ float bc[2];
+  const long long t = blockIdx.x;
+  __nv_bfloat16* z = logits + t * pitch;
+  const int nch = V >> 3;
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  float mx = -INFINITY;
+  for (int c = threadIdx.x; c < nch; c += blockDim.x) {
+    float f[8];
+    unpack8(*reinterpret_cast<const uint4*>(z + c * 8), f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) mx = fmaxf(mx, f[i]);
+  }
+  mx = warp_max(mx);
+  if (lane == 0) red[wid] = mx;
+  __syncthreads();
+  if (wid == 0) {
+    float v = lane < (int)(blockDim.x >> 5) ? red[lane] : -INFINITY;
+    v = warp_max(v);
+    if (lane == 0) bc[0] = v;
+  }
+  __syncthreads();
+  mx = bc[0];
+  float se = 0.f;
+  for (int c = threadIdx.x; c < nch; c += blockDim.x) {
+    float f[8];
+    unpack8(*reinterpret_cast<const uint4*>(z + c * 8), f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) se += __expf(f[i] - mx);
+  }
+  se = warp_sum(se);
+  __syncthreads();
+  if (lane == 0) red[wid] = se;
+  __syncthreads();
+  if (wid == 0) {
+    float v = lane < (int)(blockDim.x >> 5) ? red[lane] : 0.f;
+    v = warp_sum(v);
+    if (lane == 0) bc[1] = v;
+  }
+  __syncthreads();
+  se = bc[1];
+  const long long tgt = targets[t];
+  const float lse = mx + __logf(se);
+  if (threadIdx.x == 0) {
+    const bool valid = tgt >= 0 && tgt < V;
+    loss[t] = valid ? lse - __bfloat162float(z[tgt]) : 0.f;
+  }
+  if (!write_grad) return;
+  __syncthreads();  // z[tgt] read above before it is overwritten
+  const float inv = 1.f / se;
+  const bool valid = tgt >= 0 && tgt < V;
+  const float gs = valid ? grad_scale : 0.f;
+  for (int c = threadIdx.x; c < nch; c += blockDim.x) {
+    float f[8];
+    unpack8(*reinterpret_cast<const uint4*>(z + c * 8), f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float p = __expf(f[i] - mx) * inv;
+      if ((long long)(c * 8 + i) == tgt) p -= 1.f;
+      f[i] = p * gs;
+    }
+    *reinterpret_cast<uint4*>(z + c * 8) = pack8(f);
+  }
+}
+
+// -------------------------------------------------------------- embedding
+__global__ void embed_fwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ W,
+                                 __nv_bfloat16* __restrict__ out, long long T, int H) {
+  const int hc = H >> 3;
+  const long long total = T * hc;
+  const long long gstride = (long long)gridDim.x * blockDim.x;
+  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += gstride) {
+    const long long t = e / hc;
+    const int c = (int)(e % hc);
+    *reinterpret_cast<uint4*>(out + t * H + c * 8) = *reinterpret_cast<const uint4*>(W + ids[t] * H + c * 8);
+  }
+}
+__global__ void embed_bwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ dout,
+                                 float* __restrict__ main_grad, long long T, int H) {
+  const int hc = H >> 3;
+  const long long total = T * hc;
+  const long long gstride = (long long)gridDim.x * blockDim.x;
+  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += gstride) {
+    const long long t = e / hc;
+    const int c = (int)(e % hc);
+    float f[8];
+    unpack8(*reinterpret_cast<const uint4*>(dout + t * H + c * 8), f);
+    float* g = main_grad + ids[t] * H + c * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) atomicAdd(g + i, f[i]);
+  }
+}
+
+// bf16 elementwise add: out = a + b (residual joins not covered by a GEMM epilogue)
+__global__ void add_bf16_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b,
+                                __nv_bfloat16* __restrict__ out, long long n8) {
+  const long long gstride = (long long)gridDim.x * blockDim.x;
+  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < n8; e += gstride) {
+    float fa[8], fb[8];
+    unpack8(*reinterpret_cast<const uint4*>(a + e * 8), fa);
+    unpack8(*reinterpret_cast<const uint4*>(b + e * 8), fb);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) fa[i] += fb[i];
+    *reinterpret_cast<uint4*>(out + e * 8) = pack8(fa);
+  }
+}
+
+static inline int grid1d(long long n, int threads, int cap = 148 * 16) {
+  long long b = (n + threads - 1) / threads;
+  if (b < 1) b = 1;
+  if (b > cap) b = cap;
+  return (int)b;
+}
+
+}  // namespace sga
+
+using namespace sga;
+#define ST(s) reinterpret_cast<cudaStream_t>(s)
+#define LAUNCH_OK() (cudaGetLastError() == cudaSuccess ? 0 : -4)
+
+SGA_API int sga_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, long long rows, int H,
+                            long long x_stride, long long y_stride, int rows_per_group, long long gsx,
+                            long long gsy, float eps, void* stream) {
+  if (rows <= 0) return 0;
+  if (H & 7) return -5;
+  const int wpb = 8;
+  rmsnorm_fwd_kernel<<<(unsigned)((rows + wpb - 1) / wpb), wpb * 32, 0, ST(stream)>>>(
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, rstd, rows, H, x_stride, y_stride,
+      rows_per_group, gsx, gsy, eps);
+  return LAUNCH_OK();
+}
+
+// dw_part: scratch [nblocks * H] floats with nblocks = sga_rmsnorm_bwd_blocks().
+SGA_API int sga_rmsnorm_bwd_blocks() { return 148 * 2; }
+
+SGA_API int sga_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rstd, void* dx,
+                            float* dw_part, float* dw_out, int accumulate_dw, long long rows, int H,
+                            long long x_stride, long long dy_stride, long long dx_stride, int rows_per_group,
+                            long long gsx, long long gsdy, long long gsdx, int accumulate_dx, void* stream) {
+  if (rows <= 0) return 0;
+  if (H & 7 || H > 8192) return -5;
+  const int nb = sga_rmsnorm_bwd_blocks();
+  const int nch = (H / 8 + 31) / 32;
+  const size_t smem = (size_t)H * 4;
+#define RB(N)                                                                                                     \
+  rmsnorm_bwd_kernel<N><<<nb, 256, smem, ST(stream)>>>(                                                            \
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)dy, rstd, (__nv_bfloat16*)dx, dw_part, \
+      rows, H, x_stride, dy_stride, dx_stride, rows_per_group, gsx, gsdy, gsdx, accumulate_dx)
+  if (nch <= 1) RB(1);
+  else if (nch <= 2) RB(2);
+  else if (nch <= 4) RB(4);
+  else if (nch <= 8) RB(8);
+  else if (nch <= 16) RB(16);
+  else RB(32);
+#undef RB
+  colsum_kernel<<<(H + 255) / 256, 256, 0, ST(stream)>>>(dw_part, nb, H, dw_out, accumulate_dw);
+  return LAUNCH_OK();
+}
+
+SGA_API int sga_rope(void* x, const float* cs, const float* sn, long long T, int S, int nheads, int hd,
+                     long long pitch, int col0, float sign, void* stream) {
+  const long long total = T * nheads * (hd / 2);
+  if (total <= 0) return 0;
+  rope_kernel<<<grid1d(total, 256), 256, 0, ST(stream)>>>((__nv_bfloat16*)x, cs, sn, T, S, nheads, hd, pitch, col0,
+                                                           sign);
+  return LAUNCH_OK();
+}
+
+SGA_API int sga_swiglu_fwd(const void* in, void* out, long long T, int F, void* stream) {
+  if (T <= 0) return 0;
+  if (F & 7) return -5;
+  swiglu_fwd_kernel<<<grid1d(T * (F / 8), 256), 256, 0, ST(stream)>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out,
+                                                                      T, F);
+  return LAUNCH_OK();
+}
+SGA_API int sga_swiglu_bwd(const void* in, const void* dout, void* din, long long T, int F, void* stream) {
+  if (T <= 0) return 0;
+  if (F & 7) return -5;
+  swiglu_bwd_kernel<<<grid1d(T * (F / 8), 256), 256, 0, ST(stream)>>>(
+      (const __nv_bfloat16*)in, (const __nv_bfloat16*)dout, (__nv_bfloat16*)din, T, F);
+  return LAUNCH_OK();
+}
+
+SGA_API int sga_cross_entropy(void* logits, const long long* targets, float* loss, long long T, int V,
+                              long long pitch, float grad_scale, int write_grad, void* stream) {
+  if (T <= 0) return 0;
+  if (V & 7 || pitch & 7) return -5;
+  ce_fwd_bwd_kernel<<<(unsigned)T, 1024, 0, ST(stream)>>>((__nv_bfloat16*)logits, targets, loss, V, pitch, grad_scale,
+                                                          write_grad);
+  return LAUNCH_OK();
+}
+
+SGA_API int sga_embed_fwd(const long long* ids, const void* W, void* out, long long T, int H, void* stream) {
+  if (T <= 0) return 0;
+  if (H & 7) return -5;
+  embed_fwd_kernel<<<grid1d(T * (H / 8), 256), 256, 0, ST(stream)>>>(ids, (const __nv_bfloat16*)W,
+                                                                     (__nv_bfloat16*)out, T, H);
+  return LAUNCH_OK();
+}
+SGA_API int sga_embed_bwd(const long long* ids, const void* dout, float* main_grad, long long T, int H,
+                          void* stream) {
+  if (T <= 0) return 0;
+  if (H & 7) return -5;
+  embed_bwd_kernel<<<grid1d(T * (H / 8), 256), 256, 0, ST(stream)>>>(ids, (const __nv_bfloat16*)dout, main_grad, T,
+                                                                     H);
+  return LAUNCH_OK();
+}
+SGA_API int sga_add_bf16(const void* a, const void* b, void* out, long long n, void* stream) {
+  if (n <= 0) return 0;
+  if (n & 7) return -5;
+  add_bf16_kernel<<<grid1d(n / 8, 256), 256, 0, ST(stream)>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)b,
+                                                              (__nv_bfloat16*)out, n / 8);
+  return LAUNCH_OK();
+}

@@ -1,0 +1,425 @@
+// Support selection and support-form kernels (single GPU):
+//
+//   sga_hist_top        histogram of the top bits of |x|'s bit pattern, with
+//                       stride subsampling (the exact / balanced / fast tiers)
+//   sga_hist_low16      second radix digit: low-16-bit histogram of the
+//                       elements whose top-16 key equals one bin (gives the
+//                       exact k-th value without gathering candidates)
+//   sga_mask_ge         uint8 mask of (key >= bin) or (|x| >= thr), plus count
+//   sga_mask_stats      count + the two position checksums of a mask
+//   sga_compact_mask    mask -> ascending int32 index list (block counts,
+//                       scan, ordered scatter); also emits the 1024-stride
+//                       directory table of lower bounds
+//   sga_pack / sga_scatter / block variants / descriptors
+//   sga_block_reduce    per-block mean|max of |x|
+//   sga_expand_blocks   block mask -> element mask
+//
+// Replaces sga/plugins/selection/_histogram.py (bincount/cumsum/kthvalue
+// loops), sga/support.py:57-206 (chunked nonzero, block heads, descriptors),
+// sga/kernels.py:49-139 (pack / scatter / block gather / block scatter) and the
+// chunked checksum loop of sga/engine.py:1341-1359.
+#include "common.cuh"
+
+namespace sga {
+
+__device__ __forceinline__ uint32_t abs_bits(float x) { return __float_as_uint(x) & 0x7FFFFFFFu; }
+
+// ------------------------------------------------------------- histograms
+// Global int64 histogram; each CTA privatises into 32-bit shared counters when
+// nbins fits (<= 32769 bins -> 128 KB + 4 B of dynamic shared memory).
+__global__ void __launch_bounds__(512) hist_top_kernel(const float* __restrict__ x, long long n, int shift,
+                                                       int stride, int nbins, long long* __restrict__ hist,
+                                                       long long* __restrict__ nonfinite) {
+  extern __shared__ uint32_t sh[];
+  for (int i = threadIdx.x; i < nbins; i += blockDim.x) sh[i] = 0;
+  __syncthreads();
+  const long long ns = (n + stride - 1) / stride;  // sampled count
+  const long long gstride = (long long)gridDim.x * blockDim.x;
+  int bad = 0;
+  for (long long s = (long long)blockIdx.x * blockDim.x + threadIdx.x; s < ns; s += gstride) {
+    const uint32_t b = abs_bits(x[s * stride]);
+    if (b >= 0x7F800000u) ++bad;
+    atomicAdd(&sh[b >> shift], 1u);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < nbins; i += blockDim.x) {
+    const uint32_t c = sh[i];
+    if (c) atomicAdd(reinterpret_cast<unsigned long long*>(hist + i), (unsigned long long)c);
+  }
+  if (nonfinite && bad) atomicAdd(reinterpret_cast<unsigned long long*>(nonfinite), (unsigned long long)bad);
+}
+
+__global__ void __launch_bounds__(512) hist_low16_kernel(const float* __restrict__ x, long long n, int bin,
+                                                         long long* __restrict__ hist) {
+  extern __shared__ uint32_t sh[];  // 65536 counters = 256 KB is too large: use 2 passes of 32768
+  // The low 16 bits are split by their top bit into two half-histograms of
+  // 32768 counters; blockIdx.y selects the half so shared memory stays 128 KB.
+  const uint32_t half = blockIdx.y;
+  for (int i = threadIdx.x; i < 32768; i += blockDim.x) sh[i] = 0;
+  __syncthreads();
+  const long long gstride = (long long)gridDim.x * blockDim.x;
+  for (long long s = (long long)blockIdx.x * blockDim.x + threadIdx.x; s < n; s += gstride) {
+    const uint32_t b = abs_bits(x[s]);
+    if ((int)(b >> 16) == bin && ((b >> 15) & 1u) == half) atomicAdd(&sh[b & 0x7FFFu], 1u);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < 32768; i += blockDim.x) {
+    const uint32_t c = sh[i];
+    if (c) atomicAdd(reinterpret_cast<unsigned long long*>(hist + half * 32768 + i), (unsigned long long)c);
+  }
+}
+
+// ------------------------------------------------------------------ masks
+// mode 0: mask = (abs_bits(x) >> shift) >= bin ; mode 1: mask = |x| >= thr.
+__global__ void __launch_bounds__(256) mask_ge_kernel(const float* __restrict__ x, long long n, int mode, int shift,
+                                                      int bin, float thr, uint8_t* __restrict__ mask,
+                                                      long long* __restrict__ count) {
+  long long local = 0;
+  const long long gstride = (long long)gridDim.x * blockDim.x * 4;
+  for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += gstride) {
+    uint8_t mk[4];
+    const int lim = (int)min((long long)4, n - i);
+    for (int j = 0; j < lim; ++j) {
+      const float v = x[i + j];
+      const bool on = mode == 0 ? (int)(abs_bits(v) >> shift) >= bin : fabsf(v) >= thr;
+      mk[j] = on ? 1 : 0;
+      local += on;
+    }
+    if (lim == 4) *reinterpret_cast<uchar4*>(mask + i) = *reinterpret_cast<uchar4*>(mk);
+    else for (int j = 0; j < lim; ++j) mask[i + j] = mk[j];
+  }
+  // warp + block reduce then one atomic per block
+  for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
+  __shared__ long long red[8];
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = local;
+  __syncthreads();
+  if (threadIdx.x == 0 && count) {
+    long long t = 0;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += red[w];
+    if (t) atomicAdd(reinterpret_cast<unsigned long long*>(count), (unsigned long long)t);
+  }
+}
+
+// out[0] += count, out[1] += sum(pos), out[2] += sum((pos % 9973) * (pos % 1009)) over mask-on positions.
+__global__ void __launch_bounds__(256) mask_stats_kernel(const uint8_t* __restrict__ mask, long long n,
+                                                         long long* __restrict__ out) {
+  long long c = 0, s1 = 0, s2 = 0;
+  const long long gstride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gstride) {
+    if (mask[i]) {
+      ++c;
+      s1 += i;
+      s2 += (i % 9973) * (i % 1009);
+    }
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    c += __shfl_xor_sync(0xffffffffu, c, o);
+    s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+    s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+  }
+  if ((threadIdx.x & 31) == 0) {
+    atomicAdd(reinterpret_cast<unsigned long long*>(out + 0), (unsigned long long)c);
+    atomicAdd(reinterpret_cast<unsigned long long*>(out + 1), (unsigned long long)s1);
+    atomicAdd(reinterpret_cast<unsigned long long*>(out + 2), (unsigned long long)s2);
+  }
+}
+
+// ------------------------------------------------------------- compaction
+constexpr int CP_THREADS = 256;
+constexpr int CP_ITEMS = 16;                       // consecutive mask bytes per thread
+constexpr int CP_TILE = CP_THREADS * CP_ITEMS;     // 4096 elements per CTA
+
+__global__ void __launch_bounds__(CP_THREADS) compact_count_kernel(const uint8_t* __restrict__ mask, long long n,
+                                                                   int* __restrict__ block_counts) {
+  const long long base = (long long)blockIdx.x * CP_TILE + (long long)threadIdx.x * CP_ITEMS;
+  int c = 0;
+  if (base + CP_ITEMS <= n) {
+    const uint4 v = *reinterpret_cast<const uint4*>(mask + base);
+    const uint32_t wds[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      for (int b = 0; b < 4; ++b) c += ((wds[j] >> (8 * b)) & 0xFFu) != 0;
+  } else {
+    for (long long i = base; i < n && i < base + CP_ITEMS; ++i) c += mask[i] != 0;
+  }
+  __shared__ int red[CP_THREADS / 32];
+  for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = c;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int t = 0;
+    for (int w = 0; w < CP_THREADS / 32; ++w) t += red[w];
+    block_counts[blockIdx.x] = t;
+  }
+}
+
+// Exclusive scan of block counts in place (single CTA, any length); total -> *total_out.
+__global__ void __launch_bounds__(1024) scan_counts_kernel(int* __restrict__ counts, int nblocks,
+                                                           long long* __restrict__ total_out) {
+  __shared__ int warp_tot[32];
+  __shared__ int carry_s;
+  if (threadIdx.x == 0) carry_s = 0;
+  __syncthreads();
+  for (int base = 0; base < nblocks; base += 1024) {
+    const int i = base + threadIdx.x;
+    const int v = i < nblocks ? counts[i] : 0;
+    int x = v;
+    for (int o = 1; o < 32; o <<= 1) {
+      const int y = __shfl_up_sync(0xffffffffu, x, o);
+      if ((threadIdx.x & 31) >= o) x += y;
+    }
+    if ((threadIdx.x & 31) == 31) warp_tot[threadIdx.x >> 5] = x;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      int t = warp_tot[threadIdx.x];
+      for (int o = 1; o < 32; o <<= 1) {
+        const int y = __shfl_up_sync(0xffffffffu, t, o);
+        if (threadIdx.x >= o) t += y;
+      }
+      warp_tot[threadIdx.x] = t;
+    }
+    __syncthreads();
+    const int warp_prefix = (threadIdx.x >> 5) ? warp_tot[(threadIdx.x >> 5) - 1] : 0;
+    const int carry = carry_s;
+    if (i < nblocks) counts[i] = carry + warp_prefix + x - v;
+    __syncthreads();
+    if (threadIdx.x == 1023) carry_s = carry + warp_prefix + x;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0 && total_out) *total_out = carry_s;
+}
+
+__global__ void __launch_bounds__(CP_THREADS) compact_scatter_kernel(const uint8_t* __restrict__ mask, long long n,
+                                                                     const int* __restrict__ block_offsets,
+                                                                     int* __restrict__ idx_out, long long cap,
+                                                                     int* __restrict__ err) {
+  const long long base = (long long)blockIdx.x * CP_TILE + (long long)threadIdx.x * CP_ITEMS;
+  uint8_t mk[CP_ITEMS];
+  int c = 0;
+#pragma unroll
+  for (int j = 0; j < CP_ITEMS; ++j) {
+    mk[j] = (base + j < n) ? mask[base + j] : 0;
+    c += mk[j] != 0;
+  }
+  // block exclusive scan of c
+  __shared__ int warp_tot[CP_THREADS / 32];
+  int x = c;
+  for (int o = 1; o < 32; o <<= 1) {
+    const int y = __shfl_up_sync(0xffffffffu, x, o);
+    if ((threadIdx.x & 31) >= o) x += y;
+  }
+  if ((threadIdx.x & 31) == 31) warp_tot[threadIdx.x >> 5] = x;
+  __syncthreads();
+  int prefix = 0;
+  for (int w = 0; w < (int)(threadIdx.x >> 5); ++w) prefix += warp_tot[w];
+  long long pos = (long long)block_offsets[blockIdx.x] + prefix + x - c;
+#pragma unroll
+  for (int j = 0; j < CP_ITEMS; ++j) {
+    if (mk[j]) {
+      if (pos < cap) idx_out[pos] = (int)(base + j);
+      else if (err) atomicOr(err, SGA_ERR_CAPACITY);
+      ++pos;
+    }
+  }
+}
+
+// table[j] = lower_bound(idx[0..k), j * 1024) for j in [0, ntable).
+__global__ void dir_table_kernel(const int* __restrict__ idx, long long k, int* __restrict__ table, int ntable) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= ntable) return;
+  const long long target = (long long)j * 1024;
+  long long lo = 0, hi = k;
+  while (lo < hi) {
+    const long long mid = (lo + hi) >> 1;
+    if ((long long)idx[mid] < target) lo = mid + 1; else hi = mid;
+  }
+  table[j] = (int)lo;
+}
+
+// ----------------------------------------------------------- pack/scatter
+// vals[i] = grad[idx[i]] * factor; optionally grad[idx[i]] = 0.
+__global__ void pack_kernel(float* __restrict__ grad, const int* __restrict__ idx, long long k,
+                            float* __restrict__ vals, float factor, int scale, int zero) {
+  const long long gstride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < k; i += gstride) {
+    const int p = idx[i];
+    const float v = grad[p];
+    vals[i] = scale ? v * factor : v;
+    if (zero) grad[p] = 0.f;
+  }
+}
+__global__ void scatter_kernel(float* __restrict__ dst, const int* __restrict__ idx, const float* __restrict__ vals,
+                               long long k, int add) {
+  const long long gstride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < k; i += gstride) {
+    if (add) dst[idx[i]] += vals[i]; else dst[idx[i]] = vals[i];
+  }
+}
+// Block forms: heads[b] is the first element of an X-element run clamped by
+// mask (lanes whose mask byte is 0 carry 0 on gather and are skipped on scatter).
+__global__ void gather_blocks_kernel(float* __restrict__ grad, const uint8_t* __restrict__ mask,
+                                     const int* __restrict__ heads, long long kb, int X, long long n,
+                                     float* __restrict__ vals, float factor, int scale, int zero) {
+  const long long total = kb * X;
+  const long long gstride = (long long)gridDim.x * blockDim.x;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += gstride) {
+    const long long p = (long long)heads[t / X] + (t % X);
+    float v = 0.f;
+    if (p < n && mask[p]) {
+      v = grad[p];
+      if (scale) v = v * factor;
+      if (zero) grad[p] = 0.f;
+    }
+    vals[t] = v;
+  }
+}
+__global__ void scatter_blocks_kernel(float* __restrict__ grad, const uint8_t* __restrict__ mask,
+                                      const int* __restrict__ heads, long long kb, int X, long long n,
+                                      const float* __restrict__ vals) {
+  const long long total = kb * X;
+  const long long gstride = (long long)gridDim.x * blockDim.x;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += gstride) {
+    const long long p = (long long)heads[t / X] + (t % X);
+    if (p < n && mask[p]) grad[p] = vals[t];
+  }
+}
+
+// Per-block reduce of |x| over blocks of X elements inside one span [0, n):
+// out[b] = mean or max over the block's real length.
+__global__ void block_reduce_kernel(const float* __restrict__ x, long long n, int X, int use_max,
+                                    float* __restrict__ out, long long nblocks) {
+  const long long gstride = (long long)gridDim.x * blockDim.x;
+  for (long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x; b < nblocks; b += gstride) {
+    const long long s = b * X;
+    const long long e = min(n, s + X);
+    float acc = 0.f;
+    for (long long i = s; i < e; ++i) {
+      const float a = fabsf(x[i]);
+      acc = use_max ? fmaxf(acc, a) : acc + a;
+    }
+    out[b] = use_max ? acc : acc / (float)(e - s);
+  }
+}
+__global__ void expand_blocks_kernel(const uint8_t* __restrict__ bmask, long long nblocks, int X, long long n,
+                                     uint8_t* __restrict__ mask) {
+  const long long gstride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gstride) mask[i] = bmask[i / X];
+}
+
+static inline int grid_for(long long n, int per_block, int cap = 148 * 8) {
+  long long b = (n + per_block - 1) / per_block;
+  if (b < 1) b = 1;
+  if (b > cap) b = cap;
+  return (int)b;
+}
+
+}  // namespace sga
+
+using namespace sga;
+#define ST(s) reinterpret_cast<cudaStream_t>(s)
+#define LAUNCH_OK() (cudaGetLastError() == cudaSuccess ? 0 : -4)
+
+SGA_API int sga_hist_top(const float* x, long long n, int shift, int stride, int nbins, long long* hist,
+                         long long* nonfinite, void* stream) {
+  if (n <= 0) return 0;
+  if (nbins > 32769) return -1;
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(hist_top_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32769 * 4) != cudaSuccess)
+      return -3;
+    attr = true;
+  }
+  const long long ns = (n + stride - 1) / stride;
+  hist_top_kernel<<<grid_for(ns, 512 * 16, 148), 512, nbins * 4, ST(stream)>>>(x, n, shift, stride, nbins, hist,
+                                                                                nonfinite);
+  return LAUNCH_OK();
+}
+
+SGA_API int sga_hist_low16(const float* x, long long n, int bin, long long* hist, void* stream) {
+  if (n <= 0) return 0;
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(hist_low16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32768 * 4) !=
+        cudaSuccess)
+      return -3;
+    attr = true;
+  }
+  dim3 grid(grid_for(n, 512 * 16, 74), 2);
+  hist_low16_kernel<<<grid, 512, 32768 * 4, ST(stream)>>>(x, n, bin, hist);
+  return LAUNCH_OK();
+}
+
+SGA_API int sga_mask_ge(const float* x, long long n, int mode, int shift, int bin, float thr, uint8_t* mask,
+                        long long* count, void* stream) {
+  if (n <= 0) return 0;
+  mask_ge_kernel<<<grid_for(n, 1024), 256, 0, ST(stream)>>>(x, n, mode, shift, bin, thr, mask, count);
+  return LAUNCH_OK();
+}
+
+SGA_API int sga_mask_stats(const uint8_t* mask, long long n, long long* out3, void* stream) {
+  if (n <= 0) return 0;
+  mask_stats_kernel<<<grid_for(n, 256 * 16), 256, 0, ST(stream)>>>(mask, n, out3);
+  return LAUNCH_OK();
+}
+
+// idx_out receives the ascending positions of non-zero mask bytes; *total_out
+// the count. `block_counts` is scratch of ceil(n / 4096) ints. Positions
+// beyond `cap` are dropped and SGA_ERR_CAPACITY is set in *err.
+SGA_API int sga_compact_mask(const uint8_t* mask, long long n, int* block_counts, int* idx_out, long long cap,
+                             long long* total_out, int* err, void* stream) {
+  if (n <= 0) return 0;
+  if (n >= (1LL << 31)) return -6;
+  const int nb = (int)((n + CP_TILE - 1) / CP_TILE);
+  compact_count_kernel<<<nb, CP_THREADS, 0, ST(stream)>>>(mask, n, block_counts);
+  scan_counts_kernel<<<1, 1024, 0, ST(stream)>>>(block_counts, nb, total_out);
+  compact_scatter_kernel<<<nb, CP_THREADS, 0, ST(stream)>>>(mask, n, block_counts, idx_out, cap, err);
+  return LAUNCH_OK();
+}
+
+SGA_API int sga_dir_table(const int* idx, long long k, int* table, int ntable, void* stream) {
+  if (ntable <= 0) return 0;
+  dir_table_kernel<<<(ntable + 255) / 256, 256, 0, ST(stream)>>>(idx, k, table, ntable);
+  return LAUNCH_OK();
+}
+
+SGA_API int sga_pack(float* grad, const int* idx, long long k, float* vals, float factor, int scale, int zero,
+                     void* stream) {
+  if (k <= 0) return 0;
+  pack_kernel<<<grid_for(k, 256), 256, 0, ST(stream)>>>(grad, idx, k, vals, factor, scale, zero);
+  return LAUNCH_OK();
+}
+
+SGA_API int sga_scatter(float* dst, const int* idx, const float* vals, long long k, int add, void* stream) {
+  if (k <= 0) return 0;
+  scatter_kernel<<<grid_for(k, 256), 256, 0, ST(stream)>>>(dst, idx, vals, k, add);
+  return LAUNCH_OK();
+}
+
+SGA_API int sga_gather_blocks(float* grad, const uint8_t* mask, const int* heads, long long kb, int X, long long n,
+                              float* vals, float factor, int scale, int zero, void* stream) {
+  if (kb <= 0) return 0;
+  gather_blocks_kernel<<<grid_for(kb * X, 256), 256, 0, ST(stream)>>>(grad, mask, heads, kb, X, n, vals, factor,
+                                                                      scale, zero);
+  return LAUNCH_OK();
+}
+
+SGA_API int sga_scatter_blocks(float* grad, const uint8_t* mask, const int* heads, long long kb, int X, long long n,
+                               const float* vals, void* stream) {
+  if (kb <= 0) return 0;
+  scatter_blocks_kernel<<<grid_for(kb * X, 256), 256, 0, ST(stream)>>>(grad, mask, heads, kb, X, n, vals);
+  return LAUNCH_OK();
+}
+
+SGA_API int sga_block_reduce(const float* x, long long n, int X, int use_max, float* out, void* stream) {
+  if (n <= 0) return 0;
+  const long long nb = (n + X - 1) / X;
+  block_reduce_kernel<<<grid_for(nb, 256), 256, 0, ST(stream)>>>(x, n, X, use_max, out, nb);
+  return LAUNCH_OK();
+}
+
+SGA_API int sga_expand_blocks(const uint8_t* bmask, long long nblocks, int X, long long n, uint8_t* mask,
+                              void* stream) {
+  if (n <= 0) return 0;
+  expand_blocks_kernel<<<grid_for(n, 256), 256, 0, ST(stream)>>>(bmask, nblocks, X, n, mask);
+  return LAUNCH_OK();
+}

@@ -1,0 +1,475 @@
+"""Single-GPU A/B tests: every native kernel against a plain PyTorch reference.
+
+Optimizer tails are compared bit for bit with the fp32 PyTorch reference of the
+same operation order; selection kernels must be exact; bf16 model ops are held
+to bf16 rounding tolerances against fp32 references. Sizes include awkward
+ones (1, 1023, 1025, non multiples of the vector width).
+"""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def _k():
+    from sga_b200 import kernels
+
+    return kernels
+
+
+def _kt():
+    from sga_b200 import kernels_torch
+
+    return kernels_torch
+
+
+# ---------------------------------------------------------------- GEMM
+@pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("shape", [(256, 512, 256), (384, 768, 192), (200, 328, 136), (128, 256, 64)])
+def test_gemm_layouts(a_mn, b_mn, shape):
+    K = _k()
+    M, N, Kd = shape
+    torch.manual_seed(1)
+    Al = torch.randn(M, Kd, device=DEV) * 0.5
+    Bl = torch.randn(N, Kd, device=DEV) * 0.5
+    A = (Al.t().contiguous() if a_mn else Al).to(torch.bfloat16)
+    B = (Bl.t().contiguous() if b_mn else Bl).to(torch.bfloat16)
+    ref = (A.t() if a_mn else A).float() @ (B.t() if b_mn else B).float().t()
+    out = torch.zeros(M, N, device=DEV, dtype=torch.bfloat16)
+    K.gemm_bf16(A, B, out, a_mn=bool(a_mn), b_mn=bool(b_mn))
+    assert int(K.gemm_err_word(DEV).item()) == 0
+    assert (out.float() - ref).abs().max().item() <= 0.02 * ref.abs().max().item()
+    acc = torch.ones(M, N, device=DEV, dtype=torch.float32)
+    K.gemm_bf16(A, B, acc, a_mn=bool(a_mn), b_mn=bool(b_mn), epi=K.EPI_F32_ACC)
+    assert (acc - (ref + 1.0)).abs().max().item() <= 2e-3 * ref.abs().max().item()
+    res = torch.randn(M, N, device=DEV).to(torch.bfloat16)
+    out2 = torch.zeros_like(out)
+    K.gemm_bf16(A, B, out2, a_mn=bool(a_mn), b_mn=bool(b_mn), epi=K.EPI_BF16_ADD, residual=res)
+    assert (out2.float() - (ref + res.float())).abs().max().item() <= 0.03 * ref.abs().max().item()
+
+
+# ----------------------------------------------------------- optimizer
+def _adam_case(n, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    w = torch.randn(n, generator=g) * 0.02
+    grad = torch.randn(n, generator=g) * 1e-3
+    m = torch.randn(n, generator=g) * 1e-4
+    v = (torch.randn(n, generator=g) * 1e-4).abs()
+    mask = (torch.rand(n, generator=g) < 0.3).to(torch.uint8)
+    return w, grad, m, v, mask
+
+
+VARIANTS = [
+    dict(emit="update"), dict(emit="abs_g"), dict(emit="abs_m"), dict(emit="coi"),
+    dict(emit=None, use_mask=True, clear=True),
+    dict(emit=None, use_mask=True, clear=True, coeff=0.37),
+    dict(emit=None, use_mask=True, clear=True, fold=True, interval=4.0),
+    dict(emit=None, use_mask=False, clear=True),
+    dict(emit="update", use_mask=True, lr_scale=0.25),
+]
+
+
+@pytest.mark.parametrize("opt", ["adamw", "adams"])
+@pytest.mark.parametrize("variant", VARIANTS)
+@pytest.mark.parametrize("n", [1, 1023, 4096 + 5, 70001])
+def test_adam_step_bitwise(opt, variant, n):
+    K = _k()
+    from sga_b200.plugins.optimizer.reference import grad_correct_torch
+    from sga_b200.plugins.scores import EMIT_CODES
+
+    w, grad, m, v, mask = _adam_case(n)
+    lr, b1, b2, eps, wd, step = 3e-4, 0.9, 0.95, 1e-8, 0.1, 7
+    use_mask = variant.get("use_mask", False)
+    rw, rg, rm, rv = (t.clone().to(DEV) for t in (w, grad, m, v))  # same ops, evaluated by PyTorch on the device
+    grad_correct_torch(rw, rg, rm, rv, lr, b1, b2, eps, wd, 1 - b1 ** step, 1 - b2 ** step,
+                       mask.to(DEV) if use_mask else None, variant.get("emit"), coeff=variant.get("coeff", 1.0),
+                       clear=variant.get("clear", False), fold=variant.get("fold", False),
+                       interval=variant.get("interval", 1.0), inactive_lr_scale=variant.get("lr_scale", 1.0),
+                       optimizer=opt)
+    dw, dg, dm, dv = (t.to(DEV) for t in (w, grad, m, v))
+    model = torch.empty(n, dtype=torch.bfloat16, device=DEV)
+    table = K.SegmentTable([0], [0], n, DEV)
+    coeff = torch.tensor([variant["coeff"]], dtype=torch.float32, device=DEV) if "coeff" in variant else None
+    K.adam_step(dw, dg, dm, dv, table, [lr], [wd], beta1=b1, beta2=b2, eps=eps, step=step, model=model,
+                mask=mask.to(DEV) if use_mask else None, coeff=coeff, emit=EMIT_CODES[variant.get("emit")],
+                clear=variant.get("clear", False), fold=variant.get("fold", False),
+                interval=variant.get("interval", 1.0), lr_scale=variant.get("lr_scale", 1.0), adams=(opt == "adams"))
+    torch.cuda.synchronize()
+    assert torch.equal(dm, rm), "m differs"
+    assert torch.equal(dv, rv), "v differs"
+    assert torch.equal(dw, rw), "w differs"
+    assert torch.equal(dg, rg), "grad buffer differs"
+    assert torch.equal(model, rw.to(torch.bfloat16))
+
+
+def test_adam_step_segments_groups():
+    K = _k()
+    from sga_b200.plugins.optimizer.reference import grad_correct_torch
+
+    sizes, groups = [4096, 64, 8192 + 64, 128], [0, 1, 0, 1]
+    n = sum(sizes)
+    starts = [0]
+    for s in sizes[:-1]:
+        starts.append(starts[-1] + s)
+    w, grad, m, v, _ = _adam_case(n, seed=3)
+    lrs, wds = [1e-3, 2e-3], [0.1, 0.0]
+    rw, rg, rm, rv = (t.clone().to(DEV) for t in (w, grad, m, v))
+    for s, sz, gi in zip(starts, sizes, groups):
+        sl = slice(s, s + sz)
+        grad_correct_torch(rw[sl], rg[sl], rm[sl], rv[sl], lrs[gi], 0.9, 0.95, 1e-8, wds[gi], 1 - 0.9 ** 2,
+                           1 - 0.95 ** 2, None, "update")
+    dw, dg, dm, dv = (t.to(DEV) for t in (w, grad, m, v))
+    K.adam_step(dw, dg, dm, dv, K.SegmentTable(starts, groups, n, DEV), lrs, wds, beta1=0.9, beta2=0.95, eps=1e-8,
+                step=2, emit=0)
+    assert torch.equal(dw, rw) and torch.equal(dg, rg)
+
+
+def test_sumsq_and_clip():
+    K = _k()
+    x = torch.randn(100003, device=DEV)
+    mask = (torch.rand(100003, device=DEV) < 0.5).to(torch.uint8)
+    out = torch.zeros(1, device=DEV)
+    K.sumsq(x, out)
+    assert abs(out.item() - (x.double() ** 2).sum().item()) <= 1e-4 * out.item()
+    first = out.item()
+    K.sumsq(x, out)
+    assert out.item() == first, "sum of squares must be deterministic"
+    K.sumsq(x, out, mask=mask)
+    ref = ((x * mask).double() ** 2).sum().item()
+    assert abs(out.item() - ref) <= 1e-4 * ref
+    coeff = torch.zeros(1, device=DEV)
+    norm = torch.zeros(1, device=DEV)
+    K.clip_coeff(out, 1.0, 1.0, coeff, norm)
+    assert abs(norm.item() - math.sqrt(ref)) < 1e-2
+    assert abs(coeff.item() - 1.0 / (math.sqrt(ref) + 1e-6)) < 1e-5
+
+
+# ------------------------------------------------------------ selection
+@pytest.mark.parametrize("n", [1, 1000, 1 << 16, (1 << 20) + 77])
+@pytest.mark.parametrize("mode", [(16, 1, 32769), (16, 8, 32769), (19, 8, 4097)])
+def test_hist_top(n, mode):
+    K, KT = _k(), _kt()
+    shift, stride, nb = mode
+    x = (torch.randn(n, device=DEV) * 1e-3) * (1 + 20 * (torch.rand(n, device=DEV) < 0.01))
+    h = K.hist_top(x, shift, stride, nb)
+    ref = KT.hist_top(x.cpu(), shift, stride, nb)
+    assert torch.equal(h.cpu(), ref)
+
+
+def test_exact_threshold_two_digit():
+    K, KT = _k(), _kt()
+    n, k = (1 << 18) + 3, 2621
+    x = torch.randn(n, device=DEV) * 1e-3
+    h = K.hist_top(x, 16, 1, 32769)
+    cum = torch.cumsum(h.flip(0), 0)  # suffix counts from the top bin
+    b = 32768 - int(torch.searchsorted(cum, torch.tensor(k, device=DEV)).item())
+    above = int(h[b + 1:].sum().item())
+    h2 = K.hist_low16(x, b)
+    assert int(h2.sum().item()) == int(h[b].item())
+    cum2 = torch.cumsum(h2.flip(0), 0)
+    lb = 65535 - int(torch.searchsorted(cum2, torch.tensor(k - above, device=DEV)).item())
+    key = (b << 16) | lb
+    ref_key = torch.kthvalue(KT.abs_bit_key(x.cpu()), n - k + 1).values.item()
+    assert key == ref_key
+
+
+@pytest.mark.parametrize("n", [5, 4096, 4097, 300001])
+def test_mask_compact_stats(n):
+    K, KT = _k(), _kt()
+    x = torch.randn(n, device=DEV)
+    mask = torch.empty(n, dtype=torch.uint8, device=DEV)
+    cnt = torch.zeros(1, dtype=torch.int64, device=DEV)
+    K.mask_ge(x, mask, thr=1.0, count=cnt)
+    ref = (x.abs() >= 1.0)
+    assert torch.equal(mask.bool(), ref) and cnt.item() == int(ref.sum())
+    mask2 = torch.empty_like(mask)
+    K.mask_ge(x, mask2, bin_=0x3F80, shift=16)
+    assert torch.equal(mask2.bool(), KT.abs_bit_key(x, 16) >= 0x3F80)
+    st = K.mask_stats(mask)
+    assert torch.equal(st.cpu(), KT.mask_stats(mask.cpu()))
+    idx = torch.full((n,), -1, dtype=torch.int32, device=DEV)
+    total = torch.zeros(1, dtype=torch.int64, device=DEV)
+    K.compact_mask(mask, idx, total)
+    ref_idx = KT.compact_mask_idx(mask)
+    assert total.item() == ref_idx.numel()
+    assert torch.equal(idx[:ref_idx.numel()], ref_idx)
+    tb = K.dir_table(idx, ref_idx.numel(), n)
+    assert torch.equal(tb.cpu(), KT.dir_table(ref_idx.cpu(), ref_idx.numel(), n))
+
+
+def test_pack_scatter_blocks():
+    K, KT = _k(), _kt()
+    n = 50000
+    g = torch.randn(n, device=DEV)
+    mask = (torch.rand(n, device=DEV) < 0.1).to(torch.uint8)
+    idx = KT.compact_mask_idx(mask)
+    vals = torch.empty(idx.numel(), device=DEV)
+    g1, g2 = g.clone(), g.clone()
+    K.pack_selected(g1, idx, vals, factor=0.5, zero=True)
+    rv = torch.empty_like(vals)
+    KT.pack_selected(g2, idx, rv, factor=0.5, zero=True)
+    assert torch.equal(vals, rv) and torch.equal(g1, g2)
+    K.scatter_selected(g1, idx, vals)
+    KT.scatter_selected(g2, idx, rv)
+    assert torch.equal(g1, g2)
+    # block forms
+    x = 16
+    bmask = (torch.rand((n + x - 1) // x, device=DEV) < 0.2).to(torch.uint8)
+    emask = K.expand_blocks(bmask, x, n)
+    assert torch.equal(emask, KT.expand_blocks(bmask, x, n))
+    heads = (KT.compact_mask_idx(bmask) * x).to(torch.int32)
+    bv = torch.empty(heads.numel() * x, device=DEV)
+    rbv = torch.empty_like(bv)
+    g1, g2 = g.clone(), g.clone()
+    K.gather_selected_blocks(g1, emask, heads, x, bv, factor=0.25)
+    KT.gather_selected_blocks(g2, emask, heads, x, rbv, factor=0.25)
+    assert torch.equal(bv, rbv) and torch.equal(g1, g2)
+    K.scatter_selected_blocks(g1, emask, heads, x, bv)
+    KT.scatter_selected_blocks(g2, emask, heads, x, rbv)
+    assert torch.equal(g1, g2)
+    br = K.block_reduce(g, x, True)
+    assert torch.equal(br, KT.block_reduce(g, x, True))
+    brm = K.block_reduce(g, x, False)
+    assert torch.allclose(brm, KT.block_reduce(g, x, False), rtol=1e-5, atol=1e-7)
+
+
+# ---------------------------------------------- fused peer kernels, 1 rank
+def _channel():
+    from sga_b200.parallel.p2p import PeerChannel
+    from sga_b200.parallel.symm import SymmPool
+
+    pool = SymmPool(device=DEV)
+    return pool, PeerChannel(pool)
+
+
+@pytest.mark.parametrize("n,k", [(4096, 41), (100000, 1000), ((1 << 20) + 13, 10486), (5000, 5000), (777, 1)])
+def test_bucket_index_sync_single_rank(n, k):
+    from sga_b200.parallel import p2p
+
+    KT = _kt()
+    pool, ch = _channel()
+    try:
+        torch.manual_seed(n)
+        acc = torch.randn(n, device=DEV) * 1e-3
+        acc[::97] = 0.5  # many exact ties at the top
+        ref_mask = KT.topk_exact_flat(acc.abs().cpu(), k).to(DEV)
+        ref_idx = KT.compact_mask_idx(ref_mask)
+        slots = pool.alloc(8 * k)
+        comm = torch.zeros(n, device=DEV)
+        touched = torch.empty((n + 31) // 32, dtype=torch.int32, device=DEV)
+        sq = torch.zeros(1, device=DEV)
+        scratch = p2p.IndexSyncScratch(DEV)
+        a0 = acc.clone()
+        for rep in range(2):  # second launch checks the zero-on-exit scratch invariant
+            acc.copy_(a0)
+            comm.zero_()
+            p2p.bucket_index_sync_(ch, scratch, acc, k, slots=slots, kcap=k, comm=comm, touched=touched, scale=0.5,
+                                   sumsq_out=sq)
+            ch.check()
+            pairs = slots.view(torch.int32, 0, 2 * k).view(k, 2)
+            assert torch.equal(pairs[:, 0], ref_idx), "selected indices differ from exact top-k"
+            vals = pairs[:, 1].contiguous().view(torch.float32)
+            assert torch.equal(vals, a0[ref_idx.long()])
+            exp_acc = torch.where(ref_mask.bool(), torch.zeros_like(a0), a0)
+            assert torch.equal(acc, exp_acc), "residual write-back differs"
+            exp_comm = torch.where(ref_mask.bool(), a0 * 0.5, torch.zeros_like(a0))
+            assert torch.equal(comm, exp_comm)
+            assert abs(sq.item() - (exp_comm.double() ** 2).sum().item()) <= 1e-4 * max(sq.item(), 1e-30)
+            assert int(scratch.result[3].item()) == k
+        # select-only mode writes the bit mask
+        acc.copy_(a0)
+        p2p.bucket_index_sync_(ch, scratch, acc, k, slots=None, kcap=0, touched=touched, select_only=True)
+        ch.check()
+        bits = touched.cpu().numpy().view("uint32")
+        import numpy as np
+
+        un = np.unpackbits(bits.view("uint8"), bitorder="little")[:n]
+        assert np.array_equal(un, ref_mask.cpu().numpy())
+        assert torch.equal(acc, a0)
+    finally:
+        pool.close()
+
+
+def test_p2p_allreduce_and_mask_union_single_rank():
+    from sga_b200.parallel import p2p
+
+    KT = _kt()
+    pool, ch = _channel()
+    try:
+        n = 100003
+        buf = pool.alloc(4 * n)
+        v = buf.view(torch.float32, 0, n)
+        x = torch.randn(n, device=DEV)
+        v.copy_(x)
+        sq = torch.zeros(1, device=DEV)
+        p2p.allreduce_(ch, buf, 0, n, scale=0.5, sumsq_out=sq)
+        ch.check()
+        assert torch.equal(v, x * 0.5)
+        assert abs(sq.item() - ((x * 0.5).double() ** 2).sum().item()) <= 1e-4 * sq.item()
+        # pack -> reduce -> scatter round trip
+        grad = torch.randn(4 * n, device=DEV)
+        g0 = grad.clone()
+        mask = (torch.rand(4 * n, device=DEV) < 0.2).to(torch.uint8)
+        idx = KT.compact_mask_idx(mask)[:n]
+        p2p.allreduce_(ch, buf, 0, idx.numel(), scale=1.0, grad=grad, idx=idx, factor=0.25, pack=True,
+                       zero_after_pack=True, scatter=True)
+        ch.check()
+        exp = g0.clone()
+        exp[idx.long()] = g0[idx.long()] * 0.25
+        assert torch.equal(grad, exp)
+        # mask union (one rank: union == own mask, values scaled in place)
+        gb = pool.alloc(4 * n)
+        bb = pool.alloc(4 * ((n + 31) // 32))
+        ub = pool.alloc(4 * ((n + 31) // 32))
+        g = gb.view(torch.float32, 0, n)
+        g.copy_(x)
+        m = (torch.rand(n, device=DEV) < 0.05)
+        import numpy as np
+
+        packed = np.packbits(m.cpu().numpy().astype("uint8"), bitorder="little")
+        packed = np.concatenate([packed, np.zeros((-len(packed)) % 4, dtype="uint8")]).view("int32")
+        bb.view(torch.int32, 0, packed.size).copy_(torch.from_numpy(packed.copy()))
+        mu8 = torch.empty(n, dtype=torch.uint8, device=DEV)
+        cnt = torch.zeros(1, dtype=torch.int64, device=DEV)
+        p2p.mask_union_reduce_(ch, gb, 0, bb, 0, ub, 0, n, scale=0.5, mask_u8=mu8, sumsq_out=sq, count_out=cnt)
+        ch.check()
+        assert torch.equal(mu8.bool(), m)
+        assert torch.equal(g, torch.where(m, x * 0.5, x))
+        assert cnt.item() == int(m.sum())
+    finally:
+        pool.close()
+
+
+def test_peer_wait_times_out_cleanly():
+    """A flag that nothing sets: the bounded wait expires, the kernel returns,
+    the status word says so and the context stays usable."""
+    from sga_b200.parallel import p2p
+
+    pool, ch = _channel()
+    try:
+        ch.wait_cycles = 2_000_000  # about a millisecond
+        n = 4096
+        buf = pool.alloc(4 * n)
+        ch.seq = 5
+        d = ch.next_desc()
+        d.seq = 1 << 20  # wait for a sequence number nobody will ever publish
+        import ctypes
+
+        from sga_b200.csrc import lib
+
+        # signal uses d.seq too, so waiting on our own signal would succeed; make W=2 with a
+        # second "rank" whose flag word is our own memory that nobody writes
+        d.W = 2
+        d.flags[1] = ch.ctrl.peer_ptrs[0] + 128
+        bufs = buf.ptr_array(0)
+        bufs[1] = bufs[0]
+        ns = ch.norm_slots()
+        ns[1] = ns[0]
+        rc = lib().sga_p2p_allreduce(ctypes.byref(d), bufs, n, 1.0, None, None, 1.0, 0, 0, 0, 0, ns,
+                                     ch.cta_partials.data_ptr(), None, 0, 0, torch.cuda.current_stream().cuda_stream)
+        assert rc == 0
+        torch.cuda.synchronize()
+        with pytest.raises(p2p.PeerTimeout):
+            ch.check()
+        x = torch.ones(8, device=DEV)
+        assert (x + 1).sum().item() == 16.0
+    finally:
+        pool.close()
+
+
+# ------------------------------------------------------------ model ops
+def test_rmsnorm_fwd_bwd():
+    from sga_b200.ops import functional as F
+
+    for T, H in [(64, 2048), (37, 1024), (50, 128), (16, 4096)]:
+        x = torch.randn(T, H, device=DEV).to(torch.bfloat16)
+        w = (1 + 0.1 * torch.randn(H, device=DEV)).to(torch.bfloat16)
+        dy = torch.randn(T, H, device=DEV).to(torch.bfloat16)
+        y, rstd = F.rmsnorm_fwd(x, w, 1e-5)
+        xf = x.float().requires_grad_()
+        wf = w.float().requires_grad_()
+        ref = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * wf
+        assert (y.float() - ref).abs().max().item() < 0.05
+        ref.backward(dy.float())
+        dw = torch.zeros(H, device=DEV)
+        dx = F.rmsnorm_bwd(x, w, dy, rstd, dw_out=dw)
+        assert (dx.float() - xf.grad).abs().max().item() < 0.06
+        assert (dw - wf.grad).abs().max().item() < 0.02 * wf.grad.abs().max().item() + 0.05
+
+
+def test_rope_swiglu_ce_embed():
+    from sga_b200.ops import functional as F
+
+    T, S, nh, hd = 64, 32, 4, 64
+    x = torch.randn(T, nh * hd, device=DEV).to(torch.bfloat16)
+    cs, sn = F.rope_tables(S, hd, 500000.0, DEV)
+    x0 = x.clone()
+    F.rope_(x, cs, sn, S, nh, hd, 0, +1.0)
+    xf = x0.float().view(T, nh, hd)
+    pos = torch.arange(T, device=DEV) % S
+    c, s = cs[pos][:, None, :], sn[pos][:, None, :]
+    a, b = xf[..., :hd // 2], xf[..., hd // 2:]
+    ref = torch.cat([a * c - b * s, b * c + a * s], -1).view(T, nh * hd)
+    assert (x.float() - ref).abs().max().item() < 0.03
+    F.rope_(x, cs, sn, S, nh, hd, 0, -1.0)
+    assert (x.float() - x0.float()).abs().max().item() < 0.06
+    # swiglu
+    Fd = 256
+    gu = torch.randn(T, 2 * Fd, device=DEV).to(torch.bfloat16)
+    out = F.swiglu_fwd(gu)
+    guf = gu.float().requires_grad_()
+    ref = torch.nn.functional.silu(guf[:, :Fd]) * guf[:, Fd:]
+    assert (out.float() - ref).abs().max().item() < 0.05
+    do = torch.randn(T, Fd, device=DEV).to(torch.bfloat16)
+    ref.backward(do.float())
+    din = F.swiglu_bwd(gu, do)
+    assert (din.float() - guf.grad).abs().max().item() < 0.08
+    # cross entropy (+ in-place gradient)
+    V = 1000 * 8
+    z = (torch.randn(T, V, device=DEV) * 2).to(torch.bfloat16)
+    tgt = torch.randint(0, V, (T,), device=DEV)
+    zf = z.float().requires_grad_()
+    ref_loss = torch.nn.functional.cross_entropy(zf, tgt, reduction="none")
+    ref_loss.mean().backward()
+    loss = F.cross_entropy_(z, tgt, grad_scale=1.0 / T)
+    assert (loss - ref_loss).abs().max().item() < 2e-2
+    assert (z.float() - zf.grad).abs().max().item() < 2e-3
+    # embedding
+    W = torch.randn(500, 256, device=DEV).to(torch.bfloat16)
+    ids = torch.randint(0, 500, (T,), device=DEV)
+    e = F.embed_fwd(ids, W)
+    assert torch.equal(e, W[ids])
+    mg = torch.zeros(500, 256, device=DEV)
+    de = torch.randn(T, 256, device=DEV).to(torch.bfloat16)
+    F.embed_bwd(ids, de, mg)
+    ref = torch.zeros_like(mg).index_add_(0, ids, de.float())
+    assert (mg - ref).abs().max().item() < 1e-4
+
+
+def test_dense_adamw_ag_single_rank():
+    from sga_b200.parallel import p2p
+    from sga_b200.plugins.optimizer.reference import grad_correct_torch
+
+    K = _k()
+    pool, ch = _channel()
+    try:
+        n = 3 * 4096 + 64
+        w, grad, m, v, _ = _adam_case(n, seed=5)
+        rw, rg, rm, rv = (t.clone().to(DEV) for t in (w, grad, m, v))
+        grad_correct_torch(rw, rg * 0.5, rm, rv, 1e-3, 0.9, 0.95, 1e-8, 0.1, 1 - 0.9 ** 3, 1 - 0.95 ** 3, None, None)
+        dw, dg, dm, dv = (t.to(DEV) for t in (w, grad, m, v))
+        model = pool.alloc(2 * n)
+        bstart = torch.tensor([0, 8192], dtype=torch.int64, device=DEV)
+        blen = torch.tensor([8192, n - 8192], dtype=torch.int64, device=DEV)
+        coeff = torch.tensor([0.5], device=DEV)
+        p2p.dense_adamw_ag_(ch, dw, dg, dm, dv, model, bstart, blen, K.SegmentTable([0], [0], n, DEV), [1e-3], [0.1],
+                            beta1=0.9, beta2=0.95, eps=1e-8, step=3, coeff=coeff)
+        ch.check()
+        assert torch.equal(dw, rw) and torch.equal(dm, rm) and torch.equal(dv, rv)
+        assert torch.equal(model.view(torch.bfloat16, 0, n), rw.to(torch.bfloat16))
+    finally:
+        pool.close()
