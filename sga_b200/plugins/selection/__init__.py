@@ -1,0 +1,1 @@
+"""Selection plugins: ``topk`` with its histogram / exact / adaptive methods."""

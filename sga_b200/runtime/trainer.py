@@ -1,0 +1,318 @@
+"""Training driver: model + data-parallel layer + optimizer + (optional) SGA
+engine, one process per GPU.
+
+``Trainer.train_step(batch)`` is the public per-step call: it splits the
+rank's batch into micro-batches, runs forward/backward for each (arming
+per-bucket gradient synchronisation for the last one so that communication
+overlaps the backward pass), synchronises, clips, steps the optimizer and
+returns the mean loss as a device scalar.
+
+Three step flavours:
+
+* SGA on: ``engine.grad_sync`` + ``engine.optimizer_step`` (full or sparse by
+  the calendar).
+* SGA off, ``dense_mode=fused``: per-bucket reduce-scatter kernels overlapped
+  with the backward pass, then one kernel that runs AdamW on the slices this
+  rank owns and all-gathers the bf16 parameters through peer stores.
+* SGA off, ``dense_mode=allreduce`` (also the library baseline): bucket
+  all-reduce, multi-tensor AdamW on the replicated state.
+
+This is the counterpart of the reference's training entry + Megatron
+``pretrain`` loop (``sga/train_gpt.py:212-252``); data is synthetic (uniform
+token ids from a seed) because the headline benchmark is defined on it.
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import time
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import config as C
+from ..models.gpt import GPT, get_config
+from ..plugins.optimizer import OptContext
+from .builder import build_engine
+from .ddp import DataParallel, DDPConfig
+from .optimizer import FlatOptimizer, OptimizerConfig
+
+
+def add_trainer_args(p: argparse.ArgumentParser) -> argparse.ArgumentParser:
+    g = p.add_argument_group("training")
+    g.add_argument("--model", type=str, default="llama3_1b")
+    g.add_argument("--seq-length", type=int, default=None)
+    g.add_argument("--num-layers", type=int, default=None)
+    g.add_argument("--micro-batch-size", type=int, default=4)
+    g.add_argument("--global-batch-size", type=int, default=256)
+    g.add_argument("--train-iters", type=int, default=10)
+    g.add_argument("--lr", type=float, default=3e-4)
+    g.add_argument("--weight-decay", type=float, default=0.1)
+    g.add_argument("--adam-beta1", type=float, default=0.9)
+    g.add_argument("--adam-beta2", type=float, default=0.95)
+    g.add_argument("--adam-eps", type=float, default=1e-8)
+    g.add_argument("--clip-grad", type=float, default=1.0)
+    g.add_argument("--seed", type=int, default=1234)
+    g.add_argument("--data-seed", type=int, default=1234)
+    g.add_argument("--log-interval", type=int, default=1)
+    g.add_argument("--save", type=str, default=None)
+    g.add_argument("--load", type=str, default=None)
+    g.add_argument("--save-interval", type=int, default=0)
+    g.add_argument("--device", type=str, default=None)
+    g.add_argument("--dense-mode", type=str, default="fused", choices=("fused", "allreduce"))
+    g.add_argument("--transport", type=str, default="auto", choices=("auto", "p2p", "nccl", "gloo", "local"))
+    g.add_argument("--overlap-grad-reduce", type=C.sga_bool, default=True)
+    g.add_argument("--comm-max-ctas", type=int, default=0)
+    g.add_argument("--tensor-model-parallel-size", type=int, default=1)
+    g.add_argument("--pipeline-model-parallel-size", type=int, default=1)
+    g.add_argument("--sequence-parallel", type=C.sga_bool, default=False)
+    g.add_argument("--untie-embeddings-and-output-weights", action="store_true")
+    g.add_argument("--use-distributed-optimizer", action="store_true")
+    g.add_argument("--log-num-zeros-in-grad", action="store_true")
+    g.add_argument("--sga-allow-config-override", action="store_true")
+    return p
+
+
+def build_parser() -> argparse.ArgumentParser:
+    p = argparse.ArgumentParser("sga_b200 trainer", allow_abbrev=False)
+    add_trainer_args(p)
+    C.add_sga_args(p)
+    return p
+
+
+def init_distributed(device_type: str):
+    """One process per GPU; rendezvous from the torchrun environment."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1 and not dist.is_initialized():
+        backend = "nccl" if device_type == "cuda" else "gloo"
+        kwargs = {}
+        if device_type == "cuda":
+            local = int(os.environ.get("LOCAL_RANK", "0"))
+            torch.cuda.set_device(local)
+            kwargs["device_id"] = torch.device("cuda", local)
+        dist.init_process_group(backend=backend, **kwargs)
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    return rank, (dist.get_world_size() if dist.is_initialized() else 1)
+
+
+class SyntheticTokens:
+    """Uniform token ids over the vocabulary from a seed; each (step, rank,
+    micro-batch) draws its own stream so that every rank sees different data
+    and a given global batch is the same whatever the number of ranks."""
+
+    def __init__(self, vocab: int, seq_len: int, seed: int, pin: bool = False):
+        self.vocab, self.seq_len, self.seed = vocab, seq_len, seed
+        self.pin = pin
+
+    def batch(self, step: int, first_sample: int, n: int):
+        """``n`` sequences starting at global sample index ``first_sample`` of ``step``."""
+        out = torch.empty(n, self.seq_len + 1, dtype=torch.int64, pin_memory=self.pin)
+        for i in range(n):
+            g = torch.Generator().manual_seed((self.seed * 1000003 + step) * 1000003 + first_sample + i)
+            out[i] = torch.randint(0, self.vocab, (self.seq_len + 1,), generator=g)
+        return out
+
+
+class Trainer:
+    def __init__(self, args, quiet: bool = False):
+        self.args = args
+        dev = args.device or ("cuda" if torch.cuda.is_available() else "cpu")
+        dev_type = torch.device(dev).type
+        self.rank, self.world = init_distributed(dev_type)
+        if dev_type == "cuda":
+            local = int(os.environ.get("LOCAL_RANK", "0")) if self.world > 1 else (torch.device(dev).index or 0)
+            self.device = torch.device("cuda", local)
+            torch.cuda.set_device(self.device)
+        else:
+            self.device = torch.device("cpu")
+        cuda = self.device.type == "cuda"
+        over = {}
+        if args.seq_length:
+            over["seq_len"] = args.seq_length
+        if args.num_layers:
+            over["num_layers"] = args.num_layers
+        if args.untie_embeddings_and_output_weights:
+            over["tied_embeddings"] = False
+        self.cfg = get_config(args.model, **over)
+        self.dp_world = self.world // max(1, args.tensor_model_parallel_size * args.pipeline_model_parallel_size)
+        assert args.global_batch_size % (args.micro_batch_size * self.dp_world) == 0, (
+            "global batch must be a multiple of micro_batch * data-parallel size")
+        self.num_micro = args.global_batch_size // (args.micro_batch_size * self.dp_world)
+        transport = args.transport
+        sga_t = getattr(args, "sga_backend_transport", "auto")
+        if transport == "auto" and sga_t != "auto":
+            transport = sga_t
+        self.pool = None
+        if cuda and transport in ("auto", "p2p"):
+            from ..parallel.symm import SymmPool
+
+            self.pool = SymmPool(group=None, device=self.device)
+        self.sga = bool(args.sga_enabled)
+        need_comm = (self.sga and getattr(args, "sga_selection_locality", "shared") == "rank_local"
+                     and args.sga_backend != "torch_pipelined_mask")
+        self.model = GPT(self.cfg, device=self.device, pool=self.pool,
+                         bucket_elems=getattr(args, "sga_bucket_elems", 16 << 20), seed=args.seed,
+                         need_comm_staging=need_comm)
+        ddp_cfg = DDPConfig(average_in_collective=True, overlap_grad_reduce=bool(args.overlap_grad_reduce),
+                            comm_max_ctas=args.comm_max_ctas)
+        if getattr(args, "sga_backend_timer", None):
+            ddp_cfg.overlap_grad_reduce = False
+        self.ddp = DataParallel(self.model, group=None, transport=transport, ddp_config=ddp_cfg, pool=self.pool)
+        if self.ddp.transport == "gloo":
+            ddp_cfg.average_in_collective = False
+        self.optimizer = FlatOptimizer(self.model.arena, OptimizerConfig(
+            lr=args.lr, weight_decay=args.weight_decay, adam_beta1=args.adam_beta1, adam_beta2=args.adam_beta2,
+            adam_eps=args.adam_eps, clip_grad=args.clip_grad, log_num_zeros_in_grad=args.log_num_zeros_in_grad))
+        self.engine = None
+        if getattr(args, "sga_backend_timer", None):
+            from ..utils import backend_timer
+
+            if not backend_timer.active():
+                backend_timer.configure(args.sga_backend_timer, self.rank)
+            backend_timer.install_fullsync_wrap()
+        if self.sga:
+            self.engine = build_engine(trainer_args=args, quiet=quiet)
+            self.engine.log_interval = args.log_interval
+            self.engine.attach(self.ddp)
+        self.data = SyntheticTokens(self.cfg.vocab, self.cfg.seq_len, args.data_seed, pin=cuda)
+        self.iteration = 0
+        self._dense = None
+        if cuda:
+            self._dev_sumsq = torch.zeros(1, device=self.device)
+            self._dev_coeff = torch.ones(1, device=self.device)
+            self._dev_norm = torch.zeros(1, device=self.device)
+        self.last_grad_norm = None
+
+    # ----------------------------------------------------------------- data
+    def host_batch(self, step: int) -> torch.Tensor:
+        """This rank's ``[num_micro * micro_batch, seq + 1]`` token block for ``step`` (pinned host memory)."""
+        per_rank = self.num_micro * self.args.micro_batch_size
+        dp_rank = self.rank % self.dp_world
+        return self.data.batch(step, dp_rank * per_rank, per_rank)
+
+    # ----------------------------------------------------------------- step
+    def train_step(self, batch: torch.Tensor) -> torch.Tensor:
+        """``batch``: ``[num_micro * micro_batch, seq + 1]`` int64 token ids, on the
+        host (pinned) or already on the device. Returns the mean loss (device scalar)."""
+        self.iteration += 1
+        it = self.iteration
+        mb = self.args.micro_batch_size
+        if batch.device != self.device:
+            batch = batch.to(self.device, non_blocking=True)
+        losses = []
+        self.ddp.begin_step()
+        for i in range(self.num_micro):
+            chunk = batch[i * mb:(i + 1) * mb]
+            tokens, targets = chunk[:, :-1], chunk[:, 1:]
+            last = i == self.num_micro - 1
+            if last:
+                if self.engine is not None:
+                    self.engine.begin_step(self.ddp, it)
+                else:
+                    self._arm_dense()
+            loss = self.model.forward_backward(tokens, targets, loss_scale=1.0 / self.num_micro,
+                                               on_param_done=self.ddp.on_param_done if last else None)
+            losses.append(loss)
+        if self.engine is not None:
+            if not self.engine.grad_sync(self.ddp, False):
+                self.ddp.finish_grad_sync()
+            ok, gn, _nz = self.engine.optimizer_step(self.optimizer, [self.ddp], it)
+            self.last_grad_norm = gn
+        else:
+            self._dense_step()
+        return torch.stack(losses).mean()
+
+    # ----------------------------------------------------------- dense path
+    def _fused_dense(self) -> bool:
+        return self.args.dense_mode == "fused" and self.ddp.transport == "p2p"
+
+    def _arm_dense(self) -> None:
+        if self._fused_dense():
+            self._dev_sumsq.zero_()
+            self.ddp.arm(self._rs_bucket_sync)
+        else:
+            self.ddp.arm(None)
+
+    def _rs_bucket_sync(self, bucket) -> None:
+        from ..parallel import p2p
+
+        p2p.allreduce_(self.ddp.channel_for(bucket), self.model.arena.symm_grad, 4 * bucket.start, bucket.numel,
+                       scale=self.ddp.gradient_scaling_factor, rs_only=True, sumsq_out=self._dev_sumsq,
+                       accumulate=True, max_ctas=self.ddp.ddp_config.comm_max_ctas)
+
+    def _dense_step(self) -> None:
+        arena = self.model.arena
+        opt = self.optimizer
+        clip = float(opt.config.clip_grad or 0.0)
+        g0 = opt.param_groups[0]
+        beta1, beta2 = g0["betas"]
+        if self._fused_dense():
+            from .. import kernels as K
+            from ..parallel import p2p
+
+            self.ddp.finish_pending()
+            K.clip_coeff(self._dev_sumsq, 1.0, clip, self._dev_coeff, self._dev_norm)
+            if self._dense is None:
+                bs = torch.tensor([b.start for b in arena.buckets], dtype=torch.int64, device=self.device)
+                bl = torch.tensor([b.numel for b in arena.buckets], dtype=torch.int64, device=self.device)
+                self._dense = (bs, bl)
+            p2p.dense_adamw_ag_(self.ddp.channels[0], arena.main_param, arena.main_grad, arena.exp_avg,
+                                arena.exp_avg_sq, arena.symm_model, self._dense[0], self._dense[1],
+                                arena.segment_table(), opt.group_lr(), opt.group_wd(), beta1=beta1, beta2=beta2,
+                                eps=g0["eps"], step=opt.peek_step(), coeff=self._dev_coeff if clip > 0 else None)
+            opt.advance_step()
+            arena.main_grad.zero_()
+            self.last_grad_norm = self._dev_norm
+            return
+        self.ddp.finish_grad_sync()
+        if self.device.type == "cuda":
+            from .. import kernels as K
+
+            K.sumsq(arena.main_grad, self._dev_sumsq)
+            K.clip_coeff(self._dev_sumsq, 1.0, clip, self._dev_coeff, self._dev_norm)
+            K.adam_step(arena.main_param, arena.main_grad, arena.exp_avg, arena.exp_avg_sq, arena.segment_table(),
+                        opt.group_lr(), opt.group_wd(), beta1=beta1, beta2=beta2, eps=g0["eps"],
+                        step=opt.peek_step(), model=arena.model_param, coeff=self._dev_coeff if clip > 0 else None)
+            opt.advance_step()
+            self.last_grad_norm = self._dev_norm
+        else:
+            from ..plugins.optimizer.reference import grad_correct_torch
+
+            norm = float((arena.main_grad.double() ** 2).sum().sqrt())
+            coeff = 1.0
+            if clip > 0 and clip / (norm + 1e-6) < 1.0:
+                coeff = float(torch.tensor(clip / (norm + 1e-6), dtype=torch.float32))
+            step = opt.peek_step()
+            for s in arena.slots:
+                sl = slice(s.start, s.end)
+                grp = opt.param_groups[s.spec.group]
+                grad_correct_torch(arena.main_param[sl], arena.main_grad[sl], arena.exp_avg[sl], arena.exp_avg_sq[sl],
+                                   grp["lr"], beta1, beta2, g0["eps"], grp["weight_decay"], 1 - beta1 ** step,
+                                   1 - beta2 ** step, None, None, coeff=coeff, model_param=arena.model_param[sl])
+            opt.advance_step()
+            self.last_grad_norm = norm
+        arena.main_grad.zero_()
+
+    # ------------------------------------------------------------ utilities
+    def tokens_per_step(self) -> int:
+        return self.args.global_batch_size * self.cfg.seq_len
+
+    def check(self) -> None:
+        self.ddp.check()
+
+    def close(self) -> None:
+        if self.engine is not None and self.engine._trace is not None:
+            self.engine._trace.close()
+        if self.pool is not None:
+            self.pool.close()
+            self.pool = None
+
+
+def default_args(**overrides):
+    args = build_parser().parse_args([])
+    for k, v in overrides.items():
+        if not hasattr(args, k):
+            raise AttributeError(f"unknown trainer arg '{k}'")
+        setattr(args, k, v)
+    return args
