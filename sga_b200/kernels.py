@@ -64,9 +64,18 @@ class NativeError(RuntimeError):
     pass
 
 
+_LAUNCHES = [0]
+
+
 def _chk(rc: int, what: str) -> None:
+    _LAUNCHES[0] += 1
     if rc != 0:
         raise NativeError(f"{what} failed with code {rc}")
+
+
+def launch_count() -> int:
+    """Number of native launcher calls so far (each launches at least one kernel)."""
+    return _LAUNCHES[0]
 
 
 def _st() -> int:
