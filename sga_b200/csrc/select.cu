@@ -423,3 +423,77 @@ SGA_API int sga_expand_blocks(const uint8_t* bmask, long long nblocks, int X, lo
   expand_blocks_kernel<<<grid_for(n, 256), 256, 0, ST(stream)>>>(bmask, nblocks, X, n, mask);
   return LAUNCH_OK();
 }
+
+// ---------------------------------------------------------------------------
+// Compaction without a caller-supplied work array (see compact_noalloc.h).
+//
+// For hosts that cannot allocate device memory themselves -- all of it belongs
+// to their own arena, or they may not pay the synchronisation an allocation
+// implies, or they only ever receive input and output buffers -- the per-block
+// counters of the compaction live in this file-scope device array instead.
+// 65536 ints = 256 KiB per GPU for the life of the process; masks of up to
+// 65536 * 4096 bytes are accepted, longer ones are refused.
+//
+// Host code must not hand `g_compact_noalloc_counts` to a kernel: on the host
+// that name is only a stand-in for the symbol, not a device address. The
+// address is looked up once per device with cudaGetSymbolAddress while that
+// device is current (the first call on a device does it; do that call at
+// start-up, before any stream capture), then passed to the same three kernels
+// sga_compact_mask() uses. The array is shared by every call and keeps its
+// old contents; compact_count_kernel rewrites each entry before it is read,
+// so nothing has to be cleared, but calls that overlap on the GPU race.
+// ---------------------------------------------------------------------------
+#include "compact_noalloc.h"
+#include <mutex>
+#include <stdio.h>
+
+static __device__ __align__(256) int g_compact_noalloc_counts[SGA_COMPACT_NOALLOC_MAX_BLOCKS];
+
+namespace {
+constexpr int kNoallocMaxDevices = 64;
+int* g_noalloc_ptr[kNoallocMaxDevices] = {nullptr};
+std::mutex g_noalloc_mu;
+
+// Device address of the work array on the current device, resolved on first use.
+int* noalloc_scratch_for_current_device(int* rc) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoallocMaxDevices) {
+    *rc = SGA_COMPACT_NOALLOC_E_SETUP;
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(g_noalloc_mu);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    int* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_compact_noalloc_counts);
+    if (e != cudaSuccess || p == nullptr) {
+      fprintf(stderr, "sga_compact_mask_noalloc: cudaGetSymbolAddress failed on device %d: %s\n", dev,
+              cudaGetErrorString(e));
+      *rc = SGA_COMPACT_NOALLOC_E_SETUP;
+      return nullptr;
+    }
+    g_noalloc_ptr[dev] = p;
+  }
+  *rc = 0;
+  return g_noalloc_ptr[dev];
+}
+}  // namespace
+
+SGA_API int sga_compact_mask_noalloc(const uint8_t* mask, long long n, int* idx_out, long long cap,
+                                     long long* total_out, int* err, void* stream) {
+  if (n <= 0) return 0;
+  if (n > SGA_COMPACT_NOALLOC_MAX_ELEMS) {
+    fprintf(stderr,
+            "sga_compact_mask_noalloc: mask of %lld bytes exceeds the built-in work array (at most %lld bytes); "
+            "use sga_compact_mask with your own work array\n",
+            n, (long long)SGA_COMPACT_NOALLOC_MAX_ELEMS);
+    return SGA_COMPACT_NOALLOC_E_TOO_LARGE;
+  }
+  int rc = 0;
+  int* counts = noalloc_scratch_for_current_device(&rc);
+  if (counts == nullptr) return rc;
+  const int nb = (int)((n + CP_TILE - 1) / CP_TILE);
+  compact_count_kernel<<<nb, CP_THREADS, 0, ST(stream)>>>(mask, n, counts);
+  scan_counts_kernel<<<1, 1024, 0, ST(stream)>>>(counts, nb, total_out);
+  compact_scatter_kernel<<<nb, CP_THREADS, 0, ST(stream)>>>(mask, n, counts, idx_out, cap, err);
+  return cudaGetLastError() == cudaSuccess ? 0 : SGA_COMPACT_NOALLOC_E_LAUNCH;
+}
