@@ -1,0 +1,182 @@
+"""Worker for the multi-GPU tests (run under torchrun, one rank per GPU).
+
+Checks the peer-memory kernels against references built from NCCL
+all-gathers with the same fixed rank order of summation (so results must be
+bit-identical), then steps the tiny model through every synchronisation path
+and checks that all ranks hold identical parameters afterwards.
+Prints ``DIST_GPU_OK`` on rank 0 when everything passed.
+"""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from sga_b200 import kernels_torch as KT  # noqa: E402
+from sga_b200.parallel import p2p  # noqa: E402
+from sga_b200.parallel.symm import SymmPool  # noqa: E402
+
+
+def gather(t):
+    out = [torch.empty_like(t) for _ in range(dist.get_world_size())]
+    dist.all_gather(out, t.contiguous())
+    return out
+
+
+def pack_bits_np(mask_bool):
+    packed = np.packbits(mask_bool.cpu().numpy().astype("uint8"), bitorder="little")
+    packed = np.concatenate([packed, np.zeros((-len(packed)) % 4, dtype="uint8")]).view("int32")
+    return torch.from_numpy(packed.copy())
+
+
+def check_kernels(rank, world, dev):
+    pool = SymmPool(device=dev)
+    ch = p2p.PeerChannel(pool)
+    n = 300007
+    torch.manual_seed(100 + rank)
+    # ---- all-reduce
+    buf = pool.alloc(4 * n)
+    v = buf.view(torch.float32, 0, n)
+    x = torch.randn(n, device=dev)
+    v.copy_(x)
+    sq = torch.zeros(1, device=dev)
+    dist.barrier()
+    p2p.allreduce_(ch, buf, 0, n, scale=1.0 / world, sumsq_out=sq)
+    torch.cuda.synchronize()
+    ch.check("allreduce")
+    xs = gather(x)
+    ref = xs[0].clone()
+    for r in range(1, world):
+        ref += xs[r]
+    ref *= 1.0 / world
+    assert torch.equal(v, ref), "p2p all-reduce differs from the rank-ordered sum"
+    sqs = gather(sq)
+    assert all(torch.equal(sqs[0], s) for s in sqs), "norm must be identical on every rank"
+    assert abs(sq.item() - (ref.double() ** 2).sum().item()) <= 1e-4 * sq.item()
+    # ---- reduce-scatter only
+    v.copy_(x)
+    dist.barrier()
+    p2p.allreduce_(ch, buf, 0, n, scale=1.0 / world, rs_only=True)
+    torch.cuda.synchronize()
+    ch.check("reduce-scatter")
+    n4 = (n + 3) // 4
+    per = (n4 + world - 1) // world
+    lo, hi = min(n, per * rank * 4), min(n, per * (rank + 1) * 4)
+    assert torch.equal(v[lo:hi], ref[lo:hi])
+    # ---- mask union reduce
+    gb = pool.alloc(4 * n)
+    nw = (n + 31) // 32
+    bb, ub = pool.alloc(4 * nw), pool.alloc(4 * nw)
+    g = gb.view(torch.float32, 0, n)
+    g.copy_(x)
+    m = torch.rand(n, device=dev) < 0.03
+    bb.view(torch.int32, 0, nw).copy_(pack_bits_np(m))
+    mu8 = torch.empty(n, dtype=torch.uint8, device=dev)
+    dist.barrier()
+    p2p.mask_union_reduce_(ch, gb, 0, bb, 0, ub, 0, n, scale=1.0 / world, mask_u8=mu8, sumsq_out=sq)
+    torch.cuda.synchronize()
+    ch.check("mask union")
+    ms = gather(m.to(torch.uint8))
+    union = ms[0].clone()
+    for r in range(1, world):
+        union |= ms[r]
+    assert torch.equal(mu8, union)
+    exp = torch.where(union.bool(), ref, x)
+    assert torch.equal(g, exp), "masked entries must hold the mean, the rest the local value"
+    # ---- bucket index sync (exact rank-local top-k, (idx, val) exchange, ordered scatter-add)
+    nb, k = 200003, 2000
+    acc = torch.randn(nb, device=dev) * 1e-3
+    acc[::53] = 0.25  # ties at the top
+    a0 = acc.clone()
+    slots = pool.alloc(8 * k * world)
+    comm = torch.zeros(nb, device=dev)
+    touched = torch.empty((nb + 31) // 32, dtype=torch.int32, device=dev)
+    scratch = p2p.IndexSyncScratch(dev)
+    for rep in range(2):
+        acc.copy_(a0)
+        comm.zero_()
+        dist.barrier()
+        p2p.bucket_index_sync_(ch, scratch, acc, k, slots=slots, kcap=k, comm=comm, touched=touched,
+                               scale=1.0 / world, sumsq_out=sq)
+        torch.cuda.synchronize()
+        ch.check("bucket index sync")
+        mask = KT.topk_exact_flat(a0.abs(), k)
+        idx = KT.compact_mask_idx(mask)
+        vals = a0[idx.long()]
+        assert torch.equal(acc, torch.where(mask.bool(), torch.zeros_like(a0), a0))
+        idxs, valss = gather(idx), gather(vals)
+        refc = torch.zeros(nb, device=dev)
+        for r in range(world):
+            refc.index_add_(0, idxs[r].long(), valss[r] * (1.0 / world))
+        assert torch.equal(comm, refc), "reduced sparse gradient differs from the rank-ordered reference"
+        assert abs(sq.item() - (refc.double() ** 2).sum().item()) <= 1e-4 * max(sq.item(), 1e-30)
+    dist.barrier()
+    pool.close()
+
+
+def check_trainer(rank, world, dev):
+    from sga_b200.runtime.trainer import Trainer, default_args
+
+    common = dict(model="test_tiny", micro_batch_size=2, global_batch_size=4 * world, train_iters=6, lr=1e-3,
+                  sga_bucket_elems=30000, log_interval=0)
+    cases = {
+        "dense_fused": dict(),
+        "dense_allreduce": dict(dense_mode="allreduce"),
+        "rank_local_index": dict(sga_enabled=True, sga_score="abs_g", sga_selection_method="exact",
+                                 sga_selection_ratio_percent=2.0, sga_backend="torch_pipelined_index",
+                                 sga_selection_locality="rank_local", sga_cycle_period=3),
+        "rank_local_mask": dict(sga_enabled=True, sga_score="abs_g", sga_selection_method="exact",
+                                sga_selection_ratio_percent=5.0, sga_backend="torch_pipelined_mask",
+                                sga_selection_locality="rank_local", sga_cycle_period=4),
+        "shared_index": dict(sga_enabled=True, sga_score="update", sga_selection_method="histogram",
+                             sga_selection_histogram_mode="balanced", sga_selection_ratio_percent=10.0,
+                             sga_backend="torch_pipelined_index", sga_cycle_period=3, sga_cycle_start_iter=1),
+        "shared_mask": dict(sga_enabled=True, sga_score="abs_m", sga_selection_method="histogram",
+                            sga_selection_histogram_mode="balanced", sga_selection_ratio_percent=10.0,
+                            sga_backend="torch_pipelined_mask", sga_cycle_period=2),
+        "shared_nccl_index": dict(sga_enabled=True, sga_score="abs_g", sga_selection_method="histogram",
+                                  sga_selection_histogram_mode="balanced", sga_selection_ratio_percent=10.0,
+                                  sga_backend="nccl_pipelined_index", sga_cycle_period=2),
+    }
+    final = {}
+    for name, kw in cases.items():
+        tr = Trainer(default_args(**common, **kw), quiet=True)
+        losses = []
+        for s in range(6):
+            losses.append(float(tr.train_step(tr.host_batch(0)).item()))
+        tr.check()
+        w = tr.model.arena.model_param.clone()
+        ws = gather(w)
+        assert all(torch.equal(ws[0], t) for t in ws), f"{name}: ranks hold different parameters"
+        assert losses[-1] < losses[0], f"{name}: loss did not decrease {losses}"
+        assert all(l == l for l in losses)
+        final[name] = losses
+        tr.close()
+        dist.barrier()
+    # the two dense paths compute the same update (different execution strategy)
+    a, b = final["dense_fused"], final["dense_allreduce"]
+    assert all(abs(x - y) < 2e-2 for x, y in zip(a, b)), (a, b)
+    return final
+
+
+def main():
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    rank, world = dist.get_rank(), dist.get_world_size()
+    check_kernels(rank, world, dev)
+    final = check_trainer(rank, world, dev)
+    dist.barrier()
+    if rank == 0:
+        for k, v in final.items():
+            print(k, [round(x, 4) for x in v])
+        print("DIST_GPU_OK", flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

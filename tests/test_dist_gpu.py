@@ -1,0 +1,28 @@
+"""Multi-GPU tests: launches ``dist_gpu_worker.py`` under torchrun on the GPUs
+of this box (2 when more are visible, to keep the run short). NVLS is switched
+off in NCCL for these child processes and the framework's own kernels use
+plain peer loads and stores."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _run(nproc, timeout=600):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", "29741", os.path.join(HERE, "dist_gpu_worker.py")]
+    return subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
+
+
+@pytest.mark.timeout(900)
+def test_peer_kernels_and_trainer_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least 2 GPUs")
+    res = _run(2)
+    assert res.returncode == 0 and "DIST_GPU_OK" in res.stdout, res.stdout[-3000:] + "\n" + res.stderr[-6000:]
