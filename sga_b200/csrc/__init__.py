@@ -56,6 +56,7 @@ def _declare(L: ctypes.CDLL) -> None:
     """Argument/return types of every exported launcher (all return int)."""
     sigs = {
         "sga_gemm_bf16": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _I, _P],
+        "sga_gemm_bf16_pair": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _I, _P],
     }
     sigs.update(_EXTRA_SIGS)
     for name, args in sigs.items():

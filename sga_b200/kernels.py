@@ -98,9 +98,14 @@ def gemm_err_word(device) -> torch.Tensor:
     return _gemm_err[key]
 
 
+import os as _os
+
+GEMM_PAIR = _os.environ.get("SGA_GEMM_PAIR", "1") != "0"  # CTA-pair (256 x 256) tiles when M >= 256
+
+
 def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
               epi: int = EPI_BF16, residual: torch.Tensor | None = None, alpha: float = 1.0,
-              max_ctas: int = 0) -> torch.Tensor:
+              max_ctas: int = 0, pair: bool | None = None) -> torch.Tensor:
     """``out (epi)= alpha * A @ B^T`` on the tcgen05 tensor cores.
 
     ``a`` holds the logical ``[M, K]`` operand either K-major (stored
@@ -119,7 +124,9 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, a_mn: bool
         assert out.dtype == torch.float32
     if epi == EPI_BF16_ADD:
         assert residual is not None and residual.dtype == torch.bfloat16 and residual.stride(0) == out.stride(0)
-    rc = lib().sga_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), _p(residual), M, N, K, int(a_mn),
+    use_pair = GEMM_PAIR if pair is None else pair
+    fn = lib().sga_gemm_bf16_pair if (use_pair and M >= 256) else lib().sga_gemm_bf16
+    rc = fn(a.data_ptr(), b.data_ptr(), out.data_ptr(), _p(residual), M, N, K, int(a_mn),
                              int(b_mn), a.stride(0), b.stride(0), out.stride(0), epi, float(alpha),
                              gemm_err_word(a.device).data_ptr(), max_ctas, _st())
     _chk(rc, "sga_gemm_bf16")

@@ -28,9 +28,13 @@ def _kt():
 
 
 # ---------------------------------------------------------------- GEMM
+@pytest.mark.parametrize("pair", [False, True])
 @pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (0, 1), (1, 0), (1, 1)])
-@pytest.mark.parametrize("shape", [(256, 512, 256), (384, 768, 192), (200, 328, 136), (128, 256, 64)])
-def test_gemm_layouts(a_mn, b_mn, shape):
+@pytest.mark.parametrize("shape", [(256, 512, 256), (384, 768, 192), (200, 328, 136), (128, 256, 64),
+                                   (1024, 1280, 320)])
+def test_gemm_layouts(a_mn, b_mn, shape, pair):
+    """Single-CTA (128 x 256) and CTA-pair (256 x 256) tcgen05 kernels; the pair
+    kernel takes over from M >= 256."""
     K = _k()
     M, N, Kd = shape
     torch.manual_seed(1)
@@ -40,15 +44,15 @@ def test_gemm_layouts(a_mn, b_mn, shape):
     B = (Bl.t().contiguous() if b_mn else Bl).to(torch.bfloat16)
     ref = (A.t() if a_mn else A).float() @ (B.t() if b_mn else B).float().t()
     out = torch.zeros(M, N, device=DEV, dtype=torch.bfloat16)
-    K.gemm_bf16(A, B, out, a_mn=bool(a_mn), b_mn=bool(b_mn))
+    K.gemm_bf16(A, B, out, a_mn=bool(a_mn), b_mn=bool(b_mn), pair=pair)
     assert int(K.gemm_err_word(DEV).item()) == 0
     assert (out.float() - ref).abs().max().item() <= 0.02 * ref.abs().max().item()
     acc = torch.ones(M, N, device=DEV, dtype=torch.float32)
-    K.gemm_bf16(A, B, acc, a_mn=bool(a_mn), b_mn=bool(b_mn), epi=K.EPI_F32_ACC)
+    K.gemm_bf16(A, B, acc, a_mn=bool(a_mn), b_mn=bool(b_mn), epi=K.EPI_F32_ACC, pair=pair)
     assert (acc - (ref + 1.0)).abs().max().item() <= 2e-3 * ref.abs().max().item()
     res = torch.randn(M, N, device=DEV).to(torch.bfloat16)
     out2 = torch.zeros_like(out)
-    K.gemm_bf16(A, B, out2, a_mn=bool(a_mn), b_mn=bool(b_mn), epi=K.EPI_BF16_ADD, residual=res)
+    K.gemm_bf16(A, B, out2, a_mn=bool(a_mn), b_mn=bool(b_mn), epi=K.EPI_BF16_ADD, residual=res, pair=pair)
     assert (out2.float() - (ref + res.float())).abs().max().item() <= 0.03 * ref.abs().max().item()
 
 
