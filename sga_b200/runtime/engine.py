@@ -372,7 +372,7 @@ class SGAEngine:
         num_zeros = self._count_zeros() if optimizer.config.log_num_zeros_in_grad else None
         # 3b. trace dump slot
         if self._trace is not None:
-            self._trace.maybe_dump(self, optimizer, step, grad_norm)
+            self._trace.maybe_dump(self, optimizer, step - 1, grad_norm)
         # 4. optimizer template
         arena = self._ddp.arena
         next_full = self._cycle.is_full(step + 1)
@@ -439,7 +439,7 @@ class SGAEngine:
         reselect = self._cycle.reselect_boundary(step)
         reselected = reselect and self._shadow_score
         if self._trace is not None:
-            self._trace.maybe_dump(self, optimizer, step, grad_norm)
+            self._trace.maybe_dump(self, optimizer, step - 1, grad_norm)
         if reselected:
             self._shadow_reselect(self._refresh_records(optimizer))
         arena = self._ddp.arena
@@ -583,7 +583,7 @@ class SGAEngine:
                 K.clip_coeff(sumsq, 1.0 / world, clip, self._dev["coeff"], self._dev["norm"])
             else:
                 K.clip_coeff(sumsq, 1.0, clip, self._dev["coeff"], self._dev["norm"])
-            wants_dump = self._trace is not None and any(self._trace.wants(step))
+            wants_dump = self._trace is not None and any(self._trace.wants(step - 1))
             if wants_dump and clip > 0.0:
                 # the dump slot reads post-clip gradients: scale explicitly, hand the kernel 1.0
                 self._scale_communicated(was_full, mask)
@@ -606,7 +606,7 @@ class SGAEngine:
             c = clip / (norm + 1.0e-6)
             if c < 1.0:
                 coeff = float(torch.tensor(c, dtype=torch.float32).item())
-        wants_dump = self._trace is not None and any(self._trace.wants(step))
+        wants_dump = self._trace is not None and any(self._trace.wants(step - 1))
         if wants_dump and coeff != 1.0:
             self._scale_communicated(was_full, mask, coeff)
             return norm, 1.0
