@@ -1,0 +1,57 @@
+"""Training entry (the torchrun target): ``python -m sga_b200.train_gpt --model
+llama3_1b --sga-enabled true ...``.
+
+Parses the trainer and ``--sga-*`` flags, installs the backend timer when
+asked, runs the resume guard, builds the trainer, optionally loads a
+checkpoint, trains on synthetic tokens, logs throughput, saves checkpoints.
+Counterpart of ``sga/train_gpt.py:212-252``.
+"""
+from __future__ import annotations
+
+import sys
+import time
+
+import torch
+
+from .runtime import checkpoint as ckpt
+from .runtime.trainer import Trainer, build_parser
+
+
+def main(argv=None) -> int:
+    args = build_parser().parse_args(argv)
+    ckpt.sga_resume_guard(args)
+    tr = Trainer(args)
+    start = 0
+    if args.load:
+        start = ckpt.load_checkpoint(args.load, tr.model, tr.optimizer)
+        tr.iteration = start
+        if tr.rank == 0 and start:
+            print(f"[train] resumed from iteration {start} (the SGA cycle cold-starts: dense steps until the next "
+                  "boundary; discard the first post-resume timing)", flush=True)
+    cuda = tr.device.type == "cuda"
+    t_last = time.perf_counter()
+    for it in range(start + 1, args.train_iters + 1):
+        loss = tr.train_step(tr.host_batch(it - 1))
+        if args.log_interval and it % args.log_interval == 0:
+            lv = float(loss.item())
+            if cuda:
+                torch.cuda.synchronize()
+            now = time.perf_counter()
+            dt = (now - t_last) / args.log_interval
+            t_last = now
+            if tr.rank == 0:
+                gn = tr.last_grad_norm
+                gn = float(gn.item()) if hasattr(gn, "item") else (float(gn) if gn is not None else float("nan"))
+                print(f"[train] iteration {it}/{args.train_iters} | loss {lv:.6f} | grad norm {gn:.4f} | "
+                      f"{dt * 1e3:.1f} ms/step | {tr.tokens_per_step() / dt:.0f} tokens/s", flush=True)
+        if args.save and args.save_interval and it % args.save_interval == 0:
+            ckpt.save_checkpoint(args.save, it, args, tr.model, tr.optimizer, tr.rank)
+    if args.save:
+        ckpt.save_checkpoint(args.save, args.train_iters, args, tr.model, tr.optimizer, tr.rank)
+    tr.check()
+    tr.close()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
