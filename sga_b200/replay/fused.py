@@ -1,0 +1,501 @@
+"""Fused, parameter-sharded, multi-configuration replay.
+
+The flat parameter vector is cut into ``world`` contiguous shards (one
+process, one GPU each). Every shard streams the window's gradient files once
+and advances all R configurations of a group together: per step one pass for
+the clip norms, a boundary reselection (exact distributed top-k) where the
+calendar asks for it, and one pass that clips, updates residuals, commits Adam
+and accumulates the horizon numerators. On CUDA the two passes are the
+``csrc/replay.cu`` kernels (one read of ``g`` for all R configurations); on
+CPU the same arithmetic runs as PyTorch ops, which is what makes a one-shard
+run equal the per-configuration oracle bit for bit.
+
+Cross-shard traffic is small and goes through ``torch.distributed`` (gloo on
+CPU, NCCL on GPUs): fp64 partial sums ``[R]`` per pass, int64 radix
+histograms and tie counts per selection. Sums are reduced in fp64, so shard
+counts only reorder additions ("pure reordering band": sums agree to ~1e-6
+relative, everything discrete is exact).
+
+Reference: ``sga/replay_fused.py:97-2404`` (Comms ``:113-227``, shard_select
+``:290-402``, GPrefetcher ``:902-1104``, worker ``:1124-2083``).
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+import os
+import queue
+import threading
+import time
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from . import core as RC
+
+# kill switches: unknown values raise so that both arms of an A/B are always reachable
+ENV_KERNEL = "REPLAY_FUSED_KERNEL"      # on | off  (off: PyTorch ops even on CUDA)
+ENV_SELECT = "REPLAY_FUSED_SELECT"      # radix | gather
+
+
+def _switch(name, allowed, default):
+    v = os.environ.get(name, default)
+    if v not in allowed:
+        raise ValueError(f"{name} must be one of {allowed} (got {v!r})")
+    return v
+
+
+class Comms:
+    """Scalar / histogram plane over one process group (identity for one shard)."""
+
+    def __init__(self, rank=0, world=1, group=None, device="cpu"):
+        self.rank, self.world, self.group, self.device = rank, world, group, torch.device(device)
+        self.ops = 0
+
+    def sum_(self, t: torch.Tensor) -> torch.Tensor:
+        if self.world > 1:
+            self.ops += 1
+            dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
+        return t
+
+    def gather_i64(self, value: int) -> list:
+        if self.world == 1:
+            return [int(value)]
+        self.ops += 1
+        t = torch.tensor([int(value)], dtype=torch.int64, device=self.device)
+        out = [torch.zeros_like(t) for _ in range(self.world)]
+        dist.all_gather(out, t, group=self.group)
+        return [int(x.item()) for x in out]
+
+    def gather_to_root(self, t: torch.Tensor):
+        """Variable-length gather of a 1-D tensor; returns the concatenation on rank 0."""
+        if self.world == 1:
+            return t
+        sizes = self.gather_i64(t.numel())
+        pad = torch.zeros(max(sizes), dtype=t.dtype, device=t.device)
+        pad[:t.numel()] = t
+        out = [torch.zeros_like(pad) for _ in range(self.world)]
+        self.ops += 1
+        dist.all_gather(out, pad, group=self.group)
+        return torch.cat([o[:s] for o, s in zip(out, sizes)])
+
+
+def shard_bounds(n: int, world: int, rank: int):
+    per = (n + world - 1) // world
+    per = (per + 7) // 8 * 8
+    lo = min(n, per * rank)
+    return lo, min(n, lo + per)
+
+
+def shard_select(score_loc: torch.Tensor, k: int, comms: Comms) -> torch.Tensor:
+    """Exact distributed top-``k`` by ``|score|`` with ties filled in global
+    flat-index order (shards are contiguous and ordered by rank). Two radix
+    digits: the 16 high key bits locate the crossing bin, the 16 low bits the
+    exact key; no candidate values cross the wire."""
+    from ..plugins.selection._histogram import _ops
+
+    ops = _ops(score_loc)
+    x = score_loc.contiguous().float()
+    hist = torch.zeros(32769, dtype=torch.int64, device=x.device)
+    if x.numel():
+        ops.hist_top(x, 16, 1, 32769, hist)
+    comms.sum_(hist)
+    suffix = torch.cumsum(hist.flip(0), 0)
+    b = 32768 - int(torch.searchsorted(suffix, k).item())
+    above = int(hist[b + 1:].sum().item())
+    low = torch.zeros(65536, dtype=torch.int64, device=x.device)
+    if x.numel():
+        ops.hist_low16(x, b, low)
+    comms.sum_(low)
+    suffix2 = torch.cumsum(low.flip(0), 0)
+    lb = 65535 - int(torch.searchsorted(suffix2, k - above).item())
+    T = (b << 16) | lb
+    n_gt = above + int(low[lb + 1:].sum().item())
+    need = k - n_gt
+    key = RC.abs_key(x)
+    sel = key > T
+    ties = torch.nonzero(key == T, as_tuple=False).view(-1)
+    counts = comms.gather_i64(ties.numel())
+    before = sum(counts[:comms.rank])
+    take = max(0, min(ties.numel(), need - before))
+    if take:
+        sel[ties[:take]] = True
+    return sel
+
+
+@dataclass
+class StepInput:
+    si: int
+    g: torch.Tensor          # this shard's logged gradient (fp32 or bf16), on the device
+    grad_norm: float
+    lr: float
+
+
+class GPrefetcher:
+    """Background reader: loads each step's gradient file, slices this shard
+    out of it in catalog order and stages it (pinned when the consumer is a
+    GPU). Depth-bounded; the first failure is latched and re-raised by ``get``."""
+
+    def __init__(self, info: RC.TraceInfo, steps, lo, hi, dtype, pin: bool, depth: int = 2):
+        self.info, self.steps, self.lo, self.hi, self.dtype, self.pin = info, list(steps), lo, hi, dtype, pin
+        self.q = queue.Queue(maxsize=depth)
+        self.exc: Optional[BaseException] = None
+        self.read_s = 0.0
+        self.t = threading.Thread(target=self._run, name="sga-replay-prefetch", daemon=True)
+        self.t.start()
+
+    def _load(self, t):
+        return RC.load_g(self.info, t)
+
+    def _run(self):
+        try:
+            for t in self.steps:
+                t0 = time.perf_counter()
+                meta, payload = self._load(t)
+                flat = RC.flatten(payload, self.info, self.dtype, self.lo, self.hi)
+                if self.pin:
+                    flat = flat.pin_memory()
+                self.read_s += time.perf_counter() - t0
+                self.q.put((t, meta, flat))
+        except BaseException as e:
+            self.exc = e
+            self.q.put(None)
+
+    def get(self):
+        item = self.q.get()
+        if item is None:
+            raise RuntimeError(f"gradient prefetch failed: {self.exc!r}") from self.exc
+        return item
+
+
+class _CfgStruct(ctypes.Structure):
+    _fields_ = [("boundary", ctypes.c_int), ("fold", ctypes.c_int), ("dual", ctypes.c_int), ("adams", ctypes.c_int),
+                ("horizon", ctypes.c_int), ("fold_div", ctypes.c_float), ("coef", ctypes.c_float),
+                ("lr", ctypes.c_float), ("lr_inactive", ctypes.c_float), ("bc1", ctypes.c_float),
+                ("bc2", ctypes.c_float)]
+
+
+class FusedGroup:
+    """R configurations of one branch point advanced together on one shard."""
+
+    def __init__(self, configs, n_loc, n_total, device, comms: Comms, hp: RC.Hyper, wd_vec, w0, m0, v0, t0, W,
+                 horizons, dense_snaps, use_kernel: bool):
+        self.cfgs = list(configs)
+        self.R = len(self.cfgs)
+        if self.R > 32:
+            raise ValueError("at most 32 configurations per fused group")
+        self.n, self.n_total, self.device, self.comms, self.hp = n_loc, n_total, torch.device(device), comms, hp
+        self.t0, self.Wlen, self.horizons = t0, W, sorted(horizons)
+        self.use_kernel = use_kernel and self.device.type == "cuda"
+        R, n = self.R, n_loc
+        self.W = w0.to(self.device).unsqueeze(0).repeat(R, 1).contiguous()
+        self.M = m0.to(self.device).unsqueeze(0).repeat(R, 1).contiguous()
+        self.V = v0.to(self.device).unsqueeze(0).repeat(R, 1).contiguous()
+        self.RES = torch.zeros(R, n, dtype=torch.float32, device=self.device)
+        self.SEL = torch.zeros(R, n, dtype=torch.uint8, device=self.device)
+        self.wd = wd_vec.to(self.device)
+        self.dense = {h: t.to(self.device) for h, t in dense_snaps.items()}
+        self.k = [RC.k_for(n_total, c.ratio_percent) for c in self.cfgs]
+        self.numer = {h: [0.0] * R for h in self.horizons}
+        self.per_step = []
+        self.stats = {"pass1_s": 0.0, "select_s": 0.0, "pass3_s": 0.0, "selects": 0}
+        if self.use_kernel:
+            from ..csrc import lib
+
+            L = lib()
+            self._nb = L.sga_replay_blocks()
+            self._partials = torch.zeros(R * self._nb, dtype=torch.float64, device=self.device)
+            self._out = torch.zeros(R, dtype=torch.float64, device=self.device)
+            self._cfg_dev = torch.zeros(R * ctypes.sizeof(_CfgStruct), dtype=torch.uint8, device=self.device)
+
+    # -------------------------------------------------------------- selection
+    def initial_select(self, branch_grad_loc) -> None:
+        """Branch-point supports: the state dump's gradient is post-clip and is scored as is."""
+        g = branch_grad_loc.to(self.device).float()
+        cache = {}
+        for r, c in enumerate(self.cfgs):
+            key = (c.score, c.ratio_percent, c.optimizer)
+            if key not in cache:
+                sc = RC.replay_score(c.score, self.W[r], self.M[r], self.V[r], g, self._hp_dev(), self.t0 + 1,
+                                     c.optimizer)
+                cache[key] = shard_select(sc, self.k[r], self.comms)
+            self.SEL[r] = cache[key].to(torch.uint8)
+
+    def _hp_dev(self):
+        return RC.Hyper(wd=self.wd, beta1=self.hp.beta1, beta2=self.hp.beta2, eps=self.hp.eps, clip=self.hp.clip)
+
+    # ------------------------------------------------------------------- step
+    def _plan(self, si, count, lr):
+        plan = []
+        for c in self.cfgs:
+            adams = c.optimizer == "adams"
+            boundary = si % c.cycle_len == 0
+            lr32 = RC.f32(lr)
+            plan.append(dict(
+                boundary=boundary, fold=bool(c.fold and boundary and si > 0), fold_div=float(c.cycle_len),
+                dual=bool(c.dual_lr != 1.0), adams=adams, lr=lr32,
+                lr_inactive=float(torch.tensor(lr, dtype=torch.float32) * c.dual_lr),
+                bc1=1.0 if adams else 1.0 - self.hp.beta1 ** count, bc2=1.0 if adams else 1.0 - self.hp.beta2 ** count,
+                horizon=(si + 1) in self.dense, coef=1.0))
+        return plan
+
+    def _upload(self, plan):
+        arr = (_CfgStruct * self.R)()
+        for r, p in enumerate(plan):
+            a = arr[r]
+            a.boundary, a.fold, a.dual, a.adams, a.horizon = int(p["boundary"]), int(p["fold"]), int(p["dual"]), \
+                int(p["adams"]), int(p["horizon"])
+            a.fold_div, a.coef, a.lr, a.lr_inactive, a.bc1, a.bc2 = p["fold_div"], p["coef"], p["lr"], \
+                p["lr_inactive"], p["bc1"], p["bc2"]
+        host = torch.frombuffer(bytearray(bytes(arr)), dtype=torch.uint8)
+        self._cfg_dev.copy_(host)
+
+    def _q_pre(self, p, g, r):
+        if p["boundary"]:
+            res = RC._div(self.RES[r], p["fold_div"]) if p["fold"] else self.RES[r]
+            return g + res
+        return torch.where(self.SEL[r] > 0, g, torch.zeros_like(g))
+
+    def step(self, inp: StepInput) -> None:
+        si = inp.si
+        count = self.t0 + si + 1
+        plan = self._plan(si, count, inp.lr)
+        coef_dense = RC.f32(RC.clip_coef(inp.grad_norm ** 2, self.hp.clip)) if self.hp.clip > 0 else 1.0
+        g_dev = inp.g.to(self.device, non_blocking=True)
+        st = None
+        # ---- pass 1: clip norms
+        t0 = time.perf_counter()
+        if self.use_kernel:
+            from ..csrc import lib
+
+            st = torch.cuda.current_stream().cuda_stream
+            self._upload(plan)
+            rc = lib().sga_replay_pass1(g_dev.data_ptr(), int(g_dev.dtype == torch.bfloat16), coef_dense,
+                                        self.RES.data_ptr(), self.SEL.data_ptr(), self._cfg_dev.data_ptr(), self.R,
+                                        self.n, self._partials.data_ptr(), self._out.data_ptr(), st)
+            assert rc == 0, rc
+            sums = self._out.clone()
+            g = None
+        else:
+            g = RC._div(g_dev.float(), coef_dense)
+            sums = torch.stack([(self._q_pre(p, g, r).double() ** 2).sum() for r, p in enumerate(plan)])
+        self.comms.sum_(sums)
+        sums = sums.tolist()
+        for p, s in zip(plan, sums):
+            p["coef"] = RC.f32(RC.clip_coef(s, self.hp.clip))
+        self.stats["pass1_s"] += time.perf_counter() - t0
+        # ---- pass 2: boundary reselection on the pre-commit state (the outgoing support stays for pass 3)
+        t0 = time.perf_counter()
+        new_sel = {}
+        if any(p["boundary"] and 0 < si < self.Wlen - 1 for p in plan):
+            if g is None:
+                g = RC._div(g_dev.float(), coef_dense)
+            cache = {}
+            for r, (p, c) in enumerate(zip(plan, self.cfgs)):
+                if not (p["boundary"] and 0 < si < self.Wlen - 1):
+                    continue
+                q = self._q_pre(p, g, r) * p["coef"]
+                sc = RC.replay_score(c.score, self.W[r], self.M[r], self.V[r], q, self._hp_dev(), count, c.optimizer)
+                new_sel[r] = shard_select(sc, self.k[r], self.comms).to(torch.uint8)
+                self.stats["selects"] += 1
+        self.stats["select_s"] += time.perf_counter() - t0
+        # ---- pass 3: clip, residual, commit, horizon numerators
+        t0 = time.perf_counter()
+        h = si + 1
+        if self.use_kernel:
+            from ..csrc import lib
+
+            self._upload(plan)
+            wden = self.dense.get(h)
+            rc = lib().sga_replay_pass3(g_dev.data_ptr(), int(g_dev.dtype == torch.bfloat16), coef_dense,
+                                        self.W.data_ptr(), self.M.data_ptr(), self.V.data_ptr(), self.RES.data_ptr(),
+                                        self.SEL.data_ptr(), self.wd.data_ptr(),
+                                        wden.data_ptr() if wden is not None else None, self._cfg_dev.data_ptr(),
+                                        self.R, self.n, RC.f32(self.hp.beta1), RC.f32(1.0 - self.hp.beta1),
+                                        RC.f32(self.hp.beta2), RC.f32(1.0 - self.hp.beta2), RC.f32(self.hp.eps),
+                                        self._partials.data_ptr() if wden is not None else None,
+                                        self._out.data_ptr() if wden is not None else None, st)
+            assert rc == 0, rc
+            if wden is not None:
+                num = self.comms.sum_(self._out.clone()).tolist()
+                self.numer[h] = num
+        else:
+            for r, (p, c) in enumerate(zip(plan, self.cfgs)):
+                q = self._q_pre(p, g, r) * p["coef"]
+                sel = self.SEL[r] > 0
+                if p["boundary"]:
+                    self.RES[r].zero_()
+                else:
+                    self.RES[r] += torch.where(sel, torch.zeros_like(g), g)
+                RC.adam_commit_torch(self.W[r], self.M[r], self.V[r], q, inp.lr, self.wd, self.hp.beta1,
+                                     self.hp.beta2, self.hp.eps, count, c.optimizer,
+                                     inactive=(~sel if (p["boundary"] and p["dual"]) else None), dual_lr=c.dual_lr)
+            if h in self.dense:
+                num = torch.stack([((self.W[r].double() - self.dense[h].double()) ** 2).sum() for r in range(self.R)])
+                self.numer[h] = self.comms.sum_(num).tolist()
+        for r, m in new_sel.items():
+            self.SEL[r] = m
+        self.stats["pass3_s"] += time.perf_counter() - t0
+        self.per_step.append({"si": si, "coef": [p["coef"] for p in plan]})
+
+
+# --------------------------------------------------------------------- driver
+def group_configs(configs, max_configs: int, state_budget_mb: float, n_loc: int):
+    """Cut the configuration list into groups that fit ``max_configs`` and, when
+    given, a per-shard state budget (17 bytes per element per configuration)."""
+    per_cfg = 17.0 * n_loc / (1 << 20)
+    cap = max(1, min(32, max_configs))
+    if state_budget_mb and state_budget_mb > 0:
+        cap = max(1, min(cap, int(state_budget_mb // max(per_cfg, 1e-9))))
+    return [configs[i:i + cap] for i in range(0, len(configs), cap)]
+
+
+def run_shard(rank, world, trace_dir, t0, configs, window, horizons, device, dense_cache, max_configs,
+              state_budget_mb, score_names, ratios, group=None):
+    """One shard's work for one branch point; rank 0 returns the report fragment."""
+    info = RC.discover_trace(trace_dir)
+    dev = torch.device(device)
+    comms = Comms(rank, world, group, dev)
+    lo, hi = shard_bounds(info.numel, world, rank)
+    meta, payload = RC.load_state(info, t0)
+    steps = info.window(t0, window)
+    W = len(steps)
+    if W == 0:
+        raise ValueError(f"no gradient files at branch point {t0}")
+    horizons = sorted(h for h in horizons if h <= W) or [W]
+    groups_hp = meta["param_groups"]
+    hp = RC.Hyper(wd=None, beta1=groups_hp[0]["adam_beta1"], beta2=groups_hp[0]["adam_beta2"],
+                  eps=groups_hp[0]["adam_eps"], clip=meta["clip_grad"])
+    wd_vec = RC.group_vector(info, [g["weight_decay"] for g in groups_hp], lo, hi)
+    w0 = RC.flatten(payload["w"], info, torch.float32, lo, hi)
+    m0 = RC.flatten(payload["m"], info, torch.float32, lo, hi)
+    v0 = RC.flatten(payload["v"], info, torch.float32, lo, hi)
+    g0 = RC.flatten(payload["g"], info, torch.float32, lo, hi)
+    del payload
+    use_kernel = dev.type == "cuda" and _switch(ENV_KERNEL, ("on", "off"), "on") == "on"
+    gdtype = torch.bfloat16 if info.g_dtype == "bf16" else torch.float32
+    # ---- dense arm (element-wise: every shard replays its own slice; cached per shard)
+    optimizers = sorted({c.optimizer for c in configs})
+    dense = {}
+    metas = None
+    for opt in optimizers:
+        ident = RC.cache_ident(trace_dir, t0, W, horizons, "fp32", info.g_dtype, f"fused-{world}-{rank}", opt)
+        blob = RC.load_cache(dense_cache, ident) if dense_cache else None
+        if blob is None:
+            pf = GPrefetcher(info, steps, lo, hi, gdtype, pin=False)
+            logged, metas = [], []
+            for _ in steps:
+                _t, gm, flat = pf.get()
+                logged.append(flat)
+                metas.append(gm)
+            hp_d = RC.Hyper(wd=wd_vec, beta1=hp.beta1, beta2=hp.beta2, eps=hp.eps, clip=hp.clip)
+            snaps = RC.dense_replay(w0, m0, v0, logged, [gm["lr"][0] for gm in metas], hp_d, t0, opt, set(horizons))
+            blob = {"snap_d": snaps, "metas": metas}
+            if dense_cache:
+                RC.save_cache(dense_cache, ident, blob)
+            del logged
+        dense[opt] = blob["snap_d"]
+        metas = blob["metas"]
+    den = {}
+    for opt in optimizers:
+        d = torch.tensor([float(((dense[opt][h].double() - w0.double()) ** 2).sum()) for h in horizons],
+                         dtype=torch.float64, device=dev)
+        den[opt] = comms.sum_(d).tolist()
+    # ---- front: branch scores ranked against the realised dense displacement (the label)
+    front = {}
+    label_loc = (dense[optimizers[0]][horizons[-1]] - w0).abs().to(dev)
+    hp_dev = RC.Hyper(wd=wd_vec.to(dev), beta1=hp.beta1, beta2=hp.beta2, eps=hp.eps, clip=hp.clip)
+    for name in score_names:
+        sc = RC.replay_score(name, w0.to(dev), m0.to(dev), v0.to(dev), g0.to(dev), hp_dev, t0 + 1, optimizers[0])
+        for ratio in ratios:
+            k = RC.k_for(info.numel, ratio)
+            sel_s = shard_select(sc, k, comms)
+            sel_l = shard_select(label_loc, k, comms)
+            stats = torch.tensor([float((sel_s & sel_l).sum()), float(label_loc[~sel_s].double().sum()),
+                                  float(label_loc.double().sum()), float(sc.abs()[~sel_s].double().sum()),
+                                  float(sc.abs().double().sum())], dtype=torch.float64, device=dev)
+            comms.sum_(stats)
+            got_s = comms.gather_to_root(sc.abs()[sel_s].float())
+            got_l = comms.gather_to_root(label_loc[sel_s].float())
+            ideal = comms.gather_to_root(label_loc[sel_l].float())
+            if rank == 0:
+                disc = 1.0 / torch.log2(torch.arange(2, k + 2, dtype=torch.float64, device=dev))
+                order = torch.argsort(got_s, descending=True, stable=True)
+                idl = torch.sort(ideal.double(), descending=True).values
+                idcg = float((idl * disc[:idl.numel()]).sum())
+                ndcg = float((got_l.double()[order] * disc[:order.numel()]).sum()) / idcg if idcg > 0 else 0.0
+                s = stats.tolist()
+                front[(name, ratio)] = {"k": k, "ndcg_at_k": ndcg, "recall_at_k": s[0] / max(k, 1),
+                                        "missed_label_mass": s[1] / s[2] if s[2] > 0 else 0.0,
+                                        "missed_score_mass": s[3] / s[4] if s[4] > 0 else 0.0}
+    # ---- stream: groups of configurations, one pass over the window per group
+    n_loc = hi - lo
+    results, prof = {}, []
+    for grp in group_configs(configs, max_configs, state_budget_mb, n_loc):
+        by_opt = {}
+        fg = FusedGroup(grp, n_loc, info.numel, dev, comms, hp, wd_vec, w0, m0, v0, t0, W, horizons,
+                        dense[grp[0].optimizer] if len({c.optimizer for c in grp}) == 1 else dense[optimizers[0]],
+                        use_kernel)
+        fg.initial_select(g0)
+        pf = GPrefetcher(info, steps, lo, hi, gdtype, pin=dev.type == "cuda")
+        for si in range(W):
+            _t, gm, flat = pf.get()
+            fg.step(StepInput(si, flat, float(gm["grad_norm"]), float(gm["lr"][0])))
+        for r, c in enumerate(grp):
+            results[c] = {h: math.sqrt(fg.numer[h][r]) / math.sqrt(den[c.optimizer][hi_])
+                          if den[c.optimizer][hi_] > 0 else float("nan")
+                          for hi_, h in enumerate(horizons)}
+        prof.append(dict(fg.stats, configs=len(grp), read_s=pf.read_s, comm_ops=comms.ops))
+        last = fg
+    if rank != 0:
+        return None
+    return {"t0": t0, "window_len": W, "window_steps": steps, "horizon_steps": horizons, "front": front,
+            "results": results, "den_norm_at_horizon": {h: math.sqrt(den[optimizers[0]][i])
+                                                        for i, h in enumerate(horizons)},
+            "profile": prof, "final_state": (last.W.cpu(), last.SEL.cpu()) if world == 1 else None}
+
+
+def _worker(rank, world, port, kwargs, out_path):
+    os.environ.update(MASTER_ADDR=os.environ.get("SGA_MASTER_ADDR", "127.0.0.1"),
+                      MASTER_PORT=str(os.environ.get("SGA_MASTER_PORT", port)))
+    device = kwargs["device"]
+    cuda = str(device).startswith("cuda")
+    if cuda:
+        torch.cuda.set_device(rank % torch.cuda.device_count())
+        kwargs = dict(kwargs, device=f"cuda:{rank % torch.cuda.device_count()}")
+    dist.init_process_group("nccl" if cuda else "gloo", rank=rank, world_size=world)
+    try:
+        frag = run_shard(rank, world, **kwargs)
+        if rank == 0:
+            torch.save(frag, out_path)
+    finally:
+        dist.destroy_process_group()
+
+
+def run_fused_branch(trace_dir, t0, configs, window, horizons, world=1, device="cpu", dense_cache=None,
+                     max_configs=12, state_budget_mb=0.0, score_names=("abs_g",), ratios=(10.0,)):
+    """Replay one branch point on ``world`` shards; returns rank 0's fragment."""
+    kwargs = dict(trace_dir=trace_dir, t0=t0, configs=list(configs), window=window, horizons=list(horizons),
+                  device=device, dense_cache=dense_cache, max_configs=max_configs, state_budget_mb=state_budget_mb,
+                  score_names=list(score_names), ratios=list(ratios))
+    if world == 1:
+        return run_shard(0, 1, **kwargs)
+    import socket
+    import tempfile
+
+    import torch.multiprocessing as mp
+
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    fd, out_path = tempfile.mkstemp(suffix=".frag.pt")
+    os.close(fd)
+    try:
+        mp.spawn(_worker, args=(world, port, kwargs, out_path), nprocs=world, join=True)
+        return torch.load(out_path, weights_only=False)
+    finally:
+        if os.path.exists(out_path):
+            os.remove(out_path)

@@ -1,0 +1,183 @@
+"""Offline replay: exact selection, the from-spec cycle oracle, the fused
+engine (one shard bit-exact against the oracle, two gloo shards inside the
+pure-reordering band), cache identity, CLI report."""
+import json
+import math
+import os
+
+import pytest
+import torch
+
+from sga_b200.replay import core as RC
+from sga_b200.replay import fused as RF
+from sga_b200.replay.synth import make_synthetic_trace
+
+SIZES = (4000, 3000, 1700)   # parameters straddle the shard boundaries
+
+
+@pytest.fixture(scope="module")
+def trace(tmp_path_factory):
+    d = tmp_path_factory.mktemp("trace")
+    return make_synthetic_trace(str(d), sizes=SIZES, steps=12, g_dtype="fp32", seed=3)
+
+
+def _inputs(trace):
+    info = RC.discover_trace(trace)
+    meta, payload = RC.load_state(info, 0)
+    w0, m0, v0, g0 = (RC.flatten(payload[k], info) for k in ("w", "m", "v", "g"))
+    steps = info.window(0, 12)
+    logged, norms, lrs = [], [], []
+    for t in steps:
+        gm, gp = RC.load_g(info, t)
+        logged.append(RC.flatten(gp, info))
+        norms.append(gm["grad_norm"])
+        lrs.append(gm["lr"][0])
+    wd = RC.group_vector(info, [g["weight_decay"] for g in meta["param_groups"]])
+    hp = RC.Hyper(wd=wd, beta1=0.9, beta2=0.95, eps=1e-8, clip=meta["clip_grad"])
+    return info, w0, m0, v0, g0, logged, norms, lrs, hp
+
+
+def test_discover_and_flatten(trace):
+    info = RC.discover_trace(trace)
+    assert info.numel == sum(SIZES) and info.branch_points == [0] and info.g_steps == list(range(12))
+    assert info.window(0, 100) == list(range(12)) and info.window(5, 3) == [5, 6, 7]
+    _, p = RC.load_g(info, 3)
+    full = RC.flatten(p, info)
+    assert torch.equal(RC.flatten(p, info, lo=3990, hi=7010), full[3990:7010])
+    os.rename(os.path.join(trace, "step_000007_g.pt"), os.path.join(trace, "hidden.pt"))
+    try:
+        assert RC.discover_trace(trace).window(0, 100) == list(range(7)), "a gap ends the window"
+    finally:
+        os.rename(os.path.join(trace, "hidden.pt"), os.path.join(trace, "step_000007_g.pt"))
+
+
+def test_select_topk_flat_exact_with_index_ordered_ties():
+    x = torch.tensor([0.5, -2.0, 0.5, 3.0, 0.5, -0.5, 0.1])
+    assert RC.select_topk_flat(x, 3).tolist() == [True, True, False, True, False, False, False]
+    assert int(RC.select_topk_flat(x, 5).sum()) == 5
+    g = torch.Generator().manual_seed(0)
+    y = torch.randint(-4, 5, (5000,), generator=g).float()
+    for k in (1, 77, 2500, 5000):
+        assert int(RC.select_topk_flat(y, k).sum()) == k
+
+
+def test_shard_select_equals_flat_select():
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(30000, generator=g)
+    x[::17] = 1.25
+    for k in (1, 300, 1764, 1765, 9000):
+        assert torch.equal(RF.shard_select(x, k, RF.Comms()), RC.select_topk_flat(x, k))
+
+
+def test_ranking_metrics_sanity():
+    g = torch.Generator().manual_seed(2)
+    lab = torch.rand(2000, generator=g)
+    perfect = RC.ranking_metrics(lab.clone(), lab, 200)
+    assert perfect["recall_at_k"] == 1.0 and abs(perfect["ndcg_at_k"] - 1.0) < 1e-12
+    noise = RC.ranking_metrics(torch.rand(2000, generator=g), lab, 200)
+    assert noise["recall_at_k"] < 0.3 and noise["ndcg_at_k"] < perfect["ndcg_at_k"]
+    assert 0.0 < perfect["missed_label_mass"] < 1.0
+
+
+def test_boundary_reselect_is_load_bearing(trace):
+    info, w0, m0, v0, g0, logged, norms, lrs, hp = _inputs(trace)
+    cfg = RC.CycleConfig("abs_g", 5.0, 4)
+    a, _ = RC.reference_cycle(w0, m0, v0, logged, norms, lrs, hp, 0, cfg, g0, horizons={12})
+    b, _ = RC.reference_cycle(w0, m0, v0, logged, norms, lrs, hp, 0, cfg, g0, horizons={12}, reselect=False)
+    assert not torch.equal(a[12], b[12])
+
+
+CONFIGS = [RC.CycleConfig(s, r, T, o, f, d) for (s, r, T, o, f, d) in [
+    ("abs_g", 1.0, 1, "adamw", False, 1.0), ("abs_g", 5.0, 4, "adamw", False, 1.0),
+    ("update", 5.0, 4, "adamw", True, 1.0), ("abs_m", 10.0, 3, "adamw", False, 0.5),
+    ("coi", 5.0, 16, "adamw", False, 1.0), ("abs_g", 5.0, 4, "adams", False, 1.0)]]
+
+
+def test_fused_one_shard_equals_per_config_oracle_bitwise(trace):
+    info, w0, m0, v0, g0, logged, norms, lrs, hp = _inputs(trace)
+    horizons = [6, 12]
+    for opt in ("adamw", "adams"):
+        cfgs = [c for c in CONFIGS if c.optimizer == opt]
+        frag = RF.run_fused_branch(trace, 0, cfgs, 12, horizons, world=1, device="cpu", score_names=["abs_g"],
+                                   ratios=[5.0])
+        Wf, Sf = frag["final_state"]
+        dense = RC.dense_replay(w0, m0, v0, logged, lrs, hp, 0, opt, set(horizons))
+        for r, c in enumerate(cfgs):
+            snaps, _ = RC.reference_cycle(w0, m0, v0, logged, norms, lrs, hp, 0, c, g0, horizons=set(horizons))
+            assert torch.equal(Wf[r], snaps[12]), f"{c}: weights differ from the per-configuration replay"
+            for h in horizons:
+                want = RC.distortion(snaps[h], dense[h], w0)
+                assert frag["results"][c][h] == pytest.approx(want, rel=1e-12)
+        assert frag["window_len"] == 12 and frag["horizon_steps"] == horizons
+    m = frag["front"][("abs_g", 5.0)]
+    assert m["k"] == RC.k_for(sum(SIZES), 5.0) and 0.0 <= m["recall_at_k"] <= 1.0
+
+
+@pytest.mark.timeout(600)
+def test_fused_two_shards_stay_in_the_reordering_band(trace):
+    cfgs = [c for c in CONFIGS if c.optimizer == "adamw"]
+    one = RF.run_fused_branch(trace, 0, cfgs, 12, [6, 12], world=1, device="cpu", score_names=["abs_g", "update"],
+                              ratios=[5.0])
+    two = RF.run_fused_branch(trace, 0, cfgs, 12, [6, 12], world=2, device="cpu", score_names=["abs_g", "update"],
+                              ratios=[5.0])
+    for c in cfgs:
+        for h in (6, 12):
+            assert two["results"][c][h] == pytest.approx(one["results"][c][h], rel=1e-6)
+    for key, m in one["front"].items():
+        assert two["front"][key]["k"] == m["k"]
+        assert two["front"][key]["recall_at_k"] == m["recall_at_k"], "discrete quantities are exact"
+        assert two["front"][key]["ndcg_at_k"] == pytest.approx(m["ndcg_at_k"], rel=1e-6)
+
+
+def test_grouping_and_kill_switches(trace, monkeypatch):
+    assert [len(g) for g in RF.group_configs(list(range(10)), 4, 0, 1000)] == [4, 4, 2]
+    assert [len(g) for g in RF.group_configs(list(range(5)), 12, 17 * 2 * 1e6 / (1 << 20), 1000000)] == [2, 2, 1]
+    a = RF.run_fused_branch(trace, 0, CONFIGS[:3], 12, [12], max_configs=1)
+    b = RF.run_fused_branch(trace, 0, CONFIGS[:3], 12, [12], max_configs=12)
+    assert all(a["results"][c][12] == b["results"][c][12] for c in CONFIGS[:3]), "grouping must not change results"
+    monkeypatch.setenv("REPLAY_FUSED_KERNEL", "maybe")
+    with pytest.raises(ValueError, match="REPLAY_FUSED_KERNEL"):
+        RF._switch(RF.ENV_KERNEL, ("on", "off"), "on")
+
+
+def test_prefetch_failure_is_latched(trace, monkeypatch):
+    info = RC.discover_trace(trace)
+
+    class Boom(RF.GPrefetcher):
+        def _load(self, t):
+            if t == 2:
+                raise OSError("pread failed")
+            return super()._load(t)
+
+    pf = Boom(info, [0, 1, 2, 3], 0, info.numel, torch.float32, pin=False)
+    pf.get()
+    pf.get()
+    with pytest.raises(RuntimeError, match="prefetch failed"):
+        pf.get()
+
+
+def test_dense_cache_identity(tmp_path):
+    ident = RC.cache_ident("/x", 0, 8, [8], "fp32", "bf16", "fused-1-0", "adamw")
+    assert RC.load_cache(str(tmp_path), ident) is None
+    path = RC.save_cache(str(tmp_path), ident, {"snap_d": {8: torch.ones(3)}})
+    assert os.path.basename(path).startswith("dense_") and RC.load_cache(str(tmp_path), ident)["snap_d"][8].sum() == 3
+    other = dict(ident, window=9)
+    assert RC.load_cache(str(tmp_path), other) is None
+    blob = torch.load(path, weights_only=False)
+    blob["ident"] = other
+    torch.save(blob, path)
+    with pytest.raises(ValueError, match="ident mismatch"):
+        RC.load_cache(str(tmp_path), ident)
+
+
+@pytest.mark.gpu
+def test_fused_gpu_kernels_match_per_config_and_cpu(trace):
+    cfgs = [c for c in CONFIGS if c.optimizer == "adamw"]
+    fused = RF.run_fused_branch(trace, 0, cfgs, 12, [6, 12], device="cuda:0")
+    cpu = RF.run_fused_branch(trace, 0, cfgs, 12, [6, 12], device="cpu")
+    Wf = fused["final_state"][0]
+    for r, c in enumerate(cfgs):
+        single = RF.run_fused_branch(trace, 0, [c], 12, [6, 12], device="cuda:0")
+        assert torch.equal(single["final_state"][0][0], Wf[r]), "R configs at once == one at a time, bit for bit"
+        for h in (6, 12):
+            assert fused["results"][c][h] == pytest.approx(cpu["results"][c][h], rel=1e-5)
