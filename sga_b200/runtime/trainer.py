@@ -66,7 +66,7 @@ def add_trainer_args(p: argparse.ArgumentParser) -> argparse.ArgumentParser:
     g.add_argument("--comm-max-ctas", type=int, default=0)
     g.add_argument("--tensor-model-parallel-size", type=int, default=1)
     g.add_argument("--pipeline-model-parallel-size", type=int, default=1)
-    g.add_argument("--sequence-parallel", type=C.sga_bool, default=False)
+    g.add_argument("--sequence-parallel", action="store_true")
     g.add_argument("--untie-embeddings-and-output-weights", action="store_true")
     g.add_argument("--use-distributed-optimizer", action="store_true")
     g.add_argument("--log-num-zeros-in-grad", action="store_true")
