@@ -180,4 +180,4 @@ def test_fused_gpu_kernels_match_per_config_and_cpu(trace):
         single = RF.run_fused_branch(trace, 0, [c], 12, [6, 12], device="cuda:0")
         assert torch.equal(single["final_state"][0][0], Wf[r]), "R configs at once == one at a time, bit for bit"
         for h in (6, 12):
-            assert fused["results"][c][h] == pytest.approx(cpu["results"][c][h], rel=1e-5)
+            assert fused["results"][c][h] == pytest.approx(cpu["results"][c][h], rel=1e-4, abs=1e-6)
