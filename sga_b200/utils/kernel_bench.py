@@ -1,0 +1,212 @@
+"""Device-timed micro-benchmarks of the native kernels with their roofline
+fractions: ``python -m sga_b200.utils.kernel_bench --kernel gemm|adam|index_sync|
+allreduce|rmsnorm|swiglu|rope|ce|replay [--small]``.
+
+Each case warms up, then times with CUDA events on the launching stream
+between synchronisations, on inputs larger than the 126 MB L2 (or flushes L2
+between iterations when they are not), and prints one JSON line with the
+achieved rate and its fraction of the measured peak (``MEASURED_PEAKS.json``
+beside the repository root when present, else 6.65 TB/s and 1.59 PFLOP/s).
+``--small`` keeps the footprint to a few GB and a handful of launches so the
+same command can run under a profiler.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def peaks():
+    try:
+        p = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        return p["hbm_gbs"] * 1e9, p["bf16_tflops"] * 1e12, "measured"
+    except Exception:
+        return 6.65e12, 1.59e15, "fallback"
+
+
+def timed(fn, iters, warmup=3, flush=None):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    total = 0.0
+    for _ in range(iters):
+        if flush is not None:
+            flush.zero_()
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        total += s.elapsed_time(e)
+    return total / iters
+
+
+def emit(kernel, case, ms, bytes_=None, flops=None, **extra):
+    bw, tf, src = peaks()
+    rec = {"kernel": kernel, "case": case, "ms": round(ms, 4)}
+    if bytes_ is not None:
+        rec["GBps"] = round(bytes_ / ms / 1e6, 1)
+        rec[f"frac_of_{src}_hbm"] = round(bytes_ / (ms / 1e3) / bw, 3)
+    if flops is not None:
+        rec["TFLOPs"] = round(flops / ms / 1e9, 1)
+        rec[f"frac_of_{src}_bf16"] = round(flops / (ms / 1e3) / tf, 3)
+    rec.update(extra)
+    print(json.dumps(rec), flush=True)
+
+
+def bench_gemm(small):
+    from .. import kernels as K
+
+    dev = "cuda"
+    shapes = [("fwd qkv+o", 8192, 3072, 2048, 0, 0, 0), ("fwd fc1", 8192, 16384, 2048, 0, 0, 0),
+              ("fwd fc2", 8192, 2048, 8192, 0, 0, 0), ("dgrad fc1", 8192, 2048, 16384, 0, 1, 0),
+              ("wgrad fc1", 16384, 2048, 8192, 1, 1, 2), ("lm head", 8192, 128256, 2048, 0, 0, 0),
+              ("square", 8192, 8192, 8192, 0, 0, 0)]
+    if small:
+        shapes = [("fwd fc1", 8192, 16384, 2048, 0, 0, 0)]
+    for name, M, N, Kd, a_mn, b_mn, epi in shapes:
+        A = torch.randn((Kd, M) if a_mn else (M, Kd), device=dev).to(torch.bfloat16)
+        B = torch.randn((Kd, N) if b_mn else (N, Kd), device=dev).to(torch.bfloat16)
+        C = torch.zeros(M, N, device=dev, dtype=torch.bfloat16 if epi == 0 else torch.float32)
+        for pair in (True,) if small else (False, True):
+            ms = timed(lambda: K.gemm_bf16(A, B, C, a_mn=bool(a_mn), b_mn=bool(b_mn), epi=epi, pair=pair),
+                       2 if small else 20, warmup=1 if small else 3)
+            emit("gemm_bf16_pair" if pair else "gemm_bf16", f"{name} M={M} N={N} K={Kd}", ms, flops=2.0 * M * N * Kd)
+        if not small:
+            At, Bt = (A.t() if a_mn else A), (B.t() if b_mn else B)
+            ms = timed(lambda: torch.matmul(At, Bt.t()), 20)
+            emit("library matmul (reference point)", f"{name} M={M} N={N} K={Kd}", ms, flops=2.0 * M * N * Kd)
+    assert int(K.gemm_err_word(dev).item()) == 0
+
+
+def bench_adam(small):
+    from .. import kernels as K
+
+    n = (64 if small else 256) * 1024 * 1024
+    dev = "cuda"
+    w, g, m, v = (torch.randn(n, device=dev) * 1e-2 for _ in range(4))
+    v.abs_()
+    model = torch.empty(n, dtype=torch.bfloat16, device=dev)
+    table = K.SegmentTable([0], [0], n, dev)
+    ms = timed(lambda: K.adam_step(w, g, m, v, table, [3e-4], [0.1], beta1=0.9, beta2=0.95, eps=1e-8, step=3,
+                                   model=model, clear=True), 2 if small else 10, warmup=1)
+    emit("sga_adam_kernel", f"n={n} sparse-step form (read w,g,m,v; write w,m,v,g,bf16)", ms, bytes_=n * 34.0)
+
+
+def bench_index_sync(small):
+    from ..parallel import p2p
+    from ..parallel.symm import SymmPool
+
+    pool = SymmPool(device="cuda:0")
+    ch = p2p.PeerChannel(pool)
+    n = 32 * 1024 * 1024
+    k = n // 100
+    acc0 = torch.randn(n, device="cuda") * 1e-3
+    acc = acc0.clone()
+    slots = pool.alloc(8 * k)
+    comm = torch.zeros(n, device="cuda")
+    touched = torch.empty((n + 31) // 32, dtype=torch.int32, device="cuda")
+    scratch = p2p.IndexSyncScratch("cuda:0")
+    sq = torch.zeros(1, device="cuda")
+
+    def run():
+        p2p.bucket_index_sync_(ch, scratch, acc, k, slots=slots, kcap=k, comm=comm, touched=touched, scale=1.0,
+                               sumsq_out=sq)
+
+    ms = timed(run, 2 if small else 10, warmup=1)
+    ch.check()
+    # three reads of the bucket (two radix digits + compaction pass re-read from L2/HBM) + payload traffic
+    emit("bucket_index_sync_kernel", f"n={n} k={k} (1 rank)", ms, bytes_=n * 4.0 * 4 + k * 8.0 * 3)
+    pool.close()
+
+
+def bench_elementwise(small):
+    from ..ops import functional as F
+
+    T, H, Fd = 8192, 2048, 8192
+    dev = "cuda"
+    x = torch.randn(T, H, device=dev).to(torch.bfloat16)
+    w = torch.ones(H, device=dev, dtype=torch.bfloat16)
+    dy = torch.randn(T, H, device=dev).to(torch.bfloat16)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    it = 2 if small else 20
+    y, rstd = F.rmsnorm_fwd(x, w, 1e-5)
+    emit("rmsnorm_fwd_kernel", f"T={T} H={H}", timed(lambda: F.rmsnorm_fwd(x, w, 1e-5, out=y), it, flush=flush),
+         bytes_=T * H * 4.0)
+    dw = torch.zeros(H, device=dev)
+    dx = torch.empty_like(x)
+    emit("rmsnorm_bwd_kernel", f"T={T} H={H}",
+         timed(lambda: F.rmsnorm_bwd(x, w, dy, rstd, dw_out=dw, dx_out=dx), it, flush=flush), bytes_=T * H * 6.0)
+    gu = torch.randn(T, 2 * Fd, device=dev).to(torch.bfloat16)
+    out = torch.empty(T, Fd, device=dev, dtype=torch.bfloat16)
+    emit("swiglu_fwd_kernel", f"T={T} F={Fd}", timed(lambda: F.swiglu_fwd(gu, out=out), it, flush=flush),
+         bytes_=T * Fd * 6.0)
+    din = torch.empty_like(gu)
+    emit("swiglu_bwd_kernel", f"T={T} F={Fd}", timed(lambda: F.swiglu_bwd(gu, out, out=din), it, flush=flush),
+         bytes_=T * Fd * 10.0)
+    qkv = torch.randn(T, 3072, device=dev).to(torch.bfloat16)
+    cs, sn = F.rope_tables(2048, 64, 500000.0, dev)
+    emit("rope_kernel", f"T={T} heads=40 hd=64", timed(lambda: F.rope_(qkv, cs, sn, 2048, 40, 64, 0, 1.0), it,
+                                                       flush=flush), bytes_=T * 2560 * 4.0)
+    if not small:
+        V = 128256
+        z = torch.randn(T, V, device=dev, dtype=torch.bfloat16)
+        tgt = torch.randint(0, V, (T,), device=dev)
+        emit("ce_fwd_bwd_kernel", f"T={T} V={V}", timed(lambda: F.cross_entropy_(z, tgt, 1.0 / T), 5), bytes_=T * V * 8.0)
+
+
+def bench_replay(small):
+    import ctypes
+
+    from ..csrc import lib
+    from ..replay.fused import _CfgStruct
+
+    L = lib()
+    R, n = 18, (8 if small else 64) * 1024 * 1024
+    dev = "cuda"
+    g = (torch.randn(n, device=dev) * 1e-3).to(torch.bfloat16)
+    W, M, V, RES = (torch.randn(R, n, device=dev) * 1e-3 for _ in range(4))
+    V.abs_()
+    SEL = (torch.rand(R, n, device=dev) < 0.01).to(torch.uint8)
+    wd = torch.full((n,), 0.1, device=dev)
+    arr = (_CfgStruct * R)()
+    for r in range(R):
+        arr[r].boundary, arr[r].coef, arr[r].lr, arr[r].bc1, arr[r].bc2, arr[r].fold_div = r % 3 == 0, 0.9, 3e-4, 0.5, 0.4, 4.0
+    cfg = torch.frombuffer(bytearray(bytes(arr)), dtype=torch.uint8).to(dev)
+    nb = L.sga_replay_blocks()
+    partials = torch.zeros(R * nb, dtype=torch.float64, device=dev)
+    out = torch.zeros(R, dtype=torch.float64, device=dev)
+    st = torch.cuda.current_stream().cuda_stream
+
+    def p3():
+        assert L.sga_replay_pass3(g.data_ptr(), 1, 1.0, W.data_ptr(), M.data_ptr(), V.data_ptr(), RES.data_ptr(),
+                                  SEL.data_ptr(), wd.data_ptr(), None, cfg.data_ptr(), R, n, 0.9, 0.1, 0.95, 0.05,
+                                  1e-8, None, None, st) == 0
+
+    ms = timed(p3, 2 if small else 5, warmup=1)
+    emit("replay_pass3_kernel", f"R={R} n={n} bf16 g", ms, bytes_=n * (2.0 + 4.0 + R * 33.0))
+
+
+CASES = {"gemm": bench_gemm, "adam": bench_adam, "index_sync": bench_index_sync, "elementwise": bench_elementwise,
+         "replay": bench_replay}
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--kernel", default="all", choices=["all"] + sorted(CASES))
+    ap.add_argument("--small", action="store_true")
+    ns = ap.parse_args(argv)
+    for name, fn in CASES.items():
+        if ns.kernel in ("all", name):
+            fn(ns.small)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
