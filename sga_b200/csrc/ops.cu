@@ -69,49 +69,67 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const __nv_bfloat16* _
 // dx = rstd * (dy*w - xhat * mean(dy*w*xhat)); dw partial per CTA.
 // Each warp walks rows (strided by total warps); lanes own column chunks.
 template <int NCH>  // chunks of 8 columns per lane: H <= NCH * 256
-__global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x,
-                                                          const __nv_bfloat16* __restrict__ w,
-                                                          const __nv_bfloat16* __restrict__ dy,
-                                                          const float* __restrict__ rstd,
-                                                          __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_part,
-                                                          long long rows, int H, long long x_stride,
-                                                          long long dy_stride, long long dx_stride,
-                                                          int rows_per_group, long long gsx, long long gsdy,
-                                                          long long gsdx, int accumulate_dx) {
-  extern __shared__ float sdw[];  // [H]
+__global__ void __launch_bounds__(256, NCH <= 8 ? 2 : 1) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                                             const __nv_bfloat16* __restrict__ w,
+                                                             const __nv_bfloat16* __restrict__ dy,
+                                                             const float* __restrict__ rstd,
+                                                             __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_part,
+                                                             long long rows, int H, long long x_stride,
+                                                             long long dy_stride, long long dx_stride,
+                                                             int rows_per_group, long long gsx, long long gsdy,
+                                                             long long gsdx, int accumulate_dx) {
+  // shared: one fp32 row of H per warp; every lane owns fixed columns of its warp's row, so no atomics
+  extern __shared__ float sdw[];
   const int lane = threadIdx.x & 31;
+  const int wid = threadIdx.x >> 5;
+  const int nwarp = blockDim.x >> 5;
   const int nch = H >> 3;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) sdw[i] = 0.f;
-  __syncthreads();
-  float dwacc[NCH][8];
-#pragma unroll
-  for (int j = 0; j < NCH; ++j)
-#pragma unroll
-    for (int i = 0; i < 8; ++i) dwacc[j][i] = 0.f;
-  const long long warps = (long long)gridDim.x * (blockDim.x >> 5);
-  for (long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows; row += warps) {
+  float* myrow = sdw + (size_t)wid * H;
+  for (int i = lane; i < H; i += 32) myrow[i] = 0.f;
+  __syncwarp();
+  const long long warps = (long long)gridDim.x * nwarp;
+  for (long long row = (long long)blockIdx.x * nwarp + wid; row < rows; row += warps) {
     const long long grp = row / rows_per_group, r = row % rows_per_group;
     const __nv_bfloat16* xr = x + grp * gsx + r * x_stride;
     const __nv_bfloat16* dyr = dy + grp * gsdy + r * dy_stride;
     __nv_bfloat16* dxr = dx + grp * gsdx + r * dx_stride;
     const float rs = rstd[row];
     float dot = 0.f;
-    float xh[NCH][8], gw[NCH][8];
+    // rows up to 2048 wide stay in registers between the two passes; wider rows are re-read (L1/L2 hits)
+    constexpr bool kCache = NCH <= 8;
+    constexpr int kRegs = kCache ? NCH : 1;
+    uint4 px[kRegs], pd[kRegs];
+    if constexpr (kCache) {
+#pragma unroll
+      for (int j = 0; j < NCH; ++j) {
+        const int c = lane + 32 * j;
+        if (c < nch) {
+          px[j] = *reinterpret_cast<const uint4*>(xr + c * 8);
+          pd[j] = *reinterpret_cast<const uint4*>(dyr + c * 8);
+        }
+      }
+    }
 #pragma unroll
     for (int j = 0; j < NCH; ++j) {
       const int c = lane + 32 * j;
       if (c < nch) {
         float fx[8], fw[8], fd[8];
-        unpack8(*reinterpret_cast<const uint4*>(xr + c * 8), fx);
+        unpack8(kCache ? px[j] : *reinterpret_cast<const uint4*>(xr + c * 8), fx);
+        unpack8(kCache ? pd[j] : *reinterpret_cast<const uint4*>(dyr + c * 8), fd);
         unpack8(*reinterpret_cast<const uint4*>(w + c * 8), fw);
-        unpack8(*reinterpret_cast<const uint4*>(dyr + c * 8), fd);
+        float4* acc = reinterpret_cast<float4*>(myrow + c * 8);
+        float4 a0 = acc[0], a1 = acc[1];
+        float t[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          xh[j][i] = fx[i] * rs;
-          gw[j][i] = fd[i] * fw[i];
-          dot += gw[j][i] * xh[j][i];
-          dwacc[j][i] += fd[i] * xh[j][i];
+          const float xh = fx[i] * rs;
+          dot += fd[i] * fw[i] * xh;
+          t[i] = fd[i] * xh;
         }
+        a0.x += t[0]; a0.y += t[1]; a0.z += t[2]; a0.w += t[3];
+        a1.x += t[4]; a1.y += t[5]; a1.z += t[6]; a1.w += t[7];
+        acc[0] = a0;
+        acc[1] = a1;
       }
     }
     dot = warp_sum(dot) / (float)H;
@@ -119,9 +137,12 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const __nv_bfloat16* _
     for (int j = 0; j < NCH; ++j) {
       const int c = lane + 32 * j;
       if (c < nch) {
-        float o[8];
+        float fx[8], fw[8], fd[8], o[8];
+        unpack8(kCache ? px[j] : *reinterpret_cast<const uint4*>(xr + c * 8), fx);
+        unpack8(kCache ? pd[j] : *reinterpret_cast<const uint4*>(dyr + c * 8), fd);
+        unpack8(*reinterpret_cast<const uint4*>(w + c * 8), fw);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) o[i] = rs * (gw[j][i] - xh[j][i] * dot);
+        for (int i = 0; i < 8; ++i) o[i] = rs * (fd[i] * fw[i] - (fx[i] * rs) * dot);
         if (accumulate_dx) {
           float prev[8];
           unpack8(*reinterpret_cast<const uint4*>(dxr + c * 8), prev);
@@ -132,16 +153,12 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const __nv_bfloat16* _
       }
     }
   }
-#pragma unroll
-  for (int j = 0; j < NCH; ++j) {
-    const int c = lane + 32 * j;
-    if (c < nch) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) atomicAdd(&sdw[c * 8 + i], dwacc[j][i]);
-    }
-  }
   __syncthreads();
-  for (int i = threadIdx.x; i < H; i += blockDim.x) dw_part[(long long)blockIdx.x * H + i] = sdw[i];
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float t = 0.f;
+    for (int wv = 0; wv < nwarp; ++wv) t += sdw[(size_t)wv * H + i];
+    dw_part[(long long)blockIdx.x * H + i] = t;
+  }
 }
 
 // out[i] (+)= sum_b part[b][i]  (fixed order)
@@ -159,20 +176,36 @@ __global__ void colsum_kernel(const float* __restrict__ part, int nb, int H, flo
 // (i, i + hd/2). cos/sin: [S, hd/2] fp32. sign = +1 forward, -1 backward.
 __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const float* __restrict__ cs, const float* __restrict__ sn,
                             long long T, int S, int nheads, int hd, long long pitch, int col0, float sign) {
+  // one thread rotates 8 pairs: columns [8c, 8c+8) of the first half with the same columns of the second half
   const int half = hd >> 1;
-  const long long total = T * nheads * half;
+  const int hc = half >> 3;
+  const long long total = T * nheads * hc;
   const long long gstride = (long long)gridDim.x * blockDim.x;
   for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += gstride) {
-    const int i = (int)(e % half);
-    const long long th = e / half;
+    const int c = (int)(e % hc);
+    const long long th = e / hc;
     const int h = (int)(th % nheads);
     const long long t = th / nheads;
     const int pos = (int)(t % S);
-    __nv_bfloat16* p = x + t * pitch + col0 + (long long)h * hd;
-    const float a = __bfloat162float(p[i]), b = __bfloat162float(p[i + half]);
-    const float c = cs[pos * half + i], s = sn[pos * half + i] * sign;
-    p[i] = __float2bfloat16_rn(a * c - b * s);
-    p[i + half] = __float2bfloat16_rn(b * c + a * s);
+    __nv_bfloat16* p = x + t * pitch + col0 + (long long)h * hd + c * 8;
+    float a[8], b[8];
+    unpack8(*reinterpret_cast<const uint4*>(p), a);
+    unpack8(*reinterpret_cast<const uint4*>(p + half), b);
+    const float4 c0 = *reinterpret_cast<const float4*>(cs + pos * half + c * 8);
+    const float4 c1 = *reinterpret_cast<const float4*>(cs + pos * half + c * 8 + 4);
+    const float4 s0 = *reinterpret_cast<const float4*>(sn + pos * half + c * 8);
+    const float4 s1 = *reinterpret_cast<const float4*>(sn + pos * half + c * 8 + 4);
+    const float cc[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float ss[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    float oa[8], ob[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float sg = ss[i] * sign;
+      oa[i] = a[i] * cc[i] - b[i] * sg;
+      ob[i] = b[i] * cc[i] + a[i] * sg;
+    }
+    *reinterpret_cast<uint4*>(p) = pack8(oa);
+    *reinterpret_cast<uint4*>(p + half) = pack8(ob);
   }
 }
 
@@ -366,10 +399,21 @@ SGA_API int sga_rmsnorm_bwd(const void* x, const void* w, const void* dy, const 
                             long long x_stride, long long dy_stride, long long dx_stride, int rows_per_group,
                             long long gsx, long long gsdy, long long gsdx, int accumulate_dx, void* stream) {
   if (rows <= 0) return 0;
-  if (H & 7 || H > 8192) return -5;
+  if (H & 7 || H > 6144) return -5;
   const int nb = sga_rmsnorm_bwd_blocks();
   const int nch = (H / 8 + 31) / 32;
-  const size_t smem = (size_t)H * 4;
+  const size_t smem = (size_t)H * 4 * 8;  // one fp32 row per warp
+  if (smem > 48 * 1024) {
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr_set[dev & 63]) {
+      cudaFuncSetAttribute(rmsnorm_bwd_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+      cudaFuncSetAttribute(rmsnorm_bwd_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+      cudaFuncSetAttribute(rmsnorm_bwd_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+      attr_set[dev & 63] = true;
+    }
+  }
 #define RB(N)                                                                                                     \
   rmsnorm_bwd_kernel<N><<<nb, 256, smem, ST(stream)>>>(                                                            \
       (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)dy, rstd, (__nv_bfloat16*)dx, dw_part, \
@@ -387,7 +431,8 @@ SGA_API int sga_rmsnorm_bwd(const void* x, const void* w, const void* dy, const 
 
 SGA_API int sga_rope(void* x, const float* cs, const float* sn, long long T, int S, int nheads, int hd,
                      long long pitch, int col0, float sign, void* stream) {
-  const long long total = T * nheads * (hd / 2);
+  if (hd & 15) return -5;  // 8-wide chunks in each half
+  const long long total = T * nheads * (hd / 16);
   if (total <= 0) return 0;
   rope_kernel<<<grid1d(total, 256), 256, 0, ST(stream)>>>((__nv_bfloat16*)x, cs, sn, T, S, nheads, hd, pitch, col0,
                                                            sign);

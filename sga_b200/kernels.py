@@ -55,6 +55,8 @@ register_sigs({
     "sga_bucket_index_sync": [_P, _P, _L, _I, _P, _P, _P, _P, _P, _I, _P, _P, _F, _P, _P, _I, _I, _I, _P, _I, _P],
     "sga_dense_adamw_ag": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _P, _P, _I, _P, _F, _F, _F, _F, _F, _F, _F,
                            _I, _I, _P],
+    "sga_tp_ag_gemm": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P, _I, _P],
+    "sga_tp_gemm_rs": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "sga_replay_blocks": [],
     "sga_replay_pass1": [_P, _I, _F, _P, _P, _P, _I, _L, _P, _P, _P],
     "sga_replay_pass3": [_P, _I, _F, _P, _P, _P, _P, _P, _P, _P, _P, _I, _L, _F, _F, _F, _F, _F, _P, _P, _P],

@@ -82,39 +82,70 @@ def get_config(name: str, **overrides) -> GPTConfig:
     return replace(PRESETS[name], **overrides) if overrides else PRESETS[name]
 
 
-def param_specs(cfg: GPTConfig) -> list:
-    """Parameter specs in the order their gradients become final in the backward pass."""
+def _rows(*ranges):
+    return [(0, lo, hi) for lo, hi in ranges]
+
+
+def param_specs(cfg: GPTConfig, tp_size: int = 1, tp_rank: int = 0) -> list:
+    """Parameter specs in the order their gradients become final in the backward pass.
+
+    With ``tp_size > 1`` the linear weights are this rank's shard (QKV and the
+    fused gate|up projection by output rows, per head group / per half; the
+    output and down projections by input columns) and carry the slices of the
+    full tensor they are cut from; norm weights, the embedding and the output
+    layer are replicated (activations are sharded by rows, so each rank embeds
+    and scores its own tokens against the full vocabulary)."""
     std = cfg.init_std
+    tp = tp_size
+    nq, nkv, hd, F_, H = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, cfg.ffn, cfg.hidden
+    if tp > 1:
+        assert nq % tp == 0 and nkv % tp == 0 and F_ % tp == 0, "heads and ffn must divide over tensor-parallel ranks"
+    dup = tp > 1
+    r = tp_rank
+    nql, nkvl, Fl = nq // tp, nkv // tp, F_ // tp
+
+    def sharded(name, full_shape, pieces):
+        if tp == 1:
+            return ParamSpec(name, full_shape, 0, "normal", std)
+        dim = pieces[0][0]
+        shape = list(full_shape)
+        shape[dim] = sum(hi - lo for _, lo, hi in pieces)
+        return ParamSpec(name, tuple(shape), 0, "normal", std, tp_full_shape=tuple(full_shape), tp_pieces=pieces)
+
     specs = []
     if not cfg.tied_embeddings:
-        specs.append(ParamSpec("output_layer.weight", (cfg.vocab, cfg.hidden), 0, "normal", std))
-    specs.append(ParamSpec("decoder.final_layernorm.weight", (cfg.hidden,), 1, "ones", tp_duplicate=True))
+        specs.append(ParamSpec("output_layer.weight", (cfg.vocab, H), 0, "normal", std, tp_duplicate=dup))
+    specs.append(ParamSpec("decoder.final_layernorm.weight", (H,), 1, "ones", tp_duplicate=True))
     for i in reversed(range(cfg.num_layers)):
         p = f"decoder.layers.{i}."
-        specs.append(ParamSpec(p + "mlp.linear_fc2.weight", (cfg.hidden, cfg.ffn), 0, "normal", std))
-        specs.append(ParamSpec(p + "mlp.linear_fc1.weight", (2 * cfg.ffn, cfg.hidden), 0, "normal", std))
-        specs.append(ParamSpec(p + "pre_mlp_layernorm.weight", (cfg.hidden,), 1, "ones", tp_duplicate=True))
-        specs.append(ParamSpec(p + "self_attention.linear_proj.weight", (cfg.hidden, cfg.n_heads * cfg.head_dim), 0,
-                               "normal", std))
+        specs.append(sharded(p + "mlp.linear_fc2.weight", (H, F_), [(1, r * Fl, (r + 1) * Fl)]))
+        specs.append(sharded(p + "mlp.linear_fc1.weight", (2 * F_, H),
+                             _rows((r * Fl, (r + 1) * Fl), (F_ + r * Fl, F_ + (r + 1) * Fl))))
+        specs.append(ParamSpec(p + "pre_mlp_layernorm.weight", (H,), 1, "ones", tp_duplicate=True))
+        specs.append(sharded(p + "self_attention.linear_proj.weight", (H, nq * hd),
+                             [(1, r * nql * hd, (r + 1) * nql * hd)]))
         if cfg.qk_norm:
-            specs.append(ParamSpec(p + "self_attention.k_layernorm.weight", (cfg.head_dim,), 1, "ones",
-                                   tp_duplicate=True))
-            specs.append(ParamSpec(p + "self_attention.q_layernorm.weight", (cfg.head_dim,), 1, "ones",
-                                   tp_duplicate=True))
-        specs.append(ParamSpec(p + "self_attention.linear_qkv.weight", (cfg.qkv_dim, cfg.hidden), 0, "normal", std))
-        specs.append(ParamSpec(p + "input_layernorm.weight", (cfg.hidden,), 1, "ones", tp_duplicate=True))
-    specs.append(ParamSpec("embedding.word_embeddings.weight", (cfg.vocab, cfg.hidden), 0, "normal", std))
+            specs.append(ParamSpec(p + "self_attention.k_layernorm.weight", (hd,), 1, "ones", tp_duplicate=True))
+            specs.append(ParamSpec(p + "self_attention.q_layernorm.weight", (hd,), 1, "ones", tp_duplicate=True))
+        ko, vo = nq * hd, (nq + nkv) * hd
+        specs.append(sharded(p + "self_attention.linear_qkv.weight", (cfg.qkv_dim, H),
+                             _rows((r * nql * hd, (r + 1) * nql * hd), (ko + r * nkvl * hd, ko + (r + 1) * nkvl * hd),
+                                   (vo + r * nkvl * hd, vo + (r + 1) * nkvl * hd))))
+        specs.append(ParamSpec(p + "input_layernorm.weight", (H,), 1, "ones", tp_duplicate=True))
+    specs.append(ParamSpec("embedding.word_embeddings.weight", (cfg.vocab, H), 0, "normal", std, tp_duplicate=dup))
     return specs
 
 
 class GPT:
     def __init__(self, cfg: GPTConfig, *, device="cpu", pool=None, bucket_elems: int = 16 * 1024 * 1024,
-                 seed: int = 0, need_comm_staging: bool = False, arena: Optional[FlatArena] = None):
+                 seed: int = 0, need_comm_staging: bool = False, arena: Optional[FlatArena] = None, tp=None):
         self.cfg = cfg
         self.device = torch.device(device)
+        self.tp = tp if (tp is not None and tp.world > 1) else None
+        self.tp_size = self.tp.world if self.tp is not None else 1
         self.arena = arena if arena is not None else FlatArena(
-            param_specs(cfg), bucket_elems=bucket_elems, device=device, pool=pool,
-            need_comm_staging=need_comm_staging)
+            param_specs(cfg, self.tp_size, self.tp.rank if self.tp is not None else 0), bucket_elems=bucket_elems,
+            device=device, pool=pool, need_comm_staging=need_comm_staging)
         if arena is None:
             self.arena.init_parameters(seed)
         self.cuda = self.device.type == "cuda"
@@ -257,11 +288,140 @@ class GPT:
         self.launches += 9
         return dx
 
+    # ------------------------------------------------- tensor-parallel layers
+    # Activations between the linears are [T / tp, hidden] (this rank's rows); the
+    # column-parallel linears (QKV, gate|up) gather their input rows inside the GEMM
+    # kernel, the row-parallel ones (output, down) reduce-scatter their output rows
+    # inside it. The gathered inputs are kept for the weight gradients.
+    def _layer_fwd_tp(self, i, L, x, B, S):
+        c, tp = self.cfg, self.tp
+        T = B * S
+        cs, sn = self._rope_tables()
+        nq, nkv, hd = c.n_heads // tp.world, c.n_kv_heads // tp.world, c.head_dim
+        g1 = tp.slot(("h1", i), T, c.hidden)
+        _, rstd1 = F.rmsnorm_fwd(x, L["ln1"].model, c.norm_eps, out=g1.local)
+        qkv = tp.ag_linear(g1, L["qkv"].model)
+        qk_saved = None
+        if c.qk_norm:
+            pre = qkv[:, :(nq + nkv) * hd].clone()
+            rq = F.headnorm_fwd_(qkv, L["qn"].model, c.norm_eps, T, nq, hd, 0)
+            rk = F.headnorm_fwd_(qkv, L["kn"].model, c.norm_eps, T, nkv, hd, nq * hd)
+            qk_saved = (pre, rq, rk)
+            self.launches += 2
+        F.rope_(qkv, cs, sn, S, nq + nkv, hd, 0, +1.0)
+        ctx, att_saved = A.attn_fwd(qkv, B, S, nq, nkv, hd)
+        x_mid = tp.linear_rs(ctx, L["proj"].model, residual=x)
+        g2 = tp.slot(("h2", i), T, c.hidden)
+        _, rstd2 = F.rmsnorm_fwd(x_mid, L["ln2"].model, c.norm_eps, out=g2.local)
+        gu = tp.ag_linear(g2, L["fc1"].model)
+        s = F.swiglu_fwd(gu)
+        x_out = tp.linear_rs(s, L["fc2"].model, residual=x_mid)
+        del s
+        self.launches += 5
+        return x_out, (x, rstd1, qkv, qk_saved, ctx, att_saved, x_mid, rstd2, gu, g1, g2)
+
+    def _layer_bwd_tp(self, L, saved, gdx, B, S, done):
+        c, tp = self.cfg, self.tp
+        T = B * S
+        x, rstd1, qkv, qk_saved, ctx, att_saved, x_mid, rstd2, gu, g1, g2 = saved
+        nq, nkv, hd = c.n_heads // tp.world, c.n_kv_heads // tp.world, c.head_dim
+        cs, sn = self._rope_tables()
+        dx = gdx.local
+        # MLP: the down projection's input gradient gathers dx rows; gdx.full then feeds its weight gradient
+        s = F.swiglu_fwd(gu)
+        ds = tp.ag_linear(gdx, L["fc2"].model, b_mn=True)
+        self._wgrad(gdx.full, s, L["fc2"])
+        done(L["fc2"])
+        del s
+        dgu = F.swiglu_bwd(gu, ds)
+        del ds
+        self._wgrad(dgu, g2.full, L["fc1"])
+        done(L["fc1"])
+        dh2 = tp.linear_rs(dgu, L["fc1"].model, b_mn=True)
+        del dgu
+        F.rmsnorm_bwd(x_mid, L["ln2"].model, dh2, rstd2, dw_out=L["ln2"].grad, dx_out=dx, accumulate_dx=True)
+        done(L["ln2"])
+        del dh2
+        # attention
+        dctx = tp.ag_linear(gdx, L["proj"].model, b_mn=True)
+        self._wgrad(gdx.full, ctx, L["proj"])
+        done(L["proj"])
+        dqkv = A.attn_bwd(dctx, qkv, att_saved, B, S, nq, nkv, hd)
+        del dctx
+        F.rope_(dqkv, cs, sn, S, nq + nkv, hd, 0, -1.0)
+        if c.qk_norm:
+            pre, rq, rk = qk_saved
+            F.headnorm_bwd_(pre, dqkv, L["kn"].model, rk, L["kn"].grad, T, nkv, hd, nq * hd, nq * hd)
+            F.headnorm_bwd_(pre, dqkv, L["qn"].model, rq, L["qn"].grad, T, nq, hd, 0, 0)
+            done(L["kn"])
+            done(L["qn"])
+            self.launches += 4
+        self._wgrad(dqkv, g1.full, L["qkv"])
+        done(L["qkv"])
+        dh1 = tp.linear_rs(dqkv, L["qkv"].model, b_mn=True)
+        del dqkv
+        F.rmsnorm_bwd(x, L["ln1"].model, dh1, rstd1, dw_out=L["ln1"].grad, dx_out=dx, accumulate_dx=True)
+        done(L["ln1"])
+        self.launches += 7
+
+    def _forward_backward_tp(self, tokens, targets, loss_scale, on_param_done, backward, reduce_replicated):
+        c, tp = self.cfg, self.tp
+        B, S = tokens.shape
+        T = B * S
+        Tl = T // tp.world
+        lo = tp.rank * Tl
+        user_done = on_param_done if on_param_done is not None else (lambda slot: None)
+
+        def done(slot):
+            # a replicated parameter's gradient is final only once summed over the tensor-parallel ranks
+            if slot.spec.tp_duplicate and reduce_replicated:
+                tp.allreduce_replicated(slot.grad)
+            user_done(slot)
+
+        ids = tokens.reshape(-1)[lo:lo + Tl]
+        tgt = targets.reshape(-1)[lo:lo + Tl]
+        x = F.embed_fwd(ids, self.emb.model)
+        saved = []
+        for i, L in enumerate(self.layers):
+            x, sv = self._layer_fwd_tp(i, L, x, B, S)
+            saved.append(sv)
+        hf, rstd_f = F.rmsnorm_fwd(x, self.final_norm.model, c.norm_eps)
+        logits = self._linear(hf, self.head)
+        self.launches += 3
+        loss_tok = F.cross_entropy_(logits, tgt, grad_scale=loss_scale / T, write_grad=backward)
+        loss = tp.allreduce_scalar(loss_tok.sum() / T)
+        if not backward:
+            return loss
+        dlogits = logits
+        self._wgrad(dlogits, hf, self.head)
+        if not c.tied_embeddings:
+            done(self.head)
+        dhf = self._dgrad(dlogits, self.head)
+        del logits, dlogits, hf
+        gdx = tp.slot("dx", T, c.hidden)
+        F.rmsnorm_bwd(x, self.final_norm.model, dhf, rstd_f, dw_out=self.final_norm.grad, dx_out=gdx.local)
+        done(self.final_norm)
+        del dhf
+        for L, sv in zip(reversed(self.layers), reversed(saved)):
+            self._layer_bwd_tp(L, sv, gdx, B, S, done)
+        saved.clear()
+        F.embed_bwd(ids, gdx.local, self.emb.grad)
+        done(self.emb)
+        self.launches += 4
+        return loss
+
     def forward_backward(self, tokens: torch.Tensor, targets: torch.Tensor, *, loss_scale: float = 1.0,
-                         on_param_done: Optional[Callable] = None, backward: bool = True) -> torch.Tensor:
+                         on_param_done: Optional[Callable] = None, backward: bool = True,
+                         reduce_replicated: bool = True) -> torch.Tensor:
         """One micro-batch. ``tokens`` / ``targets``: ``[B, S]`` int64. Gradients of
         ``loss_scale * mean token loss`` are accumulated into ``main_grad``.
-        Returns the (unscaled) mean loss as a 0-dim fp32 tensor on the device."""
+        Returns the (unscaled) mean loss as a 0-dim fp32 tensor on the device.
+        Under tensor parallelism every rank of the group passes the same batch;
+        ``reduce_replicated`` (set it on the last micro-batch of a step) sums the
+        gradients of replicated parameters over the group as they become final."""
+        if self.tp is not None:
+            return self._forward_backward_tp(tokens, targets, loss_scale, on_param_done, backward,
+                                             reduce_replicated)
         c = self.cfg
         B, S = tokens.shape
         T = B * S

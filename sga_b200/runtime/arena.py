@@ -37,6 +37,8 @@ class ParamSpec:
     init: str = "normal"      # "normal" (std below) | "ones" | "zeros"
     std: float = 0.02
     tp_duplicate: bool = False  # replicated across tensor-parallel ranks (norm weights)
+    tp_full_shape: Optional[tuple] = None  # a tensor-parallel shard: shape of the full tensor ...
+    tp_pieces: Optional[list] = None       # ... and the (dim, lo, hi) slices of it, concatenated along dim
 
     @property
     def numel(self) -> int:
@@ -133,6 +135,17 @@ class FlatArena:
                 s.main.fill_(1.0)
             elif s.spec.init == "zeros":
                 s.main.zero_()
+            elif s.spec.tp_pieces is not None:
+                # draw the full tensor (the same stream as the unsharded model) and keep this rank's slices
+                full = torch.empty(s.spec.tp_full_shape)
+                flat = full.view(-1)
+                step = 1 << 24
+                for lo in range(0, flat.numel(), step):
+                    hi = min(flat.numel(), lo + step)
+                    flat[lo:hi].copy_(torch.randn(hi - lo, generator=gen) * s.spec.std)
+                dim = s.spec.tp_pieces[0][0]
+                s.main.copy_(torch.cat([full.narrow(dim, lo, hi - lo) for _, lo, hi in s.spec.tp_pieces], dim))
+                del full
             else:
                 # generated in chunks on the host: identical bits on CPU and GPU runs
                 flat = s.main.view(-1)

@@ -13,10 +13,10 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def _run(nproc, timeout=600):
+def _run(nproc, timeout=600, worker="dist_gpu_worker.py", port=29741):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
-           "--master-addr", "127.0.0.1", "--master-port", "29741", os.path.join(HERE, "dist_gpu_worker.py")]
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, worker)]
     return subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
 
 
@@ -26,3 +26,11 @@ def test_peer_kernels_and_trainer_two_gpus():
         pytest.skip("needs at least 2 GPUs")
     res = _run(2)
     assert res.returncode == 0 and "DIST_GPU_OK" in res.stdout, res.stdout[-3000:] + "\n" + res.stderr[-6000:]
+
+
+@pytest.mark.timeout(900)
+def test_tensor_parallel_fused_kernels_and_model_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least 2 GPUs")
+    res = _run(2, worker="tp_gpu_worker.py", port=29743)
+    assert res.returncode == 0 and "TP_GPU_OK" in res.stdout, res.stdout[-3000:] + "\n" + res.stderr[-6000:]
