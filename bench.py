@@ -118,6 +118,8 @@ def main() -> int:
     ap.add_argument("--seq-len", type=int, default=None)
     ap.add_argument("--ratio-percent", type=float, default=1.0)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel size (with sequence-parallel activations)")
+    ap.add_argument("--tp-comm", type=str, default="auto", choices=("auto", "fused", "library"))
     ns = ap.parse_args()
     if ns.impl == "reference":
         return _reference_arm(ns)
@@ -137,6 +139,8 @@ def main() -> int:
                 train_iters=ns.steps + ns.warmup, lr=3e-4, seed=1234, data_seed=1234, log_interval=0)
     if ns.seq_len:
         over["seq_length"] = ns.seq_len
+    if ns.tp > 1:
+        over.update(tensor_model_parallel_size=ns.tp, tp_comm=ns.tp_comm, init_on_device=True)
     if ns.mode == "sga":
         over.update(sga_enabled=True, sga_score="abs_g", sga_selection="topk", sga_selection_method="exact",
                     sga_selection_ratio_percent=ns.ratio_percent, sga_backend="torch_pipelined_index",
@@ -212,7 +216,7 @@ def main() -> int:
         baseline = pub.get("tokens_per_sec")
     except Exception:
         pass
-    par = f"dp{tr.dp_world}"
+    par = f"dp{tr.dp_world}" if tr.tp_size == 1 else f"tp{tr.tp_size}(sp,{tr.tp.transport})xdp{tr.dp_world}"
     line = {
         "metric": "train tokens/sec (device-timed, max over ranks)", "value": value, "unit": "tokens/s",
         "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_total / K, "higher_is_better": True,

@@ -49,7 +49,7 @@ constexpr int P_TMEM_COLS = 512;
 constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + 256;
 constexpr int P_COPY_UNIT = 16384;
 constexpr int P_COPY_STAGES = 2;
-constexpr int P_SMEM_BYTES_AG = P_SMEM_BYTES + P_COPY_STAGES * P_COPY_UNIT;
+constexpr int P_SMEM_BYTES_AG = P_SMEM_BYTES + P_COPY_STAGES * P_COPY_UNIT;  // also the reduce-scatter staging
 
 enum TpMode { TP_NONE = 0, TP_AG = 1, TP_RS = 2 };
 
@@ -164,7 +164,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   uint64_t* tempty_bar = tfull_bar + 2;
   uint64_t* copy_bar = tempty_bar + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(copy_bar + P_COPY_STAGES);
-  uint8_t* copy_buf = smem + P_STAGES * P_STAGE_BYTES + 1024;  // all-gather form only
+  uint8_t* copy_buf = smem + P_STAGES * P_STAGE_BYTES + 1024;  // all-gather pull ring / reduce-scatter staging
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -312,13 +312,19 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             done_seen |= 1u << chunk;
           }
           if (!__all_sync(0xffffffffu, ok)) break;
-          __nv_bfloat16* dst = tp.recv[chunk] + ((size_t)cx.rank * tp.rows_pc + lrow) * p.N + n0;
+          // Stage 32 rows x 128 columns of bf16 in this warp's shared buffer (16-byte chunks XOR-swizzled
+          // by row), then write them out two rows per instruction: 256 contiguous bytes per row cross
+          // NVLink as full packets instead of one 16-byte piece per lane.
+          uint8_t* stg = copy_buf + (warp - 2) * (32 * 256);
+          const int row0 = row - lane - chunk * tp.rows_pc;  // first local row of this warp
+          __nv_bfloat16* dst0 = tp.recv[chunk] + ((size_t)cx.rank * tp.rows_pc + row0) * p.N + n0;
 #pragma unroll 1
-          for (int c = 0; c < P_BN; c += 32) {
-            uint32_t r[32];
-            tmem_ld32(tmem_base + ((uint32_t)(lg * 32) << 16) + acc * P_BN + c, r);
-            tmem_ld_wait();
-            if (n0 + c < p.N) {
+          for (int half = 0; half < 2; ++half) {
+#pragma unroll 1
+            for (int c = 0; c < 128; c += 32) {
+              uint32_t r[32];
+              tmem_ld32(tmem_base + ((uint32_t)(lg * 32) << 16) + acc * P_BN + half * 128 + c, r);
+              tmem_ld_wait();
 #pragma unroll
               for (int v = 0; v < 4; ++v) {
                 uint4 o;
@@ -327,9 +333,22 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                 for (int i = 0; i < 4; ++i)
                   ob[i] = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * i]) * p.alpha,
                                                 __uint_as_float(r[v * 8 + 2 * i + 1]) * p.alpha);
-                *reinterpret_cast<uint4*>(dst + c + v * 8) = o;
+                const int k16 = (c >> 3) + v;  // 16-byte chunk index within the 256-byte row
+                *reinterpret_cast<uint4*>(stg + lane * 256 + ((k16 ^ (lane & 15)) << 4)) = o;
               }
             }
+            __syncwarp();
+            const int k16 = lane & 15;
+            const int col = n0 + half * 128 + k16 * 8;
+            if (col < p.N) {
+#pragma unroll 4
+              for (int rr = 0; rr < 16; ++rr) {
+                const int rw = rr * 2 + (lane >> 4);
+                const uint4 o = *reinterpret_cast<const uint4*>(stg + rw * 256 + ((k16 ^ (rw & 15)) << 4));
+                *reinterpret_cast<uint4*>(dst0 + (size_t)rw * p.N + half * 128 + k16 * 8) = o;
+              }
+            }
+            __syncwarp();
           }
           __threadfence_system();
           __syncwarp();
@@ -445,7 +464,7 @@ template <int A_MN, int B_MN, int TP>
 static int launch_pair_kernel(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, const TpParams& tp,
                               int grid, cudaStream_t st) {
   auto kern = gemm_bf16_pair_kernel<A_MN, B_MN, TP>;
-  constexpr int smem = TP == TP_AG ? P_SMEM_BYTES_AG : P_SMEM_BYTES;
+  constexpr int smem = TP != TP_NONE ? P_SMEM_BYTES_AG : P_SMEM_BYTES;
   constexpr int threads = TP == TP_AG ? P_THREADS_AG : P_THREADS;
   static bool attr[64] = {};
   int dev = 0;

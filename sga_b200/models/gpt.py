@@ -133,21 +133,28 @@ def param_specs(cfg: GPTConfig, tp_size: int = 1, tp_rank: int = 0) -> list:
                                    (vo + r * nkvl * hd, vo + (r + 1) * nkvl * hd))))
         specs.append(ParamSpec(p + "input_layernorm.weight", (H,), 1, "ones", tp_duplicate=True))
     specs.append(ParamSpec("embedding.word_embeddings.weight", (cfg.vocab, H), 0, "normal", std, tp_duplicate=dup))
+    if tp > 1:
+        # shards first, replicated parameters after them (each kind keeps its backward order), so that
+        # buckets never mix the two; bucket synchronisation is not overlapped under tensor parallelism
+        for i, s in enumerate(specs):
+            s.init_order = i  # the random-init stream keeps the unsharded model's order
+        specs = [s for s in specs if not s.tp_duplicate] + [s for s in specs if s.tp_duplicate]
     return specs
 
 
 class GPT:
     def __init__(self, cfg: GPTConfig, *, device="cpu", pool=None, bucket_elems: int = 16 * 1024 * 1024,
-                 seed: int = 0, need_comm_staging: bool = False, arena: Optional[FlatArena] = None, tp=None):
+                 seed: int = 0, need_comm_staging: bool = False, arena: Optional[FlatArena] = None, tp=None,
+                 init_on_device: bool = False):
         self.cfg = cfg
         self.device = torch.device(device)
         self.tp = tp if (tp is not None and tp.world > 1) else None
         self.tp_size = self.tp.world if self.tp is not None else 1
         self.arena = arena if arena is not None else FlatArena(
             param_specs(cfg, self.tp_size, self.tp.rank if self.tp is not None else 0), bucket_elems=bucket_elems,
-            device=device, pool=pool, need_comm_staging=need_comm_staging)
+            device=device, pool=pool, need_comm_staging=need_comm_staging, split_on_tp_duplicate=self.tp_size > 1)
         if arena is None:
-            self.arena.init_parameters(seed)
+            self.arena.init_parameters(seed, on_device=init_on_device)
         self.cuda = self.device.type == "cuda"
         self._rope = None
         a = self.arena.by_name
@@ -163,10 +170,25 @@ class GPT:
                 proj=a[p + "self_attention.linear_proj.weight"], ln2=a[p + "pre_mlp_layernorm.weight"],
                 fc1=a[p + "mlp.linear_fc1.weight"], fc2=a[p + "mlp.linear_fc2.weight"]))
         self.launches = 0  # native kernel launches issued by the model (bench bookkeeping)
+        # Under tensor parallelism the gradient of a replicated parameter is summed over the group. main_grad
+        # also carries the residual of earlier steps, which every rank already holds in full, so the step's
+        # new gradient is accumulated in a staging buffer, summed there, and only then added to main_grad.
+        self._stage = {}
+        if self.tp is not None:
+            dup = [sl for sl in self.arena.slots if sl.spec.tp_duplicate]
+            if dup:
+                lo, hi = min(sl.start for sl in dup), max(sl.end for sl in dup)
+                self._stage_buf = torch.zeros(hi - lo, dtype=torch.float32, device=self.device)
+                for sl in dup:
+                    self._stage[id(sl)] = self._stage_buf[sl.start - lo:sl.end - lo].view(sl.spec.shape)
 
     def named_parameters(self):
         for s in self.arena.slots:
             yield s.name, s.model
+
+    def _gbuf(self, slot):
+        """Where this step's gradient of ``slot`` is accumulated."""
+        return self._stage.get(id(slot), slot.grad)
 
     # --------------------------------------------------------------- GEMMs
     def _linear(self, x, slot, residual=None):
@@ -202,9 +224,9 @@ class GPT:
             from .. import kernels as K
 
             self.launches += 1
-            K.gemm_bf16(dy, x, slot.grad, a_mn=True, b_mn=True, epi=K.EPI_F32_ACC)
+            K.gemm_bf16(dy, x, self._gbuf(slot), a_mn=True, b_mn=True, epi=K.EPI_F32_ACC)
         else:
-            slot.grad += dy.float().t() @ x.float()
+            self._gbuf(slot).add_(dy.float().t() @ x.float())
 
     def _rope_tables(self):
         if self._rope is None:
@@ -339,7 +361,7 @@ class GPT:
         done(L["fc1"])
         dh2 = tp.linear_rs(dgu, L["fc1"].model, b_mn=True)
         del dgu
-        F.rmsnorm_bwd(x_mid, L["ln2"].model, dh2, rstd2, dw_out=L["ln2"].grad, dx_out=dx, accumulate_dx=True)
+        F.rmsnorm_bwd(x_mid, L["ln2"].model, dh2, rstd2, dw_out=self._gbuf(L["ln2"]), dx_out=dx, accumulate_dx=True)
         done(L["ln2"])
         del dh2
         # attention
@@ -351,8 +373,8 @@ class GPT:
         F.rope_(dqkv, cs, sn, S, nq + nkv, hd, 0, -1.0)
         if c.qk_norm:
             pre, rq, rk = qk_saved
-            F.headnorm_bwd_(pre, dqkv, L["kn"].model, rk, L["kn"].grad, T, nkv, hd, nq * hd, nq * hd)
-            F.headnorm_bwd_(pre, dqkv, L["qn"].model, rq, L["qn"].grad, T, nq, hd, 0, 0)
+            F.headnorm_bwd_(pre, dqkv, L["kn"].model, rk, self._gbuf(L["kn"]), T, nkv, hd, nq * hd, nq * hd)
+            F.headnorm_bwd_(pre, dqkv, L["qn"].model, rq, self._gbuf(L["qn"]), T, nq, hd, 0, 0)
             done(L["kn"])
             done(L["qn"])
             self.launches += 4
@@ -360,7 +382,7 @@ class GPT:
         done(L["qkv"])
         dh1 = tp.linear_rs(dqkv, L["qkv"].model, b_mn=True)
         del dqkv
-        F.rmsnorm_bwd(x, L["ln1"].model, dh1, rstd1, dw_out=L["ln1"].grad, dx_out=dx, accumulate_dx=True)
+        F.rmsnorm_bwd(x, L["ln1"].model, dh1, rstd1, dw_out=self._gbuf(L["ln1"]), dx_out=dx, accumulate_dx=True)
         done(L["ln1"])
         self.launches += 7
 
@@ -374,8 +396,13 @@ class GPT:
 
         def done(slot):
             # a replicated parameter's gradient is final only once summed over the tensor-parallel ranks
-            if slot.spec.tp_duplicate and reduce_replicated:
-                tp.allreduce_replicated(slot.grad)
+            st = self._stage.get(id(slot))
+            if st is not None:
+                if not reduce_replicated:
+                    return  # keeps accumulating in the staging buffer until the step's last micro-batch
+                tp.allreduce_replicated(st)
+                slot.grad.add_(st)
+                st.zero_()
             user_done(slot)
 
         ids = tokens.reshape(-1)[lo:lo + Tl]
@@ -399,13 +426,13 @@ class GPT:
         dhf = self._dgrad(dlogits, self.head)
         del logits, dlogits, hf
         gdx = tp.slot("dx", T, c.hidden)
-        F.rmsnorm_bwd(x, self.final_norm.model, dhf, rstd_f, dw_out=self.final_norm.grad, dx_out=gdx.local)
+        F.rmsnorm_bwd(x, self.final_norm.model, dhf, rstd_f, dw_out=self._gbuf(self.final_norm), dx_out=gdx.local)
         done(self.final_norm)
         del dhf
         for L, sv in zip(reversed(self.layers), reversed(saved)):
             self._layer_bwd_tp(L, sv, gdx, B, S, done)
         saved.clear()
-        F.embed_bwd(ids, gdx.local, self.emb.grad)
+        F.embed_bwd(ids, gdx.local, self._gbuf(self.emb))
         done(self.emb)
         self.launches += 4
         return loss

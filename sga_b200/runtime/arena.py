@@ -39,6 +39,7 @@ class ParamSpec:
     tp_duplicate: bool = False  # replicated across tensor-parallel ranks (norm weights)
     tp_full_shape: Optional[tuple] = None  # a tensor-parallel shard: shape of the full tensor ...
     tp_pieces: Optional[list] = None       # ... and the (dim, lo, hi) slices of it, concatenated along dim
+    init_order: Optional[int] = None       # position in the random-init stream when it differs from the layout order
 
     @property
     def numel(self) -> int:
@@ -81,7 +82,7 @@ class Bucket:
 
 class FlatArena:
     def __init__(self, specs, *, bucket_elems: int = 16 * 1024 * 1024, device="cpu", pool=None,
-                 need_comm_staging: bool = False):
+                 need_comm_staging: bool = False, split_on_tp_duplicate: bool = False):
         self.device = torch.device(device)
         self.pool = pool
         self.slots: list[ParamSlot] = []
@@ -89,6 +90,11 @@ class FlatArena:
         off = 0
         cur = Bucket(0, 0, 0)
         for spec in specs:
+            if split_on_tp_duplicate and cur.slots and cur.slots[-1].spec.tp_duplicate != spec.tp_duplicate:
+                # a bucket holds either shards or replicated parameters, never both: a per-bucket selection
+                # over replicated data is then the same on every tensor-parallel rank
+                self.buckets.append(cur)
+                cur = Bucket(cur.index + 1, off, off)
             n = spec.numel
             start = off
             end = start + n
@@ -126,11 +132,19 @@ class FlatArena:
         self._table = None
 
     # ------------------------------------------------------------ init
-    def init_parameters(self, seed: int = 0) -> None:
+    def init_parameters(self, seed: int = 0, on_device: bool = False) -> None:
         """Random init of the fp32 masters (same values on every data-parallel
-        rank for a given seed), then the bf16 copies."""
+        rank for a given seed), then the bf16 copies. ``on_device`` draws with
+        the device's generator instead of the host's (fast for large models;
+        the values then differ from a host-initialised run of the same seed)."""
+        if on_device and self.device.type == "cuda":
+            self._init_on_device(seed)
+            self.sync_model_from_main()
+            return
         gen = torch.Generator(device="cpu").manual_seed(seed)
-        for s in self.slots:
+        order = sorted(range(len(self.slots)), key=lambda i: (
+            self.slots[i].spec.init_order if self.slots[i].spec.init_order is not None else i))
+        for s in (self.slots[i] for i in order):
             if s.spec.init == "ones":
                 s.main.fill_(1.0)
             elif s.spec.init == "zeros":
@@ -154,6 +168,26 @@ class FlatArena:
                     hi = min(flat.numel(), lo + step)
                     flat[lo:hi].copy_(torch.randn(hi - lo, generator=gen) * s.spec.std)
         self.sync_model_from_main()
+
+    def _init_on_device(self, seed: int) -> None:
+        order = sorted(range(len(self.slots)), key=lambda i: (
+            self.slots[i].spec.init_order if self.slots[i].spec.init_order is not None else i))
+        for pos, i in enumerate(order):
+            s = self.slots[i]
+            if s.spec.init == "ones":
+                s.main.fill_(1.0)
+            elif s.spec.init == "zeros":
+                s.main.zero_()
+            else:
+                # one generator per parameter, keyed by its place in the stream: a shard draws its full tensor
+                gen = torch.Generator(device=self.device).manual_seed(seed * 1000003 + pos)
+                shape = s.spec.tp_full_shape if s.spec.tp_pieces is not None else s.spec.shape
+                full = torch.randn(shape, generator=gen, device=self.device) * s.spec.std
+                if s.spec.tp_pieces is not None:
+                    dim = s.spec.tp_pieces[0][0]
+                    full = torch.cat([full.narrow(dim, lo, hi - lo) for _, lo, hi in s.spec.tp_pieces], dim)
+                s.main.copy_(full)
+                del full
 
     def sync_model_from_main(self) -> None:
         if self.device.type == "cuda":

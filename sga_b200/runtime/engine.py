@@ -151,6 +151,8 @@ class SGAEngine:
         self._norm_spread = cfg.sga_checks_norm_spread
         self._rng_bracket = cfg.sga_checks_rng_bracket
         self._rank = dist.get_rank() if (dist.is_available() and dist.is_initialized()) else 0
+        # set by a trainer that shards the model: fn(sumsq, source, mask) folds the other shards into the norm
+        self.model_parallel_norm = None
         if not (self._count_guard and self._support_consistency and self._norm_spread and self._rng_bracket):
             if self._rank == 0:
                 msg = (f"[SGA] WARN sga_checks escape hatch active (L1_count={int(self._count_guard)} "
@@ -578,7 +580,16 @@ class SGAEngine:
                     sumsq.zero_()
             else:
                 K.sumsq(arena.main_grad, sumsq, mask=mask)
-            if world > 1 and ddp.transport != "p2p":
+            reduced_over_dp = not (world > 1 and ddp.transport != "p2p")
+            if self.model_parallel_norm is not None:
+                # shards of other tensor-parallel ranks join the norm; replicated parameters count once
+                if (not was_full) and self._compact_values and not self.rank_local:
+                    raise NotImplementedError("tensor parallelism with compact shared supports: use "
+                                              "--sga-selection-locality rank_local or a mask backend")
+                src = arena.comm if ((not was_full) and self.rank_local and self.backend.consumes == "idx") \
+                    else arena.main_grad
+                self.model_parallel_norm(sumsq, src, mask if src is arena.main_grad else None)
+            if not reduced_over_dp:
                 dist.all_reduce(sumsq, op=dist.ReduceOp.SUM, group=ddp.group)  # DP-bitwise fix
                 K.clip_coeff(sumsq, 1.0 / world, clip, self._dev["coeff"], self._dev["norm"])
             else:
@@ -597,6 +608,10 @@ class SGAEngine:
         else:
             total = float((arena.main_grad.double() ** 2).sum())
         t = torch.tensor([total], dtype=torch.float64)
+        if self.model_parallel_norm is not None:
+            src = arena.comm if ((not was_full) and self.rank_local and self.backend.consumes == "idx") \
+                else arena.main_grad
+            self.model_parallel_norm(t, src, mask if src is arena.main_grad else None)
         if world > 1 and dist.is_initialized():
             dist.all_reduce(t, op=dist.ReduceOp.SUM, group=ddp.group)
             t /= world

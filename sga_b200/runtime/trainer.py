@@ -65,6 +65,10 @@ def add_trainer_args(p: argparse.ArgumentParser) -> argparse.ArgumentParser:
     g.add_argument("--overlap-grad-reduce", type=C.sga_bool, default=True)
     g.add_argument("--comm-max-ctas", type=int, default=0)
     g.add_argument("--tensor-model-parallel-size", type=int, default=1)
+    g.add_argument("--init-on-device", action="store_true",
+                   help="draw the initial weights with the device generator (large models)")
+    g.add_argument("--tp-comm", type=str, default="auto", choices=("auto", "fused", "library"),
+                   help="tensor-parallel linears: collective fused into the GEMM kernel, or library collectives")
     g.add_argument("--pipeline-model-parallel-size", type=int, default=1)
     g.add_argument("--sequence-parallel", action="store_true")
     g.add_argument("--untie-embeddings-and-output-weights", action="store_true")
@@ -135,7 +139,25 @@ class Trainer:
         if args.untie_embeddings_and_output_weights:
             over["tied_embeddings"] = False
         self.cfg = get_config(args.model, **over)
-        self.dp_world = self.world // max(1, args.tensor_model_parallel_size * args.pipeline_model_parallel_size)
+        self.tp_size = max(1, int(args.tensor_model_parallel_size))
+        if (args.pipeline_model_parallel_size or 1) > 1:
+            raise NotImplementedError("pipeline stages are not built in this trainer (single-stage models only)")
+        assert self.world % self.tp_size == 0, "world size must be a multiple of the tensor-parallel size"
+        self.dp_world = self.world // self.tp_size
+        # adjacent ranks form a tensor-parallel group; data-parallel groups stride over them
+        self.tp_rank, self.dp_rank = self.rank % self.tp_size, self.rank // self.tp_size
+        self.tp_group = self.dp_group = None
+        if self.tp_size > 1:
+            for d in range(self.dp_world):
+                ranks = list(range(d * self.tp_size, (d + 1) * self.tp_size))
+                grp = dist.new_group(ranks=ranks)
+                if d == self.dp_rank:
+                    self.tp_group = grp
+            for t in range(self.tp_size):
+                ranks = list(range(t, self.world, self.tp_size))
+                grp = dist.new_group(ranks=ranks)
+                if t == self.tp_rank:
+                    self.dp_group = grp
         assert args.global_batch_size % (args.micro_batch_size * self.dp_world) == 0, (
             "global batch must be a multiple of micro_batch * data-parallel size")
         self.num_micro = args.global_batch_size // (args.micro_batch_size * self.dp_world)
@@ -147,18 +169,38 @@ class Trainer:
         if cuda and transport in ("auto", "p2p"):
             from ..parallel.symm import SymmPool
 
-            self.pool = SymmPool(group=None, device=self.device)
+            self.pool = SymmPool(group=self.dp_group, device=self.device)
+        self.tp = None
+        if self.tp_size > 1:
+            from ..parallel.tp import TPContext
+
+            tp_comm = args.tp_comm
+            if tp_comm == "auto":
+                tp_comm = "fused" if (cuda and transport in ("auto", "p2p")) else "library"
+            self.tp = TPContext(group=self.tp_group, device=self.device, transport=tp_comm)
         self.sga = bool(args.sga_enabled)
+        if self.sga and self.tp_size > 1 and getattr(args, "sga_selection_locality", "shared") != "rank_local":
+            raise NotImplementedError(
+                "SGA under tensor parallelism needs --sga-selection-locality rank_local: a shared support's "
+                "threshold is global over the model, so it would differ between tensor-parallel ranks and "
+                "select different coordinates of the parameters they replicate")
         need_comm = (self.sga and getattr(args, "sga_selection_locality", "shared") == "rank_local"
                      and args.sga_backend != "torch_pipelined_mask")
         self.model = GPT(self.cfg, device=self.device, pool=self.pool,
                          bucket_elems=getattr(args, "sga_bucket_elems", 16 << 20), seed=args.seed,
-                         need_comm_staging=need_comm)
+                         need_comm_staging=need_comm, tp=self.tp,
+                         init_on_device=bool(getattr(args, "init_on_device", False)))
         ddp_cfg = DDPConfig(average_in_collective=True, overlap_grad_reduce=bool(args.overlap_grad_reduce),
                             comm_max_ctas=args.comm_max_ctas)
         if getattr(args, "sga_backend_timer", None):
             ddp_cfg.overlap_grad_reduce = False
-        self.ddp = DataParallel(self.model, group=None, transport=transport, ddp_config=ddp_cfg, pool=self.pool)
+        if self.tp is not None:
+            # Both kinds of kernel wait on other GPUs. Run concurrently, two ranks could start them in
+            # opposite orders and each hold the SMs the other's peer is waiting for, so under tensor
+            # parallelism the data-parallel synchronisation follows the backward pass on one stream order.
+            ddp_cfg.overlap_grad_reduce = False
+        self.ddp = DataParallel(self.model, group=self.dp_group, transport=transport, ddp_config=ddp_cfg,
+                                pool=self.pool)
         if self.ddp.transport == "gloo":
             ddp_cfg.average_in_collective = False
         self.optimizer = FlatOptimizer(self.model.arena, OptimizerConfig(
@@ -175,6 +217,8 @@ class Trainer:
             self.engine = build_engine(trainer_args=args, quiet=quiet)
             self.engine.log_interval = args.log_interval
             self.engine.attach(self.ddp)
+            if self.tp is not None:
+                self.engine.model_parallel_norm = self._tp_norm
         self.data = SyntheticTokens(self.cfg.vocab, self.cfg.seq_len, args.data_seed, pin=cuda)
         self.iteration = 0
         self._dense = None
@@ -183,13 +227,46 @@ class Trainer:
             self._dev_coeff = torch.ones(1, device=self.device)
             self._dev_norm = torch.zeros(1, device=self.device)
         self.last_grad_norm = None
+        if self.tp is not None:
+            # merged element ranges of the parameters every tensor-parallel rank holds
+            self._dup_ranges = []
+            for sl in self.model.arena.slots:
+                if sl.spec.tp_duplicate:
+                    if self._dup_ranges and self._dup_ranges[-1][1] == sl.start:
+                        self._dup_ranges[-1][1] = sl.end
+                    else:
+                        self._dup_ranges.append([sl.start, sl.end])
+            self._dev_dup = torch.zeros(1, device=self.device) if cuda else None
+
+    def _tp_norm(self, sumsq: torch.Tensor, source: torch.Tensor, mask=None) -> None:
+        """``sumsq`` (this shard's sum of squares over ``source``) -> the model's:
+        the sharded part summed over the tensor-parallel ranks, the replicated part counted once."""
+        if self.device.type == "cuda":
+            from .. import kernels as K
+
+            first = True
+            for lo, hi in self._dup_ranges:
+                K.sumsq(source[lo:hi], self._dev_dup, mask=None if mask is None else mask[lo:hi],
+                        accumulate=not first)
+                first = False
+            dup = self._dev_dup
+        else:
+            tot = 0.0
+            for lo, hi in self._dup_ranges:
+                v = source[lo:hi].double()
+                if mask is not None:
+                    v = torch.where(mask[lo:hi] > 0, v, torch.zeros_like(v))
+                tot += float((v ** 2).sum())
+            dup = torch.tensor([tot], dtype=sumsq.dtype)
+        sumsq.sub_(dup.to(sumsq.dtype))
+        dist.all_reduce(sumsq, group=self.tp_group)
+        sumsq.add_(dup.to(sumsq.dtype))
 
     # ----------------------------------------------------------------- data
     def host_batch(self, step: int) -> torch.Tensor:
         """This rank's ``[num_micro * micro_batch, seq + 1]`` token block for ``step`` (pinned host memory)."""
         per_rank = self.num_micro * self.args.micro_batch_size
-        dp_rank = self.rank % self.dp_world
-        return self.data.batch(step, dp_rank * per_rank, per_rank)
+        return self.data.batch(step, self.dp_rank * per_rank, per_rank)
 
     # ----------------------------------------------------------------- step
     def train_step(self, batch: torch.Tensor) -> torch.Tensor:
@@ -212,7 +289,8 @@ class Trainer:
                 else:
                     self._arm_dense()
             loss = self.model.forward_backward(tokens, targets, loss_scale=1.0 / self.num_micro,
-                                               on_param_done=self.ddp.on_param_done if last else None)
+                                               on_param_done=self.ddp.on_param_done if last else None,
+                                               reduce_replicated=last)
             losses.append(loss)
         if self.engine is not None:
             if not self.engine.grad_sync(self.ddp, False):
@@ -225,7 +303,9 @@ class Trainer:
 
     # ----------------------------------------------------------- dense path
     def _fused_dense(self) -> bool:
-        return self.args.dense_mode == "fused" and self.ddp.transport == "p2p"
+        # the sharded-update kernel sees one rank's slice of the gradient; the tensor-parallel norm needs
+        # the whole replicated parameters, so that combination takes the all-reduce path
+        return self.args.dense_mode == "fused" and self.ddp.transport == "p2p" and self.tp is None
 
     def _arm_dense(self) -> None:
         if self._fused_dense():
@@ -270,6 +350,8 @@ class Trainer:
             from .. import kernels as K
 
             K.sumsq(arena.main_grad, self._dev_sumsq)
+            if self.tp is not None:
+                self._tp_norm(self._dev_sumsq, arena.main_grad)
             K.clip_coeff(self._dev_sumsq, 1.0, clip, self._dev_coeff, self._dev_norm)
             K.adam_step(arena.main_param, arena.main_grad, arena.exp_avg, arena.exp_avg_sq, arena.segment_table(),
                         opt.group_lr(), opt.group_wd(), beta1=beta1, beta2=beta2, eps=g0["eps"],
@@ -279,7 +361,10 @@ class Trainer:
         else:
             from ..plugins.optimizer.reference import grad_correct_torch
 
-            norm = float((arena.main_grad.double() ** 2).sum().sqrt())
+            sq = torch.tensor([float((arena.main_grad.double() ** 2).sum())], dtype=torch.float64)
+            if self.tp is not None:
+                self._tp_norm(sq, arena.main_grad)
+            norm = float(sq.sqrt())
             coeff = 1.0
             if clip > 0 and clip / (norm + 1e-6) < 1.0:
                 coeff = float(torch.tensor(clip / (norm + 1e-6), dtype=torch.float32))
@@ -300,10 +385,15 @@ class Trainer:
 
     def check(self) -> None:
         self.ddp.check()
+        if self.tp is not None:
+            self.tp.check()
 
     def close(self) -> None:
         if self.engine is not None and self.engine._trace is not None:
             self.engine._trace.close()
+        if self.tp is not None:
+            self.tp.close()
+            self.tp = None
         if self.pool is not None:
             self.pool.close()
             self.pool = None
