@@ -60,8 +60,8 @@ register_sigs({
     "sga_replay_blocks": [],
     "sga_replay_pass1": [_P, _I, _F, _P, _P, _P, _I, _L, _P, _P, _P],
     "sga_replay_pass3": [_P, _I, _F, _P, _P, _P, _P, _P, _P, _P, _P, _I, _L, _F, _F, _F, _F, _F, _P, _P, _P],
-    "sga_attn_fwd": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _L, _L, _L, _L, _F, _I, _P, _P],
-    "sga_attn_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _L, _L, _L, _L, _F, _I, _P, _P],
+    "sga_attn_fwd": [_P, _P, _P, _I, _I, _I, _I, _I, _L, _L, _F, _P, _P],
+    "sga_attn_bwd": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _L, _L, _F, _P, _P],
 })
 
 

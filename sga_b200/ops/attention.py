@@ -35,8 +35,8 @@ def _split(qkv, B, S, nq, nkv, hd):
     return q, k, v
 
 
-def native_available(qkv) -> bool:
-    if not qkv.is_cuda or _IMPL == "library":
+def native_available(qkv, hd: int = 64) -> bool:
+    if not qkv.is_cuda or _IMPL == "library" or hd not in (64, 128) or qkv.dtype != torch.bfloat16:
         return False
     try:
         from ..csrc import lib
@@ -49,7 +49,7 @@ def native_available(qkv) -> bool:
 def attn_fwd(qkv, B, S, nq, nkv, hd):
     """Returns ``(ctx [T, nq*hd] bf16, saved)``."""
     scale = 1.0 / math.sqrt(hd)
-    if native_available(qkv):
+    if native_available(qkv, hd):
         from . import attention_native as AN
 
         return AN.attn_fwd(qkv, B, S, nq, nkv, hd, scale)

@@ -1,6 +1,6 @@
 """Device-timed micro-benchmarks of the native kernels with their roofline
-fractions: ``python -m sga_b200.utils.kernel_bench --kernel gemm|adam|index_sync|
-allreduce|rmsnorm|swiglu|rope|ce|replay [--small]``.
+fractions: ``python -m sga_b200.utils.kernel_bench --kernel attention|gemm|adam|
+index_sync|elementwise|replay [--small]``.
 
 Each case warms up, then times with CUDA events on the launching stream
 between synchronisations, on inputs larger than the 126 MB L2 (or flushes L2
@@ -193,7 +193,31 @@ def bench_replay(small):
     emit("replay_pass3_kernel", f"R={R} n={n} bf16 g", ms, bytes_=n * (2.0 + 4.0 + R * 33.0))
 
 
-CASES = {"gemm": bench_gemm, "adam": bench_adam, "index_sync": bench_index_sync, "elementwise": bench_elementwise,
+def bench_attention(small):
+    from ..ops import attention as A
+
+    dev = "cuda"
+    cases = [(4, 2048, 32, 8, 64)] if small else [(4, 2048, 32, 8, 64), (2, 4096, 16, 8, 128), (1, 4096, 32, 8, 128)]
+    for B, S, nq, nkv, hd in cases:
+        T = B * S
+        qkv = torch.randn(T, (nq + 2 * nkv) * hd, device=dev).to(torch.bfloat16)
+        dctx = torch.randn(T, nq * hd, device=dev).to(torch.bfloat16)
+        fl_f = 4.0 * B * nq * hd * S * S / 2
+        for impl in ("native", "library"):
+            A._IMPL = impl
+            ctx, saved = A.attn_fwd(qkv, B, S, nq, nkv, hd)
+            it = 2 if small else 10
+            ms_f = timed(lambda: A.attn_fwd(qkv, B, S, nq, nkv, hd), it, warmup=1 if small else 3)
+            dq = torch.empty_like(qkv)
+            ms_b = timed(lambda: A.attn_bwd(dctx, qkv, saved, B, S, nq, nkv, hd, dq), it, warmup=1 if small else 3)
+            name = "attn_fwd_kernel" if impl == "native" else "library flash fwd (reference point)"
+            emit(name, f"B={B} S={S} heads={nq}:{nkv} hd={hd} causal", ms_f, flops=fl_f)
+            name = "attn_dq+dkv kernels" if impl == "native" else "library flash bwd (reference point)"
+            emit(name, f"B={B} S={S} heads={nq}:{nkv} hd={hd} causal (2.5x forward FLOPs)", ms_b, flops=2.5 * fl_f)
+        A._IMPL = "auto"
+
+
+CASES = {"attention": bench_attention, "gemm": bench_gemm, "adam": bench_adam, "index_sync": bench_index_sync, "elementwise": bench_elementwise,
          "replay": bench_replay}
 
 
