@@ -45,10 +45,11 @@ struct FwdCfg {
 };
 
 template <int HD>
-__global__ void __launch_bounds__(F_THREADS, 1) attn_fwd_kernel(const __grid_constant__ CUtensorMap tm,
+__global__ void __maxnreg__(200) attn_fwd_kernel(const __grid_constant__ CUtensorMap tm,
                                                                 const FwdParams p) {
   using C = FwdCfg<HD>;
   constexpr int BN = C::BN;
+  constexpr int CH = HD == 64 ? 2 : 1;  // 32-column TMEM loads per wait (register budget)
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;                                  // [2][HD/64][128][128 B]
@@ -176,52 +177,69 @@ __global__ void __launch_bounds__(F_THREADS, 1) attn_fwd_kernel(const __grid_con
       tc_fence_after();
       const int kv0 = j * BN;
       const bool diag = kv0 + BN - 1 > q0 + 128 * w;  // some key of the block lies past some row of the sub-block
-      // pass 1: row maximum of the scaled scores
-      float mx = m;
+      // pass 1: row maximum of the raw scores (four independent chains)
+      float mx4[4] = {m, m, m, m};
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
-        uint32_t v[32];
-        tmem_ld32(tS[w] + lane_off + c, v);
-        tmem_ld_wait();
+      for (int c = 0; c < BN; c += 32 * CH) {
+        uint32_t v[32 * CH];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float s = __uint_as_float(v[i]) * p.scale_log2;
-          if (!diag || kv0 + c + i <= qrow) mx = fmaxf(mx, s);
+        for (int u = 0; u < CH; ++u) tmem_ld32(tS[w] + lane_off + c + 32 * u, *reinterpret_cast<uint32_t(*)[32]>(&v[32 * u]));
+        tmem_ld_wait();
+        if (diag) {
+#pragma unroll
+          for (int i = 0; i < 32 * CH; ++i)
+            if (kv0 + c + i <= qrow) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32 * CH; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[i]));
         }
       }
-      const float alpha = exp2f(m - mx);  // m = -inf on the first block: 0
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      const float alpha = exp2f((m - mx) * p.scale_log2);  // m = -inf on the first block: 0
       // fold the previous block's P V into the running output, then move it to the new maximum
       if (j > 0) {
         ok = __all_sync(0xffffffffu, mbar_wait(&o_full[w], (j - 1) & 1, p.err));
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
-        for (int c = 0; c < HD; c += 32) {
-          uint32_t v[32];
-          tmem_ld32(tO[w] + lane_off + c, v);
+        for (int c = 0; c < HD; c += 32 * CH) {
+          uint32_t v[32 * CH];
+#pragma unroll
+          for (int u = 0; u < CH; ++u) tmem_ld32(tO[w] + lane_off + c + 32 * u, *reinterpret_cast<uint32_t(*)[32]>(&v[32 * u]));
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[c + i] = (o[c + i] + __uint_as_float(v[i])) * alpha;
+          for (int i = 0; i < 32 * CH; ++i) o[c + i] = (o[c + i] + __uint_as_float(v[i])) * alpha;
         }
       }
       l *= alpha;
       m = mx;
       // pass 2: probabilities -> bf16 operand tile, row sum
+      const float neg = -mx * p.scale_log2;
+      float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         uint32_t v[32];
         tmem_ld32(tS[w] + lane_off + c, v);
         tmem_ld_wait();
         float pr[32];
+        if (diag) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float s = __uint_as_float(v[i]) * p.scale_log2;
-          const float e = (!diag || kv0 + c + i <= qrow) ? exp2f(s - mx) : 0.f;
-          pr[i] = e;
-          l += e;
+          for (int i = 0; i < 32; ++i) {
+            const float e = kv0 + c + i <= qrow ? exp2f(fmaf(__uint_as_float(v[i]), p.scale_log2, neg)) : 0.f;
+            pr[i] = e;
+            l4[i & 3] += e;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float e = exp2f(fmaf(__uint_as_float(v[i]), p.scale_log2, neg));
+            pr[i] = e;
+            l4[i & 3] += e;
+          }
         }
         store_p32(myP, r, c, pr);
       }
+      l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
       tc_fence_before();
       fence_proxy_async_smem();
       mbar_arrive(&p_full[w]);
@@ -253,7 +271,7 @@ __global__ void __launch_bounds__(F_THREADS, 1) attn_fwd_kernel(const __grid_con
             }
           }
         }
-        if (live) p.lse[((size_t)b * p.nq + h) * p.S + qrow] = (m + log2f(l)) * 0.6931471805599453f;
+        if (live) p.lse[((size_t)b * p.nq + h) * p.S + qrow] = (m * p.scale_log2 + log2f(l)) * 0.6931471805599453f;
       }
     }
   }

@@ -206,6 +206,8 @@ __global__ void __launch_bounds__(DQ_THREADS, 1) attn_dq_kernel(const __grid_con
       if (!ok) break;
       tc_fence_after();
       const int kv0 = j * BN;
+      // some key of the block lies past some row of the sub-block, or the sub-block has rows past the sequence
+      const bool diag = kv0 + BN - 1 > q0 + 128 * w || q0 + 128 * w + 127 >= p.S;
       // the dS tile is free once the previous block's dQ product has read it
       if (j > 0) {
         ok = __all_sync(0xffffffffu, mbar_wait(&dq_done[w], (j - 1) & 1, p.err));
@@ -218,11 +220,17 @@ __global__ void __launch_bounds__(DQ_THREADS, 1) attn_dq_kernel(const __grid_con
         tmem_ld32(tW[w] + 64 + lane_off + c, vd);
         tmem_ld_wait();
         float ds[32];
+        if (diag) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const bool keep = live && kv0 + c + i <= qrow;
-          const float pr = keep ? exp2f(__uint_as_float(vs[i]) * p.scale_log2 - lse2) : 0.f;
-          ds[i] = keep ? pr * (__uint_as_float(vd[i]) - dlt) : 0.f;
+          for (int i = 0; i < 32; ++i) {
+            const bool keep = live && kv0 + c + i <= qrow;
+            const float pr = keep ? exp2f(fmaf(__uint_as_float(vs[i]), p.scale_log2, -lse2)) : 0.f;
+            ds[i] = keep ? pr * (__uint_as_float(vd[i]) - dlt) : 0.f;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            ds[i] = exp2f(fmaf(__uint_as_float(vs[i]), p.scale_log2, -lse2)) * (__uint_as_float(vd[i]) - dlt);
         }
         store_p32(myDS, r, c, ds);
       }
@@ -421,6 +429,8 @@ __global__ void __launch_bounds__(DKV_THREADS, 1) attn_dkv_kernel(const __grid_c
       const float* l2 = sStat + u * 128;
       const float* dl = l2 + 64;
       const int qb0 = i * BQ;
+      // the block's first query lies before the block's last key, or its last query past the sequence
+      const bool diag = qb0 < kv0 + 128 || qb0 + BQ > p.S;
 #pragma unroll 1
       for (int c = 0; c < BQ; c += 32) {
         uint32_t vs[32], vd[32];
@@ -428,13 +438,22 @@ __global__ void __launch_bounds__(DKV_THREADS, 1) attn_dkv_kernel(const __grid_c
         tmem_ld32(tDP[u] + lane_off + c, vd);
         tmem_ld_wait();
         float pt[32], ds[32];
+        if (diag) {
 #pragma unroll
-        for (int k = 0; k < 32; ++k) {
-          const int qpos = qb0 + c + k;
-          const bool keep = qpos >= kpos && qpos < p.S;
-          const float pr = keep ? exp2f(__uint_as_float(vs[k]) * p.scale_log2 - l2[c + k]) : 0.f;
-          pt[k] = pr;
-          ds[k] = keep ? pr * (__uint_as_float(vd[k]) - dl[c + k]) : 0.f;
+          for (int k = 0; k < 32; ++k) {
+            const int qpos = qb0 + c + k;
+            const bool keep = qpos >= kpos && qpos < p.S;
+            const float pr = keep ? exp2f(fmaf(__uint_as_float(vs[k]), p.scale_log2, -l2[c + k])) : 0.f;
+            pt[k] = pr;
+            ds[k] = keep ? pr * (__uint_as_float(vd[k]) - dl[c + k]) : 0.f;
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < 32; ++k) {
+            const float pr = exp2f(fmaf(__uint_as_float(vs[k]), p.scale_log2, -l2[c + k]));
+            pt[k] = pr;
+            ds[k] = pr * (__uint_as_float(vd[k]) - dl[c + k]);
+          }
         }
         store_p32(sPT + u * C::PT_BYTES, r, c, pt);
         store_p32(sDS + u * C::PT_BYTES, r, c, ds);
