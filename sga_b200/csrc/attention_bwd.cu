@@ -9,7 +9,7 @@
 //   step 3 (dK/dV)       one CTA per (128 keys, KV head, batch); it walks the query heads of the
 //                        group and their 64-row query blocks from the diagonal down:
 //                        S^T = K Q^T and dP^T = V dO^T into TMEM (double-buffered), threads form
-//                        P^T and dS^T (one key row each; lse and delta of the 64 queries are
+//                        P^T and dS^T (a key row and 32 queries each; lse and delta of the 64 queries are
 //                        broadcast from shared memory), and dV += P^T dO, dK += dS^T Q accumulate
 //                        in TMEM over the whole walk: the sum over the group's query heads
 //                        happens in the accumulator.
@@ -274,7 +274,7 @@ __global__ void __launch_bounds__(DQ_THREADS, 1) attn_dq_kernel(const __grid_con
 }
 
 // ------------------------------------------------------------ dK/dV kernel
-constexpr int DKV_THREADS = 192;  // one warpgroup of key rows + TMA warp + MMA warp
+constexpr int DKV_THREADS = 320;  // two warpgroups (each key row is shared by two threads: 32 queries each) + TMA warp + MMA warp
 constexpr int DKV_BQ = 64;
 
 template <int HD>
@@ -327,14 +327,14 @@ __global__ void __launch_bounds__(DKV_THREADS, 1) attn_dkv_kernel(const __grid_c
     }
     for (int u = 0; u < 2; ++u) {
       mbar_init(&st_full[u], 1);
-      mbar_init(&pt_full[u], 128);
+      mbar_init(&pt_full[u], 256);
       mbar_init(&acc_done[u], 1);
     }
     mbar_fence_init();
     tma_prefetch_desc(&tmQKV);
     tma_prefetch_desc(&tmDO);
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
@@ -347,7 +347,7 @@ __global__ void __launch_bounds__(DKV_THREADS, 1) attn_dkv_kernel(const __grid_c
   const uint32_t tDP[2] = {tmem_base + 128, tmem_base + 192};
   const uint32_t tDV = tmem_base + 256, tDK = tmem_base + 384;
 
-  if (warp == 4) {
+  if (warp == 8) {
     if (lane == 0 && nt > 0) {
       mbar_expect_tx(kv_full, C::KV_BYTES);
       load_tile(sK, &tmQKV, kv_full, (p.nq + g) * HD, row_base + kv0, 128, HD);
@@ -363,7 +363,7 @@ __global__ void __launch_bounds__(DKV_THREADS, 1) attn_dkv_kernel(const __grid_c
       }
       if (sga_aborted(p.err)) __nanosleep(200000);
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     if (lane == 0 && nt > 0) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, BQ, 0, 0);
       constexpr uint32_t idesc_a = umma_idesc_bf16(128, HD, 0, 1);
@@ -397,9 +397,10 @@ __global__ void __launch_bounds__(DKV_THREADS, 1) attn_dkv_kernel(const __grid_c
       }
     }
   } else {
-    const int r = warp * 32 + lane;            // key row within the block
+    const int r = (warp & 3) * 32 + lane;      // key row within the block
+    const int half = warp >> 2;                // which 32 of the block's 64 queries this thread covers
     const int kpos = kv0 + r;
-    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
     bool ok = true;
     // After a failed wait a warp keeps walking the steps (doing nothing) so that every warp of the
     // warpgroup meets the same number of named barriers.
@@ -407,7 +408,7 @@ __global__ void __launch_bounds__(DKV_THREADS, 1) attn_dkv_kernel(const __grid_c
       const int u = t & 1;
       const int h = g * rep + t / nqb, i = i0 + t % nqb;
       // lse (in log2 units) and delta of the block's 64 queries, broadcast through shared memory
-      {
+      if (threadIdx.x < 128) {
         const int qi = i * BQ + (threadIdx.x & 63);
         float v = 0.f;
         if (qi < p.S) {
@@ -416,7 +417,7 @@ __global__ void __launch_bounds__(DKV_THREADS, 1) attn_dkv_kernel(const __grid_c
         }
         sStat[u * 128 + threadIdx.x] = v;
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      asm volatile("bar.sync 1, 256;" ::: "memory");
       if (!ok) continue;
       ok = __all_sync(0xffffffffu, mbar_wait(&st_full[u], (t >> 1) & 1, p.err));
       if (!ok) continue;
@@ -431,8 +432,8 @@ __global__ void __launch_bounds__(DKV_THREADS, 1) attn_dkv_kernel(const __grid_c
       const int qb0 = i * BQ;
       // the block's first query lies before the block's last key, or its last query past the sequence
       const bool diag = qb0 < kv0 + 128 || qb0 + BQ > p.S;
-#pragma unroll 1
-      for (int c = 0; c < BQ; c += 32) {
+      {
+        const int c = half * 32;
         uint32_t vs[32], vd[32];
         tmem_ld32(tST[u] + lane_off + c, vs);
         tmem_ld32(tDP[u] + lane_off + c, vd);
@@ -472,7 +473,7 @@ __global__ void __launch_bounds__(DKV_THREADS, 1) attn_dkv_kernel(const __grid_c
         __nv_bfloat16* dk = p.dqkv + (size_t)(row_base + kpos) * p.ld_dqkv + (p.nq + g) * HD;
         __nv_bfloat16* dv = p.dqkv + (size_t)(row_base + kpos) * p.ld_dqkv + (p.nq + p.nkv + g) * HD;
 #pragma unroll 1
-        for (int c = 0; c < HD; c += 32) {
+        for (int c = half * (HD / 2); c < (half + 1) * (HD / 2); c += 32) {
           uint32_t a[32], bq[32];
           tmem_ld32(tDV + lane_off + c, a);
           tmem_ld32(tDK + lane_off + c, bq);
@@ -500,7 +501,7 @@ __global__ void __launch_bounds__(DKV_THREADS, 1) attn_dkv_kernel(const __grid_c
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
