@@ -45,7 +45,7 @@ struct FwdCfg {
 };
 
 template <int HD>
-__global__ void __maxnreg__(192) attn_fwd_kernel(const __grid_constant__ CUtensorMap tm,
+__global__ void __launch_bounds__(F_THREADS, 1) attn_fwd_kernel(const __grid_constant__ CUtensorMap tm,
                                                                 const FwdParams p) {
   using C = FwdCfg<HD>;
   constexpr int BN = C::BN;

@@ -336,19 +336,31 @@ __global__ void embed_fwd_kernel(const long long* __restrict__ ids, const __nv_b
     *reinterpret_cast<uint4*>(out + t * H + c * 8) = *reinterpret_cast<const uint4*>(W + ids[t] * H + c * 8);
   }
 }
-__global__ void embed_bwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ dout,
-                                 float* __restrict__ main_grad, long long T, int H) {
+// Scatter-add of the token gradients into the embedding rows without atomics: the tokens arrive
+// sorted by id (stable, so equal ids keep their position order); the CTA that sits on the first
+// token of a run adds the run's rows in that order and owns the embedding row, the others leave.
+// The sum is the same bits on every run and every rank.
+__global__ void embed_bwd_kernel(const long long* __restrict__ sorted_ids, const long long* __restrict__ perm,
+                                 const __nv_bfloat16* __restrict__ dout, float* __restrict__ main_grad, long long T,
+                                 int H) {
+  const long long p0 = blockIdx.x;
+  const long long id = sorted_ids[p0];
+  if (p0 > 0 && sorted_ids[p0 - 1] == id) return;
   const int hc = H >> 3;
-  const long long total = T * hc;
-  const long long gstride = (long long)gridDim.x * blockDim.x;
-  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += gstride) {
-    const long long t = e / hc;
-    const int c = (int)(e % hc);
-    float f[8];
-    unpack8(*reinterpret_cast<const uint4*>(dout + t * H + c * 8), f);
-    float* g = main_grad + ids[t] * H + c * 8;
+  for (int c = threadIdx.x; c < hc; c += blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (long long q = p0; q < T && sorted_ids[q] == id; ++q) {
+      float f[8];
+      unpack8(*reinterpret_cast<const uint4*>(dout + perm[q] * H + c * 8), f);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) atomicAdd(g + i, f[i]);
+      for (int i = 0; i < 8; ++i) acc[i] += f[i];
+    }
+    float4* g = reinterpret_cast<float4*>(main_grad + id * H + c * 8);
+    float4 g0 = g[0], g1 = g[1];
+    g0.x += acc[0]; g0.y += acc[1]; g0.z += acc[2]; g0.w += acc[3];
+    g1.x += acc[4]; g1.y += acc[5]; g1.z += acc[6]; g1.w += acc[7];
+    g[0] = g0;
+    g[1] = g1;
   }
 }
 
@@ -470,12 +482,14 @@ SGA_API int sga_embed_fwd(const long long* ids, const void* W, void* out, long l
                                                                      (__nv_bfloat16*)out, T, H);
   return LAUNCH_OK();
 }
-SGA_API int sga_embed_bwd(const long long* ids, const void* dout, float* main_grad, long long T, int H,
-                          void* stream) {
+// sorted_ids / perm: the token ids in ascending order (stable) and the position each came from.
+SGA_API int sga_embed_bwd(const long long* sorted_ids, const long long* perm, const void* dout, float* main_grad,
+                          long long T, int H, void* stream) {
   if (T <= 0) return 0;
   if (H & 7) return -5;
-  embed_bwd_kernel<<<grid1d(T * (H / 8), 256), 256, 0, ST(stream)>>>(ids, (const __nv_bfloat16*)dout, main_grad, T,
-                                                                     H);
+  const int threads = H / 8 >= 256 ? 256 : (H / 8 >= 128 ? 128 : 64);
+  embed_bwd_kernel<<<(unsigned)T, threads, 0, ST(stream)>>>(sorted_ids, perm, (const __nv_bfloat16*)dout, main_grad,
+                                                            T, H);
   return LAUNCH_OK();
 }
 SGA_API int sga_add_bf16(const void* a, const void* b, void* out, long long n, void* stream) {

@@ -43,7 +43,7 @@ register_sigs({
     "sga_swiglu_bwd": [_P, _P, _P, _L, _I, _P],
     "sga_cross_entropy": [_P, _P, _P, _L, _I, _L, _F, _I, _P],
     "sga_embed_fwd": [_P, _P, _P, _L, _I, _P],
-    "sga_embed_bwd": [_P, _P, _P, _L, _I, _P],
+    "sga_embed_bwd": [_P, _P, _P, _P, _L, _I, _P],
     "sga_add_bf16": [_P, _P, _P, _L, _P],
     "sga_symm_alloc": [_L, _P],
     "sga_symm_free": [_P],

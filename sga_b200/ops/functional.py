@@ -197,4 +197,7 @@ def embed_bwd(ids, dout, main_grad):
         main_grad.index_add_(0, ids, dout.float())
         return
     T, H = dout.shape
-    _chk(lib().sga_embed_bwd(ids.data_ptr(), dout.data_ptr(), main_grad.data_ptr(), T, H, _st()), "sga_embed_bwd")
+    # stable sort: rows of a repeated token are summed in position order, so the result is reproducible
+    sorted_ids, perm = torch.sort(ids.reshape(-1), stable=True)
+    _chk(lib().sga_embed_bwd(sorted_ids.data_ptr(), perm.data_ptr(), dout.data_ptr(), main_grad.data_ptr(), T, H,
+                             _st()), "sga_embed_bwd")
