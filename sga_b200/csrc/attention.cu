@@ -124,40 +124,42 @@ __global__ void __launch_bounds__(F_THREADS, 1) attn_fwd_kernel(const __grid_con
     if (lane == 0 && n_all > 0) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, BN, 0, 0);
       constexpr uint32_t idesc_o = umma_idesc_bf16(128, HD, 0, 1);
+      const uint64_t dQ0 = desc_k(smem_u32(sQ)), dP0 = desc_k(smem_u32(sP));
+      const uint64_t dK0 = desc_k(smem_u32(sKV)), dV0 = desc_mn(smem_u32(sKV + BN * HD * 2), BN);
+      constexpr uint64_t Q_STEP = (128 * HD * 2) >> 4, P_STEP = C::P_BYTES >> 4, KV_STEP = F_STAGE_BYTES >> 4;
       bool ok = mbar_wait(q_full, 0, p.err) && mbar_wait(&kv_full[0], 0, p.err);
       if (ok) {
         tc_fence_after();
         for (int w = 0; w < 2; ++w)
           if (nw[w] > 0) {
-            mma_over_hd(tS[w], smem_u32(sQ + w * (128 * HD * 2)), 128, smem_u32(sKV), BN, HD, idesc_s);
+            mma_over_hd<HD, 128, BN>(tS[w], dQ0 + w * Q_STEP, dK0, idesc_s);
             umma_commit(&s_full[w]);
           }
       }
+      int st = 0;
       for (int j = 0; j < n_all && ok; ++j) {
-        const int st = j % F_STAGES;
-        const uint32_t sv = smem_u32(sKV + st * F_STAGE_BYTES + BN * HD * 2);
+        const int sn = st + 1 == F_STAGES ? 0 : st + 1;
         bool next_ready = false;
         for (int w = 0; w < 2 && ok; ++w) {
           if (j >= nw[w]) continue;
           ok = mbar_wait(&p_full[w], j & 1, p.err);
           if (!ok) break;
           tc_fence_after();
-          mma_over_rows(tO[w], smem_u32(sP + w * C::P_BYTES), sv, BN, idesc_o, false);
+          mma_over_rows<BN>(tO[w], dP0 + w * P_STEP, dV0 + st * KV_STEP, idesc_o, false);
           umma_commit(&o_full[w]);
           if (j + 1 < nw[w]) {
-            const int sn = (j + 1) % F_STAGES;
             if (!next_ready) {
               ok = mbar_wait(&kv_full[sn], ((j + 1) / F_STAGES) & 1, p.err);
               if (!ok) break;
               tc_fence_after();
               next_ready = true;
             }
-            mma_over_hd(tS[w], smem_u32(sQ + w * (128 * HD * 2)), 128, smem_u32(sKV + sn * F_STAGE_BYTES), BN, HD,
-                        idesc_s);
+            mma_over_hd<HD, 128, BN>(tS[w], dQ0 + w * Q_STEP, dK0 + sn * KV_STEP, idesc_s);
             umma_commit(&s_full[w]);
           }
         }
         if (ok) umma_commit(&kv_empty[st]);
+        st = sn;
       }
     }
   } else {

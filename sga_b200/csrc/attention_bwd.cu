@@ -9,7 +9,7 @@
 //   step 3 (dK/dV)       one CTA per (128 keys, KV head, batch); it walks the query heads of the
 //                        group and their 64-row query blocks from the diagonal down:
 //                        S^T = K Q^T and dP^T = V dO^T into TMEM (double-buffered), threads form
-//                        P^T and dS^T (a key row and 32 queries each; lse and delta of the 64 queries are
+//                        P^T and dS^T (a key row and 16 queries each; lse and delta of the 64 queries are
 //                        broadcast from shared memory), and dV += P^T dO, dK += dS^T Q accumulate
 //                        in TMEM over the whole walk: the sum over the group's query heads
 //                        happens in the accumulator.
@@ -57,7 +57,7 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ dctx, const 
 }
 
 // --------------------------------------------------------------- dQ kernel
-constexpr int DQ_THREADS = 320;
+constexpr int DQ_THREADS = 576;  // 16 softmax warps (two threads per query row) + TMA warp + MMA warp
 constexpr int DQ_BN = 64;
 
 template <int HD>
@@ -113,14 +113,14 @@ __global__ void __launch_bounds__(DQ_THREADS, 1) attn_dq_kernel(const __grid_con
     }
     for (int w = 0; w < 2; ++w) {
       mbar_init(&sd_full[w], 1);
-      mbar_init(&ds_full[w], 128);
+      mbar_init(&ds_full[w], 256);
       mbar_init(&dq_done[w], 1);
     }
     mbar_fence_init();
     tma_prefetch_desc(&tmQKV);
     tma_prefetch_desc(&tmDO);
   }
-  if (warp == 9) {
+  if (warp == 17) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
@@ -132,7 +132,7 @@ __global__ void __launch_bounds__(DQ_THREADS, 1) attn_dq_kernel(const __grid_con
   const uint32_t tW[2] = {tmem_base, tmem_base + 256};
   const int row_base = b * p.S;
 
-  if (warp == 8) {
+  if (warp == 16) {
     if (lane == 0 && n_all > 0) {
       mbar_expect_tx(q_full, C::QDO_BYTES);
       for (int w = 0; w < 2; ++w) {
@@ -149,14 +149,17 @@ __global__ void __launch_bounds__(DQ_THREADS, 1) attn_dq_kernel(const __grid_con
       }
       if (sga_aborted(p.err)) __nanosleep(200000);
     }
-  } else if (warp == 9) {
+  } else if (warp == 17) {
     if (lane == 0 && n_all > 0) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, BN, 0, 0);
       constexpr uint32_t idesc_q = umma_idesc_bf16(128, HD, 0, 1);
+      const uint64_t dQ0 = desc_k(smem_u32(sQ)), dDO0 = desc_k(smem_u32(sDO)), dDS0 = desc_k(smem_u32(sDS));
+      const uint64_t dK0 = desc_k(smem_u32(sKV)), dV0 = desc_k(smem_u32(sKV + BN * HD * 2));
+      const uint64_t dKmn0 = desc_mn(smem_u32(sKV), BN);
+      constexpr uint64_t T_STEP = TILE >> 4, DS_STEP = C::DS_BYTES >> 4, KV_STEP = C::STAGE_BYTES >> 4;
       auto scores = [&](int w, int st) {
-        const uint32_t sk = smem_u32(sKV + st * C::STAGE_BYTES);
-        mma_over_hd(tW[w], smem_u32(sQ + w * TILE), 128, sk, BN, HD, idesc_s);
-        mma_over_hd(tW[w] + 64, smem_u32(sDO + w * TILE), 128, sk + BN * HD * 2, BN, HD, idesc_s);
+        mma_over_hd<HD, 128, BN>(tW[w], dQ0 + w * T_STEP, dK0 + st * KV_STEP, idesc_s);
+        mma_over_hd<HD, 128, BN>(tW[w] + 64, dDO0 + w * T_STEP, dV0 + st * KV_STEP, idesc_s);
         umma_commit(&sd_full[w]);
       };
       bool ok = mbar_wait(q_full, 0, p.err) && mbar_wait(&kv_full[0], 0, p.err);
@@ -173,8 +176,7 @@ __global__ void __launch_bounds__(DQ_THREADS, 1) attn_dq_kernel(const __grid_con
           ok = mbar_wait(&ds_full[w], j & 1, p.err);
           if (!ok) break;
           tc_fence_after();
-          mma_over_rows(tW[w] + 128, smem_u32(sDS + w * C::DS_BYTES), smem_u32(sKV + st * C::STAGE_BYTES), BN,
-                        idesc_q, j > 0);
+          mma_over_rows<BN>(tW[w] + 128, dDS0 + w * DS_STEP, dKmn0 + st * KV_STEP, idesc_q, j > 0);
           umma_commit(&dq_done[w]);
           if (j + 1 < nw[w]) {
             const int sn = (j + 1) % C::STAGES;
@@ -191,7 +193,8 @@ __global__ void __launch_bounds__(DQ_THREADS, 1) attn_dq_kernel(const __grid_con
       }
     }
   } else {
-    const int w = warp >> 2;
+    const int w = warp >> 3;                   // query sub-block
+    const int half = (warp >> 2) & 1;          // which 32 of the block's 64 keys this thread covers
     const int r = (warp & 3) * 32 + lane;
     const int qrow = q0 + 128 * w + r;
     const bool live = qrow < p.S;
@@ -208,13 +211,8 @@ __global__ void __launch_bounds__(DQ_THREADS, 1) attn_dq_kernel(const __grid_con
       const int kv0 = j * BN;
       // some key of the block lies past some row of the sub-block, or the sub-block has rows past the sequence
       const bool diag = kv0 + BN - 1 > q0 + 128 * w || q0 + 128 * w + 127 >= p.S;
-      // the dS tile is free once the previous block's dQ product has read it
-      if (j > 0) {
-        ok = __all_sync(0xffffffffu, mbar_wait(&dq_done[w], (j - 1) & 1, p.err));
-        if (!ok) break;
-      }
-#pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
+      {
+        const int c = half * 32;
         uint32_t vs[32], vd[32];
         tmem_ld32(tW[w] + lane_off + c, vs);
         tmem_ld32(tW[w] + 64 + lane_off + c, vd);
@@ -232,6 +230,11 @@ __global__ void __launch_bounds__(DQ_THREADS, 1) attn_dq_kernel(const __grid_con
           for (int i = 0; i < 32; ++i)
             ds[i] = exp2f(fmaf(__uint_as_float(vs[i]), p.scale_log2, -lse2)) * (__uint_as_float(vd[i]) - dlt);
         }
+        // the dS tile is free once the previous block's dQ product has read it
+        if (j > 0) {
+          ok = __all_sync(0xffffffffu, mbar_wait(&dq_done[w], (j - 1) & 1, p.err));
+          if (!ok) break;
+        }
         store_p32(myDS, r, c, ds);
       }
       tc_fence_before();
@@ -244,7 +247,7 @@ __global__ void __launch_bounds__(DQ_THREADS, 1) attn_dq_kernel(const __grid_con
         tc_fence_after();
         __nv_bfloat16* dst = p.dqkv + (size_t)(row_base + qrow) * p.ld_dqkv + h * HD;
 #pragma unroll 1
-        for (int c = 0; c < HD; c += 32) {
+        for (int c = half * (HD / 2); c < (half + 1) * (HD / 2); c += 32) {
           uint32_t v[32];
           tmem_ld32(tW[w] + 128 + lane_off + c, v);
           tmem_ld_wait();
@@ -267,14 +270,14 @@ __global__ void __launch_bounds__(DQ_THREADS, 1) attn_dq_kernel(const __grid_con
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == 17) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
 }
 
 // ------------------------------------------------------------ dK/dV kernel
-constexpr int DKV_THREADS = 320;  // two warpgroups (each key row is shared by two threads: 32 queries each) + TMA warp + MMA warp
+constexpr int DKV_THREADS = 576;  // 16 softmax warps (four threads per key row: 16 queries each) + TMA warp + MMA warp
 constexpr int DKV_BQ = 64;
 
 template <int HD>
@@ -283,7 +286,7 @@ struct DkvCfg {
   static constexpr int KV_BYTES = 2 * 128 * HD * 2;         // K and V of the block
   static constexpr int STAGE_BYTES = 2 * DKV_BQ * HD * 2;   // Q block + dO block
   static constexpr int PT_BYTES = 128 * DKV_BQ * 2;         // P^T (or dS^T) tile
-  static constexpr int SMEM = KV_BYTES + STAGES * STAGE_BYTES + 4 * PT_BYTES + 1024 + 1024;
+  static constexpr int SMEM = KV_BYTES + STAGES * STAGE_BYTES + 4 * PT_BYTES + 2048 + 1024;
 };
 
 template <int HD>
@@ -299,8 +302,8 @@ __global__ void __launch_bounds__(DKV_THREADS, 1) attn_dkv_kernel(const __grid_c
   uint8_t* sQD = sK + C::KV_BYTES;                       // [stage]{Q [HD/64][64][128 B], dO the same}
   uint8_t* sPT = sQD + C::STAGES * C::STAGE_BYTES;       // [2] P^T tiles, then [2] dS^T tiles
   uint8_t* sDS = sPT + 2 * C::PT_BYTES;
-  float* sStat = reinterpret_cast<float*>(sDS + 2 * C::PT_BYTES);  // [2]{lse2[64], delta[64]}
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sStat + 256);
+  float* sStat = reinterpret_cast<float*>(sDS + 2 * C::PT_BYTES);  // [set][2]{lse2[64], delta[64]}
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sStat + 512);
   uint64_t* kv_full = bars;
   uint64_t* qd_full = bars + 1;
   uint64_t* qd_empty = qd_full + C::STAGES;
@@ -327,14 +330,14 @@ __global__ void __launch_bounds__(DKV_THREADS, 1) attn_dkv_kernel(const __grid_c
     }
     for (int u = 0; u < 2; ++u) {
       mbar_init(&st_full[u], 1);
-      mbar_init(&pt_full[u], 256);
+      mbar_init(&pt_full[u], 512);
       mbar_init(&acc_done[u], 1);
     }
     mbar_fence_init();
     tma_prefetch_desc(&tmQKV);
     tma_prefetch_desc(&tmDO);
   }
-  if (warp == 9) {
+  if (warp == 17) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
@@ -347,7 +350,7 @@ __global__ void __launch_bounds__(DKV_THREADS, 1) attn_dkv_kernel(const __grid_c
   const uint32_t tDP[2] = {tmem_base + 128, tmem_base + 192};
   const uint32_t tDV = tmem_base + 256, tDK = tmem_base + 384;
 
-  if (warp == 8) {
+  if (warp == 16) {
     if (lane == 0 && nt > 0) {
       mbar_expect_tx(kv_full, C::KV_BYTES);
       load_tile(sK, &tmQKV, kv_full, (p.nq + g) * HD, row_base + kv0, 128, HD);
@@ -363,17 +366,21 @@ __global__ void __launch_bounds__(DKV_THREADS, 1) attn_dkv_kernel(const __grid_c
       }
       if (sga_aborted(p.err)) __nanosleep(200000);
     }
-  } else if (warp == 9) {
+  } else if (warp == 17) {
     if (lane == 0 && nt > 0) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, BQ, 0, 0);
       constexpr uint32_t idesc_a = umma_idesc_bf16(128, HD, 0, 1);
+      const uint64_t dKk = desc_k(smem_u32(sK)), dVk = desc_k(smem_u32(sV));
+      const uint64_t dQk0 = desc_k(smem_u32(sQD)), dDOk0 = desc_k(smem_u32(sQD + BQ * HD * 2));
+      const uint64_t dQmn0 = desc_mn(smem_u32(sQD), BQ), dDOmn0 = desc_mn(smem_u32(sQD + BQ * HD * 2), BQ);
+      const uint64_t dPT0 = desc_k(smem_u32(sPT)), dDS0 = desc_k(smem_u32(sDS));
+      constexpr uint64_t ST_STEP = C::STAGE_BYTES >> 4, PT_STEP = C::PT_BYTES >> 4;
       auto scores = [&](int t) -> bool {
         const int st = t % C::STAGES, u = t & 1;
         if (!mbar_wait(&qd_full[st], (t / C::STAGES) & 1, p.err)) return false;
         tc_fence_after();
-        const uint32_t sq = smem_u32(sQD + st * C::STAGE_BYTES);
-        mma_over_hd(tST[u], smem_u32(sK), 128, sq, BQ, HD, idesc_s);
-        mma_over_hd(tDP[u], smem_u32(sV), 128, sq + BQ * HD * 2, BQ, HD, idesc_s);
+        mma_over_hd<HD, 128, BQ>(tST[u], dKk, dQk0 + st * ST_STEP, idesc_s);
+        mma_over_hd<HD, 128, BQ>(tDP[u], dVk, dDOk0 + st * ST_STEP, idesc_s);
         umma_commit(&st_full[u]);
         return true;
       };
@@ -388,80 +395,88 @@ __global__ void __launch_bounds__(DKV_THREADS, 1) attn_dkv_kernel(const __grid_c
         ok = mbar_wait(&pt_full[u], (t >> 1) & 1, p.err);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t sq = smem_u32(sQD + st * C::STAGE_BYTES);
-        mma_over_rows(tDV, smem_u32(sPT + u * C::PT_BYTES), sq + BQ * HD * 2, BQ, idesc_a, t > 0);
-        mma_over_rows(tDK, smem_u32(sDS + u * C::PT_BYTES), sq, BQ, idesc_a, t > 0);
+        mma_over_rows<BQ>(tDV, dPT0 + u * PT_STEP, dDOmn0 + st * ST_STEP, idesc_a, t > 0);
+        mma_over_rows<BQ>(tDK, dDS0 + u * PT_STEP, dQmn0 + st * ST_STEP, idesc_a, t > 0);
         umma_commit(&acc_done[u]);
         umma_commit(&qd_empty[st]);
         if (t + 2 < nt) ok = scores(t + 2);
       }
     }
   } else {
+    // Sixteen warps share a step: a key row belongs to four threads, 16 queries each.
     const int r = (warp & 3) * 32 + lane;      // key row within the block
-    const int half = warp >> 2;                // which 32 of the block's 64 queries this thread covers
+    const int quarter = warp >> 2;
     const int kpos = kv0 + r;
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
     bool ok = true;
-    // After a failed wait a warp keeps walking the steps (doing nothing) so that every warp of the
-    // warpgroup meets the same number of named barriers.
+    // lse (in log2 units) and delta of a step's 64 queries go through shared memory (threads 0..127 load
+    // them one step ahead, so the global latency is off the step's critical path)
+    auto load_stat = [&](int t) -> float {
+      const int h = g * rep + t / nqb, i = i0 + t % nqb;
+      const int qi = i * BQ + (threadIdx.x & 63);
+      if (t >= nt || qi >= p.S) return 0.f;
+      const size_t at = ((size_t)b * p.nq + h) * p.S + qi;
+      return threadIdx.x < 64 ? p.lse[at] * 1.4426950408889634f : p.delta[at];
+    };
+    if (threadIdx.x < 128) sStat[threadIdx.x] = load_stat(0);
+    // After a failed wait a warp keeps walking the steps (doing nothing) so that every warp meets the
+    // same number of named barriers.
     for (int t = 0; t < nt; ++t) {
       const int u = t & 1;
-      const int h = g * rep + t / nqb, i = i0 + t % nqb;
-      // lse (in log2 units) and delta of the block's 64 queries, broadcast through shared memory
-      if (threadIdx.x < 128) {
-        const int qi = i * BQ + (threadIdx.x & 63);
-        float v = 0.f;
-        if (qi < p.S) {
-          const size_t at = ((size_t)b * p.nq + h) * p.S + qi;
-          v = threadIdx.x < 64 ? p.lse[at] * 1.4426950408889634f : p.delta[at];
+      const int i = i0 + t % nqb;
+      asm volatile("bar.sync 1, 512;" ::: "memory");
+      // everyone has left step t - 1, whose statistics lived in the other buffer: refill it for step t + 1
+      float nxt = 0.f;
+      if (threadIdx.x < 128) nxt = load_stat(t + 1);
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&st_full[u], (t >> 1) & 1, p.err));
+      if (ok) {
+        tc_fence_after();
+        const int qb0 = i * BQ;
+        const int c = quarter * 16;
+        const float4* l4 = reinterpret_cast<const float4*>(sStat + u * 128 + c);
+        const float4* d4 = reinterpret_cast<const float4*>(sStat + u * 128 + 64 + c);
+        // the block's first query lies before the block's last key, or its last query past the sequence
+        const bool diag = qb0 < kv0 + 128 || qb0 + BQ > p.S;
+        uint32_t vs[16], vd[16];
+        tmem_ld16(tST[u] + lane_off + c, vs);
+        tmem_ld16(tDP[u] + lane_off + c, vd);
+        float l2[16], dl[16];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float4 a = l4[k], d = d4[k];
+          l2[4 * k] = a.x; l2[4 * k + 1] = a.y; l2[4 * k + 2] = a.z; l2[4 * k + 3] = a.w;
+          dl[4 * k] = d.x; dl[4 * k + 1] = d.y; dl[4 * k + 2] = d.z; dl[4 * k + 3] = d.w;
         }
-        sStat[u * 128 + threadIdx.x] = v;
-      }
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      if (!ok) continue;
-      ok = __all_sync(0xffffffffu, mbar_wait(&st_full[u], (t >> 1) & 1, p.err));
-      if (!ok) continue;
-      tc_fence_after();
-      // the tiles of buffer u are free once the products of step t - 2 have read them
-      if (t >= 2) {
-        ok = __all_sync(0xffffffffu, mbar_wait(&acc_done[u], ((t - 2) >> 1) & 1, p.err));
-        if (!ok) continue;
-      }
-      const float* l2 = sStat + u * 128;
-      const float* dl = l2 + 64;
-      const int qb0 = i * BQ;
-      // the block's first query lies before the block's last key, or its last query past the sequence
-      const bool diag = qb0 < kv0 + 128 || qb0 + BQ > p.S;
-      {
-        const int c = half * 32;
-        uint32_t vs[32], vd[32];
-        tmem_ld32(tST[u] + lane_off + c, vs);
-        tmem_ld32(tDP[u] + lane_off + c, vd);
         tmem_ld_wait();
-        float pt[32], ds[32];
+        float pt[16], ds[16];
         if (diag) {
 #pragma unroll
-          for (int k = 0; k < 32; ++k) {
+          for (int k = 0; k < 16; ++k) {
             const int qpos = qb0 + c + k;
             const bool keep = qpos >= kpos && qpos < p.S;
-            const float pr = keep ? exp2f(fmaf(__uint_as_float(vs[k]), p.scale_log2, -l2[c + k])) : 0.f;
+            const float pr = keep ? exp2f(fmaf(__uint_as_float(vs[k]), p.scale_log2, -l2[k])) : 0.f;
             pt[k] = pr;
-            ds[k] = keep ? pr * (__uint_as_float(vd[k]) - dl[c + k]) : 0.f;
+            ds[k] = keep ? pr * (__uint_as_float(vd[k]) - dl[k]) : 0.f;
           }
         } else {
 #pragma unroll
-          for (int k = 0; k < 32; ++k) {
-            const float pr = exp2f(fmaf(__uint_as_float(vs[k]), p.scale_log2, -l2[c + k]));
+          for (int k = 0; k < 16; ++k) {
+            const float pr = exp2f(fmaf(__uint_as_float(vs[k]), p.scale_log2, -l2[k]));
             pt[k] = pr;
-            ds[k] = pr * (__uint_as_float(vd[k]) - dl[c + k]);
+            ds[k] = pr * (__uint_as_float(vd[k]) - dl[k]);
           }
         }
-        store_p32(sPT + u * C::PT_BYTES, r, c, pt);
-        store_p32(sDS + u * C::PT_BYTES, r, c, ds);
+        // the tiles of buffer u are free once the products of step t - 2 have read them
+        if (t >= 2) ok = __all_sync(0xffffffffu, mbar_wait(&acc_done[u], ((t - 2) >> 1) & 1, p.err));
+        if (ok) {
+          store_p16(sPT + u * C::PT_BYTES, r, c, pt);
+          store_p16(sDS + u * C::PT_BYTES, r, c, ds);
+          tc_fence_before();
+          fence_proxy_async_smem();
+          mbar_arrive(&pt_full[u]);
+        }
       }
-      tc_fence_before();
-      fence_proxy_async_smem();
-      mbar_arrive(&pt_full[u]);
+      if (threadIdx.x < 128) sStat[(u ^ 1) * 128 + threadIdx.x] = nxt;
     }
     if (ok && nt > 0) {
       // the last commit covers every earlier product
@@ -473,14 +488,14 @@ __global__ void __launch_bounds__(DKV_THREADS, 1) attn_dkv_kernel(const __grid_c
         __nv_bfloat16* dk = p.dqkv + (size_t)(row_base + kpos) * p.ld_dqkv + (p.nq + g) * HD;
         __nv_bfloat16* dv = p.dqkv + (size_t)(row_base + kpos) * p.ld_dqkv + (p.nq + p.nkv + g) * HD;
 #pragma unroll 1
-        for (int c = half * (HD / 2); c < (half + 1) * (HD / 2); c += 32) {
-          uint32_t a[32], bq[32];
-          tmem_ld32(tDV + lane_off + c, a);
-          tmem_ld32(tDK + lane_off + c, bq);
+        for (int c = quarter * (HD / 4); c < (quarter + 1) * (HD / 4); c += 16) {
+          uint32_t a[16], bq[16];
+          tmem_ld16(tDV + lane_off + c, a);
+          tmem_ld16(tDK + lane_off + c, bq);
           tmem_ld_wait();
           if (live) {
 #pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
+            for (int q4 = 0; q4 < 2; ++q4) {
               uint4 u1, u2;
               __nv_bfloat162* b1 = reinterpret_cast<__nv_bfloat162*>(&u1);
               __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&u2);
@@ -501,7 +516,7 @@ __global__ void __launch_bounds__(DKV_THREADS, 1) attn_dkv_kernel(const __grid_c
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == 17) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
