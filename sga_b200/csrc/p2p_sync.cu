@@ -297,6 +297,7 @@ __device__ __forceinline__ void find_bin(const unsigned* hist, int nb, long long
 __global__ void __launch_bounds__(IS_THREADS, 1) bucket_index_sync_kernel(const IndexSyncArgs a) {
   extern __shared__ unsigned sh_hist[];  // 32769 counters
   __shared__ int warp_tot[32];
+  __shared__ int tile_cnt[64];
   __shared__ int sh_i[4];
   __shared__ float red[IS_THREADS];
   const PeerCtx& c = a.c;
@@ -337,12 +338,26 @@ __global__ void __launch_bounds__(IS_THREADS, 1) bucket_index_sync_kernel(const 
   int bin;
   long long above;
   find_bin(a.hist1, 32769, a.k, sh_i, bin, above, warp_tot);
-  for (long long i = r0 + (long long)threadIdx.x * 4; i < r1; i += IS_TILE) {
-    const int lim = (int)min((long long)4, a.n - i);
-    for (int j = 0; j < lim; ++j) {
-      const uint32_t key = key_of(a.acc[i + j]);
-      if ((int)(key >> 16) == bin) atomicAdd(&a.hist2[key & 0xFFFFu], 1u);
+  for (long long i = r0 + (long long)threadIdx.x * 4; i < r1; i += 2 * IS_TILE) {
+    // two tiles per trip: both loads are in flight before either is used
+    float v[8];
+    int lim[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const long long ii = i + (long long)h * IS_TILE;
+      lim[h] = ii < r1 ? (int)min((long long)4, a.n - ii) : 0;
+      if (lim[h] == 4) {
+        *reinterpret_cast<float4*>(v + 4 * h) = *reinterpret_cast<const float4*>(a.acc + ii);
+      } else {
+        for (int j = 0; j < lim[h]; ++j) v[4 * h + j] = a.acc[ii + j];
+      }
     }
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+      for (int j = 0; j < lim[h]; ++j) {
+        const uint32_t key = key_of(v[4 * h + j]);
+        if ((int)(key >> 16) == bin) atomicAdd(&a.hist2[key & 0xFFFFu], 1u);
+      }
   }
   __threadfence();
   grid_barrier(c.grid_counter, gen, c.err);
@@ -355,13 +370,26 @@ __global__ void __launch_bounds__(IS_THREADS, 1) bucket_index_sync_kernel(const 
   const long long n_gt = above + above2;           // keys strictly greater than T
   const int need = (int)((long long)a.k - n_gt);   // ties (key == T) to take, in index order
   int my_gt = 0, my_eq = 0;
-  for (long long i = r0 + (long long)threadIdx.x * 4; i < r1; i += IS_TILE) {
-    const int lim = (int)min((long long)4, a.n - i);
-    for (int j = 0; j < lim; ++j) {
-      const uint32_t key = key_of(a.acc[i + j]);
-      my_gt += key > T;
-      my_eq += key == T;
+  for (long long i = r0 + (long long)threadIdx.x * 4; i < r1; i += 2 * IS_TILE) {
+    float v[8];
+    int lim[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const long long ii = i + (long long)h * IS_TILE;
+      lim[h] = ii < r1 ? (int)min((long long)4, a.n - ii) : 0;
+      if (lim[h] == 4) {
+        *reinterpret_cast<float4*>(v + 4 * h) = *reinterpret_cast<const float4*>(a.acc + ii);
+      } else {
+        for (int j = 0; j < lim[h]; ++j) v[4 * h + j] = a.acc[ii + j];
+      }
     }
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+      for (int j = 0; j < lim[h]; ++j) {
+        const uint32_t key = key_of(v[4 * h + j]);
+        my_gt += key > T;
+        my_eq += key == T;
+      }
   }
   {
     int tot;
@@ -400,10 +428,47 @@ __global__ void __launch_bounds__(IS_THREADS, 1) bucket_index_sync_kernel(const 
       else for (int j = 0; j < lim; ++j) v[j] = a.acc[i + j];
       for (int j = 0; j < lim; ++j) key[j] = key_of(v[j]);
     }
-    int eqc = 0;
-    for (int j = 0; j < lim; ++j) eqc += key[j] == T;
-    int eq_tot;
-    const int eq_pre = block_excl_scan(eqc, warp_tot, eq_tot);
+    // Ordered positions with one barrier per tile: a packed (greater | ties << 16) count is scanned
+    // inside each warp, the warp totals go through shared memory (double-buffered by tile parity), and
+    // every warp derives from the 32 totals where its own ties and its own selections start.
+    int gtc = 0, eqc = 0;
+    for (int j = 0; j < lim; ++j) {
+      gtc += key[j] > T;
+      eqc += key[j] == T;
+    }
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int packed = gtc | (eqc << 16);
+    int incl = packed;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int y = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += y;
+    }
+    int* wcnt = tile_cnt + (((t0 - r0) / IS_TILE) & 1) * 32;
+    if (lane == 31) wcnt[wid] = incl;
+    __syncthreads();
+    const int wp = wcnt[lane];                 // lane l looks at warp l's totals
+    const int g_l = wp & 0xFFFF, e_l = wp >> 16;
+    int e_incl = e_l;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int y = __shfl_up_sync(0xffffffffu, e_incl, o);
+      if (lane >= o) e_incl += y;
+    }
+    const long long ties_before_l = tie_base + (e_incl - e_l);
+    const int take_l = (int)max(0LL, min((long long)e_l, (long long)need - ties_before_l));
+    const int s_l = g_l + take_l;              // selections of warp l in this tile
+    int s_incl = s_l;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int y = __shfl_up_sync(0xffffffffu, s_incl, o);
+      if (lane >= o) s_incl += y;
+    }
+    const int eq_tot = __shfl_sync(0xffffffffu, e_incl, 31);
+    const int sel_tot = __shfl_sync(0xffffffffu, s_incl, 31);
+    const int warp_tie0 = __shfl_sync(0xffffffffu, e_incl - e_l, wid);   // ties of the tile before my warp
+    const int warp_sel0 = __shfl_sync(0xffffffffu, s_incl - s_l, wid);   // selections of the tile before my warp
+    const int eq_pre = warp_tie0 + ((incl - packed) >> 16);               // ties of the tile before my elements
     int selc = 0;
     uint32_t selbits = 0;
     {
@@ -414,8 +479,13 @@ __global__ void __launch_bounds__(IS_THREADS, 1) bucket_index_sync_kernel(const 
         if (s) { selbits |= 1u << j; ++selc; }
       }
     }
-    int sel_tot;
-    const int sel_pre = block_excl_scan(selc, warp_tot, sel_tot);
+    int sc_incl = selc;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int y = __shfl_up_sync(0xffffffffu, sc_incl, o);
+      if (lane >= o) sc_incl += y;
+    }
+    const int sel_pre = warp_sel0 + sc_incl - selc;
     if (a.mode == 1) {
       // compose the 32-bit mask word from 8 consecutive lanes' nibbles
       uint32_t word = selbits << ((threadIdx.x & 7) * 4);
