@@ -201,6 +201,7 @@ def bench_attention(small):
 
     dev = "cuda"
     cases = [(4, 2048, 32, 8, 64)] if small else [(4, 2048, 32, 8, 64), (2, 4096, 16, 8, 128), (1, 4096, 32, 8, 128)]
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)  # the operands fit in L2: flush it
     for B, S, nq, nkv, hd in cases:
         T = B * S
         qkv = torch.randn(T, (nq + 2 * nkv) * hd, device=dev).to(torch.bfloat16)
@@ -210,9 +211,10 @@ def bench_attention(small):
             A._IMPL = impl
             ctx, saved = A.attn_fwd(qkv, B, S, nq, nkv, hd)
             it = 2 if small else 10
-            ms_f = timed(lambda: A.attn_fwd(qkv, B, S, nq, nkv, hd), it, warmup=1 if small else 3)
+            ms_f = timed(lambda: A.attn_fwd(qkv, B, S, nq, nkv, hd), it, warmup=1 if small else 3, flush=flush)
             dq = torch.empty_like(qkv)
-            ms_b = timed(lambda: A.attn_bwd(dctx, qkv, saved, B, S, nq, nkv, hd, dq), it, warmup=1 if small else 3)
+            ms_b = timed(lambda: A.attn_bwd(dctx, qkv, saved, B, S, nq, nkv, hd, dq), it, warmup=1 if small else 3,
+                         flush=flush)
             name = "attn_fwd_kernel" if impl == "native" else "library flash fwd (reference point)"
             emit(name, f"B={B} S={S} heads={nq}:{nkv} hd={hd} causal", ms_f, flops=fl_f)
             name = "attn_dq+dkv kernels" if impl == "native" else "library flash bwd (reference point)"
