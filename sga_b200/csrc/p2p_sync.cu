@@ -235,6 +235,25 @@ struct IndexSyncArgs {
 
 __device__ __forceinline__ uint32_t key_of(float x) { return __float_as_uint(x) & 0x7FFFFFFFu; }
 
+// Four consecutive values from element i (a multiple of 4); returns how many lie inside [0, limit)
+// (0 when i is past it). Entries past the end are left at zero and must be ignored by the caller.
+__device__ __forceinline__ int load4(const float* __restrict__ acc, long long i, long long limit, float (&v)[4]) {
+  if (i + 4 <= limit) {
+    *reinterpret_cast<float4*>(v) = *reinterpret_cast<const float4*>(acc + i);
+    return 4;
+  }
+  int lim = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    v[j] = 0.f;
+    if (i + j < limit) {
+      v[j] = acc[i + j];
+      lim = j + 1;
+    }
+  }
+  return lim;
+}
+
 // Block-wide exclusive scan of one int per thread (1024 threads); returns the
 // exclusive prefix, total in `total` (same for all threads).
 __device__ __forceinline__ int block_excl_scan(int v, int* warp_tot, int& total) {
@@ -315,16 +334,18 @@ __global__ void __launch_bounds__(IS_THREADS, 1) bucket_index_sync_kernel(const 
     for (long long w = (r0 >> 5) + threadIdx.x; w < ((r1 + 31) >> 5); w += IS_THREADS) a.touched[w] = 0;
   }
   __syncthreads();
-  for (long long i = r0 + (long long)threadIdx.x * 4; i < r1; i += IS_TILE) {
-    if (i + 4 <= a.n) {
-      const float4 v = *reinterpret_cast<const float4*>(a.acc + i);
-      atomicAdd(&sh_hist[key_of(v.x) >> 16], 1u);
-      atomicAdd(&sh_hist[key_of(v.y) >> 16], 1u);
-      atomicAdd(&sh_hist[key_of(v.z) >> 16], 1u);
-      atomicAdd(&sh_hist[key_of(v.w) >> 16], 1u);
-    } else {
-      for (long long j = i; j < a.n; ++j) atomicAdd(&sh_hist[key_of(a.acc[j]) >> 16], 1u);
-    }
+  const long long lim_all = min(a.n, r1);
+  for (long long i = r0 + (long long)threadIdx.x * 4; i < r1; i += 2 * IS_TILE) {
+    // two tiles per trip: both loads are in flight before either is used
+    float v0[4], v1[4];
+    const int l0 = load4(a.acc, i, lim_all, v0);
+    const int l1 = load4(a.acc, i + IS_TILE, lim_all, v1);
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (j < l0) atomicAdd(&sh_hist[key_of(v0[j]) >> 16], 1u);
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (j < l1) atomicAdd(&sh_hist[key_of(v1[j]) >> 16], 1u);
   }
   __syncthreads();
   for (int i = threadIdx.x; i < 32769; i += IS_THREADS) {
@@ -339,25 +360,15 @@ __global__ void __launch_bounds__(IS_THREADS, 1) bucket_index_sync_kernel(const 
   long long above;
   find_bin(a.hist1, 32769, a.k, sh_i, bin, above, warp_tot);
   for (long long i = r0 + (long long)threadIdx.x * 4; i < r1; i += 2 * IS_TILE) {
-    // two tiles per trip: both loads are in flight before either is used
-    float v[8];
-    int lim[2];
+    float v0[4], v1[4];
+    const int l0 = load4(a.acc, i, lim_all, v0);
+    const int l1 = load4(a.acc, i + IS_TILE, lim_all, v1);
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const long long ii = i + (long long)h * IS_TILE;
-      lim[h] = ii < r1 ? (int)min((long long)4, a.n - ii) : 0;
-      if (lim[h] == 4) {
-        *reinterpret_cast<float4*>(v + 4 * h) = *reinterpret_cast<const float4*>(a.acc + ii);
-      } else {
-        for (int j = 0; j < lim[h]; ++j) v[4 * h + j] = a.acc[ii + j];
-      }
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t k0 = key_of(v0[j]), k1 = key_of(v1[j]);
+      if (j < l0 && (int)(k0 >> 16) == bin) atomicAdd(&a.hist2[k0 & 0xFFFFu], 1u);
+      if (j < l1 && (int)(k1 >> 16) == bin) atomicAdd(&a.hist2[k1 & 0xFFFFu], 1u);
     }
-#pragma unroll
-    for (int h = 0; h < 2; ++h)
-      for (int j = 0; j < lim[h]; ++j) {
-        const uint32_t key = key_of(v[4 * h + j]);
-        if ((int)(key >> 16) == bin) atomicAdd(&a.hist2[key & 0xFFFFu], 1u);
-      }
   }
   __threadfence();
   grid_barrier(c.grid_counter, gen, c.err);
@@ -371,25 +382,15 @@ __global__ void __launch_bounds__(IS_THREADS, 1) bucket_index_sync_kernel(const 
   const int need = (int)((long long)a.k - n_gt);   // ties (key == T) to take, in index order
   int my_gt = 0, my_eq = 0;
   for (long long i = r0 + (long long)threadIdx.x * 4; i < r1; i += 2 * IS_TILE) {
-    float v[8];
-    int lim[2];
+    float v0[4], v1[4];
+    const int l0 = load4(a.acc, i, lim_all, v0);
+    const int l1 = load4(a.acc, i + IS_TILE, lim_all, v1);
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const long long ii = i + (long long)h * IS_TILE;
-      lim[h] = ii < r1 ? (int)min((long long)4, a.n - ii) : 0;
-      if (lim[h] == 4) {
-        *reinterpret_cast<float4*>(v + 4 * h) = *reinterpret_cast<const float4*>(a.acc + ii);
-      } else {
-        for (int j = 0; j < lim[h]; ++j) v[4 * h + j] = a.acc[ii + j];
-      }
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t k0 = key_of(v0[j]), k1 = key_of(v1[j]);
+      my_gt += (j < l0 && k0 > T) + (j < l1 && k1 > T);
+      my_eq += (j < l0 && k0 == T) + (j < l1 && k1 == T);
     }
-#pragma unroll
-    for (int h = 0; h < 2; ++h)
-      for (int j = 0; j < lim[h]; ++j) {
-        const uint32_t key = key_of(v[4 * h + j]);
-        my_gt += key > T;
-        my_eq += key == T;
-      }
   }
   {
     int tot;
@@ -417,24 +418,28 @@ __global__ void __launch_bounds__(IS_THREADS, 1) bucket_index_sync_kernel(const 
   long long out_base = gt_before + min((long long)need, eq_before);
   long long tie_base = eq_before;
   if (a.mode == 0 && c.prev_seq > 0) peer_wait(c, 1, c.prev_seq);  // peers finished reading my previous payload
+  float nv[4];
+  int nlim = load4(a.acc, r0 + (long long)threadIdx.x * 4, lim_all, nv);
   for (long long t0 = r0; t0 < r1; t0 += IS_TILE) {
     const long long i = t0 + (long long)threadIdx.x * 4;
-    float v[4] = {0.f, 0.f, 0.f, 0.f};
-    uint32_t key[4] = {0, 0, 0, 0};
-    int lim = 0;
-    if (i < a.n) {
-      lim = (int)min((long long)4, a.n - i);
-      if (lim == 4) *reinterpret_cast<float4*>(v) = *reinterpret_cast<const float4*>(a.acc + i);
-      else for (int j = 0; j < lim; ++j) v[j] = a.acc[i + j];
-      for (int j = 0; j < lim; ++j) key[j] = key_of(v[j]);
+    float v[4];
+    uint32_t key[4];
+    const int lim = nlim;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      v[j] = nv[j];
+      key[j] = key_of(v[j]);
     }
+    // the next tile's values are on their way while this one is scanned
+    nlim = load4(a.acc, i + IS_TILE, lim_all, nv);
     // Ordered positions with one barrier per tile: a packed (greater | ties << 16) count is scanned
     // inside each warp, the warp totals go through shared memory (double-buffered by tile parity), and
     // every warp derives from the 32 totals where its own ties and its own selections start.
     int gtc = 0, eqc = 0;
-    for (int j = 0; j < lim; ++j) {
-      gtc += key[j] > T;
-      eqc += key[j] == T;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      gtc += j < lim && key[j] > T;
+      eqc += j < lim && key[j] == T;
     }
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int packed = gtc | (eqc << 16);
@@ -473,10 +478,13 @@ __global__ void __launch_bounds__(IS_THREADS, 1) bucket_index_sync_kernel(const 
     uint32_t selbits = 0;
     {
       long long tr = tie_base + eq_pre;
-      for (int j = 0; j < lim; ++j) {
-        bool s = key[j] > T;
-        if (key[j] == T) { s = tr < need; ++tr; }
-        if (s) { selbits |= 1u << j; ++selc; }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (j < lim) {
+          bool s = key[j] > T;
+          if (key[j] == T) { s = tr < need; ++tr; }
+          if (s) { selbits |= 1u << j; ++selc; }
+        }
       }
     }
     int sc_incl = selc;
@@ -495,7 +503,8 @@ __global__ void __launch_bounds__(IS_THREADS, 1) bucket_index_sync_kernel(const 
       if ((threadIdx.x & 7) == 0 && i < ((a.n + 31) & ~31LL)) a.touched[i >> 5] = word;
     } else if (selc) {
       long long pos = out_base + sel_pre;
-      for (int j = 0; j < lim; ++j) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
         if (selbits & (1u << j)) {
           if (pos < a.kcap) {
             int2 pr;
