@@ -118,6 +118,9 @@ def main() -> int:
     ap.add_argument("--seq-len", type=int, default=None)
     ap.add_argument("--ratio-percent", type=float, default=1.0)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--sga-backend", type=str, default="index", choices=("index", "mask"),
+                    help="index: rank-local exact top-k, (index, value) exchange; mask: shared support, mask-union reduce")
+    ap.add_argument("--cycle-period", type=int, default=None, help="dense flush every N steps (mask backend default 4)")
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel size (with sequence-parallel activations)")
     ap.add_argument("--tp-comm", type=str, default="auto", choices=("auto", "fused", "library"))
     ns = ap.parse_args()
@@ -141,10 +144,15 @@ def main() -> int:
         over["seq_length"] = ns.seq_len
     if ns.tp > 1:
         over.update(tensor_model_parallel_size=ns.tp, tp_comm=ns.tp_comm, init_on_device=True)
-    if ns.mode == "sga":
+    if ns.mode == "sga" and ns.sga_backend == "index":
         over.update(sga_enabled=True, sga_score="abs_g", sga_selection="topk", sga_selection_method="exact",
                     sga_selection_ratio_percent=ns.ratio_percent, sga_backend="torch_pipelined_index",
-                    sga_optimizer="adamw", sga_selection_locality="rank_local", sga_cycle_period=0,
+                    sga_optimizer="adamw", sga_selection_locality="rank_local",
+                    sga_cycle_period=ns.cycle_period or 0, sga_cycle_start_iter=0, sga_checks=False)
+    elif ns.mode == "sga":
+        over.update(sga_enabled=True, sga_score="abs_g", sga_selection="topk", sga_selection_method="histogram",
+                    sga_selection_histogram_mode="balanced", sga_selection_ratio_percent=ns.ratio_percent,
+                    sga_backend="torch_pipelined_mask", sga_optimizer="adamw", sga_cycle_period=ns.cycle_period or 4,
                     sga_cycle_start_iter=0, sga_checks=False)
     elif ns.mode == "nccl_baseline":
         over.update(transport="nccl", dense_mode="allreduce")
@@ -224,9 +232,14 @@ def main() -> int:
         "data": "synthetic uniform token ids (seed 1234), random-init weights N(0, 0.02^2)",
         "config": {"model": tr.cfg.name, "global_batch": args.global_batch_size, "seq_len": tr.cfg.seq_len,
                    "micro_batch": args.micro_batch_size, "parallelism": par, "mode": ns.mode,
-                   "sga": ("score=|g+residual|, per-bucket exact top-%g%%, index backend, residual-aware AdamW"
-                           % ns.ratio_percent) if ns.mode == "sga" else None,
-                   "transport": tr.ddp.transport, "l2": "inputs larger than L2 (weights 2.5 GB, grads 5 GB)",
+                   "sga": (("score=|g+residual|, per-bucket exact top-%g%%, index backend, residual-aware AdamW"
+                            % ns.ratio_percent) if ns.sga_backend == "index" else
+                           ("score=|g+residual|, shared support top-%g%% (balanced histogram), mask backend, "
+                            "dense flush every %d steps, residual-aware AdamW"
+                            % (ns.ratio_percent, ns.cycle_period or 4))) if ns.mode == "sga" else None,
+                   "transport": tr.ddp.transport,
+                   "l2": "inputs larger than L2 (weights %.1f GB, grads %.1f GB per rank)" % (
+                       2e-9 * tr.model.arena.numel, 4e-9 * tr.model.arena.numel),
                    "params": tr.cfg.num_params()},
         "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
         "mfu_bf16_of_measured_burst": None,
