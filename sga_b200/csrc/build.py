@@ -61,9 +61,9 @@ def _flags_for(src: str, extra: list[str]) -> list[str]:
     return flags
 
 
-def _compile_one(src: str, extra: list[str], verbose: bool) -> tuple[str, bool, str]:
+def _compile_one(src: str, extra: list[str], verbose: bool, objdir: str = "build") -> tuple[str, bool, str]:
     path = os.path.join(HERE, src)
-    obj = os.path.join(HERE, "build", src[:-3] + ".o")
+    obj = os.path.join(HERE, objdir, src[:-3] + ".o")
     stamp = obj + ".sha1"
     flags = _flags_for(src, extra)
     dig = _digest(path, flags)
@@ -78,22 +78,25 @@ def _compile_one(src: str, extra: list[str], verbose: bool) -> tuple[str, bool, 
     return obj, True, res.stdout + res.stderr
 
 
-def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) -> str:
-    """Compile (if stale) and link the library; returns its path."""
-    os.makedirs(os.path.join(HERE, "build"), exist_ok=True)
+def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False, bounds: bool = False) -> str:
+    """Compile (if stale) and link the library; returns its path. ``bounds`` builds the debug
+    variant ``libsga_b200_bounds.so`` with ``-DSGA_BOUNDS`` (index checks in the index-following
+    kernels) beside the production library."""
+    objdir = "build_bounds" if bounds else "build"
+    os.makedirs(os.path.join(HERE, objdir), exist_ok=True)
     if force:
-        for f in os.listdir(os.path.join(HERE, "build")):
-            os.remove(os.path.join(HERE, "build", f))
-    extra = ["-Xptxas", "-v"] if ptxas_info else []
+        for f in os.listdir(os.path.join(HERE, objdir)):
+            os.remove(os.path.join(HERE, objdir, f))
+    extra = (["-Xptxas", "-v"] if ptxas_info else []) + (["-DSGA_BOUNDS"] if bounds else [])
     srcs = sources()
     objs, rebuilt, logs = [], False, []
     with cf.ThreadPoolExecutor(max_workers=min(8, max(1, len(srcs)))) as pool:
-        for obj, did, log in pool.map(lambda s: _compile_one(s, extra, verbose), srcs):
+        for obj, did, log in pool.map(lambda s: _compile_one(s, extra, verbose, objdir), srcs):
             objs.append(obj)
             rebuilt |= did
             if log.strip():
                 logs.append(log)
-    out = os.path.join(HERE, LIB_NAME)
+    out = os.path.join(HERE, LIB_NAME.replace(".so", "_bounds.so") if bounds else LIB_NAME)
     if rebuilt or not os.path.exists(out):
         cmd = [_nvcc(), "-shared", "-o", out] + objs + ["-gencode", "arch=compute_100a,code=sm_100a", "-lcudart"]
         res = subprocess.run(cmd, capture_output=True, text=True)
@@ -105,5 +108,6 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
 
 
 if __name__ == "__main__":
-    p = build(force="--force" in sys.argv, verbose=True, ptxas_info="--ptxas" in sys.argv)
+    p = build(force="--force" in sys.argv, verbose=True, ptxas_info="--ptxas" in sys.argv,
+              bounds="--bounds" in sys.argv)
     print(p)

@@ -237,12 +237,31 @@ __global__ void dir_table_kernel(const int* __restrict__ idx, long long k, int* 
 }
 
 // ----------------------------------------------------------- pack/scatter
+// Debug build (-DSGA_BOUNDS, libsga_b200_bounds.so): the index-following kernels below check every
+// index against a window the host registers with sga_bounds_set_limit(); an index outside it is
+// counted and its access skipped. The production build compiles the checks away.
+#ifdef SGA_BOUNDS
+static __device__ long long g_bounds_limit = 0x7fffffffffffffffLL;
+static __device__ unsigned long long g_bounds_hits = 0ULL;
+__device__ __forceinline__ bool sga_index_ok(long long p) {
+  if (p >= 0 && p < g_bounds_limit) return true;
+  atomicAdd(&g_bounds_hits, 1ULL);
+  return false;
+}
+#else
+__device__ __forceinline__ bool sga_index_ok(long long) { return true; }
+#endif
+
 // vals[i] = grad[idx[i]] * factor; optionally grad[idx[i]] = 0.
 __global__ void pack_kernel(float* __restrict__ grad, const int* __restrict__ idx, long long k,
                             float* __restrict__ vals, float factor, int scale, int zero) {
   const long long gstride = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < k; i += gstride) {
     const int p = idx[i];
+    if (!sga_index_ok(p)) {
+      vals[i] = 0.f;
+      continue;
+    }
     const float v = grad[p];
     vals[i] = scale ? v * factor : v;
     if (zero) grad[p] = 0.f;
@@ -252,6 +271,7 @@ __global__ void scatter_kernel(float* __restrict__ dst, const int* __restrict__ 
                                long long k, int add) {
   const long long gstride = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < k; i += gstride) {
+    if (!sga_index_ok(idx[i])) continue;
     if (add) dst[idx[i]] += vals[i]; else dst[idx[i]] = vals[i];
   }
 }
@@ -265,7 +285,7 @@ __global__ void gather_blocks_kernel(float* __restrict__ grad, const uint8_t* __
   for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += gstride) {
     const long long p = (long long)heads[t / X] + (t % X);
     float v = 0.f;
-    if (p < n && mask[p]) {
+    if (p < n && sga_index_ok(p) && mask[p]) {
       v = grad[p];
       if (scale) v = v * factor;
       if (zero) grad[p] = 0.f;
@@ -280,7 +300,7 @@ __global__ void scatter_blocks_kernel(float* __restrict__ grad, const uint8_t* _
   const long long gstride = (long long)gridDim.x * blockDim.x;
   for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += gstride) {
     const long long p = (long long)heads[t / X] + (t % X);
-    if (p < n && mask[p]) grad[p] = vals[t];
+    if (p < n && sga_index_ok(p) && mask[p]) grad[p] = vals[t];
   }
 }
 
@@ -380,6 +400,27 @@ SGA_API int sga_dir_table(const int* idx, long long k, int* table, int ntable, v
   if (ntable <= 0) return 0;
   dir_table_kernel<<<(ntable + 255) / 256, 256, 0, ST(stream)>>>(idx, k, table, ntable);
   return LAUNCH_OK();
+}
+
+// Bounds build only: register the window [0, limit) / read and clear the count of indices seen
+// outside it. The production build answers -1 to both.
+SGA_API long long sga_bounds_set_limit(long long limit) {
+#ifdef SGA_BOUNDS
+  return cudaMemcpyToSymbol(g_bounds_limit, &limit, sizeof(limit)) == cudaSuccess ? 0 : -2;
+#else
+  (void)limit;
+  return -1;
+#endif
+}
+SGA_API long long sga_bounds_hits() {
+#ifdef SGA_BOUNDS
+  unsigned long long h = 0, z = 0;
+  if (cudaMemcpyFromSymbol(&h, g_bounds_hits, sizeof(h)) != cudaSuccess) return -2;
+  cudaMemcpyToSymbol(g_bounds_hits, &z, sizeof(z));
+  return (long long)h;
+#else
+  return -1;
+#endif
 }
 
 SGA_API int sga_pack(float* grad, const int* idx, long long k, float* vals, float factor, int scale, int zero,
