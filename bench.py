@@ -123,6 +123,7 @@ def main() -> int:
     ap.add_argument("--cycle-period", type=int, default=None, help="dense flush every N steps (mask backend default 4)")
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel size (with sequence-parallel activations)")
     ap.add_argument("--tp-comm", type=str, default="auto", choices=("auto", "fused", "library"))
+    ap.add_argument("--pp", type=int, default=1, help="pipeline stages (untied embeddings; 1F1B over NCCL p2p)")
     ns = ap.parse_args()
     if ns.impl == "reference":
         return _reference_arm(ns)
@@ -144,6 +145,8 @@ def main() -> int:
         over["seq_length"] = ns.seq_len
     if ns.tp > 1:
         over.update(tensor_model_parallel_size=ns.tp, tp_comm=ns.tp_comm, init_on_device=True)
+    if ns.pp > 1:
+        over.update(pipeline_model_parallel_size=ns.pp, untie_embeddings_and_output_weights=True)
     if ns.mode == "sga" and ns.sga_backend == "index":
         over.update(sga_enabled=True, sga_score="abs_g", sga_selection="topk", sga_selection_method="exact",
                     sga_selection_ratio_percent=ns.ratio_percent, sga_backend="torch_pipelined_index",
@@ -225,6 +228,8 @@ def main() -> int:
     except Exception:
         pass
     par = f"dp{tr.dp_world}" if tr.tp_size == 1 else f"tp{tr.tp_size}(sp,{tr.tp.transport})xdp{tr.dp_world}"
+    if tr.pp_size > 1:
+        par = f"pp{tr.pp_size}(1f1b)x" + par
     line = {
         "metric": "train tokens/sec (device-timed, max over ranks)", "value": value, "unit": "tokens/s",
         "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_total / K, "higher_is_better": True,

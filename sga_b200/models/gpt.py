@@ -86,8 +86,19 @@ def _rows(*ranges):
     return [(0, lo, hi) for lo, hi in ranges]
 
 
-def param_specs(cfg: GPTConfig, tp_size: int = 1, tp_rank: int = 0) -> list:
+def stage_layers(num_layers: int, pp_size: int, pp_rank: int) -> range:
+    """Layers of pipeline stage ``pp_rank`` (contiguous, sizes differing by at most one)."""
+    base, extra = divmod(num_layers, pp_size)
+    lo = pp_rank * base + min(pp_rank, extra)
+    return range(lo, lo + base + (1 if pp_rank < extra else 0))
+
+
+def param_specs(cfg: GPTConfig, tp_size: int = 1, tp_rank: int = 0, pp_size: int = 1, pp_rank: int = 0) -> list:
     """Parameter specs in the order their gradients become final in the backward pass.
+
+    With ``pp_size > 1`` only the parameters of stage ``pp_rank`` are returned:
+    its contiguous run of layers, the embedding on the first stage, the final
+    norm and the output layer on the last (untied embeddings only).
 
     With ``tp_size > 1`` the linear weights are this rank's shard (QKV and the
     fused gate|up projection by output rows, per head group / per half; the
@@ -133,11 +144,26 @@ def param_specs(cfg: GPTConfig, tp_size: int = 1, tp_rank: int = 0) -> list:
                                    (vo + r * nkvl * hd, vo + (r + 1) * nkvl * hd))))
         specs.append(ParamSpec(p + "input_layernorm.weight", (H,), 1, "ones", tp_duplicate=True))
     specs.append(ParamSpec("embedding.word_embeddings.weight", (cfg.vocab, H), 0, "normal", std, tp_duplicate=dup))
+    if tp > 1 or pp_size > 1:
+        for i, s in enumerate(specs):
+            s.init_order = i  # every parameter keeps the random stream it has in the whole model
+    if pp_size > 1:
+        if cfg.tied_embeddings:
+            raise ValueError("pipeline stages need untied embeddings (the two uses live on different stages)")
+        mine = set(stage_layers(cfg.num_layers, pp_size, pp_rank))
+        first, last = pp_rank == 0, pp_rank == pp_size - 1
+
+        def keep(name: str) -> bool:
+            if name.startswith("decoder.layers."):
+                return int(name.split(".")[2]) in mine
+            if name.startswith("embedding."):
+                return first
+            return last  # final norm, output layer
+
+        specs = [s for s in specs if keep(s.name)]
     if tp > 1:
         # shards first, replicated parameters after them (each kind keeps its backward order), so that
         # buckets never mix the two; bucket synchronisation is not overlapped under tensor parallelism
-        for i, s in enumerate(specs):
-            s.init_order = i  # the random-init stream keeps the unsharded model's order
         specs = [s for s in specs if not s.tp_duplicate] + [s for s in specs if s.tp_duplicate]
     return specs
 
@@ -145,24 +171,30 @@ def param_specs(cfg: GPTConfig, tp_size: int = 1, tp_rank: int = 0) -> list:
 class GPT:
     def __init__(self, cfg: GPTConfig, *, device="cpu", pool=None, bucket_elems: int = 16 * 1024 * 1024,
                  seed: int = 0, need_comm_staging: bool = False, arena: Optional[FlatArena] = None, tp=None,
-                 init_on_device: bool = False):
+                 init_on_device: bool = False, pp_size: int = 1, pp_rank: int = 0):
         self.cfg = cfg
         self.device = torch.device(device)
         self.tp = tp if (tp is not None and tp.world > 1) else None
         self.tp_size = self.tp.world if self.tp is not None else 1
+        self.pp_size, self.pp_rank = pp_size, pp_rank
+        if pp_size > 1 and self.tp is not None:
+            raise NotImplementedError("pipeline stages combined with tensor parallelism are not built")
+        self.first_stage, self.last_stage = pp_rank == 0, pp_rank == pp_size - 1
+        self.layer_ids = stage_layers(cfg.num_layers, pp_size, pp_rank)
         self.arena = arena if arena is not None else FlatArena(
-            param_specs(cfg, self.tp_size, self.tp.rank if self.tp is not None else 0), bucket_elems=bucket_elems,
-            device=device, pool=pool, need_comm_staging=need_comm_staging, split_on_tp_duplicate=self.tp_size > 1)
+            param_specs(cfg, self.tp_size, self.tp.rank if self.tp is not None else 0, pp_size, pp_rank),
+            bucket_elems=bucket_elems, device=device, pool=pool, need_comm_staging=need_comm_staging,
+            split_on_tp_duplicate=self.tp_size > 1)
         if arena is None:
             self.arena.init_parameters(seed, on_device=init_on_device)
         self.cuda = self.device.type == "cuda"
         self._rope = None
         a = self.arena.by_name
-        self.emb = a["embedding.word_embeddings.weight"]
-        self.head = self.emb if cfg.tied_embeddings else a["output_layer.weight"]
-        self.final_norm = a["decoder.final_layernorm.weight"]
+        self.emb = a.get("embedding.word_embeddings.weight")
+        self.head = self.emb if cfg.tied_embeddings else a.get("output_layer.weight")
+        self.final_norm = a.get("decoder.final_layernorm.weight")
         self.layers = []
-        for i in range(cfg.num_layers):
+        for i in self.layer_ids:
             p = f"decoder.layers.{i}."
             self.layers.append(dict(
                 ln1=a[p + "input_layernorm.weight"], qkv=a[p + "self_attention.linear_qkv.weight"],
@@ -449,36 +481,62 @@ class GPT:
         if self.tp is not None:
             return self._forward_backward_tp(tokens, targets, loss_scale, on_param_done, backward,
                                              reduce_replicated)
+        loss, ctx = self.stage_forward(tokens, targets, None, loss_scale=loss_scale, write_grad=backward)
+        if backward:
+            self.stage_backward(ctx, None, on_param_done)
+        return loss
+
+    # ------------------------------------------------------- pipeline stages
+    # One micro-batch through this stage's layers. The first stage embeds ``tokens``; later stages take
+    # the previous stage's activation ``x_in`` ``[T, hidden]``. The last stage computes the loss (and,
+    # in the same kernel, the logit gradient); earlier stages return the activation to send on.
+    def stage_forward(self, tokens, targets, x_in, *, loss_scale: float = 1.0, write_grad: bool = True):
         c = self.cfg
         B, S = tokens.shape
         T = B * S
-        done = on_param_done if on_param_done is not None else (lambda slot: None)
-        ids = tokens.reshape(-1)
-        x = F.embed_fwd(ids, self.emb.model)
+        ids = tokens.reshape(-1) if self.first_stage else None
+        x = F.embed_fwd(ids, self.emb.model) if self.first_stage else x_in
         saved = []
         for L in self.layers:
             x, sv = self._layer_fwd(L, x, B, S)
             saved.append(sv)
+        self.launches += 1
+        if not self.last_stage:
+            return x, dict(B=B, S=S, ids=ids, saved=saved)
         hf, rstd_f = F.rmsnorm_fwd(x, self.final_norm.model, c.norm_eps)
         logits = self._linear(hf, self.head)
-        self.launches += 3
-        loss_tok = F.cross_entropy_(logits, targets.reshape(-1), grad_scale=loss_scale / T, write_grad=backward)
-        loss = loss_tok.mean()
-        if not backward:
-            return loss
-        dlogits = logits  # overwritten in place by the loss kernel
-        self._wgrad(dlogits, hf, self.head)
-        if not c.tied_embeddings:
-            done(self.head)
-        dhf = self._dgrad(dlogits, self.head)
-        del logits, dlogits, hf
-        dx = F.rmsnorm_bwd(x, self.final_norm.model, dhf, rstd_f, dw_out=self.final_norm.grad)
-        done(self.final_norm)
-        del dhf
+        self.launches += 2
+        loss_tok = F.cross_entropy_(logits, targets.reshape(-1), grad_scale=loss_scale / T, write_grad=write_grad)
+        # logits now holds the logit gradient (the loss kernel overwrites it in place)
+        return loss_tok.mean(), dict(B=B, S=S, ids=ids, saved=saved, x=x, hf=hf, rstd_f=rstd_f, dlogits=logits)
+
+    def stage_backward(self, ctx, dx_out, on_param_done: Optional[Callable] = None):
+        """Backward of one micro-batch through this stage. ``dx_out`` is the gradient of the stage's
+        output received from the next stage (``None`` on the last stage); returns the gradient of the
+        stage's input (``None`` on the first stage)."""
+        c = self.cfg
+        done = on_param_done if on_param_done is not None else (lambda slot: None)
+        B, S, saved = ctx["B"], ctx["S"], ctx["saved"]
+        if self.last_stage:
+            dlogits, hf = ctx.pop("dlogits"), ctx.pop("hf")
+            self._wgrad(dlogits, hf, self.head)
+            if not c.tied_embeddings:
+                done(self.head)
+            dhf = self._dgrad(dlogits, self.head)
+            del dlogits, hf
+            dx = F.rmsnorm_bwd(ctx.pop("x"), self.final_norm.model, dhf, ctx.pop("rstd_f"),
+                               dw_out=self.final_norm.grad)
+            done(self.final_norm)
+            del dhf
+            self.launches += 3
+        else:
+            dx = dx_out
         for L, sv in zip(reversed(self.layers), reversed(saved)):
             dx = self._layer_bwd(L, sv, dx, B, S, done)
         saved.clear()
-        F.embed_bwd(ids, dx, self.emb.grad)
-        done(self.emb)
-        self.launches += 4
-        return loss
+        if self.first_stage:
+            F.embed_bwd(ctx["ids"], dx, self.emb.grad)
+            done(self.emb)
+            self.launches += 1
+            return None
+        return dx

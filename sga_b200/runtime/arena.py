@@ -141,39 +141,40 @@ class FlatArena:
             self._init_on_device(seed)
             self.sync_model_from_main()
             return
-        gen = torch.Generator(device="cpu").manual_seed(seed)
+        # One generator per parameter, keyed by its place in the model's full parameter list: a shard or
+        # a pipeline stage that holds only some parameters still draws the values of the whole model.
         order = sorted(range(len(self.slots)), key=lambda i: (
             self.slots[i].spec.init_order if self.slots[i].spec.init_order is not None else i))
-        for s in (self.slots[i] for i in order):
+        for i in order:
+            s = self.slots[i]
+            pos = s.spec.init_order if s.spec.init_order is not None else i
+            gen = torch.Generator(device="cpu").manual_seed(seed * 1000003 + pos)
             if s.spec.init == "ones":
                 s.main.fill_(1.0)
             elif s.spec.init == "zeros":
                 s.main.zero_()
-            elif s.spec.tp_pieces is not None:
-                # draw the full tensor (the same stream as the unsharded model) and keep this rank's slices
-                full = torch.empty(s.spec.tp_full_shape)
+            else:
+                # generated in chunks on the host: identical bits on CPU and GPU runs
+                shape = s.spec.tp_full_shape if s.spec.tp_pieces is not None else s.spec.shape
+                full = torch.empty(shape)
                 flat = full.view(-1)
                 step = 1 << 24
                 for lo in range(0, flat.numel(), step):
                     hi = min(flat.numel(), lo + step)
                     flat[lo:hi].copy_(torch.randn(hi - lo, generator=gen) * s.spec.std)
-                dim = s.spec.tp_pieces[0][0]
-                s.main.copy_(torch.cat([full.narrow(dim, lo, hi - lo) for _, lo, hi in s.spec.tp_pieces], dim))
+                if s.spec.tp_pieces is not None:
+                    dim = s.spec.tp_pieces[0][0]
+                    full = torch.cat([full.narrow(dim, lo, hi - lo) for _, lo, hi in s.spec.tp_pieces], dim)
+                s.main.copy_(full)
                 del full
-            else:
-                # generated in chunks on the host: identical bits on CPU and GPU runs
-                flat = s.main.view(-1)
-                step = 1 << 24
-                for lo in range(0, flat.numel(), step):
-                    hi = min(flat.numel(), lo + step)
-                    flat[lo:hi].copy_(torch.randn(hi - lo, generator=gen) * s.spec.std)
         self.sync_model_from_main()
 
     def _init_on_device(self, seed: int) -> None:
         order = sorted(range(len(self.slots)), key=lambda i: (
             self.slots[i].spec.init_order if self.slots[i].spec.init_order is not None else i))
-        for pos, i in enumerate(order):
+        for i in order:
             s = self.slots[i]
+            pos = s.spec.init_order if s.spec.init_order is not None else i
             if s.spec.init == "ones":
                 s.main.fill_(1.0)
             elif s.spec.init == "zeros":

@@ -62,10 +62,11 @@ def latest_iteration(root: str):
 
 
 def save_checkpoint(root: str, iteration: int, args, model, optimizer, rank: int = 0, tp_rank: int = 0,
-                    dp_rank: int | None = None) -> str:
-    """The first data-parallel replica writes (every replica holds the same state):
-    one ``mp_rank_XX`` file per tensor-parallel rank, the tracker by tensor-parallel rank 0."""
-    path = checkpoint_name(root, iteration, tp_rank)
+                    dp_rank: int | None = None, pp_rank: int = 0, pp_size: int = 1) -> str:
+    """The first data-parallel replica writes (every replica holds the same state): one
+    ``mp_rank_XX[_YYY]`` file per tensor-parallel rank (and pipeline stage), the tracker by the
+    first of them."""
+    path = checkpoint_name(root, iteration, tp_rank, pp_rank, pp_size)
     if (dp_rank if dp_rank is not None else rank) != 0:
         return path
     os.makedirs(os.path.dirname(path), exist_ok=True)
@@ -79,19 +80,20 @@ def save_checkpoint(root: str, iteration: int, args, model, optimizer, rank: int
     tmp = path + ".tmp"
     torch.save(state, tmp)
     os.replace(tmp, path)
-    if tp_rank == 0:
+    if tp_rank == 0 and pp_rank == 0:
         with open(tracker_path(root) + ".tmp", "w") as fh:
             fh.write(str(iteration))
         os.replace(tracker_path(root) + ".tmp", tracker_path(root))
     return path
 
 
-def load_checkpoint(root: str, model, optimizer, tp_rank: int = 0):
+def load_checkpoint(root: str, model, optimizer, tp_rank: int = 0, pp_rank: int = 0, pp_size: int = 1):
     """Loads the latest checkpoint; returns its iteration (0 when there is none)."""
     it = latest_iteration(root)
     if it is None:
         return 0
-    state = torch.load(checkpoint_name(root, it, tp_rank), map_location="cpu", weights_only=False)
+    state = torch.load(checkpoint_name(root, it, tp_rank, pp_rank, pp_size), map_location="cpu",
+                       weights_only=False)
     sd = dict(state["optimizer"]["optimizer"])
     sd["fp32_from_fp16_params"] = state["optimizer"]["fp32_from_fp16_params"]
     optimizer.load_state_dict(sd)

@@ -140,13 +140,18 @@ class Trainer:
             over["tied_embeddings"] = False
         self.cfg = get_config(args.model, **over)
         self.tp_size = max(1, int(args.tensor_model_parallel_size))
-        if (args.pipeline_model_parallel_size or 1) > 1:
-            raise NotImplementedError("pipeline stages are not built in this trainer (single-stage models only)")
-        assert self.world % self.tp_size == 0, "world size must be a multiple of the tensor-parallel size"
-        self.dp_world = self.world // self.tp_size
-        # adjacent ranks form a tensor-parallel group; data-parallel groups stride over them
-        self.tp_rank, self.dp_rank = self.rank % self.tp_size, self.rank // self.tp_size
-        self.tp_group = self.dp_group = None
+        self.pp_size = max(1, int(args.pipeline_model_parallel_size or 1))
+        if self.pp_size > 1 and self.tp_size > 1:
+            raise NotImplementedError("pipeline stages combined with tensor parallelism are not built")
+        mp = self.tp_size * self.pp_size
+        assert self.world % mp == 0, "world size must be a multiple of tensor-parallel x pipeline-parallel size"
+        self.dp_world = self.world // mp
+        # rank = (pp_rank * dp + dp_rank) * tp + tp_rank: adjacent ranks form a tensor-parallel group,
+        # data-parallel groups stride over them inside a pipeline stage, stages are the outermost axis
+        self.tp_rank = self.rank % self.tp_size
+        self.dp_rank = (self.rank // self.tp_size) % self.dp_world
+        self.pp_rank = self.rank // (self.tp_size * self.dp_world)
+        self.tp_group = self.dp_group = self.pp_group = None
         if self.tp_size > 1:
             for d in range(self.dp_world):
                 ranks = list(range(d * self.tp_size, (d + 1) * self.tp_size))
@@ -158,6 +163,17 @@ class Trainer:
                 grp = dist.new_group(ranks=ranks)
                 if t == self.tp_rank:
                     self.dp_group = grp
+        if self.pp_size > 1:
+            for pstage in range(self.pp_size):
+                ranks = list(range(pstage * self.dp_world, (pstage + 1) * self.dp_world))
+                grp = dist.new_group(ranks=ranks)
+                if pstage == self.pp_rank:
+                    self.dp_group = grp
+            for d in range(self.dp_world):
+                ranks = [d + pstage * self.dp_world for pstage in range(self.pp_size)]
+                grp = dist.new_group(ranks=ranks)
+                if d == self.dp_rank:
+                    self.pp_group = grp
         assert args.global_batch_size % (args.micro_batch_size * self.dp_world) == 0, (
             "global batch must be a multiple of micro_batch * data-parallel size")
         self.num_micro = args.global_batch_size // (args.micro_batch_size * self.dp_world)
@@ -189,7 +205,15 @@ class Trainer:
         self.model = GPT(self.cfg, device=self.device, pool=self.pool,
                          bucket_elems=getattr(args, "sga_bucket_elems", 16 << 20), seed=args.seed,
                          need_comm_staging=need_comm, tp=self.tp,
-                         init_on_device=bool(getattr(args, "init_on_device", False)))
+                         init_on_device=bool(getattr(args, "init_on_device", False)),
+                         pp_size=self.pp_size, pp_rank=self.pp_rank)
+        self.pipeline = None
+        if self.pp_size > 1:
+            from ..parallel.pp import Pipeline
+
+            self.pipeline = Pipeline(self.model, pp_rank=self.pp_rank, pp_size=self.pp_size,
+                                     prev_rank=self.rank - self.dp_world if self.pp_rank > 0 else None,
+                                     next_rank=self.rank + self.dp_world if self.pp_rank < self.pp_size - 1 else None)
         ddp_cfg = DDPConfig(average_in_collective=True, overlap_grad_reduce=bool(args.overlap_grad_reduce),
                             comm_max_ctas=args.comm_max_ctas)
         if getattr(args, "sga_backend_timer", None):
@@ -217,7 +241,7 @@ class Trainer:
             self.engine = build_engine(trainer_args=args, quiet=quiet)
             self.engine.log_interval = args.log_interval
             self.engine.attach(self.ddp)
-            if self.tp is not None:
+            if self.tp is not None or self.pp_size > 1:
                 self.engine.model_parallel_norm = self._tp_norm
         self.data = SyntheticTokens(self.cfg.vocab, self.cfg.seq_len, args.data_seed, pin=cuda)
         self.iteration = 0
@@ -227,9 +251,10 @@ class Trainer:
             self._dev_coeff = torch.ones(1, device=self.device)
             self._dev_norm = torch.zeros(1, device=self.device)
         self.last_grad_norm = None
+        self._dup_ranges = []
+        self._dev_dup = None
         if self.tp is not None:
             # merged element ranges of the parameters every tensor-parallel rank holds
-            self._dup_ranges = []
             for sl in self.model.arena.slots:
                 if sl.spec.tp_duplicate:
                     if self._dup_ranges and self._dup_ranges[-1][1] == sl.start:
@@ -239,28 +264,32 @@ class Trainer:
             self._dev_dup = torch.zeros(1, device=self.device) if cuda else None
 
     def _tp_norm(self, sumsq: torch.Tensor, source: torch.Tensor, mask=None) -> None:
-        """``sumsq`` (this shard's sum of squares over ``source``) -> the model's:
-        the sharded part summed over the tensor-parallel ranks, the replicated part counted once."""
-        if self.device.type == "cuda":
-            from .. import kernels as K
+        """``sumsq`` (this rank's sum of squares over ``source``) -> the whole model's: the sharded part
+        summed over the tensor-parallel ranks with the replicated part counted once, then the stages of
+        the pipeline added up."""
+        if self.tp is not None:
+            if self.device.type == "cuda":
+                from .. import kernels as K
 
-            first = True
-            for lo, hi in self._dup_ranges:
-                K.sumsq(source[lo:hi], self._dev_dup, mask=None if mask is None else mask[lo:hi],
-                        accumulate=not first)
-                first = False
-            dup = self._dev_dup
-        else:
-            tot = 0.0
-            for lo, hi in self._dup_ranges:
-                v = source[lo:hi].double()
-                if mask is not None:
-                    v = torch.where(mask[lo:hi] > 0, v, torch.zeros_like(v))
-                tot += float((v ** 2).sum())
-            dup = torch.tensor([tot], dtype=sumsq.dtype)
-        sumsq.sub_(dup.to(sumsq.dtype))
-        dist.all_reduce(sumsq, group=self.tp_group)
-        sumsq.add_(dup.to(sumsq.dtype))
+                first = True
+                for lo, hi in self._dup_ranges:
+                    K.sumsq(source[lo:hi], self._dev_dup, mask=None if mask is None else mask[lo:hi],
+                            accumulate=not first)
+                    first = False
+                dup = self._dev_dup
+            else:
+                tot = 0.0
+                for lo, hi in self._dup_ranges:
+                    v = source[lo:hi].double()
+                    if mask is not None:
+                        v = torch.where(mask[lo:hi] > 0, v, torch.zeros_like(v))
+                    tot += float((v ** 2).sum())
+                dup = torch.tensor([tot], dtype=sumsq.dtype)
+            sumsq.sub_(dup.to(sumsq.dtype))
+            dist.all_reduce(sumsq, group=self.tp_group)
+            sumsq.add_(dup.to(sumsq.dtype))
+        if self.pp_group is not None:
+            dist.all_reduce(sumsq, group=self.pp_group)
 
     # ----------------------------------------------------------------- data
     def host_batch(self, step: int) -> torch.Tensor:
@@ -279,19 +308,31 @@ class Trainer:
             batch = batch.to(self.device, non_blocking=True)
         losses = []
         self.ddp.begin_step()
-        for i in range(self.num_micro):
-            chunk = batch[i * mb:(i + 1) * mb]
-            tokens, targets = chunk[:, :-1], chunk[:, 1:]
-            last = i == self.num_micro - 1
-            if last:
-                if self.engine is not None:
-                    self.engine.begin_step(self.ddp, it)
-                else:
-                    self._arm_dense()
-            loss = self.model.forward_backward(tokens, targets, loss_scale=1.0 / self.num_micro,
-                                               on_param_done=self.ddp.on_param_done if last else None,
-                                               reduce_replicated=last)
-            losses.append(loss)
+
+        def arm_last():
+            if self.engine is not None:
+                self.engine.begin_step(self.ddp, it)
+            else:
+                self._arm_dense()
+
+        if self.pipeline is not None:
+            mbs = []
+            for i in range(self.num_micro):
+                chunk = batch[i * mb:(i + 1) * mb]
+                mbs.append((chunk[:, :-1], chunk[:, 1:]))
+            losses = self.pipeline.run(mbs, loss_scale=1.0 / self.num_micro,
+                                       on_param_done_last=self.ddp.on_param_done, before_last_backward=arm_last)
+        else:
+            for i in range(self.num_micro):
+                chunk = batch[i * mb:(i + 1) * mb]
+                tokens, targets = chunk[:, :-1], chunk[:, 1:]
+                last = i == self.num_micro - 1
+                if last:
+                    arm_last()
+                loss = self.model.forward_backward(tokens, targets, loss_scale=1.0 / self.num_micro,
+                                                   on_param_done=self.ddp.on_param_done if last else None,
+                                                   reduce_replicated=last)
+                losses.append(loss)
         if self.engine is not None:
             if not self.engine.grad_sync(self.ddp, False):
                 self.ddp.finish_grad_sync()
@@ -299,6 +340,12 @@ class Trainer:
             self.last_grad_norm = gn
         else:
             self._dense_step()
+        if self.pipeline is not None:
+            # the loss lives on the last stage: hand it to every stage of the replica
+            t = torch.stack(losses).mean() if losses else torch.zeros((), dtype=torch.float32, device=self.device)
+            t = t.reshape(1).clone()
+            dist.broadcast(t, src=self.rank % self.dp_world + (self.pp_size - 1) * self.dp_world, group=self.pp_group)
+            return t[0]
         return torch.stack(losses).mean()
 
     # ----------------------------------------------------------- dense path
@@ -332,6 +379,8 @@ class Trainer:
             from ..parallel import p2p
 
             self.ddp.finish_pending()
+            if self.pp_group is not None:
+                dist.all_reduce(self._dev_sumsq, group=self.pp_group)  # the other stages' share of the norm
             K.clip_coeff(self._dev_sumsq, 1.0, clip, self._dev_coeff, self._dev_norm)
             if self._dense is None:
                 bs = torch.tensor([b.start for b in arena.buckets], dtype=torch.int64, device=self.device)
@@ -350,7 +399,7 @@ class Trainer:
             from .. import kernels as K
 
             K.sumsq(arena.main_grad, self._dev_sumsq)
-            if self.tp is not None:
+            if self.tp is not None or self.pp_group is not None:
                 self._tp_norm(self._dev_sumsq, arena.main_grad)
             K.clip_coeff(self._dev_sumsq, 1.0, clip, self._dev_coeff, self._dev_norm)
             K.adam_step(arena.main_param, arena.main_grad, arena.exp_avg, arena.exp_avg_sq, arena.segment_table(),
@@ -362,7 +411,7 @@ class Trainer:
             from ..plugins.optimizer.reference import grad_correct_torch
 
             sq = torch.tensor([float((arena.main_grad.double() ** 2).sum())], dtype=torch.float64)
-            if self.tp is not None:
+            if self.tp is not None or self.pp_group is not None:
                 self._tp_norm(sq, arena.main_grad)
             norm = float(sq.sqrt())
             coeff = 1.0

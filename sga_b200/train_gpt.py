@@ -23,7 +23,7 @@ def main(argv=None) -> int:
     tr = Trainer(args)
     start = 0
     if args.load:
-        start = ckpt.load_checkpoint(args.load, tr.model, tr.optimizer, tr.tp_rank)
+        start = ckpt.load_checkpoint(args.load, tr.model, tr.optimizer, tr.tp_rank, tr.pp_rank, tr.pp_size)
         tr.iteration = start
         if tr.rank == 0 and start:
             print(f"[train] resumed from iteration {start} (the SGA cycle cold-starts: dense steps until the next "
@@ -45,9 +45,9 @@ def main(argv=None) -> int:
                 print(f"[train] iteration {it}/{args.train_iters} | loss {lv:.6f} | grad norm {gn:.4f} | "
                       f"{dt * 1e3:.1f} ms/step | {tr.tokens_per_step() / dt:.0f} tokens/s", flush=True)
         if args.save and args.save_interval and it % args.save_interval == 0:
-            ckpt.save_checkpoint(args.save, it, args, tr.model, tr.optimizer, tr.rank, tr.tp_rank, tr.dp_rank)
+            ckpt.save_checkpoint(args.save, it, args, tr.model, tr.optimizer, tr.rank, tr.tp_rank, tr.dp_rank, tr.pp_rank, tr.pp_size)
     if args.save:
-        ckpt.save_checkpoint(args.save, args.train_iters, args, tr.model, tr.optimizer, tr.rank, tr.tp_rank, tr.dp_rank)
+        ckpt.save_checkpoint(args.save, args.train_iters, args, tr.model, tr.optimizer, tr.rank, tr.tp_rank, tr.dp_rank, tr.pp_rank, tr.pp_size)
     tr.check()
     tr.close()
     return 0

@@ -34,3 +34,11 @@ def test_tensor_parallel_fused_kernels_and_model_two_gpus():
         pytest.skip("needs at least 2 GPUs")
     res = _run(2, worker="tp_gpu_worker.py", port=29743)
     assert res.returncode == 0 and "TP_GPU_OK" in res.stdout, res.stdout[-3000:] + "\n" + res.stderr[-6000:]
+
+
+@pytest.mark.timeout(900)
+def test_pipeline_parallel_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least 2 GPUs")
+    res = _run(2, worker="pp_gpu_worker.py", port=29745)
+    assert res.returncode == 0 and "PP_GPU_OK" in res.stdout, res.stdout[-3000:] + "\n" + res.stderr[-6000:]
