@@ -46,7 +46,8 @@ def main():
                               pipeline_model_parallel_size=2, log_interval=0, sga_enabled=True, sga_score="abs_g",
                               sga_selection_method="exact", sga_selection_ratio_percent=5.0,
                               sga_backend="torch_pipelined_index", sga_selection_locality="rank_local",
-                              sga_cycle_period=3, sga_bucket_elems=1 << 20), quiet=True)
+                              sga_cycle_period=3, sga_bucket_elems=1 << 20,
+                              untie_embeddings_and_output_weights=True), quiet=True)
     ls = [float(tr.train_step(tr.host_batch(0)).item()) for _ in range(6)]
     tr.check()
     assert ls[-1] < ls[0] and all(x == x for x in ls), ls
