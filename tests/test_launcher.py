@@ -148,3 +148,23 @@ def test_select_best(tmp_path):
     assert mod.overrides_for("update@T8@fold@dl0.5", 10.0) == {
         "sga_score": "update", "sga_selection_ratio_percent": 10.0, "sga_cycle_period": 8,
         "sga_optimizer_residual_mean": True, "sga_optimizer_full_sync_inactive_lr_scale": 0.5}
+
+
+def test_env_and_setup_scripts_check_the_checkout():
+    """``env.sh --check`` accepts the checkout it lives in and refuses a shadowing copy of the package;
+    ``setup.sh`` reports against ``manifest.yaml`` (reference counterparts: ``env.sh:1-137``, ``setup.sh:1-70``)."""
+    import os
+    import subprocess
+    import tempfile
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    ok = subprocess.run(["bash", "-c", f"source {root}/env.sh --check"], capture_output=True, text=True,
+                        env={k: v for k, v in os.environ.items() if k != "PYTHONPATH"})
+    assert ok.returncode == 0 and "env.sh: ok" in ok.stdout, ok.stdout + ok.stderr
+    with tempfile.TemporaryDirectory() as d:
+        os.makedirs(os.path.join(d, "sga_b200"))
+        open(os.path.join(d, "sga_b200", "__init__.py"), "w").close()
+        # python puts the working directory first on its path: a stray copy there shadows the checkout
+        bad = subprocess.run(["bash", "-c", f"cd {d} && export PYTHONPATH={d} && source {root}/env.sh --check"],
+                             capture_output=True, text=True)
+        assert bad.returncode != 0 and "resolves to" in bad.stderr, bad.stdout + bad.stderr
