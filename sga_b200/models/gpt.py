@@ -171,8 +171,12 @@ def param_specs(cfg: GPTConfig, tp_size: int = 1, tp_rank: int = 0, pp_size: int
 class GPT:
     def __init__(self, cfg: GPTConfig, *, device="cpu", pool=None, bucket_elems: int = 16 * 1024 * 1024,
                  seed: int = 0, need_comm_staging: bool = False, arena: Optional[FlatArena] = None, tp=None,
-                 init_on_device: bool = False, pp_size: int = 1, pp_rank: int = 0):
+                 init_on_device: bool = False, pp_size: int = 1, pp_rank: int = 0, recompute: bool = False):
         self.cfg = cfg
+        # False: the normalised inputs of the two column-parallel linears and the SwiGLU output are kept
+        # for the backward pass (about 0.2 GB per layer at 8192 tokens; HBM is not the scarce resource);
+        # True: they are recomputed from what the backward pass holds anyway
+        self.recompute = recompute
         self.device = torch.device(device)
         self.tp = tp if (tp is not None and tp.world > 1) else None
         self.tp_size = self.tp.world if self.tp is not None else 1
@@ -272,7 +276,8 @@ class GPT:
         cs, sn = self._rope_tables()
         h1, rstd1 = F.rmsnorm_fwd(x, L["ln1"].model, c.norm_eps)
         qkv = self._linear(h1, L["qkv"])
-        del h1
+        if self.recompute:
+            h1 = None
         nq, nkv, hd = c.n_heads, c.n_kv_heads, c.head_dim
         qk_saved = None
         if c.qk_norm:
@@ -286,28 +291,30 @@ class GPT:
         x_mid = self._linear(ctx, L["proj"], residual=x)
         h2, rstd2 = F.rmsnorm_fwd(x_mid, L["ln2"].model, c.norm_eps)
         gu = self._linear(h2, L["fc1"])
-        del h2
         s = F.swiglu_fwd(gu)
         x_out = self._linear(s, L["fc2"], residual=x_mid)
-        del s
+        if self.recompute:
+            h2 = s = None
         self.launches += 5
-        return x_out, (x, rstd1, qkv, qk_saved, ctx, att_saved, x_mid, rstd2, gu)
+        return x_out, (x, rstd1, qkv, qk_saved, ctx, att_saved, x_mid, rstd2, gu, h1, h2, s)
 
     def _layer_bwd(self, L, saved, dx, B, S, done):
         c = self.cfg
         T = B * S
-        x, rstd1, qkv, qk_saved, ctx, att_saved, x_mid, rstd2, gu = saved
+        x, rstd1, qkv, qk_saved, ctx, att_saved, x_mid, rstd2, gu, h1, h2, s = saved
         nq, nkv, hd = c.n_heads, c.n_kv_heads, c.head_dim
         cs, sn = self._rope_tables()
         # MLP
-        s = F.swiglu_fwd(gu)
+        if s is None:
+            s = F.swiglu_fwd(gu)
         self._wgrad(dx, s, L["fc2"])
         done(L["fc2"])
         ds = self._dgrad(dx, L["fc2"])
         del s
         dgu = F.swiglu_bwd(gu, ds)
         del ds
-        h2, _ = F.rmsnorm_fwd(x_mid, L["ln2"].model, c.norm_eps, want_rstd=False)
+        if h2 is None:
+            h2, _ = F.rmsnorm_fwd(x_mid, L["ln2"].model, c.norm_eps, want_rstd=False)
         self._wgrad(dgu, h2, L["fc1"])
         done(L["fc1"])
         del h2
@@ -331,7 +338,8 @@ class GPT:
             done(L["kn"])
             done(L["qn"])
             self.launches += 4
-        h1, _ = F.rmsnorm_fwd(x, L["ln1"].model, c.norm_eps, want_rstd=False)
+        if h1 is None:
+            h1, _ = F.rmsnorm_fwd(x, L["ln1"].model, c.norm_eps, want_rstd=False)
         self._wgrad(dqkv, h1, L["qkv"])
         done(L["qkv"])
         del h1
@@ -370,19 +378,21 @@ class GPT:
         gu = tp.ag_linear(g2, L["fc1"].model)
         s = F.swiglu_fwd(gu)
         x_out = tp.linear_rs(s, L["fc2"].model, residual=x_mid)
-        del s
+        if self.recompute:
+            s = None
         self.launches += 5
-        return x_out, (x, rstd1, qkv, qk_saved, ctx, att_saved, x_mid, rstd2, gu, g1, g2)
+        return x_out, (x, rstd1, qkv, qk_saved, ctx, att_saved, x_mid, rstd2, gu, g1, g2, s)
 
     def _layer_bwd_tp(self, L, saved, gdx, B, S, done):
         c, tp = self.cfg, self.tp
         T = B * S
-        x, rstd1, qkv, qk_saved, ctx, att_saved, x_mid, rstd2, gu, g1, g2 = saved
+        x, rstd1, qkv, qk_saved, ctx, att_saved, x_mid, rstd2, gu, g1, g2, s = saved
         nq, nkv, hd = c.n_heads // tp.world, c.n_kv_heads // tp.world, c.head_dim
         cs, sn = self._rope_tables()
         dx = gdx.local
         # MLP: the down projection's input gradient gathers dx rows; gdx.full then feeds its weight gradient
-        s = F.swiglu_fwd(gu)
+        if s is None:
+            s = F.swiglu_fwd(gu)
         ds = tp.ag_linear(gdx, L["fc2"].model, b_mn=True)
         self._wgrad(gdx.full, s, L["fc2"])
         done(L["fc2"])

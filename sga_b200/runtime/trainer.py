@@ -65,6 +65,8 @@ def add_trainer_args(p: argparse.ArgumentParser) -> argparse.ArgumentParser:
     g.add_argument("--overlap-grad-reduce", type=C.sga_bool, default=True)
     g.add_argument("--comm-max-ctas", type=int, default=0)
     g.add_argument("--tensor-model-parallel-size", type=int, default=1)
+    g.add_argument("--recompute-activations", action="store_true",
+                   help="recompute the norm outputs and the SwiGLU output in the backward pass instead of keeping them")
     g.add_argument("--init-on-device", action="store_true",
                    help="draw the initial weights with the device generator (large models)")
     g.add_argument("--tp-comm", type=str, default="auto", choices=("auto", "fused", "library"),
@@ -206,7 +208,8 @@ class Trainer:
                          bucket_elems=getattr(args, "sga_bucket_elems", 16 << 20), seed=args.seed,
                          need_comm_staging=need_comm, tp=self.tp,
                          init_on_device=bool(getattr(args, "init_on_device", False)),
-                         pp_size=self.pp_size, pp_rank=self.pp_rank)
+                         pp_size=self.pp_size, pp_rank=self.pp_rank,
+                         recompute=bool(getattr(args, "recompute_activations", False)))
         self.pipeline = None
         if self.pp_size > 1:
             from ..parallel.pp import Pipeline
