@@ -35,22 +35,30 @@ struct BwdParams {
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ dctx, const __nv_bfloat16* __restrict__ ctx,
                                   float* __restrict__ delta, int B, int S, int nq, int hd, long long ld_d,
                                   long long ld_c) {
-  const long long gw = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
+  // hd / 8 consecutive lanes share one (token, head): each loads 16 bytes of dO and of O
+  const int per = hd >> 3;                      // 8 (hd 64) or 16 (hd 128) lanes per row
+  const long long gt = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long row = gt / per;               // (token, head) index
+  const int part = (int)(gt % per);
   const long long total = (long long)B * S * nq;
-  if (gw >= total) return;
-  const int h = (int)(gw % nq);
-  const long long t = gw / nq;
-  const __nv_bfloat16* a = dctx + t * ld_d + (long long)h * hd;
-  const __nv_bfloat16* c = ctx + t * ld_c + (long long)h * hd;
   float acc = 0.f;
-  for (int i = lane * 2; i < hd; i += 64) {
-    const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(a + i));
-    const float2 y = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(c + i));
-    acc += x.x * y.x + x.y * y.y;
+  int h = 0;
+  long long t = 0;
+  if (row < total) {
+    h = (int)(row % nq);
+    t = row / nq;
+    const uint4 a = *reinterpret_cast<const uint4*>(dctx + t * ld_d + (long long)h * hd + part * 8);
+    const uint4 c = *reinterpret_cast<const uint4*>(ctx + t * ld_c + (long long)h * hd + part * 8);
+    const __nv_bfloat162* ab = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* cb = reinterpret_cast<const __nv_bfloat162*>(&c);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 x = __bfloat1622float2(ab[i]), y = __bfloat1622float2(cb[i]);
+      acc += x.x * y.x + x.y * y.y;
+    }
   }
-  acc = warp_sum(acc);
-  if (lane == 0) {
+  for (int o = per >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (row < total && part == 0) {
     const int b = (int)(t / S), s = (int)(t % S);
     delta[((long long)b * nq + h) * S + s] = acc;
   }
@@ -570,7 +578,7 @@ SGA_API int sga_attn_bwd(const void* dctx, const void* qkv, const void* ctx, con
   if (rc) return rc;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const long long rows = (long long)B * S * nq;
-  attn_delta_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, st>>>(
+  attn_delta_kernel<<<(unsigned)((rows * (hd / 8) + 255) / 256), 256, 0, st>>>(
       reinterpret_cast<const __nv_bfloat16*>(dctx), reinterpret_cast<const __nv_bfloat16*>(ctx), delta, B, S, nq, hd,
       ld_ctx, ld_ctx);
   if (cudaGetLastError() != cudaSuccess) return -4;

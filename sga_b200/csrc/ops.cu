@@ -161,13 +161,24 @@ __global__ void __launch_bounds__(256, NCH <= 8 ? 2 : 1) rmsnorm_bwd_kernel(cons
   }
 }
 
-// out[i] (+)= sum_b part[b][i]  (fixed order)
-__global__ void colsum_kernel(const float* __restrict__ part, int nb, int H, float* __restrict__ out, int accumulate) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= H) return;
+// out[i] (+)= sum_b part[b][i]. A CTA owns 32 columns; its 8 warps each add every eighth row of the
+// partials and the 8 partial sums are added in warp order: the order of summation is fixed.
+__global__ void __launch_bounds__(256) colsum_kernel(const float* __restrict__ part, int nb, int H,
+                                                      float* __restrict__ out, int accumulate) {
+  __shared__ float sh[8][32];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int i = blockIdx.x * 32 + lane;
   float s = 0.f;
-  for (int b = 0; b < nb; ++b) s += part[(long long)b * H + i];
-  out[i] = accumulate ? out[i] + s : s;
+  if (i < H)
+    for (int b = w; b < nb; b += 8) s += part[(long long)b * H + i];
+  sh[w][lane] = s;
+  __syncthreads();
+  if (w == 0 && i < H) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += sh[k][lane];
+    out[i] = accumulate ? out[i] + t : t;
+  }
 }
 
 // ------------------------------------------------------------------- RoPE
@@ -437,7 +448,7 @@ SGA_API int sga_rmsnorm_bwd(const void* x, const void* w, const void* dy, const 
   else if (nch <= 16) RB(16);
   else RB(32);
 #undef RB
-  colsum_kernel<<<(H + 255) / 256, 256, 0, ST(stream)>>>(dw_part, nb, H, dw_out, accumulate_dw);
+  colsum_kernel<<<(H + 31) / 32, 256, 0, ST(stream)>>>(dw_part, nb, H, dw_out, accumulate_dw);
   return LAUNCH_OK();
 }
 

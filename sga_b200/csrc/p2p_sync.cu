@@ -210,6 +210,8 @@ __global__ void __launch_bounds__(512) p2p_mask_union_kernel(const MaskUnionArgs
 // ------------------------------------------------------ bucket index sync
 constexpr int IS_THREADS = 1024;
 constexpr int IS_TILE = IS_THREADS * 4;
+constexpr int IS_LIST = 8192;  // per-CTA list of the low key halves met inside the crossing bin
+constexpr int IS_SMEM = 32772 * 4 + IS_LIST * 2;
 
 struct IndexSyncArgs {
   PeerCtx c;
@@ -314,7 +316,9 @@ __device__ __forceinline__ void find_bin(const unsigned* hist, int nb, long long
 }
 
 __global__ void __launch_bounds__(IS_THREADS, 1) bucket_index_sync_kernel(const IndexSyncArgs a) {
-  extern __shared__ unsigned sh_hist[];  // 32769 counters
+  extern __shared__ unsigned sh_hist[];  // 32769 counters, then the crossing-bin list
+  unsigned short* sh_list = reinterpret_cast<unsigned short*>(sh_hist + 32772);
+  __shared__ int sh_nlist;
   __shared__ int warp_tot[32];
   __shared__ int tile_cnt[64];
   __shared__ int sh_i[4];
@@ -359,6 +363,11 @@ __global__ void __launch_bounds__(IS_THREADS, 1) bucket_index_sync_kernel(const 
   int bin;
   long long above;
   find_bin(a.hist1, 32769, a.k, sh_i, bin, above, warp_tot);
+  // The crossing bin holds a sliver of the bucket. Its low key halves are also kept in a per-CTA
+  // list, so that once the threshold is known this CTA can count its keys above / equal to it from the
+  // phase-1 histogram and the list instead of reading its range a third time.
+  if (threadIdx.x == 0) sh_nlist = 0;
+  __syncthreads();
   for (long long i = r0 + (long long)threadIdx.x * 4; i < r1; i += 2 * IS_TILE) {
     float v0[4], v1[4];
     const int l0 = load4(a.acc, i, lim_all, v0);
@@ -366,8 +375,16 @@ __global__ void __launch_bounds__(IS_THREADS, 1) bucket_index_sync_kernel(const 
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const uint32_t k0 = key_of(v0[j]), k1 = key_of(v1[j]);
-      if (j < l0 && (int)(k0 >> 16) == bin) atomicAdd(&a.hist2[k0 & 0xFFFFu], 1u);
-      if (j < l1 && (int)(k1 >> 16) == bin) atomicAdd(&a.hist2[k1 & 0xFFFFu], 1u);
+      if (j < l0 && (int)(k0 >> 16) == bin) {
+        atomicAdd(&a.hist2[k0 & 0xFFFFu], 1u);
+        const int at = atomicAdd(&sh_nlist, 1);
+        if (at < IS_LIST) sh_list[at] = (unsigned short)(k0 & 0xFFFFu);
+      }
+      if (j < l1 && (int)(k1 >> 16) == bin) {
+        atomicAdd(&a.hist2[k1 & 0xFFFFu], 1u);
+        const int at = atomicAdd(&sh_nlist, 1);
+        if (at < IS_LIST) sh_list[at] = (unsigned short)(k1 & 0xFFFFu);
+      }
     }
   }
   __threadfence();
@@ -381,15 +398,27 @@ __global__ void __launch_bounds__(IS_THREADS, 1) bucket_index_sync_kernel(const 
   const long long n_gt = above + above2;           // keys strictly greater than T
   const int need = (int)((long long)a.k - n_gt);   // ties (key == T) to take, in index order
   int my_gt = 0, my_eq = 0;
-  for (long long i = r0 + (long long)threadIdx.x * 4; i < r1; i += 2 * IS_TILE) {
-    float v0[4], v1[4];
-    const int l0 = load4(a.acc, i, lim_all, v0);
-    const int l1 = load4(a.acc, i + IS_TILE, lim_all, v1);
+  const int nlist = sh_nlist;  // written before the grid barrier
+  if (nlist <= IS_LIST) {
+    // keys in higher bins (this CTA's own phase-1 histogram) + listed keys of the crossing bin
+    for (int bb = bin + 1 + threadIdx.x; bb < 32769; bb += IS_THREADS) my_gt += (int)sh_hist[bb];
+    for (int q = threadIdx.x; q < nlist; q += IS_THREADS) {
+      const int lowk = sh_list[q];
+      my_gt += lowk > (lowbin & 0xFFFF);
+      my_eq += lowk == (lowbin & 0xFFFF);
+    }
+  } else {
+    // the list overflowed (a bucket crowded into one bin): count by reading the range again
+    for (long long i = r0 + (long long)threadIdx.x * 4; i < r1; i += 2 * IS_TILE) {
+      float v0[4], v1[4];
+      const int l0 = load4(a.acc, i, lim_all, v0);
+      const int l1 = load4(a.acc, i + IS_TILE, lim_all, v1);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const uint32_t k0 = key_of(v0[j]), k1 = key_of(v1[j]);
-      my_gt += (j < l0 && k0 > T) + (j < l1 && k1 > T);
-      my_eq += (j < l0 && k0 == T) + (j < l1 && k1 == T);
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t k0 = key_of(v0[j]), k1 = key_of(v1[j]);
+        my_gt += (j < l0 && k0 > T) + (j < l1 && k1 > T);
+        my_eq += (j < l0 && k0 == T) + (j < l1 && k1 == T);
+      }
     }
   }
   {
@@ -674,7 +703,7 @@ SGA_API int sga_bucket_index_sync(const SgaPeerDesc* d, float* acc, long long n,
   a.mode = mode; a.zero_selected = zero_selected; a.result = result;
   static bool attr = false;
   if (!attr) {
-    if (cudaFuncSetAttribute(bucket_index_sync_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32769 * 4) !=
+    if (cudaFuncSetAttribute(bucket_index_sync_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, IS_SMEM) !=
         cudaSuccess)
       return -3;
     attr = true;
@@ -685,7 +714,7 @@ SGA_API int sga_bucket_index_sync(const SgaPeerDesc* d, float* acc, long long n,
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   long long need = (n + IS_TILE - 1) / IS_TILE;
   if (need < grid) grid = (int)need;
-  return coop_launch(bucket_index_sync_kernel, a, grid, IS_THREADS, 32769 * 4, st);
+  return coop_launch(bucket_index_sync_kernel, a, grid, IS_THREADS, IS_SMEM, st);
 }
 
 // ---------------------------------------------------------- symmetric memory

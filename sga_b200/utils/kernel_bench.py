@@ -124,8 +124,8 @@ def bench_index_sync(small):
 
     ms = timed(run, 2 if small else 10, warmup=1)
     ch.check()
-    # three reads of the bucket (two radix digits + compaction pass re-read from L2/HBM) + payload traffic
-    emit("bucket_index_sync_kernel", f"n={n} k={k} (1 rank)", ms, bytes_=n * 4.0 * 4 + k * 8.0 * 3)
+    # three reads of the bucket (two radix digits, compaction) + payload write, read-back and scatter
+    emit("bucket_index_sync_kernel", f"n={n} k={k} (1 rank)", ms, bytes_=n * 4.0 * 3 + k * 8.0 * 3)
     pool.close()
 
 
