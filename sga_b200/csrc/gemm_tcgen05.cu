@@ -18,10 +18,7 @@
 //
 // Replaces the cuBLAS / TransformerEngine GEMMs that the reference reaches
 // through its external Megatron stack (examples/llama3/train_1b_adamw.yaml:89,107).
-#include "common.cuh"
-#include <cuda.h>
-#include <cudaTypedefs.h>
-#include <stdio.h>
+#include "gemm_common.cuh"
 
 namespace sga {
 
@@ -36,32 +33,6 @@ constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int GEMM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
 constexpr int GEMM_SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
-
-enum EpiMode { EPI_BF16 = 0, EPI_F32 = 1, EPI_F32_ACC = 2, EPI_BF16_ADD = 3 };
-
-struct GemmParams {
-  int M, N, K;
-  int ldc;
-  int epi;
-  int tiles_m, tiles_n;
-  float alpha;
-  void* C;
-  const void* R;  // optional bf16 residual added in EPI_BF16_ADD (same ld as C)
-  int* err;
-};
-
-__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
-  // Grouped raster: 16 row-tiles share each column sweep so that the B tile
-  // (weights) and a band of A stay hot in L2 for the CTAs running together.
-  constexpr int GROUP = 16;
-  const int per_group = GROUP * tiles_n;
-  const int g = tile / per_group;
-  const int first_m = g * GROUP;
-  const int gsize = min(tiles_m - first_m, GROUP);
-  const int r = tile - g * per_group;
-  tm = first_m + (r % gsize);
-  tn = r / gsize;
-}
 
 template <int A_MN, int B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -185,75 +156,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_after();
       const int row = tm * BM + lg * 32 + lane;
       const int n0 = tn * BN;
-      const bool row_ok = row < p.M;
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         uint32_t r[32];
         tmem_ld32(tmem_base + ((uint32_t)(lg * 32) << 16) + acc * BN + c, r);
         tmem_ld_wait();
-        const int col = n0 + c;
-        if (!row_ok || col >= p.N) continue;
-        const bool full = (col + 32 <= p.N);
-        const size_t off = (size_t)row * p.ldc + col;
-        if (p.epi == EPI_BF16 || p.epi == EPI_BF16_ADD) {
-          __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + off;
-          const __nv_bfloat16* res = reinterpret_cast<const __nv_bfloat16*>(p.R) + off;
-          if (full) {
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              float f[8];
-#pragma unroll
-              for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(r[v * 8 + i]) * p.alpha;
-              if (p.epi == EPI_BF16_ADD) {
-                uint4 rv = *reinterpret_cast<const uint4*>(res + v * 8);
-                const __nv_bfloat162* rb = reinterpret_cast<const __nv_bfloat162*>(&rv);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  float2 x = __bfloat1622float2(rb[i]);
-                  f[2 * i] += x.x;
-                  f[2 * i + 1] += x.y;
-                }
-              }
-              uint4 o;
-              __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-              for (int i = 0; i < 4; ++i) ob[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
-              *reinterpret_cast<uint4*>(out + v * 8) = o;
-            }
-          } else {
-            for (int i = 0; i < 32 && col + i < p.N; ++i) {
-              float f = __uint_as_float(r[i]) * p.alpha;
-              if (p.epi == EPI_BF16_ADD) f += __bfloat162float(res[i]);
-              out[i] = __float2bfloat16_rn(f);
-            }
-          }
-        } else {
-          float* out = reinterpret_cast<float*>(p.C) + off;
-          if (full) {
-#pragma unroll
-            for (int v = 0; v < 8; ++v) {
-              float4 o;
-              o.x = __uint_as_float(r[v * 4 + 0]) * p.alpha;
-              o.y = __uint_as_float(r[v * 4 + 1]) * p.alpha;
-              o.z = __uint_as_float(r[v * 4 + 2]) * p.alpha;
-              o.w = __uint_as_float(r[v * 4 + 3]) * p.alpha;
-              if (p.epi == EPI_F32_ACC) {
-                const float4 old = *reinterpret_cast<const float4*>(out + v * 4);
-                o.x += old.x;
-                o.y += old.y;
-                o.z += old.z;
-                o.w += old.w;
-              }
-              *reinterpret_cast<float4*>(out + v * 4) = o;
-            }
-          } else {
-            for (int i = 0; i < 32 && col + i < p.N; ++i) {
-              float f = __uint_as_float(r[i]) * p.alpha;
-              if (p.epi == EPI_F32_ACC) f += out[i];
-              out[i] = f;
-            }
-          }
-        }
+        store_row32(p, r, row, n0 + c);
       }
       tc_fence_before();
       __syncwarp();
@@ -270,31 +178,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 }
 
 // ------------------------------------------------------------------ host
-static PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
-
-static int ensure_encode() {
-  if (g_encode) return 0;
-  void* fn = nullptr;
-  cudaDriverEntryPointQueryResult q;
-  cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
-  if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn) return -1;
-  g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
-  return 0;
-}
-
-// 2-D bf16 tensor map: `inner` contiguous elements per row, `outer` rows,
-// row pitch `ld` elements, box (box_inner x box_outer), 128-byte swizzle.
-static int make_map(CUtensorMap* m, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
-                    uint32_t box_inner, uint32_t box_outer) {
-  cuuint64_t dims[2] = {inner, outer};
-  cuuint64_t strides[1] = {ld * 2};
-  cuuint32_t box[2] = {box_inner, box_outer};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -2;
-}
+static TmaEncoder g_enc;
 
 static int g_num_sms = 0;
 static bool g_attr_set[4] = {false, false, false, false};
@@ -322,7 +206,7 @@ SGA_API int sga_gemm_bf16(const void* A, const void* B, void* C, const void* R, 
                           void* stream) {
   using namespace sga;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if (ensure_encode()) return -1;
+  if (g_enc.ensure()) return -1;
   if ((lda & 7) || (ldb & 7) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
     return -5;
   if ((reinterpret_cast<uintptr_t>(C) & 15) || (ldc & 7)) return -5;
@@ -334,14 +218,14 @@ SGA_API int sga_gemm_bf16(const void* A, const void* B, void* C, const void* R, 
   CUtensorMap ta, tb;
   int rc;
   if (a_mn)
-    rc = make_map(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, 64, BK);
+    rc = g_enc.make(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, 64, BK);
   else
-    rc = make_map(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, BM);
+    rc = g_enc.make(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, BM);
   if (rc) return rc;
   if (b_mn)
-    rc = make_map(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, BK);
+    rc = g_enc.make(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, BK);
   else
-    rc = make_map(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, BN);
+    rc = g_enc.make(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, BN);
   if (rc) return rc;
   GemmParams p;
   p.M = M;
