@@ -62,7 +62,11 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--dual-lr", default="1", help="comma floats")
     p.add_argument("--fused", action="store_true", help="accepted for compatibility; the fused engine is the only one")
     p.add_argument("--fused-shards", type=int, default=1)
-    p.add_argument("--selection-semantics", choices=("topk", "balanced-histogram"), default="topk")
+    p.add_argument("--selection-semantics", choices=("topk", "balanced-histogram"), default=None,
+                   help="rule behind the branch-point and boundary selections: balanced-histogram (the default of "
+                        "single-node cycle replay: the online engine's stride-8, whole-crossing-bin histogram "
+                        "mode) or topk (exact global top-k with index-ordered ties; the default with --nodes and "
+                        "for zerofill)")
     p.add_argument("--fused-max-configs", type=int, default=12)
     p.add_argument("--fused-state-budget-mb", type=float, default=0.0)
     p.add_argument("--nodes", default=None, help="comma host list for a multi-node replay")
@@ -90,6 +94,12 @@ def build_configs(ns):
     if ns.cycle_len is not None and ns.cycle_lens is not None:
         raise ValueError("give --cycle-len or --cycle-lens, not both")
     Ts = [ns.cycle_len] if ns.cycle_len is not None else (_ints(ns.cycle_lens) if ns.cycle_lens else [1])
+    # the reference's defaults (sga/replay.py:1703-1715, 1876-1882): single-node cycle replay selects by
+    # the online balanced-histogram rule; zerofill and multi-node replays need exact top-k
+    if ns.selection_semantics is None:
+        ns.selection_semantics = "balanced-histogram" if (ns.replay_mode == "cycle" and not ns.nodes) else "topk"
+    if ns.selection_semantics == "balanced-histogram" and (ns.replay_mode != "cycle" or ns.nodes):
+        raise ValueError("--selection-semantics balanced-histogram requires --replay-mode cycle on a single node")
     if ns.replay_mode == "zerofill":
         Ts = [10 ** 9]  # never a second boundary: unselected gradient mass just accumulates
     opts = [o for o in str(ns.optimizer).split(",") if o]
@@ -164,7 +174,7 @@ def run(ns) -> dict:
             frag = RF.run_fused_branch(ns.trace_dir, t0, cfgs, ns.window, horizons, world=ns.fused_shards,
                                        device=ns.device, dense_cache=ns.dense_cache,
                                        max_configs=ns.fused_max_configs, state_budget_mb=ns.fused_state_budget_mb,
-                                       score_names=scores, ratios=ratios)
+                                       score_names=scores, ratios=ratios, semantics=ns.selection_semantics)
         meta, _ = RC.load_state(info, t0)
         per_ratio = {}
         for r in ratios:

@@ -184,8 +184,10 @@ def f32(x: float) -> float:
     return float(torch.tensor(x, dtype=torch.float32))
 
 
-def adam_commit_torch(w, m, v, q, lr, wd, beta1, beta2, eps, count, optimizer="adamw", inactive=None, dual_lr=1.0):
-    """In-place commit in the replay form ``w * (1 - lr * wd) - lr * u``."""
+def adam_commit_torch(w, m, v, q, lr, wd, beta1, beta2, eps, count, optimizer="adamw", inactive=None, dual_lr=1.0,
+                      label=None):
+    """In-place commit in the replay form ``w * (1 - lr * wd) - lr * u``. ``label``
+    (optional) accumulates the squared gradient-driven step ``(lr * u)^2``."""
     adams = optimizer == "adams"
     bc1 = 1.0 if adams else 1.0 - beta1 ** count
     bc2 = 1.0 if adams else 1.0 - beta2 ** count
@@ -198,6 +200,9 @@ def adam_commit_torch(w, m, v, q, lr, wd, beta1, beta2, eps, count, optimizer="a
     if inactive is not None and dual_lr != 1.0:
         lr_t = torch.where(inactive, lr_t * dual_lr, lr_t)
     decay = 1.0 - lr_t * wd
+    if label is not None:
+        step = lr_t * u
+        label.add_(step * step)
     w.copy_(w * decay - lr_t * u)
     m.copy_(m1)
     v.copy_(v1)
@@ -241,14 +246,18 @@ class CycleConfig:
         return k
 
 
-def dense_replay(w0, m0, v0, logged, lrs, hp: Hyper, t0, optimizer="adamw", horizons=()):
+def dense_replay(w0, m0, v0, logged, lrs, hp: Hyper, t0, optimizer="adamw", horizons=(), label_out=None):
     """The dense trajectory: the logged (already clipped) gradients as committed.
-    Returns ``{h: w at horizon h}`` (h counts commits, 1-based)."""
+    Returns ``{h: w at horizon h}`` (h counts commits, 1-based). With ``label_out`` (a zeroed
+    tensor like ``w0``) it also accumulates the ranking label of the reference's front block: the
+    per-coordinate sum over the window of the squared gradient-driven step ``(lr * u)^2``
+    (``sga/replay.py:646-668,790-812``; weight decay does not enter it)."""
     w, m, v = w0.clone(), m0.clone(), v0.clone()
     snaps = {}
     for si, g in enumerate(logged):
         lr = lrs[si]
-        adam_commit_torch(w, m, v, g.float(), lr, hp.wd, hp.beta1, hp.beta2, hp.eps, t0 + si + 1, optimizer)
+        adam_commit_torch(w, m, v, g.float(), lr, hp.wd, hp.beta1, hp.beta2, hp.eps, t0 + si + 1, optimizer,
+                          label=label_out)
         if si + 1 in horizons:
             snaps[si + 1] = w.clone()
     return snaps

@@ -125,6 +125,49 @@ def shard_select(score_loc: torch.Tensor, k: int, comms: Comms) -> torch.Tensor:
     return sel
 
 
+def shard_entries(info, lo: int, hi: int) -> list:
+    """This shard's slice of every parameter: ``(local offset, offset inside the parameter, length)``."""
+    out = []
+    for off, sh in zip(info.offsets, info.shapes):
+        n = int(math.prod(sh)) if sh else 1
+        a, b = max(off, lo), min(off + n, hi)
+        if a < b:
+            out.append((a - lo, a - off, b - a))
+    return out
+
+
+def shard_select_balanced(score_loc: torch.Tensor, k: int, comms: Comms, entries) -> torch.Tensor:
+    """The online engine's ``balanced`` histogram selection replayed on a sharded flat vector
+    (``sga/replay_fused.py:405-489``): the histogram of the 16 high key bits is built on every 8th
+    element of each parameter, on the parameter's own grid (a shard that starts inside a parameter
+    continues that grid), the crossing bin is searched at rank ``max(1, round(n_sampled * (n_total -
+    k + 1) / n_total))`` and the WHOLE crossing bin is kept, so slightly more than ``k`` coordinates
+    are selected. Shard histograms and counts are disjoint partials: their sums are the unsharded
+    values and every shard derives the same bin."""
+    from ..plugins.selection._histogram import HIST_MODES, _ops, balanced_crossing_bin
+
+    if comms.world > 1 and os.environ.get("SGA_MASTER_ADDR") is not None:
+        raise ValueError("--selection-semantics balanced-histogram supports only the single-node engine")
+    x = score_loc.contiguous().float()
+    if not bool(torch.isfinite(x).all()):
+        raise ValueError("shard_select_balanced requires finite scores")
+    shift, nbins, stride = HIST_MODES["balanced"]
+    ops = _ops(x)
+    hist = torch.zeros(nbins, dtype=torch.int64, device=x.device)
+    n_tot = n_smp = 0
+    for a, p_off, n in entries:
+        phase = (-p_off) % stride
+        n_tot += n
+        if n > phase:
+            n_smp += (n - phase + stride - 1) // stride
+            ops.hist_top(x[a + phase:a + n], shift, stride, nbins, hist)
+    comms.sum_(hist)
+    counts = torch.tensor([n_tot, n_smp], dtype=torch.int64, device=x.device)
+    comms.sum_(counts)
+    b = balanced_crossing_bin(hist, int(counts[0]), int(counts[1]), k, replicas=1)
+    return (RC.abs_key(x) >> shift) >= b
+
+
 @dataclass
 class StepInput:
     si: int
@@ -181,8 +224,9 @@ class FusedGroup:
     """R configurations of one branch point advanced together on one shard."""
 
     def __init__(self, configs, n_loc, n_total, device, comms: Comms, hp: RC.Hyper, wd_vec, w0, m0, v0, t0, W,
-                 horizons, dense_snaps, use_kernel: bool):
+                 horizons, dense_snaps, use_kernel: bool, semantics: str = "topk", entries=None):
         self.cfgs = list(configs)
+        self.semantics, self.entries = semantics, entries
         self.R = len(self.cfgs)
         if self.R > 32:
             raise ValueError("at most 32 configurations per fused group")
@@ -220,8 +264,14 @@ class FusedGroup:
             if key not in cache:
                 sc = RC.replay_score(c.score, self.W[r], self.M[r], self.V[r], g, self._hp_dev(), self.t0 + 1,
                                      c.optimizer)
-                cache[key] = shard_select(sc, self.k[r], self.comms)
+                cache[key] = self._select(sc, self.k[r])
             self.SEL[r] = cache[key].to(torch.uint8)
+
+    def _select(self, sc, k):
+        """The trajectory-driving selection: exact top-k, or the online balanced-histogram rule."""
+        if self.semantics == "balanced-histogram":
+            return shard_select_balanced(sc, k, self.comms, self.entries)
+        return shard_select(sc, k, self.comms)
 
     def _hp_dev(self):
         return RC.Hyper(wd=self.wd, beta1=self.hp.beta1, beta2=self.hp.beta2, eps=self.hp.eps, clip=self.hp.clip)
@@ -298,7 +348,7 @@ class FusedGroup:
                     continue
                 q = self._q_pre(p, g, r) * p["coef"]
                 sc = RC.replay_score(c.score, self.W[r], self.M[r], self.V[r], q, self._hp_dev(), count, c.optimizer)
-                new_sel[r] = shard_select(sc, self.k[r], self.comms).to(torch.uint8)
+                new_sel[r] = self._select(sc, self.k[r]).to(torch.uint8)
                 self.stats["selects"] += 1
         self.stats["select_s"] += time.perf_counter() - t0
         # ---- pass 3: clip, residual, commit, horizon numerators
@@ -353,8 +403,10 @@ def group_configs(configs, max_configs: int, state_budget_mb: float, n_loc: int)
 
 
 def run_shard(rank, world, trace_dir, t0, configs, window, horizons, device, dense_cache, max_configs,
-              state_budget_mb, score_names, ratios, group=None):
-    """One shard's work for one branch point; rank 0 returns the report fragment."""
+              state_budget_mb, score_names, ratios, group=None, semantics="topk"):
+    """One shard's work for one branch point; rank 0 returns the report fragment.
+    ``semantics`` picks the rule behind the branch-point and boundary selections; the ranking
+    diagnostics of the front block stay on exact top-k under either (``sga/replay_fused.py:1407-1413``)."""
     info = RC.discover_trace(trace_dir)
     dev = torch.device(device)
     comms = Comms(rank, world, group, dev)
@@ -378,10 +430,10 @@ def run_shard(rank, world, trace_dir, t0, configs, window, horizons, device, den
     gdtype = torch.bfloat16 if info.g_dtype == "bf16" else torch.float32
     # ---- dense arm (element-wise: every shard replays its own slice; cached per shard)
     optimizers = sorted({c.optimizer for c in configs})
-    dense = {}
+    dense, labels = {}, {}
     metas = None
     for opt in optimizers:
-        ident = RC.cache_ident(trace_dir, t0, W, horizons, "fp32", info.g_dtype, f"fused-{world}-{rank}", opt)
+        ident = RC.cache_ident(trace_dir, t0, W, horizons, "fp32", info.g_dtype, f"fused-v2-{world}-{rank}", opt)
         blob = RC.load_cache(dense_cache, ident) if dense_cache else None
         if blob is None:
             pf = GPrefetcher(info, steps, lo, hi, gdtype, pin=False)
@@ -391,21 +443,24 @@ def run_shard(rank, world, trace_dir, t0, configs, window, horizons, device, den
                 logged.append(flat)
                 metas.append(gm)
             hp_d = RC.Hyper(wd=wd_vec, beta1=hp.beta1, beta2=hp.beta2, eps=hp.eps, clip=hp.clip)
-            snaps = RC.dense_replay(w0, m0, v0, logged, [gm["lr"][0] for gm in metas], hp_d, t0, opt, set(horizons))
-            blob = {"snap_d": snaps, "metas": metas}
+            label = torch.zeros_like(w0)
+            snaps = RC.dense_replay(w0, m0, v0, logged, [gm["lr"][0] for gm in metas], hp_d, t0, opt, set(horizons),
+                                    label_out=label)
+            blob = {"snap_d": snaps, "metas": metas, "label": label}
             if dense_cache:
                 RC.save_cache(dense_cache, ident, blob)
             del logged
         dense[opt] = blob["snap_d"]
+        labels[opt] = blob["label"]
         metas = blob["metas"]
     den = {}
     for opt in optimizers:
         d = torch.tensor([float(((dense[opt][h].double() - w0.double()) ** 2).sum()) for h in horizons],
                          dtype=torch.float64, device=dev)
         den[opt] = comms.sum_(d).tolist()
-    # ---- front: branch scores ranked against the realised dense displacement (the label)
+    # ---- front: branch scores ranked against the label, the window's summed squared gradient-driven step
     front = {}
-    label_loc = (dense[optimizers[0]][horizons[-1]] - w0).abs().to(dev)
+    label_loc = labels[optimizers[0]].to(dev)
     hp_dev = RC.Hyper(wd=wd_vec.to(dev), beta1=hp.beta1, beta2=hp.beta2, eps=hp.eps, clip=hp.clip)
     for name in score_names:
         sc = RC.replay_score(name, w0.to(dev), m0.to(dev), v0.to(dev), g0.to(dev), hp_dev, t0 + 1, optimizers[0])
@@ -437,7 +492,7 @@ def run_shard(rank, world, trace_dir, t0, configs, window, horizons, device, den
         by_opt = {}
         fg = FusedGroup(grp, n_loc, info.numel, dev, comms, hp, wd_vec, w0, m0, v0, t0, W, horizons,
                         dense[grp[0].optimizer] if len({c.optimizer for c in grp}) == 1 else dense[optimizers[0]],
-                        use_kernel)
+                        use_kernel, semantics=semantics, entries=shard_entries(info, lo, hi))
         fg.initial_select(g0)
         pf = GPrefetcher(info, steps, lo, hi, gdtype, pin=dev.type == "cuda")
         for si in range(W):
@@ -475,11 +530,12 @@ def _worker(rank, world, port, kwargs, out_path):
 
 
 def run_fused_branch(trace_dir, t0, configs, window, horizons, world=1, device="cpu", dense_cache=None,
-                     max_configs=12, state_budget_mb=0.0, score_names=("abs_g",), ratios=(10.0,)):
+                     max_configs=12, state_budget_mb=0.0, score_names=("abs_g",), ratios=(10.0,),
+                     semantics="topk"):
     """Replay one branch point on ``world`` shards; returns rank 0's fragment."""
     kwargs = dict(trace_dir=trace_dir, t0=t0, configs=list(configs), window=window, horizons=list(horizons),
                   device=device, dense_cache=dense_cache, max_configs=max_configs, state_budget_mb=state_budget_mb,
-                  score_names=list(score_names), ratios=list(ratios))
+                  score_names=list(score_names), ratios=list(ratios), semantics=semantics)
     if world == 1:
         return run_shard(0, 1, **kwargs)
     import socket

@@ -181,3 +181,41 @@ def test_fused_gpu_kernels_match_per_config_and_cpu(trace):
         assert torch.equal(single["final_state"][0][0], Wf[r]), "R configs at once == one at a time, bit for bit"
         for h in (6, 12):
             assert fused["results"][c][h] == pytest.approx(cpu["results"][c][h], rel=1e-4, abs=1e-6)
+
+
+def test_cli_matches_reference_golden_values(tmp_path):
+    """Golden values: the reference's own ``python -m sga.replay`` (its torch-eager arm) on this exact
+    synthetic trace (``make_synthetic_trace(sizes=(40000, 30000, 17000), steps=6)``, seed 0), for both
+    selection semantics. Distortions and the ranking metrics must agree to the printed digits; the
+    default semantics of single-node cycle replay is balanced-histogram, as in ``sga/replay.py:1703``."""
+    import json
+
+    from sga_b200.replay import cli
+    from sga_b200.replay.synth import make_synthetic_trace
+
+    trace = make_synthetic_trace(str(tmp_path / "t"), sizes=(40000, 30000, 17000), steps=6)
+    golden = {
+        "balanced-histogram": {("1.0", "abs_g@T4"): 0.50748199, ("1.0", "abs_m@T4"): 0.50587264,
+                               ("5.0", "abs_g@T4"): 0.49913694, ("5.0", "abs_m@T4"): 0.49359006},
+        "topk": {("1.0", "abs_g@T4"): 0.50759871, ("1.0", "abs_m@T4"): 0.5056148,
+                 ("5.0", "abs_g@T4"): 0.49945374, ("5.0", "abs_m@T4"): 0.49333816},
+    }
+    ndcg = {("1.0", "abs_g"): 0.56205288, ("1.0", "abs_m"): 0.15672116, ("5.0", "abs_g"): 0.49448113,
+            ("5.0", "abs_m"): 0.22009503}
+    recall = {("1.0", "abs_g"): 0.02414, ("5.0", "abs_g"): 0.24069, ("1.0", "abs_m"): 0.00805,
+              ("5.0", "abs_m"): 0.04782}
+    for sem, want in golden.items():
+        out = str(tmp_path / f"{sem}.json")
+        argv = ["--trace-dir", trace, "--branch-point", "0", "--ratios", "1,5", "--replay-mode", "cycle",
+                "--cycle-lens", "1,4", "--score-names", "abs_g,abs_m", "--window", "6", "--device", "cpu", "--out", out]
+        if sem == "topk":  # balanced-histogram is the default and must not need the flag
+            argv += ["--selection-semantics", "topk"]
+        assert cli.main(argv) == 0
+        per_ratio = json.load(open(out))["branch_results"]["0"]["per_ratio"]
+        for (r, key), val in want.items():
+            got = per_ratio[r]["scores"][key]["distortion"]["6"]
+            assert abs(got - val) < 2e-8, (sem, r, key, got, val)
+            assert per_ratio[r]["scores"][key.replace("T4", "T1")]["distortion"]["6"] < 1e-6
+        for (r, sc), val in ndcg.items():  # ranking diagnostics stay on exact top-k under either semantics
+            m = per_ratio[r]["scores"][f"{sc}@T4"]
+            assert abs(m["ndcg_at_k"] - val) < 2e-8 and abs(m["recall_at_k"] - recall[(r, sc)]) < 1e-5, (sem, r, sc, m)

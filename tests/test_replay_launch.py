@@ -78,7 +78,8 @@ def test_self_check_on_a_real_trace(tmp_path):
 @pytest.mark.timeout(600)
 def test_multinode_local_executor_matches_single_process(trace, tmp_path, monkeypatch):
     monkeypatch.setenv("SGA_LAUNCH_EXECUTOR", "local")
-    one = _cli(trace, tmp_path, "--fused-shards", "1")
+    # multi-node replays select by exact top-k (the balanced rule is single-node only): same rule on both arms
+    one = _cli(trace, tmp_path, "--fused-shards", "1", "--selection-semantics", "topk")
     two = _cli(trace, tmp_path, "--fused-shards", "2", "--nodes", "nodeA,nodeB", "--launch-log-dir",
                str(tmp_path / "launch"), "--preflight-timeout", "120")
     a = one["branch_results"]["0"]["per_ratio"]["5.0"]["scores"]
