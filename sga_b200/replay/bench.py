@@ -65,7 +65,7 @@ def main(argv=None) -> int:
            "elem_configs_per_s": round(ns.elems * len(cfgs) * ns.steps / wall / 1e9, 3),
            "unit": "1e9 element-configs/s (wall clock, includes trace reads and process start)",
            "profile": frag.get("profile")}
-    if ref is not None and "distortions" in ref:
+    if ref is not None and "distortions" in ref and "unavailable" not in ref:
         worst = 0.0
         for c in cfgs:
             mine = frag["results"][c][ns.steps]
@@ -93,7 +93,7 @@ def _reference_arm(ns, tdir, scores, ratios, Ts) -> dict:
         fh.write('raise ImportError("hidden: the reference replay kernels pin another Triton release")\n')
     out = os.path.join(tempfile.mkdtemp(prefix="sga_ref_out_"), "report.json")
     cache = tempfile.mkdtemp(prefix="sga_ref_cache_")
-    dev = "cuda:0" if ns.device.startswith("cuda") else "cpu"
+    dev = "cuda" if ns.device.startswith("cuda") else "cpu"  # the reference maps shards to local GPU indices itself
     cmd = [sys.executable, "-m", "sga.replay", "--trace-dir", tdir, "--branch-point", "0", "--ratios",
            ",".join(str(r) for r in ratios), "--replay-mode", "cycle", "--cycle-lens", ",".join(str(t) for t in Ts),
            "--score-names", ",".join(scores), "--window", str(ns.steps), "--device", dev, "--dense-cache", cache,
@@ -103,14 +103,15 @@ def _reference_arm(ns, tdir, scores, ratios, Ts) -> dict:
     t0 = time.perf_counter()
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, cwd=tempfile.gettempdir())
     wall = time.perf_counter() - t0
+    if res.returncode != 0 or not os.path.exists(out):
+        why = (res.stderr or res.stdout).strip().splitlines()[-1][:300] if (res.stderr or res.stdout) else "failed"
+        return {"bench": "fused replay", "impl": "reference", "unavailable": why}
     rec = {"bench": "fused replay", "impl": "reference", "elems": ns.elems, "steps": ns.steps,
            "configs": len(scores) * len(ratios) * len(Ts), "shards": ns.shards, "device": dev,
            "replay_wall_s": round(wall, 3), "ms_per_step": round(1e3 * wall / ns.steps, 2),
            "elem_configs_per_s": round(ns.elems * len(scores) * len(ratios) * len(Ts) * ns.steps / wall / 1e9, 3),
-           "kernels": "torch eager (the reference's fallback when Triton is not importable)"}
-    if res.returncode != 0 or not os.path.exists(out):
-        rec["unavailable"] = (res.stderr or res.stdout).strip().splitlines()[-1][:300] if (res.stderr or res.stdout) else "failed"
-        return rec
+           "kernels": "torch eager (the reference's fallback when Triton is not importable)",
+           "unit": "wall clock of the child process: interpreter start, imports, dense cache, replay"}
     per_ratio = json.load(open(out))["branch_results"]["0"]["per_ratio"]
     dist = {}
     for r, entry in per_ratio.items():

@@ -256,8 +256,8 @@ def dense_replay(w0, m0, v0, logged, lrs, hp: Hyper, t0, optimizer="adamw", hori
     snaps = {}
     for si, g in enumerate(logged):
         lr = lrs[si]
-        adam_commit_torch(w, m, v, g.float(), lr, hp.wd, hp.beta1, hp.beta2, hp.eps, t0 + si + 1, optimizer,
-                          label=label_out)
+        adam_commit_torch(w, m, v, g.to(w.device).float(), lr, hp.wd, hp.beta1, hp.beta2, hp.eps, t0 + si + 1,
+                          optimizer, label=label_out)
         if si + 1 in horizons:
             snaps[si + 1] = w.clone()
     return snaps

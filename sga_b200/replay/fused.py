@@ -442,11 +442,12 @@ def run_shard(rank, world, trace_dir, t0, configs, window, horizons, device, den
                 _t, gm, flat = pf.get()
                 logged.append(flat)
                 metas.append(gm)
-            hp_d = RC.Hyper(wd=wd_vec, beta1=hp.beta1, beta2=hp.beta2, eps=hp.eps, clip=hp.clip)
-            label = torch.zeros_like(w0)
-            snaps = RC.dense_replay(w0, m0, v0, logged, [gm["lr"][0] for gm in metas], hp_d, t0, opt, set(horizons),
-                                    label_out=label)
-            blob = {"snap_d": snaps, "metas": metas, "label": label}
+            # the dense arm runs where the sparse arms run (same arithmetic on both sides of the distortion)
+            hp_d = RC.Hyper(wd=wd_vec.to(dev), beta1=hp.beta1, beta2=hp.beta2, eps=hp.eps, clip=hp.clip)
+            label = torch.zeros_like(w0, device=dev)
+            snaps = RC.dense_replay(w0.to(dev), m0.to(dev), v0.to(dev), logged, [gm["lr"][0] for gm in metas], hp_d,
+                                    t0, opt, set(horizons), label_out=label)
+            blob = {"snap_d": {h: t.cpu() for h, t in snaps.items()}, "metas": metas, "label": label.cpu()}
             if dense_cache:
                 RC.save_cache(dense_cache, ident, blob)
             del logged
