@@ -1,0 +1,252 @@
+"""Bit-for-bit parity with the reference's own Python modules, where a plain
+copy of the reference package is present under ``baseline/_ref`` (it is not
+part of the repository; without it every test here is skipped).
+
+Covered: the score registry, the torch optimizer references (AdamW and AdamS,
+every fusion knob), mask compaction and the block forms, the cycle calendar,
+the flag surface and its validation, the three histogram selection modes, the
+exact selection, the adaptive threshold controller over a sequence of steps,
+and the replay CLI on a trace written by this framework's own trace collector.
+"""
+import argparse
+import importlib
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF = os.path.join(ROOT, "baseline", "_ref")
+pytestmark = pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "sga")),
+                                reason="no copy of the reference package under baseline/_ref")
+
+
+@pytest.fixture(scope="module")
+def ref():
+    """Imports reference modules by name with Triton hidden from them (their replay kernels refuse
+    every Triton release but one; without Triton the reference takes its torch paths)."""
+    saved = sys.modules.get("triton", "absent")
+    sys.modules["triton"] = None
+    sys.path.insert(0, REF)
+    try:
+        yield lambda name: importlib.import_module(name)
+    finally:
+        sys.path.remove(REF)
+        if saved == "absent":
+            sys.modules.pop("triton", None)
+        else:
+            sys.modules["triton"] = saved
+
+
+def _same_masks(a, b):
+    return all(torch.equal(x.view(-1).to(torch.uint8), y.view(-1).to(torch.uint8)) for x, y in zip(a, b))
+
+
+def test_scores_bitwise(ref):
+    RS = ref("sga.plugins.scores")
+    from sga_b200.plugins import scores as MS
+
+    RS.register_default_scores()
+    MS.register_default_scores()
+    assert sorted(RS.score_names()) == sorted(MS.score_names())
+    torch.manual_seed(0)
+    n = 4000
+    w, m, g = torch.randn(n) * 0.02, torch.randn(n) * 1e-3, torch.randn(n) * 1e-2
+    v = (torch.randn(n) * 1e-3) ** 2
+    for step in (1, 7, 300):
+        bc1, bc2 = 1 - 0.9 ** step, 1 - 0.95 ** step
+        for name in RS.score_names():
+            for inc in (True, False):
+                want = RS.get_score_spec(name).formula(w, m, v, g, 0.9, 0.95, 1e-8, 0.1, bc1, bc2, update_includes_wd=inc)
+                got = MS.compute_score(name, w, m, v, g, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, bc1=bc1,
+                                       bc2=bc2, update_includes_wd=inc)
+                assert torch.equal(want, got), (name, step, inc)
+
+
+def test_optimizer_references_bitwise(ref):
+    R_w = ref("sga.plugins.optimizer.adamw_torch").grad_correct_torch
+    R_s = ref("sga.plugins.optimizer.adams_torch").adams_grad_correct_torch
+    from sga_b200.plugins.optimizer.reference import grad_correct_torch as M
+
+    torch.manual_seed(1)
+    n = 3000
+    w, m, g = torch.randn(n) * 0.02, torch.randn(n) * 1e-3, torch.randn(n) * 1e-2
+    v = (torch.randn(n) * 1e-3) ** 2
+    mask = (torch.rand(n) < 0.1).to(torch.uint8)
+    cases = [dict(mask=None, emit_score=s) for s in ("abs_g", "update", "coi", "abs_m")] + [
+        dict(mask=mask, emit_score=None), dict(mask=mask, emit_score=None, coeff=0.37, clear=True),
+        dict(mask=mask, emit_score=None, clear=True, fold=True, interval=4.0),
+        dict(mask=mask, emit_score="update", inactive_lr_scale=0.25)]
+    bc1, bc2 = 1 - 0.9 ** 7, 1 - 0.95 ** 7
+    for opt in ("adamw", "adams"):
+        for kw in cases:
+            a = [t.clone() for t in (w, g, m, v)]
+            b = [t.clone() for t in (w, g, m, v)]
+            if opt == "adamw":
+                R_w(*a, 3e-4, 0.9, 0.95, 1e-8, 0.1, bc1, bc2, **kw)
+            else:
+                R_s(*a, 3e-4, 0.9, 0.95, 1e-8, 0.1, **kw)
+            M(*b, 3e-4, 0.9, 0.95, 1e-8, 0.1, bc1, bc2, optimizer=opt, **kw)
+            assert all(torch.equal(x, y) for x, y in zip(a, b)), (opt, {k: v for k, v in kw.items() if k != "mask"})
+
+
+def test_support_forms_bitwise(ref):
+    R = ref("sga.support")
+    from sga_b200 import support as M
+
+    torch.manual_seed(2)
+    n = 16384
+    mk = (torch.rand(n) < 0.13).to(torch.uint8)
+    assert torch.equal(R.compact_mask_u8(mk), M.compact_mask_u8(mk))
+    spans = [(0, 4096), (4096, 4160), (4160, 12288), (12288, 16384)]
+    for x in (4, 8, 64):
+        heads = R.block_idx_from_mask(mk, spans, x)
+        assert torch.equal(heads, M.block_idx_from_mask(mk, spans, x))
+        full = torch.zeros(n, dtype=torch.uint8)
+        for h in heads.tolist():
+            end = next(e for s, e in spans if s <= h < e)
+            full[h:min(h + x, end)] = 1
+        assert torch.equal(R.block_desc_from_mask(full, spans, x), M.block_desc_from_mask(full, spans, x))
+
+
+def test_cycle_calendar(ref):
+    R = ref("sga.engine").CycleManager
+    from sga_b200.runtime.engine import CycleManager as M
+
+    for cfg in [(0, 4, False, None), (20, 8, False, None), (5, 8, True, 4), (1, 1, False, None), (3, 6, True, 2)]:
+        a, b = R(*cfg), M(*cfg)
+        assert a.fold_window == b.fold_window
+        for step in range(1, 90):
+            for force in (False, True):
+                assert (a.is_full(step, force), a.reselect_boundary(step), a.extra_full(step)) == \
+                       (b.is_full(step, force), b.reselect_boundary(step), b.extra_full(step)), (cfg, step, force)
+
+
+def test_flag_surface_and_validation(ref):
+    R_add = ref("sga.config.arguments").add_sga_args
+    R_val = ref("sga.config.validation").validate_sga_args
+    from sga_b200.config.arguments import add_sga_args as M_add
+    from sga_b200.config.validation import validate_sga_args as M_val
+
+    pr, pm = argparse.ArgumentParser(), argparse.ArgumentParser()
+    R_add(pr)
+    M_add(pm)
+    ra = {a.dest: a for a in pr._actions if a.dest.startswith("sga_")}
+    ma = {a.dest: a for a in pm._actions if a.dest.startswith("sga_")}
+    assert not set(ra) - set(ma)
+    assert set(ma) - set(ra) == {"sga_backend_transport", "sga_bucket_elems", "sga_selection_locality"}
+    for d, x in ra.items():
+        y = ma[d]
+        assert x.default == y.default and x.option_strings == y.option_strings, d
+        assert (x.choices is None) == (y.choices is None) and (x.choices is None or list(x.choices) == list(y.choices)), d
+
+    base = ["--sga-enabled", "true", "--sga-score", "abs_g", "--sga-backend", "torch_pipelined_index",
+            "--sga-selection-ratio-percent", "10", "--sga-cycle-period", "8", "--sga-selection-method", "histogram",
+            "--sga-selection-histogram-mode", "balanced"]
+    trials = [[], ["--sga-cycle-start-iter", "20"], ["--sga-cycle-start-iter-percent", "10"],
+              ["--sga-selection-method", "exact"], ["--sga-selection-histogram-mode", "fast"],
+              ["--sga-selection-block-size", "8"], ["--sga-selection-block-size", "3"],
+              ["--sga-backend", "torch_pipelined_mask"], ["--sga-optimizer", "adams"], ["--sga-score", "coi"],
+              ["--sga-selection-ratio-percent", "0"], ["--sga-selection-ratio-percent", "100"],
+              ["--sga-trace-dir", "/tmp/x", "--sga-trace-branch-points", "3,1,2"], ["--sga-shadow", "true"],
+              ["--sga-always-sync-layers", "embedding,final"], ["--sga-backend-index-slices", "3"],
+              ["--sga-cycle-decouple-full-sync-interval-and-period", "true", "--sga-cycle-full-sync-interval", "4"],
+              ["--sga-cycle-full-sync-interval", "4"], ["--sga-optimizer-full-sync-inactive-lr-scale", "0.5"],
+              ["--sga-optimizer-residual-mean", "true"], ["--sga-checks", "false"],
+              ["--sga-backend-layout", "bb", "--sga-selection-block-size", "8"], ["--sga-backend-emission", "writeback"],
+              ["--sga-selection-method", "adaptive"]]
+
+    def run(add, val, argv):
+        p = argparse.ArgumentParser()
+        add(p)
+        ns = p.parse_args(argv)
+        ns.train_iters, ns.pipeline_model_parallel_size, ns.tensor_model_parallel_size = 100, 1, 1
+        try:
+            val(ns)
+        except ValueError:
+            return "refused", None
+        return "ok", {k: v for k, v in vars(ns).items() if k.startswith("sga_")}
+
+    for t in trials:
+        a, b = run(R_add, R_val, base + t), run(M_add, M_val, base + t)
+        assert a[0] == b[0], (t, a[0], b[0])
+        if a[0] == "ok":
+            assert not {k for k in a[1] if a[1][k] != b[1].get(k)}, t
+
+
+def test_selection_plugins_bitwise(ref):
+    R_hist = ref("sga.plugins.selection._histogram").select_masks_histogram
+    R_ex = ref("sga.plugins.selection._exact").select_masks_exact_kthvalue
+    RA = ref("sga.plugins.selection._adaptive").AdaptiveTau
+    from sga_b200.plugins.selection._adaptive import AdaptiveTau as MA
+    from sga_b200.plugins.selection._exact import select_masks_exact_kthvalue as M_ex
+    from sga_b200.plugins.selection._histogram import select_masks_histogram as M_hist
+
+    torch.manual_seed(3)
+    views = [torch.randn(40000) * 1e-3, torch.randn(7), torch.randn(123457) * 3e-2, torch.zeros(1000),
+             (torch.randn(5000) * 1e-3).abs()]
+    views[2][::13] = 0.05  # a tie layer
+    total = sum(v.numel() for v in views)
+    for mode in ("exact", "balanced", "fast"):
+        for k in (1, 17, 1000, 50000, total - 5):
+            tr, mr = R_hist([v.clone() for v in views], k, None, mode=mode, global_allreduce=False)
+            tm, mm = M_hist([v.clone() for v in views], k, None, mode=mode, global_allreduce=False)
+            assert float(tr) == float(tm) and _same_masks(mr, mm), (mode, k)
+    small = [views[0][:4000], views[1], views[2][:12345]]
+    for k in (1, 17, 900, 8000):
+        tr, mr = R_ex([v.clone() for v in small], k, None)
+        tm, mm = M_ex([v.clone() for v in small], k, None)
+        assert float(tr) == float(tm) and _same_masks(mr, mm), k
+    for wm in ("balanced", "fast", "exact"):
+        for ws in (1, 3):
+            a, b = RA(5.0, ws, wm, False), MA(5.0, ws, wm, False)
+            gen = torch.Generator().manual_seed(5)
+            for it in range(14):
+                scale = 1e-3 * (1 + 0.3 * ((it * 7) % 5))
+                gs = [torch.randn(20000, generator=gen) * scale, torch.randn(10000, generator=gen) * scale * 2]
+                wa, wb = a.warmup_sync_target(0, 4), b.warmup_sync_target(0, 4)
+                ra = a.select([x.clone() for x in gs], 1500, None, wa)
+                rb = b.select([x.clone() for x in gs], 1500, None, wb)
+                assert wa == wb and float(ra[0]) == float(rb[0]) and _same_masks(ra[1], rb[1]), (wm, ws, it)
+
+
+@pytest.mark.timeout(600)
+def test_reference_replay_reads_our_trace_and_agrees(tmp_path):
+    """A trace written by this framework's collector during a real (CPU) training run is consumed by
+    the reference's replay CLI, and both replays report the same distortions and ranking metrics."""
+    from sga_b200.replay import cli
+    from sga_b200.runtime.trainer import Trainer, default_args
+
+    tdir = str(tmp_path / "trace")
+    tr = Trainer(default_args(model="test_tiny", micro_batch_size=2, global_batch_size=2, train_iters=12, device="cpu",
+                              lr=1e-3, sga_bucket_elems=30000, log_interval=0, sga_enabled=True, sga_shadow=True,
+                              sga_score="abs_g", sga_selection_method="histogram",
+                              sga_selection_histogram_mode="balanced", sga_selection_ratio_percent=10.0,
+                              sga_backend="torch_pipelined_index", sga_cycle_period=2, sga_trace_dir=tdir,
+                              sga_trace_branch_points="2", sga_trace_window=6), quiet=True)
+    for s in range(10):
+        tr.train_step(tr.host_batch(s))
+    tr.close()
+    hide = tmp_path / "hide" / "triton"
+    hide.mkdir(parents=True)
+    (hide / "__init__.py").write_text('raise ImportError("hidden")\n')
+    common = ["--trace-dir", tdir, "--branch-point", "2", "--ratios", "5,10", "--replay-mode", "cycle", "--cycle-lens",
+              "1,2", "--score-names", "abs_g,update", "--window", "6", "--device", "cpu"]
+    ref_out, our_out = str(tmp_path / "ref.json"), str(tmp_path / "our.json")
+    env = dict(os.environ, PYTHONPATH=str(tmp_path / "hide") + os.pathsep + REF)
+    res = subprocess.run([sys.executable, "-m", "sga.replay"] + common + ["--dense-cache", str(tmp_path / "cache"), "--out",
+                         ref_out], env=env, capture_output=True, text=True, cwd=str(tmp_path))
+    assert res.returncode == 0, res.stderr[-2000:]
+    assert cli.main(common + ["--out", our_out]) == 0
+    a = json.load(open(ref_out))["branch_results"]["2"]["per_ratio"]
+    b = json.load(open(our_out))["branch_results"]["2"]["per_ratio"]
+    for r in a:
+        for key, want in a[r]["scores"].items():
+            got = b[r]["scores"][key]
+            if not key.endswith("T1"):
+                assert abs(got["distortion"]["6"] - want["distortion"]["6"]) < 5e-8, (r, key)
+            for mname in ("ndcg_at_k", "recall_at_k", "missed_label_mass", "missed_score_mass"):
+                assert abs(got[mname] - want[mname]) < 5e-8, (r, key, mname, got[mname], want[mname])
