@@ -250,3 +250,102 @@ def test_reference_replay_reads_our_trace_and_agrees(tmp_path):
                 assert abs(got["distortion"]["6"] - want["distortion"]["6"]) < 5e-8, (r, key)
             for mname in ("ndcg_at_k", "recall_at_k", "missed_label_mass", "missed_score_mass"):
                 assert abs(got[mname] - want[mname]) < 5e-8, (r, key, mname, got[mname], want[mname])
+
+
+@pytest.mark.skipif(not os.path.exists(os.path.join(REF, "tests", "ref_engine_harness.py")),
+                    reason="no copy of the reference's engine test harness under baseline/_ref/tests")
+def test_engine_flow_matches_reference_engine(ref, monkeypatch):
+    """The reference engine, driven by its own fake data-parallel chunk and optimizer wrapper
+    (``tests/test_engine_unit.py:647-730`` there), against this framework's engine on the same
+    parameters and the same per-step gradients, for a mask-consuming and an index-consuming
+    configuration with and without the residual fold: same full / sparse calendar, bit-identical
+    residual buffer, weights and gradient norms equal to fp32 rounding (the reference's dense steps
+    run ``torch.optim.Adam``, whose operation order differs from the fused form by an ulp)."""
+    import copy
+    import types
+
+    from sga_b200 import config as C
+    from sga_b200.runtime.arena import FlatArena, ParamSpec
+    from sga_b200.runtime.builder import build_engine
+    from sga_b200.runtime.ddp import DataParallel, DDPConfig
+    from sga_b200.runtime.optimizer import FlatOptimizer, OptimizerConfig
+
+    # the two helper predicates the reference engine imports from its external training stack
+    mods = {n: types.ModuleType(n) for n in ("megatron", "megatron.core", "megatron.core.tensor_parallel",
+                                             "megatron.core.transformer", "megatron.core.transformer.module")}
+    mods["megatron.core.tensor_parallel"].param_is_not_tensor_parallel_duplicate = lambda p, g=None: True
+    mods["megatron.core.transformer.module"].param_is_not_shared = lambda p: True
+    for n, m in mods.items():
+        monkeypatch.setitem(sys.modules, n, m)
+    monkeypatch.setenv("SGA_ALLOW_FROZEN_SELECTION", "1")  # the harness builds without the validation gate
+    monkeypatch.syspath_prepend(os.path.join(REF, "tests"))
+    ref("sga.engine")
+    H = importlib.import_module("ref_engine_harness")
+
+    def run_reference(combo, steps, seed, extra):
+        torch.manual_seed(seed)
+        chunk = H._FakeChunk(n_params=3, numel_per=64)
+        mp = H._FakeMPOpt(chunk)
+        p0 = [p.detach().clone() for p in chunk.params]
+        eng = H._build_engine(combo, extra)
+        eng.attach(chunk)
+        grads, log = [], []
+        gen = torch.Generator().manual_seed(seed + 1)
+        with H._ReplicaWorld(world=1):
+            for step in range(1, steps + 1):
+                g = torch.randn(chunk.bucket.grad_data.numel(), generator=gen)
+                grads.append(g.clone())
+                chunk.bucket.grad_data += g
+                assert eng.grad_sync(chunk, force_all_reduce=False) is True
+                full = bool(eng._step_full)
+                _ok, gn, _nz = eng.optimizer_step(mp, [chunk], step)
+                log.append((step, full, float(gn)))
+        return p0, grads, log, [m.detach().clone() for m in mp.main_params], chunk.bucket.grad_data.clone()
+
+    def run_ours(combo, p0, grads, extra):
+        kw = {**combo["config"], **combo["selection_params"], **combo["opt_params"], **combo.get("backend_params", {}),
+              "sga_score": combo["score"], "sga_selection": combo["selection"], "sga_optimizer": combo["opt"],
+              "sga_backend": combo["backend"], "sga_enabled": True, **(extra or {})}
+        C.set_args(C.make_args(**kw))
+        model = types.SimpleNamespace()
+        model.arena = FlatArena([ParamSpec(f"p{i}", tuple(p.shape), 0, "zeros") for i, p in enumerate(p0)],
+                                bucket_elems=10 ** 9, device="cpu")
+        model.named_parameters = lambda: [(s.name, s.model) for s in model.arena.slots]
+        for s, p in zip(model.arena.slots, p0):
+            s.main.copy_(p)
+        model.arena.sync_model_from_main()
+        ddp = DataParallel(model, transport="local",
+                           ddp_config=DDPConfig(average_in_collective=False, overlap_grad_reduce=False))
+        opt = FlatOptimizer(model.arena, OptimizerConfig(lr=1e-3, weight_decay=1e-2, adam_beta1=0.9, adam_beta2=0.95,
+                                                         adam_eps=1e-8, clip_grad=1.0))
+        eng = build_engine(quiet=True)
+        eng.log_interval = 0
+        eng.attach(ddp)
+        log = []
+        for step, g in enumerate(grads, 1):
+            off = 0
+            for s in model.arena.slots:
+                n = s.end - s.start
+                model.arena.main_grad[s.start:s.end] += g[off:off + n]
+                off += n
+            ddp.begin_step()
+            eng.begin_step(ddp, step)
+            if not eng.grad_sync(ddp, False):
+                ddp.finish_grad_sync()
+            full = bool(eng._step_full)
+            _ok, gn, _nz = eng.optimizer_step(opt, [ddp], step)
+            log.append((step, full, float(gn.item() if hasattr(gn, "item") else gn)))
+        return (log, [s.main.clone() for s in model.arena.slots],
+                torch.cat([model.arena.main_grad[s.start:s.end] for s in model.arena.slots]))
+
+    for combo in (H._UPDATE, H._ABS_M):
+        for extra in (None, {"sga_optimizer_residual_mean": True}):
+            c = copy.deepcopy(combo)
+            p0, grads, rlog, rfinal, rres = run_reference(c, 12, 7, extra)
+            olog, ofinal, ores = run_ours(c, p0, grads, extra)
+            assert [(s, f) for s, f, _ in rlog] == [(s, f) for s, f, _ in olog], (combo["score"], extra)
+            assert torch.equal(rres, ores), "residual buffer differs"
+            for (_, _, a), (_, _, b) in zip(rlog, olog):
+                assert abs(a - b) <= 5e-7 * max(a, 1e-9)
+            for a, b in zip(rfinal, ofinal):
+                assert float((a - b).abs().max()) <= 1e-7
