@@ -720,9 +720,12 @@ SGA_API int sga_bucket_index_sync(const SgaPeerDesc* d, float* acc, long long n,
 // ---------------------------------------------------------- symmetric memory
 SGA_API int sga_symm_alloc(long long bytes, void** out) {
   cudaError_t e = cudaMalloc(out, (size_t)bytes);
-  if (e != cudaSuccess) return -1;
-  cudaMemset(*out, 0, (size_t)bytes);
-  return 0;
+  if (e != cudaSuccess) {
+    cudaGetLastError();  // a failed allocation must not poison the next runtime call
+    return -(int)e;
+  }
+  e = cudaMemset(*out, 0, (size_t)bytes);
+  return e == cudaSuccess ? 0 : -(int)e;
 }
 SGA_API int sga_symm_free(void* p) { return cudaFree(p) == cudaSuccess ? 0 : -1; }
 SGA_API int sga_ipc_get_handle(void* p, void* handle64) {

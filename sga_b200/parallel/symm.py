@@ -19,6 +19,7 @@ from dataclasses import dataclass, field
 import torch
 import torch.distributed as dist
 
+from .. import kernels as _kernels  # noqa: F401  (declares the argument types of every launcher: 64-bit sizes)
 from ..csrc import lib
 
 _DT_SIZE = {torch.float32: 4, torch.int32: 4, torch.bfloat16: 2, torch.uint8: 1, torch.int64: 8, torch.float16: 2}
@@ -83,8 +84,11 @@ class SymmPool:
         L = lib()
         with torch.cuda.device(self.device):
             out = ctypes.c_void_p()
-            if L.sga_symm_alloc(nbytes, ctypes.byref(out)) != 0:
-                raise RuntimeError(f"symmetric allocation of {nbytes} bytes failed")
+            rc = L.sga_symm_alloc(nbytes, ctypes.byref(out))
+            if rc != 0:
+                free, total = torch.cuda.mem_get_info(self.device)
+                raise RuntimeError(f"symmetric allocation of {nbytes} bytes failed (CUDA error {-rc}; "
+                                   f"{free >> 20} MiB free of {total >> 20} MiB)")
             local = out.value
             peers = [local]
             opened = []
