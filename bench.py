@@ -42,7 +42,10 @@ def _reference_arm(ns) -> int:
     why = ("reference is not installable offline (pip: neither setup.py nor pyproject.toml) and its training "
            "entry needs the external Megatron-LM fork + TransformerEngine, absent from this image")
     if os.path.isdir(os.path.join(ref_dir, "sga")):
-        why = "reference package present but its training entry imports megatron (external fork, absent)"
+        why = ("the reference's training entry (forward / backward, data-parallel buckets) is an external Megatron-LM "
+               "fork + TransformerEngine + flash-attn, absent from this image; the part it implements itself is "
+               "measured on the same box by baseline/ref_sync_bench.py (gradient sync + optimizer step) and "
+               "sga_b200/replay/bench.py --impl both (offline replay)")
     if int(os.environ.get("RANK", "0")) == 0:
         print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
     return 0
