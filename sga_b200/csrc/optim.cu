@@ -103,7 +103,7 @@ __global__ void __launch_bounds__(ADAM_THREADS) sga_adam_kernel(const AdamArgs a
         } else if (a.mask && !active) {
           g = 0.f;
         }
-        if (do_coeff && active) g = g * coeff;
+        if (do_coeff && (active || a.lr_split)) g = g * coeff;  // the dual-lr boundary commits every lane
         const float m0 = mv[j], v0 = vv[j], w0 = wv[j];
         const float m1 = m0 * a.beta1 + g * a.omb1;
         const float g2 = (g * a.omb2) * g;

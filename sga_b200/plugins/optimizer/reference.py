@@ -42,7 +42,8 @@ def grad_correct_torch(param, grad, m, v, lr, beta1, beta2, eps, weight_decay, b
         g = grad
         lr_apply = lr
     if coeff != 1.0:
-        g = torch.where(active, g * coeff, g) if active is not None else g * coeff
+        # the dual-lr boundary commits every lane, so the clip coefficient reaches every lane too
+        g = torch.where(active, g * coeff, g) if (active is not None and inactive_lr_scale == 1.0) else g * coeff
     m_new = m * beta1 + g * (1.0 - beta1)
     g2 = (g * (1.0 - beta2)) * g
     if adams:

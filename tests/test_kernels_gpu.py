@@ -74,6 +74,7 @@ VARIANTS = [
     dict(emit=None, use_mask=True, clear=True, fold=True, interval=4.0),
     dict(emit=None, use_mask=False, clear=True),
     dict(emit="update", use_mask=True, lr_scale=0.25),
+    dict(emit="update", use_mask=True, lr_scale=0.25, coeff=0.37),
 ]
 
 

@@ -96,6 +96,21 @@ def test_grad_correct_full_step_emits_score_and_dual_lr():
     assert torch.equal(c[1][~on], g[~on]), "the residual stays in the grad buffer"
 
 
+def test_dual_lr_boundary_clips_every_lane():
+    """The boundary commit under a split lr consumes the whole merged buffer, so a deferred clip
+    coefficient scales the gradient at inactive lanes as well (a sparse step scales only active ones)."""
+    w, m, v, g = _state(300, 5)
+    mask = (torch.arange(300) % 4 == 0).to(torch.uint8)
+    a = [t.clone() for t in (w, g, m, v)]
+    grad_correct_torch(a[0], a[1], a[2], a[3], 1e-3, 0.9, 0.95, 1e-8, 0.1, 0.5, 0.4, mask, "abs_g", coeff=0.37,
+                       inactive_lr_scale=0.5)
+    b = [t.clone() for t in (w, g * 0.37, m, v)]
+    grad_correct_torch(b[0], b[1], b[2], b[3], 1e-3, 0.9, 0.95, 1e-8, 0.1, 0.5, 0.4, mask, "abs_g",
+                       inactive_lr_scale=0.5)
+    for x, y in zip(a, b):
+        assert torch.equal(x, y)
+
+
 def test_adams_has_no_bias_correction_and_rebuilds_v():
     w, m, v, g = _state(64, 4)
     a = [t.clone() for t in (w, g, m, v)]

@@ -257,8 +257,9 @@ def test_reference_replay_reads_our_trace_and_agrees(tmp_path):
 def test_engine_flow_matches_reference_engine(ref, monkeypatch):
     """The reference engine, driven by its own fake data-parallel chunk and optimizer wrapper
     (``tests/test_engine_unit.py:647-730`` there), against this framework's engine on the same
-    parameters and the same per-step gradients, for a mask-consuming and an index-consuming
-    configuration with and without the residual fold: same full / sparse calendar, bit-identical
+    parameters and the same per-step gradients, for mask- and index-consuming backends across scores,
+    both optimizers, the residual fold, the boundary dual lr, every selection method and histogram
+    mode, sliced and block transports and the decoupled calendar: same full / sparse calendar, bit-identical
     residual buffer, weights and gradient norms equal to fp32 rounding (the reference's dense steps
     run ``torch.optim.Adam``, whose operation order differs from the fused form by an ulp)."""
     import copy
@@ -338,14 +339,35 @@ def test_engine_flow_matches_reference_engine(ref, monkeypatch):
         return (log, [s.main.clone() for s in model.arena.slots],
                 torch.cat([model.arena.main_grad[s.start:s.end] for s in model.arena.slots]))
 
-    for combo in (H._UPDATE, H._ABS_M):
-        for extra in (None, {"sga_optimizer_residual_mean": True}):
-            c = copy.deepcopy(combo)
-            p0, grads, rlog, rfinal, rres = run_reference(c, 12, 7, extra)
-            olog, ofinal, ores = run_ours(c, p0, grads, extra)
-            assert [(s, f) for s, f, _ in rlog] == [(s, f) for s, f, _ in olog], (combo["score"], extra)
-            assert torch.equal(rres, ores), "residual buffer differs"
-            for (_, _, a), (_, _, b) in zip(rlog, olog):
-                assert abs(a - b) <= 5e-7 * max(a, 1e-9)
-            for a, b in zip(rfinal, ofinal):
-                assert float((a - b).abs().max()) <= 1e-7
+    U, M = H._UPDATE, H._ABS_M
+    ratio = {"sga_selection_ratio_percent": 30.0}
+    cases = [(c, e) for c in (U, M) for e in (None, {"sga_optimizer_residual_mean": True})] + [
+        ({**M, "score": "abs_g"}, {"sga_backend_emission": "writeback"}),
+        ({**M, "score": "abs_g"}, {"sga_backend_index_slices": 3}),
+        ({**U, "score": "coi"}, None),
+        ({**M, "score": "update"}, None),
+        ({**U, "score": "abs_m", "opt": "adams"}, None),
+        ({**M, "score": "abs_g", "opt": "adams"}, None),
+        (U, {"sga_optimizer_full_sync_inactive_lr_scale": 0.5}),
+        (U, {"sga_optimizer_full_sync_inactive_lr_scale": 0.25, "sga_optimizer_residual_mean": True}),
+        ({**M, "opt": "adams"}, {"sga_optimizer_full_sync_inactive_lr_scale": 0.0}),
+        (M, {"sga_selection_histogram_mode": "balanced"}),
+        (M, {"sga_selection_histogram_mode": "fast"}),
+        ({**M, "selection_params": {"sga_selection_method": "exact", **ratio}}, None),
+        ({**M, "selection_params": {"sga_selection_method": "adaptive", **ratio}}, None),
+        ({**U, "config": {"sga_cycle_start_iter": 0, "sga_cycle_period": 6, "sga_cycle_full_sync_interval": 3,
+                          "sga_cycle_decouple_full_sync_interval_and_period": True}}, None),
+        ({**M, "score": "abs_g"}, {"sga_selection_block_size": 8, "sga_selection_histogram_mode": "exact",
+                                   "sga_backend_emission": "writeback"}),
+    ]
+    for combo, extra in cases:
+        c = copy.deepcopy(combo)
+        tag = (combo["score"], combo["backend"], combo["opt"], extra)
+        p0, grads, rlog, rfinal, rres = run_reference(c, 14, 7, extra)
+        olog, ofinal, ores = run_ours(c, p0, grads, extra)
+        assert [(s, f) for s, f, _ in rlog] == [(s, f) for s, f, _ in olog], tag
+        assert torch.equal(rres, ores), ("residual buffer differs", tag)
+        for (_, _, a), (_, _, b) in zip(rlog, olog):
+            assert abs(a - b) <= 5e-7 * max(a, 1e-9), tag
+        for a, b in zip(rfinal, ofinal):
+            assert float((a - b).abs().max()) <= 2e-7, tag
