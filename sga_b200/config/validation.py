@@ -40,16 +40,16 @@ def sga_defaults() -> dict:
 
 
 def parse_branch_points(raw):
-    """Comma token, int, or list of ints -> sorted de-duplicated list (or None)."""
+    """Comma token, int, or list of ints -> sorted de-duplicated list (empty when unset)."""
     if raw is None:
-        return None
+        return []
     if isinstance(raw, bool):
         raise TypeError(f"branch points must be ints (got {raw!r})")
     if isinstance(raw, int):
         items = [raw]
     elif isinstance(raw, str):
         if not raw.strip():
-            return None
+            return []
         if raw.strip().lower() == "null":
             raise ValueError("'null' is not accepted here; leave the flag unset for no state dumps")
         items = [tok.strip() for tok in raw.split(",")]
@@ -70,7 +70,7 @@ def parse_branch_points(raw):
         if it < 0:
             raise ValueError(f"branch points must be >= 0 (got {it})")
         out.add(it)
-    return sorted(out) or None
+    return sorted(out)
 
 
 def parse_layer_patterns(raw):

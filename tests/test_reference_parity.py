@@ -177,6 +177,62 @@ def test_flag_surface_and_validation(ref):
             assert not {k for k in a[1] if a[1][k] != b[1].get(k)}, t
 
 
+def test_validation_differential_fuzz(ref, monkeypatch):
+    """Seeded random configurations (one to six keys drawn from legal, boundary and illegal values on
+    top of a valid base) through both validators: the same accept / refuse decision every time, and
+    the same namespace after the write-backs of an accepted configuration."""
+    import random
+
+    monkeypatch.setenv("SGA_ALLOW_FROZEN_SELECTION", "1")
+    RV = ref("sga.config.validation")
+    import sga_b200.config.validation as OV
+
+    dom = {
+        "sga_score": [None, "update", "abs_g", "abs_m", "coi"],
+        "sga_backend": ["dense", "torch_pipelined_index", "torch_pipelined_mask", "nccl_pipelined_index", "bogus"],
+        "sga_selection": ["topk", "bogus"], "sga_optimizer": ["adamw", "adams"], "sga_checks": [True, False],
+        "sga_cycle_start_iter": [0, 5], "sga_cycle_start_iter_percent": [None, 10.0, 150.0],
+        "sga_cycle_period": [1, 4, 6, 0], "sga_cycle_decouple_full_sync_interval_and_period": [False, True],
+        "sga_cycle_full_sync_interval": [None, 2, 3, 4, 6], "sga_trace_dir": [None, "/tmp/x", ""],
+        "sga_trace_branch_points": [None, "2,4", "a", "-1"], "sga_trace_window": [100, 0, 5],
+        "sga_trace_dump_dtype": ["fp32", "bf16"], "sga_trace_async": [False, True],
+        "sga_trace_async_backend": ["cpu_snapshot", "pinned_cuda"], "sga_trace_async_queue_depth": [1, 4],
+        "sga_trace_async_worker_count": [2, 8], "sga_shadow": [False, True], "sga_shadow_score": [True, False],
+        "sga_always_sync_layers": [None, "embedding", "a,,b", "null"],
+        "sga_optimizer_full_sync_inactive_lr_scale": [1.0, 0.5, 0.0, -1.0],
+        "sga_optimizer_residual_mean": [False, True], "sga_backend_emission": ["compact", "writeback"],
+        "sga_selection_method": [None, "histogram", "exact", "adaptive", "bogus"],
+        "sga_selection_histogram_mode": ["fast", "balanced", "exact"], "sga_selection_block_size": [1, 8, 3],
+        "sga_selection_ratio_percent": [None, 1.0, 0.0, 100.0, 101.0], "sga_backend_index_slices": [1, 3, 0],
+        "sga_backend_mask_slices": [2, 0], "sga_optimizer_compact_search": ["table", "bisect", "bogus"],
+        "train_iters": [None, 100], "pipeline_model_parallel_size": [1, 2],
+    }
+    rd, od = RV.sga_defaults(), OV.sga_defaults()
+    assert all(k in rd for k in dom if k.startswith("sga_"))
+    rng = random.Random(0)
+    accepted = refused = 0
+    for _ in range(2500):
+        over = {"sga_enabled": True, "sga_score": "update", "sga_backend": "torch_pipelined_index",
+                "sga_selection_method": "histogram", "sga_selection_ratio_percent": 1.0}
+        for k in rng.sample(sorted(dom), rng.choice([1, 2, 3, 4, 6])):
+            over[k] = rng.choice(dom[k])
+        sides = []
+        for defaults, V in ((rd, RV), (od, OV)):
+            ns = argparse.Namespace(**{"train_iters": None, "pipeline_model_parallel_size": 1, **defaults, **over})
+            try:
+                V.validate_sga_args(ns)
+                sides.append(ns)
+            except (ValueError, TypeError):
+                sides.append(None)
+        assert (sides[0] is None) == (sides[1] is None), over
+        if sides[0] is None:
+            refused += 1
+        else:
+            accepted += 1
+            assert not {k for k in rd if getattr(sides[0], k) != getattr(sides[1], k)}, over
+    assert accepted > 300 and refused > 300
+
+
 def test_selection_plugins_bitwise(ref):
     R_hist = ref("sga.plugins.selection._histogram").select_masks_histogram
     R_ex = ref("sga.plugins.selection._exact").select_masks_exact_kthvalue
@@ -259,7 +315,7 @@ def test_engine_flow_matches_reference_engine(ref, monkeypatch):
     (``tests/test_engine_unit.py:647-730`` there), against this framework's engine on the same
     parameters and the same per-step gradients, for mask- and index-consuming backends across scores,
     both optimizers, the residual fold, the boundary dual lr, every selection method and histogram
-    mode, sliced and block transports and the decoupled calendar: same full / sparse calendar, bit-identical
+    mode, sliced and block transports, always-synchronised parameters and the decoupled calendar: same full / sparse calendar, bit-identical
     residual buffer, weights and gradient norms equal to fp32 rounding (the reference's dense steps
     run ``torch.optim.Adam``, whose operation order differs from the fused form by an ulp)."""
     import copy
@@ -357,6 +413,9 @@ def test_engine_flow_matches_reference_engine(ref, monkeypatch):
         ({**M, "selection_params": {"sga_selection_method": "adaptive", **ratio}}, None),
         ({**U, "config": {"sga_cycle_start_iter": 0, "sga_cycle_period": 6, "sga_cycle_full_sync_interval": 3,
                           "sga_cycle_decouple_full_sync_interval_and_period": True}}, None),
+        (U, {"sga_always_sync_layers": ["p1"]}),
+        (M, {"sga_always_sync_layers": ["p0", "p2"], "sga_optimizer_residual_mean": True}),
+        (U, {"sga_checks": False}),
         ({**M, "score": "abs_g"}, {"sga_selection_block_size": 8, "sga_selection_histogram_mode": "exact",
                                    "sga_backend_emission": "writeback"}),
     ]
@@ -370,4 +429,4 @@ def test_engine_flow_matches_reference_engine(ref, monkeypatch):
         for (_, _, a), (_, _, b) in zip(rlog, olog):
             assert abs(a - b) <= 5e-7 * max(a, 1e-9), tag
         for a, b in zip(rfinal, ofinal):
-            assert float((a - b).abs().max()) <= 2e-7, tag
+            assert float((a - b).abs().max()) <= 3e-7, tag
