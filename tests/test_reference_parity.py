@@ -430,3 +430,18 @@ def test_engine_flow_matches_reference_engine(ref, monkeypatch):
             assert abs(a - b) <= 5e-7 * max(a, 1e-9), tag
         for a, b in zip(rfinal, ofinal):
             assert float((a - b).abs().max()) <= 3e-7, tag
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_engine_flow_matches_reference_engine_multirank(world):
+    """``world`` gloo ranks with different gradients per rank: see ``tests/ref_parity_worker.py``."""
+    import socket
+
+    with socket.socket() as sk:
+        sk.bind(("127.0.0.1", 0))
+        port = sk.getsockname()[1]
+    res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+                          "--master-addr", "127.0.0.1", "--master-port", str(port),
+                          os.path.join(ROOT, "tests", "ref_parity_worker.py")], capture_output=True, text=True,
+                         timeout=600, cwd=ROOT)
+    assert res.returncode == 0 and "PARITY OK" in res.stdout, (res.stdout[-1500:], res.stderr[-1500:])
