@@ -164,8 +164,10 @@ def run_reference(ns, rank, world, dev):
         def _copy_main_params_to_model_params(self):
             torch._foreach_copy_(self.float16_groups[0], self.main_params)
 
+    torch.manual_seed(1234)  # data-parallel replicas start from the same weights
     chunk = Chunk()
     opt = MixedPrecisionOptimizer(chunk)
+    p0 = [m.cpu() for m in opt.main_params] if ns.check else None
     eng = SGAEngine(SGA["sga_score"], build_selection(SGA["sga_selection"]), build_optimizer(SGA["sga_optimizer"]),
                     build_backend_plugin(SGA["sga_backend"]))
     eng._dp_cp_group = lambda: group
@@ -174,21 +176,43 @@ def run_reference(ns, rank, world, dev):
     views = [b.grad_data for b in chunk.bucket_list]
     phases = []
 
+    probe = []
+
+    def lane_state(lane):
+        b, off = divmod(lane, ns.bucket)
+        j, o = divmod(off, ns.param)
+        mp = opt.main_params[sum(len(x.params_list) for x in chunk.bucket_list[:b]) + j]
+        st = opt.optimizer.state.get(mp, {})
+        mask = eng._bucket_states[b].active_mask_u8
+        return [float(mp[o]), float(st["exp_avg"][o]) if "exp_avg" in st else 0.0,
+                float(st["exp_avg_sq"][o]) if "exp_avg_sq" in st else 0.0,
+                float(chunk.bucket_list[b].grad_data[off]), int(mask.view(-1)[off]) if mask is not None else -1]
+
     def step(s):
+        pre = [float(chunk.bucket_list[l // ns.bucket].grad_data[l % ns.bucket]) for l in ns.lanes]
         handled = eng.grad_sync(chunk, force_all_reduce=False)
         if not handled:
             chunk.finish_grad_sync()
         phases.append("full" if eng._step_full else "sparse")
         ok, _gn, _nz = eng.optimizer_step(opt, [chunk], s)
         assert ok
+        if ns.lanes:
+            probe.append({"step": s, "phase": phases[-1], "grad_norm": float(_gn), "local_grad": pre,
+                          "w_m_v_buf_active": [lane_state(l) for l in ns.lanes]})
 
     ms = timed_steps(step, lambda s: fill_grads(views, s, rank), ns.steps, ns.warmup, world)
-    return {"impl": "reference", "ms": ms, "phases": phases[ns.warmup:],
-            "kernels": "reference engine + backends + its Triton optimizer kernels; NCCL via torch.distributed"}
+    out = {"impl": "reference", "ms": ms, "phases": phases[ns.warmup:],
+           "kernels": "reference engine + backends + its Triton optimizer kernels; NCCL via torch.distributed"}
+    if ns.lanes:
+        out["probe"] = probe
+    if ns.check:
+        out["_state"] = (p0, torch.cat([m.reshape(-1) for m in opt.main_params]).cpu(),
+                         torch.cat([b.grad_data for b in chunk.bucket_list]).cpu())
+    return out
 
 
 # ------------------------------------------------------------------------ our arm
-def run_ours(ns, rank, world, dev):
+def run_ours(ns, rank, world, dev, p0=None):
     from sga_b200 import config as C
     from sga_b200.runtime.arena import FlatArena, ParamSpec
     from sga_b200.runtime.builder import build_engine
@@ -206,6 +230,10 @@ def run_ours(ns, rank, world, dev):
     model = types.SimpleNamespace()
     model.arena = FlatArena(specs, bucket_elems=ns.bucket, device=dev, pool=pool)
     model.arena.init_parameters(0, on_device=True)
+    if p0 is not None:  # start from the reference arm's weights
+        for slot, p in zip(model.arena.slots, p0):
+            slot.main.copy_(p.to(dev))
+        model.arena.sync_model_from_main()
     model.named_parameters = lambda: [(s.name, s.model) for s in model.arena.slots]
     ddp = DataParallel(model, transport=ns.transport if world > 1 or pool is not None else "local",
                        ddp_config=DDPConfig(average_in_collective=True, overlap_grad_reduce=False), pool=pool)
@@ -217,7 +245,17 @@ def run_ours(ns, rank, world, dev):
     views = [model.arena.main_grad[b.start:b.end] for b in model.arena.buckets]
     phases = []
 
+    probe = []
+    per_bucket = [len(sizes) for sizes in geometry(ns.elems, ns.bucket, ns.param)]
+
+    def flat(lane):
+        b, off = divmod(lane, ns.bucket)
+        j, o = divmod(off, ns.param)
+        return model.arena.slots[sum(per_bucket[:b]) + j].start + o
+
     def step(s):
+        a = model.arena
+        pre = [float(a.main_grad[flat(l)]) for l in ns.lanes]
         ddp.begin_step()
         eng.begin_step(ddp, s)
         if not eng.grad_sync(ddp, False):
@@ -225,10 +263,21 @@ def run_ours(ns, rank, world, dev):
         phases.append("full" if eng._step_full else "sparse")
         ok, _gn, _nz = eng.optimizer_step(opt, [ddp], s)
         assert ok
+        if ns.lanes:
+            mask = eng._active_mask_arena() if eng._active_support is not None else None
+            probe.append({"step": s, "phase": phases[-1], "grad_norm": float(_gn), "local_grad": pre,
+                          "w_m_v_buf_active": [[float(a.main_param[flat(l)]), float(a.exp_avg[flat(l)]),
+                                                float(a.exp_avg_sq[flat(l)]), float(a.main_grad[flat(l)]),
+                                                int(mask[flat(l)]) if mask is not None else -1] for l in ns.lanes]})
 
     ms = timed_steps(step, lambda s: fill_grads(views, s, rank), ns.steps, ns.warmup, world)
     ddp.check()
     out = {"impl": "ours", "ms": ms, "phases": phases[ns.warmup:], "transport": ddp.transport}
+    if ns.lanes:
+        out["probe"] = probe
+    if ns.check:
+        out["_state"] = (None, torch.cat([sl.main.reshape(-1) for sl in model.arena.slots]).cpu(),
+                         torch.cat([model.arena.main_grad[sl.start:sl.end] for sl in model.arena.slots]).cpu())
     if pool is not None:
         pool.close()
     return out
@@ -251,7 +300,16 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=12)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--transport", default="p2p", choices=("p2p", "nccl"))
+    ap.add_argument("--check", action="store_true",
+                    help="with --impl both: start our arm from the reference arm's weights and report how far the "
+                         "two arms' weights and residual buffers are apart after the run")
+    ap.add_argument("--lanes", type=lambda t: [int(x) for x in t.split(",") if x], default=[],
+                    help="comma list of flat element numbers: each arm also reports, after every step, the weight, "
+                         "both moments, the gradient-buffer value and the support bit there (a diagnostic; the "
+                         "per-step device reads make the timings meaningless)")
+    ap.add_argument("--clip", type=float, default=HP["clip"], help="gradient-norm clip of both arms (0 = off)")
     ns = ap.parse_args()
+    HP["clip"] = ns.clip
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
@@ -263,8 +321,14 @@ def main() -> int:
     os.environ.setdefault("WORLD_SIZE", "1")
     dist.init_process_group("nccl", device_id=dev)
     rank = dist.get_rank()
+    states = {}
     for impl in (("reference", "ours") if ns.impl == "both" else (ns.impl,)):
-        res = run_reference(ns, rank, world, dev) if impl == "reference" else run_ours(ns, rank, world, dev)
+        if impl == "reference":
+            res = run_reference(ns, rank, world, dev)
+        else:
+            res = run_ours(ns, rank, world, dev, p0=states["reference"][0] if "reference" in states else None)
+        if "_state" in res:
+            states[impl] = res.pop("_state")
         if "ms" in res:
             ms, ph = res["ms"], res["phases"]
             res.update(n_gpus=world, elems=ns.elems, bucket_elems=ns.bucket, steps=ns.steps, warmup=ns.warmup,
@@ -279,6 +343,22 @@ def main() -> int:
         if rank == 0:
             print(json.dumps(res), flush=True)
         torch.cuda.empty_cache()
+    if ns.check and len(states) == 2:
+        (_, rw, rr), (_, ow, orr) = states["reference"], states["ours"]
+        moved = float((rw - torch.cat([p.reshape(-1) for p in states["reference"][0]])).abs().max())
+        cmp = {"check": "reference vs ours after the run", "max_abs_dw": float((rw - ow).abs().max()),
+               "max_weight_movement": moved, "residual_lanes_differing": int((rr != orr).sum()),
+               "residual_lanes": int(rr.numel()), "max_abs_dresidual": float((rr - orr).abs().max()),
+               "weight_lanes_off_by_1e-6": int(((rw - ow).abs() > 1e-6).sum())}
+        off = ((rw - ow).abs() > 1e-6).nonzero().view(-1)[:8]
+        w0 = torch.cat([p.reshape(-1) for p in states["reference"][0]])
+        cmp["lanes_off"] = [{"lane": int(i), "w0": float(w0[i]), "reference": float(rw[i]), "ours": float(ow[i])} for i in off]
+        t = torch.tensor([cmp["max_abs_dw"], float(cmp["residual_lanes_differing"]), cmp["max_abs_dresidual"]],
+                         dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        cmp["max_abs_dw"], cmp["residual_lanes_differing"], cmp["max_abs_dresidual"] = t[0].item(), int(t[1]), t[2].item()
+        if rank == 0:
+            print(json.dumps(cmp), flush=True)
     dist.destroy_process_group()
     return 0
 
