@@ -167,6 +167,7 @@ def bench_elementwise(small):
 def bench_replay(small):
     import ctypes
 
+    from .. import kernels as _k  # noqa: F401  (declares the launchers' argument types)
     from ..csrc import lib
     from ..replay.fused import _CfgStruct
 

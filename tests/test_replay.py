@@ -183,6 +183,61 @@ def test_fused_gpu_kernels_match_per_config_and_cpu(trace):
             assert fused["results"][c][h] == pytest.approx(cpu["results"][c][h], rel=1e-4, abs=1e-6)
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("g_dtype", [torch.float32, torch.bfloat16])
+def test_replay_vector_kernels_equal_scalar_kernels(g_dtype):
+    """The four-elements-per-thread kernels (row length a multiple of 4) against the scalar ones (any
+    row length) on the common prefix of the same data: state bit for bit, fp64 sums to rounding."""
+    import ctypes
+
+    from sga_b200.csrc import lib
+    from sga_b200.replay.fused import _CfgStruct
+
+    L, dev, R, n = lib(), "cuda", 7, 4096 * 5
+    gen = torch.Generator().manual_seed(4)
+    base = {k: torch.randn(R, n + 3, generator=gen) * 1e-3 for k in ("W", "M", "V", "RES")}
+    base["V"].abs_()
+    sel = (torch.rand(R, n + 3, generator=gen) < 0.1).to(torch.uint8)
+    g = (torch.randn(n + 3, generator=gen) * 1e-3).to(g_dtype)
+    wd = torch.rand(n + 3, generator=gen) * 0.1
+    wden = torch.randn(n + 3, generator=gen) * 1e-3
+    arr = (_CfgStruct * R)()
+    for r in range(R):
+        a = arr[r]
+        a.boundary, a.fold, a.dual, a.adams, a.horizon = int(r % 3 == 0), int(r % 2 == 0), int(r == 3), int(r == 5), int(r != 1)
+        a.fold_div, a.coef, a.lr, a.lr_inactive, a.bc1, a.bc2 = 4.0, 0.9 - 0.05 * r, 3e-4, 1e-4, 0.5, 0.4
+    cfg = torch.frombuffer(bytearray(bytes(arr)), dtype=torch.uint8).to(dev)
+    nb = L.sga_replay_blocks()
+    st = torch.cuda.current_stream().cuda_stream
+    outs = {}
+    for rows in (n, n + 3):  # vector path, scalar path
+        t = {k: v[:, :rows].contiguous().to(dev) for k, v in base.items()}
+        s_, g_, wd_, wden_ = sel[:, :rows].contiguous().to(dev), g[:rows].contiguous().to(dev), \
+            wd[:rows].contiguous().to(dev), wden[:rows].contiguous().to(dev)
+        part = torch.zeros(R * nb, dtype=torch.float64, device=dev)
+        o1, o3 = torch.zeros(R, dtype=torch.float64, device=dev), torch.zeros(R, dtype=torch.float64, device=dev)
+        assert L.sga_replay_pass1(g_.data_ptr(), int(g_dtype == torch.bfloat16), 1.25, t["RES"].data_ptr(), s_.data_ptr(),
+                                  cfg.data_ptr(), R, rows, part.data_ptr(), o1.data_ptr(), st) == 0
+        assert L.sga_replay_pass3(g_.data_ptr(), int(g_dtype == torch.bfloat16), 1.25, t["W"].data_ptr(),
+                                  t["M"].data_ptr(), t["V"].data_ptr(), t["RES"].data_ptr(), s_.data_ptr(),
+                                  wd_.data_ptr(), wden_.data_ptr(), cfg.data_ptr(), R, rows, 0.9, 0.1, 0.95, 0.05, 1e-8,
+                                  part.data_ptr(), o3.data_ptr(), st) == 0
+        torch.cuda.synchronize()
+        outs[rows] = (t, o1.cpu(), o3.cpu())
+    (tv, v1, v3), (ts, s1, s3) = outs[n], outs[n + 3]
+    for k in ("W", "M", "V", "RES"):
+        assert torch.equal(tv[k], ts[k][:, :n]), k
+    # the scalar run covers three more elements per row: remove their share from its sums on the host
+    tail = slice(n, n + 3)
+    gq = g.float() / torch.tensor(1.25)
+    for r in range(R):
+        res = base["RES"][r, tail] / torch.tensor(4.0) if (arr[r].boundary and arr[r].fold) else base["RES"][r, tail]
+        q = gq[tail] + res if arr[r].boundary else torch.where(sel[r, tail] > 0, gq[tail], torch.zeros(3))
+        assert float(s1[r] - (q.double() ** 2).sum()) == pytest.approx(float(v1[r]), rel=1e-12)
+        extra = ((ts["W"][r, tail].cpu().double() - wden[tail].double()) ** 2).sum() if arr[r].horizon else 0.0
+        assert float(s3[r] - extra) == pytest.approx(float(v3[r]), rel=1e-12, abs=1e-300)
+
+
 def test_cli_matches_reference_golden_values(tmp_path):
     """Golden values: the reference's own ``python -m sga.replay`` (its torch-eager arm) on this exact
     synthetic trace (``make_synthetic_trace(sizes=(40000, 30000, 17000), steps=6)``, seed 0), for both
