@@ -38,6 +38,8 @@ from . import core as RC
 # kill switches: unknown values raise so that both arms of an A/B are always reachable
 ENV_KERNEL = "REPLAY_FUSED_KERNEL"      # on | off  (off: PyTorch ops even on CUDA)
 ENV_SELECT = "REPLAY_FUSED_SELECT"      # radix | gather
+ENV_WINDOW_HOST_GIB = "REPLAY_FUSED_WINDOW_HOST_GIB"  # host bytes (GiB, default 8) a shard may spend keeping the
+#                                          window's gradients between the dense arm and the stream
 
 
 def _switch(name, allowed, default):
@@ -403,10 +405,22 @@ def group_configs(configs, max_configs: int, state_budget_mb: float, n_loc: int)
 
 
 def run_shard(rank, world, trace_dir, t0, configs, window, horizons, device, dense_cache, max_configs,
-              state_budget_mb, score_names, ratios, group=None, semantics="topk"):
+              state_budget_mb, score_names, ratios, group=None, semantics="topk", keep_state=False):
     """One shard's work for one branch point; rank 0 returns the report fragment.
     ``semantics`` picks the rule behind the branch-point and boundary selections; the ranking
-    diagnostics of the front block stay on exact top-k under either (``sga/replay_fused.py:1407-1413``)."""
+    diagnostics of the front block stay on exact top-k under either (``sga/replay_fused.py:1407-1413``).
+    ``keep_state`` (single shard) also returns the last group's final weights and supports on the host."""
+    t_phase = time.perf_counter()
+    phases = {}
+
+    def lap(name):
+        nonlocal t_phase
+        if torch.device(device).type == "cuda":
+            torch.cuda.synchronize(torch.device(device))
+        now = time.perf_counter()
+        phases[name] = round(phases.get(name, 0.0) + now - t_phase, 4)
+        t_phase = now
+
     info = RC.discover_trace(trace_dir)
     dev = torch.device(device)
     comms = Comms(rank, world, group, dev)
@@ -432,11 +446,15 @@ def run_shard(rank, world, trace_dir, t0, configs, window, horizons, device, den
     optimizers = sorted({c.optimizer for c in configs})
     dense, labels = {}, {}
     metas = None
+    # the window's gradients, read once for the dense arm, serve the stream below too while they fit the budget
+    window_g = None
+    keep_bytes = int(float(os.environ.get(ENV_WINDOW_HOST_GIB, "8")) * (1 << 30))
+    lap("setup")
     for opt in optimizers:
         ident = RC.cache_ident(trace_dir, t0, W, horizons, "fp32", info.g_dtype, f"fused-v2-{world}-{rank}", opt)
         blob = RC.load_cache(dense_cache, ident) if dense_cache else None
         if blob is None:
-            pf = GPrefetcher(info, steps, lo, hi, gdtype, pin=False)
+            pf = GPrefetcher(info, steps, lo, hi, gdtype, pin=dev.type == "cuda")
             logged, metas = [], []
             for _ in steps:
                 _t, gm, flat = pf.get()
@@ -450,6 +468,8 @@ def run_shard(rank, world, trace_dir, t0, configs, window, horizons, device, den
             blob = {"snap_d": {h: t.cpu() for h, t in snaps.items()}, "metas": metas, "label": label.cpu()}
             if dense_cache:
                 RC.save_cache(dense_cache, ident, blob)
+            if window_g is None and sum(t.numel() * t.element_size() for t in logged) <= keep_bytes:
+                window_g = list(zip(steps, metas, logged))
             del logged
         dense[opt] = blob["snap_d"]
         labels[opt] = blob["label"]
@@ -459,8 +479,10 @@ def run_shard(rank, world, trace_dir, t0, configs, window, horizons, device, den
         d = torch.tensor([float(((dense[opt][h].double() - w0.double()) ** 2).sum()) for h in horizons],
                          dtype=torch.float64, device=dev)
         den[opt] = comms.sum_(d).tolist()
+    lap("dense_arm")
     # ---- front: branch scores ranked against the label, the window's summed squared gradient-driven step
     front = {}
+    label_sel = {}
     label_loc = labels[optimizers[0]].to(dev)
     hp_dev = RC.Hyper(wd=wd_vec.to(dev), beta1=hp.beta1, beta2=hp.beta2, eps=hp.eps, clip=hp.clip)
     for name in score_names:
@@ -468,7 +490,9 @@ def run_shard(rank, world, trace_dir, t0, configs, window, horizons, device, den
         for ratio in ratios:
             k = RC.k_for(info.numel, ratio)
             sel_s = shard_select(sc, k, comms)
-            sel_l = shard_select(label_loc, k, comms)
+            if ratio not in label_sel:
+                label_sel[ratio] = shard_select(label_loc, k, comms)
+            sel_l = label_sel[ratio]
             stats = torch.tensor([float((sel_s & sel_l).sum()), float(label_loc[~sel_s].double().sum()),
                                   float(label_loc.double().sum()), float(sc.abs()[~sel_s].double().sum()),
                                   float(sc.abs().double().sum())], dtype=torch.float64, device=dev)
@@ -486,6 +510,8 @@ def run_shard(rank, world, trace_dir, t0, configs, window, horizons, device, den
                 front[(name, ratio)] = {"k": k, "ndcg_at_k": ndcg, "recall_at_k": s[0] / max(k, 1),
                                         "missed_label_mass": s[1] / s[2] if s[2] > 0 else 0.0,
                                         "missed_score_mass": s[3] / s[4] if s[4] > 0 else 0.0}
+    del label_sel
+    lap("front")
     # ---- stream: groups of configurations, one pass over the window per group
     n_loc = hi - lo
     results, prof = {}, []
@@ -495,22 +521,26 @@ def run_shard(rank, world, trace_dir, t0, configs, window, horizons, device, den
                         dense[grp[0].optimizer] if len({c.optimizer for c in grp}) == 1 else dense[optimizers[0]],
                         use_kernel, semantics=semantics, entries=shard_entries(info, lo, hi))
         fg.initial_select(g0)
-        pf = GPrefetcher(info, steps, lo, hi, gdtype, pin=dev.type == "cuda")
+        pf = None if window_g is not None else GPrefetcher(info, steps, lo, hi, gdtype, pin=dev.type == "cuda")
         for si in range(W):
-            _t, gm, flat = pf.get()
+            _t, gm, flat = window_g[si] if pf is None else pf.get()
             fg.step(StepInput(si, flat, float(gm["grad_norm"]), float(gm["lr"][0])))
         for r, c in enumerate(grp):
             results[c] = {h: math.sqrt(fg.numer[h][r]) / math.sqrt(den[c.optimizer][hi_])
                           if den[c.optimizer][hi_] > 0 else float("nan")
                           for hi_, h in enumerate(horizons)}
-        prof.append(dict(fg.stats, configs=len(grp), read_s=pf.read_s, comm_ops=comms.ops))
+        prof.append(dict(fg.stats, configs=len(grp), read_s=pf.read_s if pf is not None else 0.0,
+                         comm_ops=comms.ops))
         last = fg
+    lap("stream")
+    if prof:
+        prof[0]["phases_s"] = phases
     if rank != 0:
         return None
     return {"t0": t0, "window_len": W, "window_steps": steps, "horizon_steps": horizons, "front": front,
             "results": results, "den_norm_at_horizon": {h: math.sqrt(den[optimizers[0]][i])
                                                         for i, h in enumerate(horizons)},
-            "profile": prof, "final_state": (last.W.cpu(), last.SEL.cpu()) if world == 1 else None}
+            "profile": prof, "final_state": (last.W.cpu(), last.SEL.cpu()) if (world == 1 and keep_state) else None}
 
 
 def _worker(rank, world, port, kwargs, out_path):
@@ -532,11 +562,11 @@ def _worker(rank, world, port, kwargs, out_path):
 
 def run_fused_branch(trace_dir, t0, configs, window, horizons, world=1, device="cpu", dense_cache=None,
                      max_configs=12, state_budget_mb=0.0, score_names=("abs_g",), ratios=(10.0,),
-                     semantics="topk"):
+                     semantics="topk", keep_state=False):
     """Replay one branch point on ``world`` shards; returns rank 0's fragment."""
     kwargs = dict(trace_dir=trace_dir, t0=t0, configs=list(configs), window=window, horizons=list(horizons),
                   device=device, dense_cache=dense_cache, max_configs=max_configs, state_budget_mb=state_budget_mb,
-                  score_names=list(score_names), ratios=list(ratios), semantics=semantics)
+                  score_names=list(score_names), ratios=list(ratios), semantics=semantics, keep_state=keep_state)
     if world == 1:
         return run_shard(0, 1, **kwargs)
     import socket

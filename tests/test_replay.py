@@ -99,7 +99,7 @@ def test_fused_one_shard_equals_per_config_oracle_bitwise(trace):
     for opt in ("adamw", "adams"):
         cfgs = [c for c in CONFIGS if c.optimizer == opt]
         frag = RF.run_fused_branch(trace, 0, cfgs, 12, horizons, world=1, device="cpu", score_names=["abs_g"],
-                                   ratios=[5.0])
+                                   ratios=[5.0], keep_state=True)
         Wf, Sf = frag["final_state"]
         dense = RC.dense_replay(w0, m0, v0, logged, lrs, hp, 0, opt, set(horizons))
         for r, c in enumerate(cfgs):
@@ -173,11 +173,11 @@ def test_dense_cache_identity(tmp_path):
 @pytest.mark.gpu
 def test_fused_gpu_kernels_match_per_config_and_cpu(trace):
     cfgs = [c for c in CONFIGS if c.optimizer == "adamw"]
-    fused = RF.run_fused_branch(trace, 0, cfgs, 12, [6, 12], device="cuda:0")
+    fused = RF.run_fused_branch(trace, 0, cfgs, 12, [6, 12], device="cuda:0", keep_state=True)
     cpu = RF.run_fused_branch(trace, 0, cfgs, 12, [6, 12], device="cpu")
     Wf = fused["final_state"][0]
     for r, c in enumerate(cfgs):
-        single = RF.run_fused_branch(trace, 0, [c], 12, [6, 12], device="cuda:0")
+        single = RF.run_fused_branch(trace, 0, [c], 12, [6, 12], device="cuda:0", keep_state=True)
         assert torch.equal(single["final_state"][0][0], Wf[r]), "R configs at once == one at a time, bit for bit"
         for h in (6, 12):
             assert fused["results"][c][h] == pytest.approx(cpu["results"][c][h], rel=1e-4, abs=1e-6)
