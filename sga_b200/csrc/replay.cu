@@ -6,9 +6,10 @@
 //                  otherwise), accumulated in fp64 with a fixed reduction
 //                  order -> the clip coefficients
 //   replay_pass3   per configuration: clip, residual update, Adam commit in
-//                  the form w * (1 - lr * wd) - lr * u (AdamW or AdamS,
-//                  optional boundary dual lr), and at horizon steps the fp64
-//                  sum of (w - w_dense)^2
+//                  the form w * (1 - lr * wd) - lr * u (AdamW or AdamS; on a
+//                  dual-lr boundary w - (w * wd + u) * step with the lane's
+//                  step size, the form of sga/replay.py:674-684), and at
+//                  horizon steps the fp64 sum of (w - w_dense)^2
 //
 // State is laid out [R, n] per array. Compiled with -fmad=false and without
 // fast-math: each fp32 operation rounds on its own, in the order of the
@@ -133,9 +134,16 @@ __global__ void __launch_bounds__(RP_THREADS) replay_pass3_kernel(
           vh = v1 / c.bc2;
         }
         const float u = mh / (sqrtf(vh) + eps);
-        const float lr = (c.dual && c.boundary && !sel) ? c.lr_inactive : c.lr;
-        const float decay = 1.0f - lr * wdi;
-        const float w1 = w0 * decay - lr * u;
+        float w1;
+        if (c.dual && c.boundary) {
+          // boundary dual lr: the whole displacement (decay term included) scales with the lane's step size
+          const float step = sel ? c.lr : c.lr_inactive;
+          const float full = w0 * wdi + u;
+          w1 = w0 - full * step;
+        } else {
+          const float decay = 1.0f - c.lr * wdi;
+          w1 = w0 * decay - c.lr * u;
+        }
         W[o] = w1;
         M[o] = m1;
         V[o] = v1;
@@ -274,9 +282,14 @@ __device__ __forceinline__ void rv_lane(const ReplayCfg& c, float g, float wdi, 
     vh = v1 / c.bc2;
   }
   const float u = mh / (sqrtf(vh) + eps);
-  const float lr = (c.dual && c.boundary && !sel) ? c.lr_inactive : c.lr;
-  const float decay = 1.0f - lr * wdi;
-  w = w0 * decay - lr * u;
+  if (c.dual && c.boundary) {
+    const float step = sel ? c.lr : c.lr_inactive;
+    const float full = w0 * wdi + u;
+    w = w0 - full * step;
+  } else {
+    const float decay = 1.0f - c.lr * wdi;
+    w = w0 * decay - c.lr * u;
+  }
   m = m1;
   v = v1;
 }

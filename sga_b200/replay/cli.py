@@ -7,12 +7,18 @@ x fold x dual-lr`` over the window, and reports the branch-point ranking
 quality of each score (NDCG@k, recall@k, missed masses against the realised
 dense displacement) and each configuration's distortion at the horizons.
 
-Report JSON (shape of ``sga/replay.py:1387-1416,2022-2070``)::
+Report JSON (keys and value forms of ``sga/replay.py:2022-2070`` and ``sga/replay_fused.py:1985-2075``; floats
+rounded to 8 decimals)::
 
-    {"trace_dir", "config": {...},
+    {"trace_dir", "config": {"branch_points", "ratios", "horizons", "device", ..., "score_names", "window", "seed"},
      "branch_results": {t0: {"t0", "state_absent", "window_len", "window_steps", "cycle_lens",
-                             "horizon_steps", "meta", "replay": {...}, "scores": {...},
-                             "per_ratio": {r: {"k", "scores": {key: {"distortion": {h: d}, "ndcg_at_k", ...}}}}}}}
+                             "horizon_steps": {h: steps replayed}, "meta": {lr, grad_norm, clip_grad, ...},
+                             "replay": {"dtype", "trace_dtype", "dense_cache_hit", "per_step": [reconstruction
+                                        check of every logged gradient], "den_norm_at_horizon", "label_total",
+                                        "label_stats", "profile"},
+                             "scores": {name: {numel, sum, mean, min, max, fraction_zero}},
+                             "per_ratio": {r: {"k", "scores": {key: {"threshold", "distortion": {h: d},
+                                                                      "ndcg_at_k", "recall_at_k", ...}}}}}}}
 
 Arm keys carry ``@T{t}``, ``@{opt}``, ``@fold``, ``@dl{g}`` suffixes only for
 axes with more than one value. CLI surface: ``sga/replay.py:1609-1797``.
@@ -51,7 +57,7 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--device", default="cpu")
     p.add_argument("--chunk-mb", type=int, default=256)
     p.add_argument("--replay-dtype", choices=("fp32", "fp64"), default="fp32")
-    p.add_argument("--norm-dtype", choices=("fp32", "fp64"), default="fp64")
+    p.add_argument("--norm-dtype", choices=("fp32", "fp64"), default="fp32")
     p.add_argument("--trace-dtype", choices=("fp32", "bf16"), default=None)
     p.add_argument("--dense-cache", default=None)
     p.add_argument("--replay-mode", choices=("zerofill", "cycle"), default="cycle")
@@ -59,9 +65,13 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--cycle-lens", default=None)
     p.add_argument("--optimizer", default="adamw", help="comma set of {adamw, adams}")
     p.add_argument("--fold", default="off", help="comma set of {off, on}")
-    p.add_argument("--dual-lr", default="1", help="comma floats")
+    p.add_argument("--dual-lr", default="1",
+                   help="comma set of boundary inactive-lr scales: floats, or T-relative multiples of each "
+                        "configuration's cycle length ('T', 'T/2')")
     p.add_argument("--fused", action="store_true", help="accepted for compatibility; the fused engine is the only one")
-    p.add_argument("--fused-shards", type=int, default=1)
+    p.add_argument("--fused-shards", type=int, default=None,
+                   help="parameter shards, one process (and GPU) each; default: min(8, visible GPUs) on cuda "
+                        "(the reference's 8 on an 8-GPU node), 1 on cpu")
     p.add_argument("--selection-semantics", choices=("topk", "balanced-histogram"), default=None,
                    help="rule behind the branch-point and boundary selections: balanced-histogram (the default of "
                         "single-node cycle replay: the online engine's stride-8, whole-crossing-bin histogram "
@@ -81,6 +91,48 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--seed", type=int, default=1234)
     p.add_argument("--verbose", action="store_true")
     return p
+
+
+def resolve_dual_lr_token(tok: str, T: int) -> float:
+    """One ``--dual-lr`` token against a cycle length: a plain float, ``T`` (the cycle length) or ``T/k``
+    (``sga/replay.py:299-331``)."""
+    s_ = tok.strip()
+    if s_ in ("T", "t"):
+        return float(T)
+    if s_[:2] in ("T/", "t/"):
+        try:
+            k = float(s_[2:])
+        except ValueError:
+            raise ValueError(f"--dual-lr token {tok!r}: the divisor after 'T/' must be a number") from None
+        if not (math.isfinite(k) and k > 0.0):
+            raise ValueError(f"--dual-lr token {tok!r}: the divisor after 'T/' must be finite > 0")
+        return float(T) / k
+    try:
+        return float(s_)
+    except ValueError:
+        raise ValueError(f"--dual-lr token {tok!r} is neither a number nor a T-relative multiple ('T', 'T/2', ...)") \
+            from None
+
+
+def parse_dual_lr_set(spec: str, Ts) -> list:
+    """Validated token list ordered by the scale at the largest cycle length; tokens must resolve to scales
+    that are finite, >= 0 and distinct (also in the report key's %g form) at every cycle length
+    (``sga/replay.py:342-378``)."""
+    toks = [t for t in str(spec).replace(" ", "").split(",") if t]
+    if not toks:
+        raise ValueError(f"--dual-lr {spec!r} names no dual-lr value")
+    if len(set(toks)) != len(toks):
+        raise ValueError(f"--dual-lr {spec!r} carries duplicate tokens")
+    at_max = {}
+    for tok in toks:
+        at_max[tok] = resolve_dual_lr_token(tok, max(Ts))
+        if not (math.isfinite(at_max[tok]) and at_max[tok] >= 0.0):
+            raise ValueError(f"--dual-lr token {tok!r} resolves to {at_max[tok]!r}; scales must be finite >= 0")
+    for T in Ts:
+        scales = [resolve_dual_lr_token(tok, T) for tok in toks]
+        if len({f"{x:g}" for x in scales}) != len(scales):
+            raise ValueError(f"--dual-lr {spec!r}: tokens collide at T={T} (resolved scales {scales})")
+    return sorted(toks, key=lambda tok: at_max[tok])
 
 
 def build_configs(ns):
@@ -107,10 +159,11 @@ def build_configs(ns):
         if o not in ("adamw", "adams"):
             raise ValueError(f"unknown optimizer '{o}'")
     folds = [f == "on" for f in str(ns.fold).split(",") if f]
-    duals = _floats(ns.dual_lr)
+    duals = parse_dual_lr_set(ns.dual_lr, Ts if ns.replay_mode == "cycle" else [1])
+    ns.dual_lr_set = duals
     multi = {"cycle_len": len(Ts) > 1, "optimizer": len(opts) > 1, "fold": len(folds) > 1, "dual_lr": len(duals) > 1}
-    cfgs = [RC.CycleConfig(s, r, T, o, f, d) for o in opts for f in folds for d in duals for T in Ts for r in ratios
-            for s in scores]
+    cfgs = [RC.CycleConfig(s, r, T, o, f, resolve_dual_lr_token(d, T)) for o in opts for f in folds for d in duals
+            for T in Ts for r in ratios for s in scores]
     return cfgs, scores, ratios, Ts, multi
 
 
@@ -138,16 +191,43 @@ def self_check(trace_dir, t_from, t_to, device="cpu") -> dict:
     return {"from": t_from, "to": t_to, "max_abs_err": err, "scale": float(want.abs().max())}
 
 
-def sanitize(obj):
+def sanitize(obj, nd=8):
+    """JSON-safe copy with floats rounded to ``nd`` decimals (``sga/replay.py:1544-1561``, called with 8)."""
     if isinstance(obj, dict):
-        return {str(k): sanitize(v) for k, v in obj.items()}
+        return {str(k): sanitize(v, nd) for k, v in obj.items()}
     if isinstance(obj, (list, tuple)):
-        return [sanitize(v) for v in obj]
-    if isinstance(obj, float) and (math.isnan(obj) or math.isinf(obj)):
-        return None
+        return [sanitize(v, nd) for v in obj]
+    if isinstance(obj, float):
+        return None if (math.isnan(obj) or math.isinf(obj)) else round(obj, nd)
     if isinstance(obj, torch.Tensor):
-        return obj.tolist()
+        return sanitize(obj.tolist(), nd)
     return obj
+
+
+def report_config(ns, bps, scores, ratios, Ts) -> dict:
+    """The ``config`` block of the report, keys and value forms of ``sga/replay.py:2022-2070``: the
+    per-configuration axes and the selection rule are echoed only when they differ from the defaults."""
+    cfg = {"branch_points": list(bps), "ratios": list(ratios), "horizons": _ints(ns.horizons) if ns.horizons else None,
+           "device": ns.device, "chunk_mb": ns.chunk_mb, "replay_dtype": ns.replay_dtype,
+           "trace_dtype": ns.trace_dtype, "norm_dtype": ns.norm_dtype, "dense_cache": ns.dense_cache,
+           "replay_mode": ns.replay_mode, "cycle_len": ns.cycle_len, "cycle_lens": list(Ts), "fused": bool(ns.fused),
+           "fused_effective": True, "fused_shards": ns.fused_shards, "fused_max_configs": ns.fused_max_configs,
+           "nodes": ns.nodes, "fused_g_residency": bool(ns.fused_g_residency),
+           "fused_dev_reduce": bool(ns.fused_dev_reduce), "score_names": list(scores), "window": ns.window,
+           "seed": ns.seed}
+    if ns.fused_state_budget_mb and ns.fused_state_budget_mb > 0:
+        cfg["fused_state_budget_mb"] = ns.fused_state_budget_mb
+    opts = sorted({o for o in str(ns.optimizer).split(",") if o})
+    if opts != ["adamw"]:
+        cfg["optimizer"] = opts
+    folds = [f for f in str(ns.fold).split(",") if f]
+    if folds != ["off"]:
+        cfg["fold"] = folds
+    if getattr(ns, "dual_lr_set", ["1"]) != ["1"]:
+        cfg["dual_lr"] = list(ns.dual_lr_set)
+    if ns.selection_semantics != "topk":
+        cfg["selection_semantics"] = ns.selection_semantics
+    return cfg
 
 
 def run(ns) -> dict:
@@ -156,8 +236,12 @@ def run(ns) -> dict:
         raise ValueError(f"--trace-dtype {ns.trace_dtype} but the trace stores {info.g_dtype}")
     cfgs, scores, ratios, Ts, multi = build_configs(ns)
     bps = info.branch_points if ns.branch_point == "all" else _ints(ns.branch_point)
-    report = {"trace_dir": os.path.abspath(ns.trace_dir),
-              "config": {k: v for k, v in vars(ns).items() if k not in ("out",)}, "branch_results": {}}
+    ns.trace_dtype = ns.trace_dtype or info.g_dtype
+    if ns.fused_shards is None:
+        ns.fused_shards = min(8, torch.cuda.device_count()) if str(ns.device).startswith("cuda") else 1
+        ns.fused_shards = max(1, ns.fused_shards)
+    report = {"trace_dir": os.path.abspath(ns.trace_dir), "config": report_config(ns, bps, scores, ratios, Ts),
+              "branch_results": {}}
     if ns.self_check:
         report["self_check"] = self_check(ns.trace_dir, ns.self_check[0], ns.self_check[1], ns.device)
     for t0 in bps:
@@ -166,6 +250,8 @@ def run(ns) -> dict:
             continue
         W = len(info.window(t0, ns.window))
         horizons = _ints(ns.horizons) if ns.horizons else [W]
+        if report["config"]["horizons"] is None:
+            report["config"]["horizons"] = list(horizons)
         if ns.nodes:
             from . import launch
 
@@ -175,7 +261,7 @@ def run(ns) -> dict:
                                        device=ns.device, dense_cache=ns.dense_cache,
                                        max_configs=ns.fused_max_configs, state_budget_mb=ns.fused_state_budget_mb,
                                        score_names=scores, ratios=ratios, semantics=ns.selection_semantics)
-        meta, _ = RC.load_state(info, t0)
+        meta = frag.get("state_meta") or RC.load_state(info, t0)[0]
         per_ratio = {}
         for r in ratios:
             entry = {"k": RC.k_for(info.numel, r), "scores": {}}
@@ -183,18 +269,42 @@ def run(ns) -> dict:
                 if c.ratio_percent != r:
                     continue
                 key = c.key(multi)
-                rank = frag["front"].get((c.score, r), {})
-                entry["scores"][key] = dict({"distortion": frag["results"][c]},
-                                            **{k: v for k, v in rank.items() if k != "k"})
+                rank = frag["front"].get((c.score, r, c.optimizer), {})
+                entry["scores"][key] = dict({"threshold": rank.get("threshold"), "distortion": frag["results"][c]},
+                                            **{k: v for k, v in rank.items() if k not in ("k", "threshold")})
             per_ratio[r] = entry
+        Wl = frag["window_len"]
+        lr = meta.get("lr", [])
+        # one optimizer keeps the flat views; several nest them under the optimizer's name and key the score
+        # statistics "name@optimizer" (sga/replay_fused.py:2025-2038, 2066-2068)
+        fopts = frag.get("optimizers") or ["adamw"]
+        one = len(fopts) == 1
+
+        def view(d):
+            d = d or {}
+            return d.get(fopts[0]) if one else {o: d.get(o) for o in fopts}
         report["branch_results"][t0] = {
-            "t0": t0, "state_absent": False, "window_len": frag["window_len"], "window_steps": frag["window_steps"],
-            "cycle_lens": Ts, "horizon_steps": frag["horizon_steps"],
-            "meta": {k: meta[k] for k in ("step", "phase", "clip_grad", "lr", "grad_norm") if k in meta},
-            "replay": {"dtype": ns.replay_dtype, "trace_dtype": info.g_dtype, "dense_cache_hit": None,
+            "t0": t0, "state_absent": False, "window_len": Wl, "window_steps": frag["window_steps"],
+            "cycle_lens": Ts, "horizon_steps": {str(h): max(1, min(h, Wl)) for h in horizons},
+            # the state dump's scalars, with the reference's defaults where a trace carries its
+            # hyper-parameters per parameter group only (sga/replay_fused.py:2047-2056)
+            "meta": {"lr": [float(x) for x in (lr if isinstance(lr, (list, tuple)) else [lr])],
+                     "grad_norm": float(meta.get("grad_norm", float("nan"))),
+                     "clip_grad": float(meta.get("clip_grad", 0.0)),
+                     "weight_decay": float(meta.get("weight_decay", 0.0)),
+                     "adam_beta1": float(meta.get("adam_beta1", 0.9)), "adam_beta2": float(meta.get("adam_beta2", 0.999)),
+                     "adam_eps": float(meta.get("adam_eps", 1e-8)),
+                     **{k: meta[k] for k in ("step", "phase") if k in meta}},
+            "replay": {"dtype": ns.replay_dtype, "trace_dtype": info.g_dtype,
+                       "dense_cache_hit": view(frag.get("dense_cache_hit")),
                        "g_residency": bool(ns.fused_g_residency), "dev_reduce": bool(ns.fused_dev_reduce),
-                       "den_norm_at_horizon": frag["den_norm_at_horizon"], "profile": frag["profile"]},
-            "scores": {s: {"ranked": True} for s in scores}, "per_ratio": per_ratio}
+                       "per_step": frag.get("per_step", []),
+                       "den_norm_at_horizon": view(frag["den_norm_at_horizon"]),
+                       "label_total": view(frag.get("label_total")), "label_stats": view(frag.get("label_stats")),
+                       "profile": frag["profile"]},
+            "scores": {(s if one else f"{s}@{o}"): frag.get("score_stats", {}).get((s, o), {})
+                       for s in scores for o in fopts},
+            "per_ratio": per_ratio}
     return sanitize(report)
 
 
@@ -203,7 +313,7 @@ def print_summary(report) -> None:
         if br.get("state_absent"):
             print(f"branch {t0}: state absent")
             continue
-        print(f"branch {t0}: window {br['window_len']} horizons {br['horizon_steps']}")
+        print(f"branch {t0}: window {br['window_len']} horizons {sorted(int(h) for h in br['horizon_steps'])}")
         for r, entry in br["per_ratio"].items():
             print(f"  ratio {r}% (k={entry['k']})")
             for key, s in sorted(entry["scores"].items()):

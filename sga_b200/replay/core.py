@@ -197,13 +197,17 @@ def adam_commit_torch(w, m, v, q, lr, wd, beta1, beta2, eps, count, optimizer="a
     mh, vh = (m1, v1) if adams else (_div(m1, bc1), _div(v1, bc2))
     u = mh / (torch.sqrt(vh) + eps)
     lr_t = lr if isinstance(lr, torch.Tensor) else torch.full_like(w, lr)
-    if inactive is not None and dual_lr != 1.0:
-        lr_t = torch.where(inactive, lr_t * dual_lr, lr_t)
-    decay = 1.0 - lr_t * wd
     if label is not None:
         step = lr_t * u
         label.add_(step * step)
-    w.copy_(w * decay - lr_t * u)
+    if inactive is not None and dual_lr != 1.0:
+        # boundary dual lr (sga/replay.py:674-684): the whole displacement, decay term included, times the
+        # lane's step size -- at every lane of the boundary commit, so the rounding differs from the form below
+        lr_in = lr_t * dual_lr if isinstance(lr, torch.Tensor) else torch.full_like(w, lr * dual_lr)
+        step_t = torch.where(inactive, lr_in, lr_t)
+        w.copy_(w - (w * wd + u) * step_t)
+    else:
+        w.copy_(w * (1.0 - lr_t * wd) - lr_t * u)
     m.copy_(m1)
     v.copy_(v1)
 
@@ -212,6 +216,19 @@ def clip_coef(sumsq: float, clip: float) -> float:
     if clip <= 0.0:
         return 1.0
     return min(1.0, clip / (math.sqrt(sumsq) + 1.0e-6))
+
+
+def coef_dense_for(gmeta: dict):
+    """``(coefficient, flag)``: the clip coefficient the trainer applied to a logged gradient, from the step's
+    own metadata (``min(1, clip / (norm + 1e-6))``), or 1.0 with the reason nobody clipped
+    (``sga/replay.py:628-645``)."""
+    clip = float(gmeta.get("clip_grad", 0.0))
+    norm = float(gmeta.get("grad_norm", float("nan")))
+    if clip <= 0.0:
+        return 1.0, "clipping_disabled"
+    if not math.isfinite(norm) or norm <= 0.0:
+        return 1.0, "grad_norm_unavailable"
+    return min(clip / (norm + 1.0e-6), 1.0), None
 
 
 def replay_score(name, w, m, v, q, hp: Hyper, count, optimizer="adamw"):

@@ -25,6 +25,7 @@ import ctypes
 import math
 import os
 import queue
+import struct
 import threading
 import time
 from dataclasses import dataclass
@@ -62,6 +63,12 @@ class Comms:
             dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
         return t
 
+    def min_(self, t: torch.Tensor) -> torch.Tensor:
+        if self.world > 1:
+            self.ops += 1
+            dist.all_reduce(t, op=dist.ReduceOp.MIN, group=self.group)
+        return t
+
     def gather_i64(self, value: int) -> list:
         if self.world == 1:
             return [int(value)]
@@ -91,11 +98,17 @@ def shard_bounds(n: int, world: int, rank: int):
     return lo, min(n, lo + per)
 
 
-def shard_select(score_loc: torch.Tensor, k: int, comms: Comms) -> torch.Tensor:
+def _key_float(key: int) -> float:
+    """The non-negative fp32 whose bit pattern is ``key``."""
+    return struct.unpack("<f", struct.pack("<I", key & 0x7FFFFFFF))[0]
+
+
+def shard_select(score_loc: torch.Tensor, k: int, comms: Comms, return_threshold: bool = False):
     """Exact distributed top-``k`` by ``|score|`` with ties filled in global
     flat-index order (shards are contiguous and ordered by rank). Two radix
     digits: the 16 high key bits locate the crossing bin, the 16 low bits the
-    exact key; no candidate values cross the wire."""
+    exact key; no candidate values cross the wire. ``return_threshold`` also
+    returns the k-th largest ``|score|``."""
     from ..plugins.selection._histogram import _ops
 
     ops = _ops(score_loc)
@@ -124,7 +137,29 @@ def shard_select(score_loc: torch.Tensor, k: int, comms: Comms) -> torch.Tensor:
     take = max(0, min(ties.numel(), need - before))
     if take:
         sel[ties[:take]] = True
-    return sel
+    return (sel, _key_float(T)) if return_threshold else sel
+
+
+def _unclip(g: torch.Tensor, gmeta: dict, dev) -> torch.Tensor:
+    """The logged (clipped) gradient divided by the clip coefficient its step applied."""
+    coef, _flag = RC.coef_dense_for(gmeta)
+    return g.to(dev).float() / coef
+
+
+def shard_stats(flat: torch.Tensor, comms: Comms) -> dict:
+    """numel / sum / mean / min / max / fraction of zeros of a sharded vector: shard-partial sums
+    combined in fp64, the rest exact (``sga/replay_fused.py:2085-2112``)."""
+    n = flat.numel()
+    row = torch.tensor([float(n), float(flat.sum()) if n else 0.0, float((flat == 0).sum()) if n else 0.0],
+                       dtype=torch.float64, device=comms.device)
+    ext = torch.tensor([float(flat.min()) if n else float("inf"), -float(flat.max()) if n else float("inf")],
+                       dtype=torch.float64, device=comms.device)
+    comms.sum_(row)
+    comms.min_(ext)
+    total, ssum, nzero = int(row[0]), float(row[1]), int(row[2])
+    return {"numel": total, "sum": ssum, "mean": ssum / total if total else 0.0,
+            "min": float(ext[0]) if total else 0.0, "max": -float(ext[1]) if total else 0.0,
+            "fraction_zero": nzero / total if total else 0.0}
 
 
 def shard_entries(info, lo: int, hi: int) -> list:
@@ -138,7 +173,7 @@ def shard_entries(info, lo: int, hi: int) -> list:
     return out
 
 
-def shard_select_balanced(score_loc: torch.Tensor, k: int, comms: Comms, entries) -> torch.Tensor:
+def shard_select_balanced(score_loc: torch.Tensor, k: int, comms: Comms, entries, return_threshold: bool = False):
     """The online engine's ``balanced`` histogram selection replayed on a sharded flat vector
     (``sga/replay_fused.py:405-489``): the histogram of the 16 high key bits is built on every 8th
     element of each parameter, on the parameter's own grid (a shard that starts inside a parameter
@@ -167,7 +202,8 @@ def shard_select_balanced(score_loc: torch.Tensor, k: int, comms: Comms, entries
     counts = torch.tensor([n_tot, n_smp], dtype=torch.int64, device=x.device)
     comms.sum_(counts)
     b = balanced_crossing_bin(hist, int(counts[0]), int(counts[1]), k, replicas=1)
-    return (RC.abs_key(x) >> shift) >= b
+    sel = (RC.abs_key(x) >> shift) >= b
+    return (sel, _key_float(int(b) << shift)) if return_threshold else sel  # threshold: the bin's lower edge
 
 
 @dataclass
@@ -288,7 +324,7 @@ class FusedGroup:
             plan.append(dict(
                 boundary=boundary, fold=bool(c.fold and boundary and si > 0), fold_div=float(c.cycle_len),
                 dual=bool(c.dual_lr != 1.0), adams=adams, lr=lr32,
-                lr_inactive=float(torch.tensor(lr, dtype=torch.float32) * c.dual_lr),
+                lr_inactive=RC.f32(lr * c.dual_lr),
                 bc1=1.0 if adams else 1.0 - self.hp.beta1 ** count, bc2=1.0 if adams else 1.0 - self.hp.beta2 ** count,
                 horizon=(si + 1) in self.dense, coef=1.0))
         return plan
@@ -395,13 +431,17 @@ class FusedGroup:
 
 # --------------------------------------------------------------------- driver
 def group_configs(configs, max_configs: int, state_budget_mb: float, n_loc: int):
-    """Cut the configuration list into groups that fit ``max_configs`` and, when
-    given, a per-shard state budget (17 bytes per element per configuration)."""
+    """Cut the configuration list into groups of one optimizer that fit ``max_configs`` and,
+    when given, a per-shard state budget (17 bytes per element per configuration)."""
     per_cfg = 17.0 * n_loc / (1 << 20)
     cap = max(1, min(32, max_configs))
     if state_budget_mb and state_budget_mb > 0:
         cap = max(1, min(cap, int(state_budget_mb // max(per_cfg, 1e-9))))
-    return [configs[i:i + cap] for i in range(0, len(configs), cap)]
+    groups = []
+    for opt in sorted({c.optimizer for c in configs}):  # a group shares one dense trajectory: one optimizer
+        part = [c for c in configs if c.optimizer == opt]
+        groups += [part[i:i + cap] for i in range(0, len(part), cap)]
+    return groups
 
 
 def run_shard(rank, world, trace_dir, t0, configs, window, horizons, device, dense_cache, max_configs,
@@ -450,9 +490,11 @@ def run_shard(rank, world, trace_dir, t0, configs, window, horizons, device, den
     window_g = None
     keep_bytes = int(float(os.environ.get(ENV_WINDOW_HOST_GIB, "8")) * (1 << 30))
     lap("setup")
+    cache_hit = {}
     for opt in optimizers:
-        ident = RC.cache_ident(trace_dir, t0, W, horizons, "fp32", info.g_dtype, f"fused-v2-{world}-{rank}", opt)
+        ident = RC.cache_ident(trace_dir, t0, W, horizons, "fp32", info.g_dtype, f"fused-v3-{world}-{rank}", opt)
         blob = RC.load_cache(dense_cache, ident) if dense_cache else None
+        cache_hit[opt] = blob is not None
         if blob is None:
             pf = GPrefetcher(info, steps, lo, hi, gdtype, pin=dev.type == "cuda")
             logged, metas = [], []
@@ -465,51 +507,66 @@ def run_shard(rank, world, trace_dir, t0, configs, window, horizons, device, den
             label = torch.zeros_like(w0, device=dev)
             snaps = RC.dense_replay(w0.to(dev), m0.to(dev), v0.to(dev), logged, [gm["lr"][0] for gm in metas], hp_d,
                                     t0, opt, set(horizons), label_out=label)
-            blob = {"snap_d": {h: t.cpu() for h, t in snaps.items()}, "metas": metas, "label": label.cpu()}
+            # reconstruction check of the logged gradients: the norm of g / coef over the whole vector
+            recon = torch.stack([(_unclip(g, gm, dev).double() ** 2).sum() for g, gm in zip(logged, metas)])
+            recon = comms.sum_(recon.to(torch.float64)).tolist()
+            blob = {"snap_d": snaps, "metas": metas, "label": label, "recon2": recon}  # stays on the replay device
             if dense_cache:
-                RC.save_cache(dense_cache, ident, blob)
+                RC.save_cache(dense_cache, ident, {"snap_d": {h: t.cpu() for h, t in snaps.items()}, "metas": metas,
+                                                   "label": label.cpu(), "recon2": recon})
             if window_g is None and sum(t.numel() * t.element_size() for t in logged) <= keep_bytes:
                 window_g = list(zip(steps, metas, logged))
             del logged
         dense[opt] = blob["snap_d"]
         labels[opt] = blob["label"]
         metas = blob["metas"]
+        recon2 = blob["recon2"]
     den = {}
+    w0_dev = w0.to(dev)
     for opt in optimizers:
-        d = torch.tensor([float(((dense[opt][h].double() - w0.double()) ** 2).sum()) for h in horizons],
-                         dtype=torch.float64, device=dev)
-        den[opt] = comms.sum_(d).tolist()
+        d = torch.stack([((dense[opt][h].to(dev).double() - w0_dev.double()) ** 2).sum() for h in horizons])
+        den[opt] = comms.sum_(d.to(torch.float64)).tolist()
+    del w0_dev
     lap("dense_arm")
     # ---- front: branch scores ranked against the label, the window's summed squared gradient-driven step
     front = {}
-    label_sel = {}
-    label_loc = labels[optimizers[0]].to(dev)
     hp_dev = RC.Hyper(wd=wd_vec.to(dev), beta1=hp.beta1, beta2=hp.beta2, eps=hp.eps, clip=hp.clip)
-    for name in score_names:
-        sc = RC.replay_score(name, w0.to(dev), m0.to(dev), v0.to(dev), g0.to(dev), hp_dev, t0 + 1, optimizers[0])
-        for ratio in ratios:
-            k = RC.k_for(info.numel, ratio)
-            sel_s = shard_select(sc, k, comms)
-            if ratio not in label_sel:
-                label_sel[ratio] = shard_select(label_loc, k, comms)
-            sel_l = label_sel[ratio]
-            stats = torch.tensor([float((sel_s & sel_l).sum()), float(label_loc[~sel_s].double().sum()),
-                                  float(label_loc.double().sum()), float(sc.abs()[~sel_s].double().sum()),
-                                  float(sc.abs().double().sum())], dtype=torch.float64, device=dev)
-            comms.sum_(stats)
-            got_s = comms.gather_to_root(sc.abs()[sel_s].float())
-            got_l = comms.gather_to_root(label_loc[sel_s].float())
-            ideal = comms.gather_to_root(label_loc[sel_l].float())
-            if rank == 0:
-                disc = 1.0 / torch.log2(torch.arange(2, k + 2, dtype=torch.float64, device=dev))
-                order = torch.argsort(got_s, descending=True, stable=True)
-                idl = torch.sort(ideal.double(), descending=True).values
-                idcg = float((idl * disc[:idl.numel()]).sum())
-                ndcg = float((got_l.double()[order] * disc[:order.numel()]).sum()) / idcg if idcg > 0 else 0.0
-                s = stats.tolist()
-                front[(name, ratio)] = {"k": k, "ndcg_at_k": ndcg, "recall_at_k": s[0] / max(k, 1),
-                                        "missed_label_mass": s[1] / s[2] if s[2] > 0 else 0.0,
-                                        "missed_score_mass": s[3] / s[4] if s[4] > 0 else 0.0}
+    score_stats, thresholds, label_stats = {}, {}, {}
+    entries = shard_entries(info, lo, hi)
+    for opt in optimizers:
+        label_sel = {}
+        label_loc = labels[opt].to(dev)
+        label_stats[opt] = shard_stats(label_loc, comms)
+        for name in score_names:
+            sc = RC.replay_score(name, w0.to(dev), m0.to(dev), v0.to(dev), g0.to(dev), hp_dev, t0 + 1, opt)
+            score_stats[(name, opt)] = shard_stats(sc.abs(), comms)
+            for ratio in ratios:
+                k = RC.k_for(info.numel, ratio)
+                sel_s, th = shard_select(sc, k, comms, return_threshold=True)
+                if semantics == "balanced-histogram":  # the trajectory's rule reports the crossing bin's lower edge
+                    th = shard_select_balanced(sc, k, comms, entries, return_threshold=True)[1]
+                thresholds[(name, ratio, opt)] = th
+                if ratio not in label_sel:
+                    label_sel[ratio] = shard_select(label_loc, k, comms)
+                sel_l = label_sel[ratio]
+                stats = torch.tensor([float((sel_s & sel_l).sum()), float(label_loc[~sel_s].double().sum()),
+                                      float(label_loc.double().sum()), float(sc.abs()[~sel_s].double().sum()),
+                                      float(sc.abs().double().sum())], dtype=torch.float64, device=dev)
+                comms.sum_(stats)
+                got_s = comms.gather_to_root(sc.abs()[sel_s].float())
+                got_l = comms.gather_to_root(label_loc[sel_s].float())
+                ideal = comms.gather_to_root(label_loc[sel_l].float())
+                if rank == 0:
+                    disc = 1.0 / torch.log2(torch.arange(2, k + 2, dtype=torch.float64, device=dev))
+                    order = torch.argsort(got_s, descending=True, stable=True)
+                    idl = torch.sort(ideal.double(), descending=True).values
+                    idcg = float((idl * disc[:idl.numel()]).sum())
+                    ndcg = float((got_l.double()[order] * disc[:order.numel()]).sum()) / idcg if idcg > 0 else 0.0
+                    s = stats.tolist()
+                    front[(name, ratio, opt)] = {"k": k, "threshold": th, "ndcg_at_k": ndcg,
+                                                 "recall_at_k": s[0] / max(k, 1),
+                                                 "missed_label_mass": s[1] / s[2] if s[2] > 0 else 0.0,
+                                                 "missed_score_mass": s[3] / s[4] if s[4] > 0 else 0.0}
     del label_sel
     lap("front")
     # ---- stream: groups of configurations, one pass over the window per group
@@ -518,8 +575,8 @@ def run_shard(rank, world, trace_dir, t0, configs, window, horizons, device, den
     for grp in group_configs(configs, max_configs, state_budget_mb, n_loc):
         by_opt = {}
         fg = FusedGroup(grp, n_loc, info.numel, dev, comms, hp, wd_vec, w0, m0, v0, t0, W, horizons,
-                        dense[grp[0].optimizer] if len({c.optimizer for c in grp}) == 1 else dense[optimizers[0]],
-                        use_kernel, semantics=semantics, entries=shard_entries(info, lo, hi))
+                        dense[grp[0].optimizer],
+                        use_kernel, semantics=semantics, entries=entries)
         fg.initial_select(g0)
         pf = None if window_g is not None else GPrefetcher(info, steps, lo, hi, gdtype, pin=dev.type == "cuda")
         for si in range(W):
@@ -537,9 +594,24 @@ def run_shard(rank, world, trace_dir, t0, configs, window, horizons, device, den
         prof[0]["phases_s"] = phases
     if rank != 0:
         return None
+    per_step = []
+    for t, gm, r2 in zip(steps, metas, recon2):
+        coef, flag = RC.coef_dense_for(gm)
+        norm = float(gm.get("grad_norm", float("nan")))
+        lrs = [float(x) for x in gm.get("lr", [])]
+        mean_lr = sum(lrs) / len(lrs) if lrs else 0.0
+        rn = math.sqrt(r2)
+        per_step.append({"step": t, "lr": mean_lr, "lr_max_abs_diff": max((abs(x - mean_lr) for x in lrs), default=0.0),
+                         "grad_norm": norm, "clip_grad": float(gm.get("clip_grad", 0.0)), "coef_dense": coef,
+                         "reconstruct_flag": flag, "recon_grad_norm": rn,
+                         "recon_rel_err": (rn - norm) / norm if (math.isfinite(norm) and norm > 0.0) else None})
     return {"t0": t0, "window_len": W, "window_steps": steps, "horizon_steps": horizons, "front": front,
-            "results": results, "den_norm_at_horizon": {h: math.sqrt(den[optimizers[0]][i])
-                                                        for i, h in enumerate(horizons)},
+            "score_stats": score_stats, "label_stats": label_stats,
+            "label_total": {opt: label_stats[opt]["sum"] for opt in optimizers},
+            "per_step": per_step, "dense_cache_hit": cache_hit, "state_meta": meta,
+            "results": results, "optimizers": optimizers,
+            "den_norm_at_horizon": {opt: {h: math.sqrt(den[opt][i]) for i, h in enumerate(horizons)}
+                                    for opt in optimizers},
             "profile": prof, "final_state": (last.W.cpu(), last.SEL.cpu()) if (world == 1 and keep_state) else None}
 
 

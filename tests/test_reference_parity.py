@@ -445,3 +445,84 @@ def test_engine_flow_matches_reference_engine_multirank(world):
                           os.path.join(ROOT, "tests", "ref_parity_worker.py")], capture_output=True, text=True,
                          timeout=600, cwd=ROOT)
     assert res.returncode == 0 and "PARITY OK" in res.stdout, (res.stdout[-1500:], res.stderr[-1500:])
+
+
+@pytest.mark.skipif(not os.path.exists(os.path.join(REF, "tests", "ref_engine_harness.py")),
+                    reason="no copy of the reference's engine test harness under baseline/_ref/tests")
+def test_replay_reports_equal_on_a_trace_written_by_the_reference(ref, monkeypatch, tmp_path):
+    """The other direction of the trace format: the reference engine and its trace collector write a
+    trace (CPU, the reference's own fakes), then both replay CLIs run every per-configuration axis on it
+    (two optimizers, fold off / on, plain and T-relative dual lr, two cycle lengths, default
+    balanced-histogram semantics). The whole report must agree: same keys and nesting, every number
+    (distortions, thresholds, ranking metrics, score and label statistics, the per-step reconstruction
+    check) to 5e-8; this framework adds ``step`` / ``phase`` to ``meta`` and a ``profile`` block."""
+    import copy
+    import types
+
+    from sga_b200.replay import cli
+
+    mods = {n: types.ModuleType(n) for n in ("megatron", "megatron.core", "megatron.core.tensor_parallel",
+                                             "megatron.core.transformer", "megatron.core.transformer.module")}
+    mods["megatron.core.tensor_parallel"].param_is_not_tensor_parallel_duplicate = lambda p, g=None: True
+    mods["megatron.core.transformer.module"].param_is_not_shared = lambda p: True
+    for n, m in mods.items():
+        monkeypatch.setitem(sys.modules, n, m)
+    monkeypatch.setenv("SGA_ALLOW_FROZEN_SELECTION", "1")
+    monkeypatch.syspath_prepend(os.path.join(REF, "tests"))
+    ref("sga.engine")
+    H = importlib.import_module("ref_engine_harness")
+    tdir = str(tmp_path / "trace")
+    torch.manual_seed(3)
+    chunk = H._FakeChunk(n_params=3, numel_per=4096)
+    mp = H._FakeMPOpt(chunk)
+    eng = H._build_engine(copy.deepcopy(H._ABS_M), {"sga_trace_dir": tdir, "sga_trace_branch_points": [3],
+                                                    "sga_trace_window": 6})
+    eng.attach(chunk)
+    gen = torch.Generator().manual_seed(4)
+    with H._ReplicaWorld(world=1):
+        for step in range(1, 12):
+            chunk.bucket.grad_data += torch.randn(chunk.bucket.grad_data.numel(), generator=gen)
+            eng.grad_sync(chunk, force_all_reduce=False)
+            eng.optimizer_step(mp, [chunk], step)
+    assert os.path.exists(os.path.join(tdir, "step_000003_state.pt"))
+    hide = tmp_path / "hide" / "triton"
+    hide.mkdir(parents=True)
+    (hide / "__init__.py").write_text('raise ImportError("hidden")\n')
+    common = ["--trace-dir", tdir, "--branch-point", "3", "--ratios", "5", "--replay-mode", "cycle", "--cycle-lens", "2,3",
+              "--score-names", "abs_g,update", "--window", "6", "--device", "cpu", "--optimizer", "adamw,adams",
+              "--fold", "off,on", "--dual-lr", "1,T/4", "--fused-shards", "1", "--dense-cache"]
+    ref_out, our_out = str(tmp_path / "ref.json"), str(tmp_path / "our.json")
+    env = dict(os.environ, PYTHONPATH=str(tmp_path / "hide") + os.pathsep + REF)
+    res = subprocess.run([sys.executable, "-m", "sga.replay"] + common + [str(tmp_path / "rc"), "--out", ref_out], env=env,
+                         capture_output=True, text=True, cwd=str(tmp_path))
+    assert res.returncode == 0, res.stderr[-2000:]
+    assert cli.main(common + [str(tmp_path / "oc"), "--out", our_out]) == 0
+    a, b = json.load(open(ref_out)), json.load(open(our_out))
+    diffs = []
+
+    def walk(x, y, path):
+        if isinstance(x, dict):
+            if not isinstance(y, dict):
+                return diffs.append((path, "type"))
+            for k in x:
+                if k not in y:
+                    diffs.append((path + "/" + k, "missing"))
+                else:
+                    walk(x[k], y[k], path + "/" + k)
+            diffs.extend((path + "/" + k, "extra") for k in y if k not in x)
+        elif isinstance(x, list):
+            if not isinstance(y, list) or len(x) != len(y):
+                return diffs.append((path, "list"))
+            for i, (p, q) in enumerate(zip(x, y)):
+                walk(p, q, f"{path}[{i}]")
+        elif isinstance(x, float) or isinstance(y, float):
+            if x is None or y is None or abs(x - y) > 6e-8 * max(1.0, abs(x)):
+                diffs.append((path, x, y))
+        elif x != y:
+            diffs.append((path, x, y))
+
+    walk(a, b, "")
+    allowed = {"/config/dense_cache", "/branch_results/3/meta/step", "/branch_results/3/meta/phase",
+               "/branch_results/3/replay/profile"}
+    assert not [d for d in diffs if d[0] not in allowed], diffs[:10]
+    assert len(a["branch_results"]["3"]["per_ratio"]["5.0"]["scores"]) == 32

@@ -109,7 +109,7 @@ def test_fused_one_shard_equals_per_config_oracle_bitwise(trace):
                 want = RC.distortion(snaps[h], dense[h], w0)
                 assert frag["results"][c][h] == pytest.approx(want, rel=1e-12)
         assert frag["window_len"] == 12 and frag["horizon_steps"] == horizons
-    m = frag["front"][("abs_g", 5.0)]
+    m = frag["front"][("abs_g", 5.0, opt)]
     assert m["k"] == RC.k_for(sum(SIZES), 5.0) and 0.0 <= m["recall_at_k"] <= 1.0
 
 
@@ -130,8 +130,11 @@ def test_fused_two_shards_stay_in_the_reordering_band(trace):
 
 
 def test_grouping_and_kill_switches(trace, monkeypatch):
-    assert [len(g) for g in RF.group_configs(list(range(10)), 4, 0, 1000)] == [4, 4, 2]
-    assert [len(g) for g in RF.group_configs(list(range(5)), 12, 17 * 2 * 1e6 / (1 << 20), 1000000)] == [2, 2, 1]
+    mk = lambda n, opt="adamw": [RC.CycleConfig("abs_g", float(i + 1), 4, opt) for i in range(n)]  # noqa: E731
+    assert [len(g) for g in RF.group_configs(mk(10), 4, 0, 1000)] == [4, 4, 2]
+    assert [len(g) for g in RF.group_configs(mk(5), 12, 17 * 2 * 1e6 / (1 << 20), 1000000)] == [2, 2, 1]
+    mixed = RF.group_configs(mk(3) + mk(3, "adams"), 12, 0, 1000)
+    assert [len(g) for g in mixed] == [3, 3] and all(len({c.optimizer for c in g}) == 1 for g in mixed)
     a = RF.run_fused_branch(trace, 0, CONFIGS[:3], 12, [12], max_configs=1)
     b = RF.run_fused_branch(trace, 0, CONFIGS[:3], 12, [12], max_configs=12)
     assert all(a["results"][c][12] == b["results"][c][12] for c in CONFIGS[:3]), "grouping must not change results"

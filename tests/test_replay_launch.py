@@ -32,7 +32,7 @@ def test_cli_report_shape(trace, tmp_path, capsys):
     rep = _cli(trace, tmp_path)
     assert set(rep) >= {"trace_dir", "config", "branch_results"}
     br = rep["branch_results"]["0"]
-    assert br["window_len"] == 8 and br["horizon_steps"] == [4, 8] and br["cycle_lens"] == [1, 4]
+    assert br["window_len"] == 8 and br["horizon_steps"] == {"4": 4, "8": 8} and br["cycle_lens"] == [1, 4]
     assert set(br["per_ratio"]) == {"5.0", "20.0"}
     keys = set(br["per_ratio"]["5.0"]["scores"])
     assert keys == {"abs_g@T1", "abs_g@T4", "update@T1", "update@T4"}, "suffix only for multi-valued axes"
