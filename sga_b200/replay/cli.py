@@ -60,23 +60,26 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--norm-dtype", choices=("fp32", "fp64"), default="fp32")
     p.add_argument("--trace-dtype", choices=("fp32", "bf16"), default=None)
     p.add_argument("--dense-cache", default=None)
-    p.add_argument("--replay-mode", choices=("zerofill", "cycle"), default="cycle")
+    p.add_argument("--replay-mode", choices=("zerofill", "cycle"), default="zerofill",
+                   help="zerofill (default): frozen support, the gradient zero-filled outside it on every step of "
+                        "the window, re-clipped on its own norm, AdamW. cycle: residual accumulation, boundary "
+                        "merge (and fold) and re-selection every --cycle-len steps")
     p.add_argument("--cycle-len", type=int, default=None)
     p.add_argument("--cycle-lens", default=None)
-    p.add_argument("--optimizer", default="adamw", help="comma set of {adamw, adams}")
-    p.add_argument("--fold", default="off", help="comma set of {off, on}")
-    p.add_argument("--dual-lr", default="1",
+    p.add_argument("--optimizer", default=None, help="comma set of {adamw, adams} (cycle mode; default adamw)")
+    p.add_argument("--fold", default=None, help="comma set of {off, on} (cycle mode; default off)")
+    p.add_argument("--dual-lr", default=None,
                    help="comma set of boundary inactive-lr scales: floats, or T-relative multiples of each "
                         "configuration's cycle length ('T', 'T/2')")
     p.add_argument("--fused", action="store_true", help="accepted for compatibility; the fused engine is the only one")
     p.add_argument("--fused-shards", type=int, default=None,
                    help="parameter shards, one process (and GPU) each; default: min(8, visible GPUs) on cuda "
                         "(the reference's 8 on an 8-GPU node), 1 on cpu")
-    p.add_argument("--selection-semantics", choices=("topk", "balanced-histogram"), default=None,
-                   help="rule behind the branch-point and boundary selections: balanced-histogram (the default of "
-                        "single-node cycle replay: the online engine's stride-8, whole-crossing-bin histogram "
-                        "mode) or topk (exact global top-k with index-ordered ties; the default with --nodes and "
-                        "for zerofill)")
+    p.add_argument("--selection-semantics", choices=("topk", "balanced-histogram"), default="balanced-histogram",
+                   help="rule behind the branch-point and boundary selections: balanced-histogram (default: the "
+                        "online engine's stride-8, whole-crossing-bin histogram mode; single-node cycle replay "
+                        "only) or topk (exact global top-k with index-ordered ties; zerofill and --nodes need it "
+                        "spelled out)")
     p.add_argument("--fused-max-configs", type=int, default=12)
     p.add_argument("--fused-state-budget-mb", type=float, default=0.0)
     p.add_argument("--nodes", default=None, help="comma host list for a multi-node replay")
@@ -143,23 +146,43 @@ def build_configs(ns):
         if s not in score_names():
             raise ValueError(f"unknown score '{s}' (registered: {score_names()})")
     ratios = _floats(ns.ratios)
-    if ns.cycle_len is not None and ns.cycle_lens is not None:
+    if ns.cycle_len is not None and ns.cycle_lens:
         raise ValueError("give --cycle-len or --cycle-lens, not both")
-    Ts = [ns.cycle_len] if ns.cycle_len is not None else (_ints(ns.cycle_lens) if ns.cycle_lens else [1])
-    # the reference's defaults (sga/replay.py:1703-1715, 1876-1882): single-node cycle replay selects by
-    # the online balanced-histogram rule; zerofill and multi-node replays need exact top-k
-    if ns.selection_semantics is None:
-        ns.selection_semantics = "balanced-histogram" if (ns.replay_mode == "cycle" and not ns.nodes) else "topk"
-    if ns.selection_semantics == "balanced-histogram" and (ns.replay_mode != "cycle" or ns.nodes):
-        raise ValueError("--selection-semantics balanced-histogram requires --replay-mode cycle on a single node")
+    # sga/replay.py:1813-1835: --cycle-lens is a comma set, --cycle-len its single spelling (default 20, echoed
+    # into the report even where zerofill does not use it)
+    if ns.cycle_lens:
+        Ts = sorted(set(_ints(ns.cycle_lens)))
+    else:
+        if ns.cycle_len is None:
+            ns.cycle_len = 20
+        Ts = [ns.cycle_len]
+    if any(t < 1 for t in Ts):
+        raise ValueError(f"cycle lengths must be >= 1 (got {Ts})")
+    # sga/replay.py:1840-1882: the per-configuration axes exist in cycle mode only; balanced-histogram is the
+    # default everywhere and is refused, not silently replaced, where only exact top-k exists (a dense
+    # --self-check selects nothing and needs no override)
+    if (ns.optimizer is not None or ns.fold is not None or ns.dual_lr is not None) and ns.replay_mode != "cycle":
+        raise ValueError("--optimizer/--fold/--dual-lr are only supported with --replay-mode cycle")
+    if ns.replay_mode == "cycle" and ns.self_check is not None:
+        raise ValueError("--replay-mode cycle cannot be combined with --self-check")
+    if ns.nodes and ns.replay_mode != "cycle":
+        raise ValueError("--nodes is only supported with --replay-mode cycle")
+    if ns.self_check is None and ns.selection_semantics != "topk" and (ns.replay_mode != "cycle" or ns.nodes):
+        raise ValueError("--selection-semantics balanced-histogram requires --replay-mode cycle on a single node "
+                         "(zerofill and --nodes require an explicit --selection-semantics topk)")
+    ns.report_cycle_lens = list(Ts)
     if ns.replay_mode == "zerofill":
-        Ts = [10 ** 9]  # never a second boundary: unselected gradient mass just accumulates
-    opts = [o for o in str(ns.optimizer).split(",") if o]
+        Ts = [0]  # never a boundary: frozen support, zero-filled gradient on every step
+    opts = sorted({o for o in str(ns.optimizer or "adamw").replace(" ", "").split(",") if o})
     for o in opts:
         if o not in ("adamw", "adams"):
             raise ValueError(f"unknown optimizer '{o}'")
-    folds = [f == "on" for f in str(ns.fold).split(",") if f]
-    duals = parse_dual_lr_set(ns.dual_lr, Ts if ns.replay_mode == "cycle" else [1])
+    fold_toks = [f for f in str(ns.fold or "off").replace(" ", "").split(",") if f]
+    if any(f not in ("off", "on") for f in fold_toks) or len(set(fold_toks)) != len(fold_toks):
+        raise ValueError(f"--fold {ns.fold!r}: a comma set of off / on")
+    folds = sorted({f == "on" for f in fold_toks})
+    ns.optimizer_set, ns.fold_set = opts, folds
+    duals = parse_dual_lr_set(ns.dual_lr, Ts) if ns.dual_lr is not None else ["1"]
     ns.dual_lr_set = duals
     multi = {"cycle_len": len(Ts) > 1, "optimizer": len(opts) > 1, "fold": len(folds) > 1, "dual_lr": len(duals) > 1}
     cfgs = [RC.CycleConfig(s, r, T, o, f, resolve_dual_lr_token(d, T)) for o in opts for f in folds for d in duals
@@ -210,19 +233,18 @@ def report_config(ns, bps, scores, ratios, Ts) -> dict:
     cfg = {"branch_points": list(bps), "ratios": list(ratios), "horizons": _ints(ns.horizons) if ns.horizons else None,
            "device": ns.device, "chunk_mb": ns.chunk_mb, "replay_dtype": ns.replay_dtype,
            "trace_dtype": ns.trace_dtype, "norm_dtype": ns.norm_dtype, "dense_cache": ns.dense_cache,
-           "replay_mode": ns.replay_mode, "cycle_len": ns.cycle_len, "cycle_lens": list(Ts), "fused": bool(ns.fused),
-           "fused_effective": True, "fused_shards": ns.fused_shards, "fused_max_configs": ns.fused_max_configs,
+           "replay_mode": ns.replay_mode, "cycle_len": ns.cycle_len,
+           "cycle_lens": list(getattr(ns, "report_cycle_lens", Ts)), "fused": bool(ns.fused),
+           "fused_effective": bool(ns.fused) or ns.replay_mode == "cycle", "fused_shards": ns.fused_shards, "fused_max_configs": ns.fused_max_configs,
            "nodes": ns.nodes, "fused_g_residency": bool(ns.fused_g_residency),
            "fused_dev_reduce": bool(ns.fused_dev_reduce), "score_names": list(scores), "window": ns.window,
            "seed": ns.seed}
     if ns.fused_state_budget_mb and ns.fused_state_budget_mb > 0:
         cfg["fused_state_budget_mb"] = ns.fused_state_budget_mb
-    opts = sorted({o for o in str(ns.optimizer).split(",") if o})
-    if opts != ["adamw"]:
-        cfg["optimizer"] = opts
-    folds = [f for f in str(ns.fold).split(",") if f]
-    if folds != ["off"]:
-        cfg["fold"] = folds
+    if getattr(ns, "optimizer_set", ["adamw"]) != ["adamw"]:
+        cfg["optimizer"] = list(ns.optimizer_set)
+    if getattr(ns, "fold_set", [False]) != [False]:
+        cfg["fold"] = ["on" if f else "off" for f in ns.fold_set]
     if getattr(ns, "dual_lr_set", ["1"]) != ["1"]:
         cfg["dual_lr"] = list(ns.dual_lr_set)
     if ns.selection_semantics != "topk":
@@ -285,7 +307,7 @@ def run(ns) -> dict:
             return d.get(fopts[0]) if one else {o: d.get(o) for o in fopts}
         report["branch_results"][t0] = {
             "t0": t0, "state_absent": False, "window_len": Wl, "window_steps": frag["window_steps"],
-            "cycle_lens": Ts, "horizon_steps": {str(h): max(1, min(h, Wl)) for h in horizons},
+            "cycle_lens": list(ns.report_cycle_lens), "horizon_steps": {str(h): max(1, min(h, Wl)) for h in horizons},
             # the state dump's scalars, with the reference's defaults where a trace carries its
             # hyper-parameters per parameter group only (sga/replay_fused.py:2047-2056)
             "meta": {"lr": [float(x) for x in (lr if isinstance(lr, (list, tuple)) else [lr])],
@@ -305,6 +327,9 @@ def run(ns) -> dict:
             "scores": {(s if one else f"{s}@{o}"): frag.get("score_stats", {}).get((s, o), {})
                        for s in scores for o in fopts},
             "per_ratio": per_ratio}
+        if ns.replay_mode == "zerofill":  # the cycle engine's echoes do not exist in this mode
+            br = report["branch_results"][t0]
+            del br["cycle_lens"], br["replay"]["g_residency"], br["replay"]["dev_reduce"]
     return sanitize(report)
 
 

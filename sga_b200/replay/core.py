@@ -252,7 +252,7 @@ class CycleConfig:
 
     def key(self, multi: dict) -> str:
         k = self.score
-        if multi.get("cycle_len"):
+        if multi.get("cycle_len") and self.cycle_len > 0:
             k += f"@T{self.cycle_len}"
         if multi.get("optimizer"):
             k += f"@{self.optimizer}"
@@ -295,7 +295,7 @@ def reference_cycle(w0, m0, v0, logged, grad_norms, lrs, hp: Hyper, t0, cfg: Cyc
         count = t0 + si + 1
         coef_dense = f32(clip_coef(grad_norms[si] ** 2, hp.clip)) if hp.clip > 0 else 1.0
         g = _div(g_logged.float(), coef_dense)
-        boundary = si % T == 0
+        boundary = T > 0 and si % T == 0  # cycle length 0: zerofill, the support stays frozen and nothing merges
         out_sel = None
         if boundary:
             if cfg.fold and si > 0:

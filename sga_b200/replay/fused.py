@@ -319,10 +319,10 @@ class FusedGroup:
         plan = []
         for c in self.cfgs:
             adams = c.optimizer == "adams"
-            boundary = si % c.cycle_len == 0
+            boundary = c.cycle_len > 0 and si % c.cycle_len == 0  # cycle length 0: zerofill, never a boundary
             lr32 = RC.f32(lr)
             plan.append(dict(
-                boundary=boundary, fold=bool(c.fold and boundary and si > 0), fold_div=float(c.cycle_len),
+                boundary=boundary, fold=bool(c.fold and boundary and si > 0), fold_div=float(max(c.cycle_len, 1)),
                 dual=bool(c.dual_lr != 1.0), adams=adams, lr=lr32,
                 lr_inactive=RC.f32(lr * c.dual_lr),
                 bc1=1.0 if adams else 1.0 - self.hp.beta1 ** count, bc2=1.0 if adams else 1.0 - self.hp.beta2 ** count,

@@ -453,7 +453,7 @@ def test_replay_reports_equal_on_a_trace_written_by_the_reference(ref, monkeypat
     """The other direction of the trace format: the reference engine and its trace collector write a
     trace (CPU, the reference's own fakes), then both replay CLIs run every per-configuration axis on it
     (two optimizers, fold off / on, plain and T-relative dual lr, two cycle lengths, default
-    balanced-histogram semantics). The whole report must agree: same keys and nesting, every number
+    balanced-histogram semantics) and the zerofill mode (frozen exact top-k support) on it. The whole report must agree: same keys and nesting, every number
     (distortions, thresholds, ranking metrics, score and label statistics, the per-step reconstruction
     check) to 5e-8; this framework adds ``step`` / ``phase`` to ``meta`` and a ``profile`` block."""
     import copy
@@ -488,19 +488,11 @@ def test_replay_reports_equal_on_a_trace_written_by_the_reference(ref, monkeypat
     hide = tmp_path / "hide" / "triton"
     hide.mkdir(parents=True)
     (hide / "__init__.py").write_text('raise ImportError("hidden")\n')
-    common = ["--trace-dir", tdir, "--branch-point", "3", "--ratios", "5", "--replay-mode", "cycle", "--cycle-lens", "2,3",
-              "--score-names", "abs_g,update", "--window", "6", "--device", "cpu", "--optimizer", "adamw,adams",
-              "--fold", "off,on", "--dual-lr", "1,T/4", "--fused-shards", "1", "--dense-cache"]
-    ref_out, our_out = str(tmp_path / "ref.json"), str(tmp_path / "our.json")
     env = dict(os.environ, PYTHONPATH=str(tmp_path / "hide") + os.pathsep + REF)
-    res = subprocess.run([sys.executable, "-m", "sga.replay"] + common + [str(tmp_path / "rc"), "--out", ref_out], env=env,
-                         capture_output=True, text=True, cwd=str(tmp_path))
-    assert res.returncode == 0, res.stderr[-2000:]
-    assert cli.main(common + [str(tmp_path / "oc"), "--out", our_out]) == 0
-    a, b = json.load(open(ref_out)), json.load(open(our_out))
-    diffs = []
+    allowed = {"/config/dense_cache", "/branch_results/3/meta/step", "/branch_results/3/meta/phase",
+               "/branch_results/3/replay/profile"}
 
-    def walk(x, y, path):
+    def walk(x, y, path, diffs):
         if isinstance(x, dict):
             if not isinstance(y, dict):
                 return diffs.append((path, "type"))
@@ -508,21 +500,32 @@ def test_replay_reports_equal_on_a_trace_written_by_the_reference(ref, monkeypat
                 if k not in y:
                     diffs.append((path + "/" + k, "missing"))
                 else:
-                    walk(x[k], y[k], path + "/" + k)
+                    walk(x[k], y[k], path + "/" + k, diffs)
             diffs.extend((path + "/" + k, "extra") for k in y if k not in x)
         elif isinstance(x, list):
             if not isinstance(y, list) or len(x) != len(y):
                 return diffs.append((path, "list"))
             for i, (p, q) in enumerate(zip(x, y)):
-                walk(p, q, f"{path}[{i}]")
+                walk(p, q, f"{path}[{i}]", diffs)
         elif isinstance(x, float) or isinstance(y, float):
             if x is None or y is None or abs(x - y) > 6e-8 * max(1.0, abs(x)):
                 diffs.append((path, x, y))
         elif x != y:
             diffs.append((path, x, y))
 
-    walk(a, b, "")
-    allowed = {"/config/dense_cache", "/branch_results/3/meta/step", "/branch_results/3/meta/phase",
-               "/branch_results/3/replay/profile"}
-    assert not [d for d in diffs if d[0] not in allowed], diffs[:10]
-    assert len(a["branch_results"]["3"]["per_ratio"]["5.0"]["scores"]) == 32
+    base = ["--trace-dir", tdir, "--branch-point", "3", "--window", "6", "--device", "cpu", "--fused-shards", "1"]
+    runs = {"cycle": (["--ratios", "5", "--replay-mode", "cycle", "--cycle-lens", "2,3", "--score-names", "abs_g,update",
+                       "--optimizer", "adamw,adams", "--fold", "off,on", "--dual-lr", "1,T/4"], 32),
+            "zerofill": (["--ratios", "5,20", "--replay-mode", "zerofill", "--score-names", "abs_g,abs_m,coi",
+                          "--selection-semantics", "topk"], 3)}
+    for tag, (extra, arms) in runs.items():
+        ref_out, our_out = str(tmp_path / f"ref_{tag}.json"), str(tmp_path / f"our_{tag}.json")
+        res = subprocess.run([sys.executable, "-m", "sga.replay"] + base + extra + ["--dense-cache", str(tmp_path / f"rc_{tag}"),
+                             "--out", ref_out], env=env, capture_output=True, text=True, cwd=str(tmp_path))
+        assert res.returncode == 0, res.stderr[-2000:]
+        assert cli.main(base + extra + ["--dense-cache", str(tmp_path / f"oc_{tag}"), "--out", our_out]) == 0
+        a, b = json.load(open(ref_out)), json.load(open(our_out))
+        diffs = []
+        walk(a, b, "", diffs)
+        assert not [d for d in diffs if d[0] not in allowed], (tag, diffs[:10])
+        assert len(a["branch_results"]["3"]["per_ratio"]["5.0"]["scores"]) == arms

@@ -22,8 +22,8 @@ def trace(tmp_path_factory):
 
 def _cli(trace, tmp_path, *extra):
     out = tmp_path / "report.json"
-    argv = ["--trace-dir", trace, "--ratios", "5,20", "--cycle-lens", "1,4", "--score-names", "abs_g,update",
-            "--window", "8", "--horizons", "4,8", "--out", str(out)] + list(extra)
+    argv = ["--trace-dir", trace, "--ratios", "5,20", "--replay-mode", "cycle", "--cycle-lens", "1,4", "--score-names",
+            "abs_g,update", "--window", "8", "--horizons", "4,8", "--out", str(out)] + list(extra)
     assert cli.main(argv) == 0
     return json.load(open(out))
 
@@ -53,10 +53,21 @@ def test_cli_report_shape(trace, tmp_path, capsys):
 def test_cli_absent_branch_point_and_single_axis_keys(trace, tmp_path):
     out = tmp_path / "r.json"
     cli.main(["--trace-dir", trace, "--branch-point", "0,3", "--ratios", "10", "--score-names", "abs_g", "--window",
-              "8", "--out", str(out)])
+              "8", "--replay-mode", "cycle", "--out", str(out)])
     rep = json.load(open(out))
     assert rep["branch_results"]["3"] == {"t0": 3, "state_absent": True}
     assert set(rep["branch_results"]["0"]["per_ratio"]["10.0"]["scores"]) == {"abs_g"}
+    assert rep["config"]["cycle_lens"] == [20] and rep["config"]["selection_semantics"] == "balanced-histogram"
+    # the default mode is zerofill, which exists for exact top-k only: the default selection rule is refused there
+    with pytest.raises(ValueError, match="requires --replay-mode cycle"):
+        cli.main(["--trace-dir", trace, "--ratios", "10", "--score-names", "abs_g", "--window", "8"])
+    with pytest.raises(ValueError, match="only supported with --replay-mode cycle"):
+        cli.main(["--trace-dir", trace, "--selection-semantics", "topk", "--fold", "on"])
+    cli.main(["--trace-dir", trace, "--ratios", "10", "--score-names", "abs_g", "--window", "8", "--selection-semantics",
+              "topk", "--out", str(out)])
+    z = json.load(open(out))["branch_results"]["0"]
+    assert "cycle_lens" not in z and set(z["per_ratio"]["10.0"]["scores"]) == {"abs_g"}
+    assert 0 < z["per_ratio"]["10.0"]["scores"]["abs_g"]["distortion"]["8"] < 5
 
 
 def test_self_check_on_a_real_trace(tmp_path):
@@ -81,7 +92,7 @@ def test_multinode_local_executor_matches_single_process(trace, tmp_path, monkey
     # multi-node replays select by exact top-k (the balanced rule is single-node only): same rule on both arms
     one = _cli(trace, tmp_path, "--fused-shards", "1", "--selection-semantics", "topk")
     two = _cli(trace, tmp_path, "--fused-shards", "2", "--nodes", "nodeA,nodeB", "--launch-log-dir",
-               str(tmp_path / "launch"), "--preflight-timeout", "120")
+               str(tmp_path / "launch"), "--preflight-timeout", "120", "--selection-semantics", "topk")
     a = one["branch_results"]["0"]["per_ratio"]["5.0"]["scores"]
     b = two["branch_results"]["0"]["per_ratio"]["5.0"]["scores"]
     for key in a:
