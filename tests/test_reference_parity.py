@@ -513,6 +513,28 @@ def test_replay_reports_equal_on_a_trace_written_by_the_reference(ref, monkeypat
         elif x != y:
             diffs.append((path, x, y))
 
+    # the bf16 screening copy: both converters on that trace, same file set, same contents
+    from sga_b200 import trace_convert as TC
+
+    ca, cb = str(tmp_path / "conv_ref"), str(tmp_path / "conv_ours")
+    res = subprocess.run([sys.executable, "-m", "sga.trace_convert", "--src", tdir, "--dst", ca, "--from-step", "4"], env=env,
+                         capture_output=True, text=True, cwd=str(tmp_path))
+    assert res.returncode == 0, res.stderr[-2000:]
+    assert TC.main(["--src", tdir, "--dst", cb, "--from-step", "4"]) == 0
+    assert sorted(os.listdir(ca)) == sorted(os.listdir(cb)) and len(os.listdir(ca)) == 6
+
+    def same(x, y):
+        if isinstance(x, dict):
+            return isinstance(y, dict) and x.keys() == y.keys() and all(same(x[k], y[k]) for k in x)
+        if torch.is_tensor(x):
+            return torch.is_tensor(y) and x.dtype == y.dtype and torch.equal(x, y)
+        if isinstance(x, (list, tuple)):
+            return len(x) == len(y) and all(same(p, q) for p, q in zip(x, y))
+        return x == y
+
+    for f in os.listdir(ca):
+        assert same(torch.load(os.path.join(ca, f), weights_only=False), torch.load(os.path.join(cb, f), weights_only=False)), f
+
     base = ["--trace-dir", tdir, "--branch-point", "3", "--window", "6", "--device", "cpu", "--fused-shards", "1"]
     runs = {"cycle": (["--ratios", "5", "--replay-mode", "cycle", "--cycle-lens", "2,3", "--score-names", "abs_g,update",
                        "--optimizer", "adamw,adams", "--fold", "off,on", "--dual-lr", "1,T/4"], 32),

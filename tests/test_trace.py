@@ -84,6 +84,16 @@ def test_bf16_dump_equals_converted_fp32(tmp_path):
         x = torch.load(b / name, weights_only=False)["payload"]
         y = torch.load(c / name, weights_only=False)["payload"]
         assert all(x[k].dtype == torch.bfloat16 and torch.equal(x[k], y[k]) for k in x)
+    # a destination that holds files is refused; --overwrite purges its trace files first; ranges are half-open
+    with pytest.raises(ValueError, match="not empty"):
+        convert_trace(str(a), str(c))
+    with pytest.raises(ValueError, match="must differ"):
+        convert_trace(str(a), str(a))
+    res = convert_trace(str(a), str(c), overwrite=True, from_step=3, to_step=4)
+    assert res["g_files"] == 1 and res["state_files"] == 0
+    assert sorted(os.listdir(c)) == ["catalog.pt", "step_000003_g.pt"]
+    again = convert_trace(str(c), str(tmp_path / "twice"))  # already bf16: an identical copy, with a warning
+    assert again["g_files"] == 1
 
 
 def test_resume_catalog_identity(tmp_path):
