@@ -436,10 +436,12 @@ class SGAEngine:
             self._finish(iteration)
             return (False, None, None)
         self._step_full = True
-        grad_norm, coeff = self._masked_clip_grad_norm(optimizer, True, step, shadow=True)
-        num_zeros = self._count_zeros() if optimizer.config.log_num_zeros_in_grad else 0
         reselect = self._cycle.reselect_boundary(step)
         reselected = reselect and self._shadow_score
+        # the boundary score reads the post-clip gradient (the stock step has clipped in place by then,
+        # sga/shadow.py:34-36): on a scoring step the coefficient is applied now instead of inside the commit
+        grad_norm, coeff = self._masked_clip_grad_norm(optimizer, True, step, shadow=True, scale_now=reselected)
+        num_zeros = self._count_zeros() if optimizer.config.log_num_zeros_in_grad else 0
         if self._trace is not None:
             self._trace.maybe_dump(self, optimizer, step - 1, grad_norm)
         if reselected:
@@ -550,7 +552,7 @@ class SGAEngine:
         self.last_ratio = support.total_selected / max(support.total_elements, 1)
 
     # ------------------------------------------------------------------- clip
-    def _masked_clip_grad_norm(self, optimizer, was_full, step, shadow=False):
+    def _masked_clip_grad_norm(self, optimizer, was_full, step, shadow=False, scale_now=False):
         """Norm over what was communicated this step; returns ``(norm, coeff)``.
         On CUDA both stay on the device (``coeff`` is a device scalar the
         optimizer kernel reads); the norm is fetched once, for the log."""
@@ -594,7 +596,7 @@ class SGAEngine:
                 K.clip_coeff(sumsq, 1.0 / world, clip, self._dev["coeff"], self._dev["norm"])
             else:
                 K.clip_coeff(sumsq, 1.0, clip, self._dev["coeff"], self._dev["norm"])
-            wants_dump = self._trace is not None and any(self._trace.wants(step - 1))
+            wants_dump = scale_now or (self._trace is not None and any(self._trace.wants(step - 1)))
             if wants_dump and clip > 0.0:
                 # the dump slot reads post-clip gradients: scale explicitly, hand the kernel 1.0
                 self._scale_communicated(was_full, mask)
@@ -621,7 +623,7 @@ class SGAEngine:
             c = clip / (norm + 1.0e-6)
             if c < 1.0:
                 coeff = float(torch.tensor(c, dtype=torch.float32).item())
-        wants_dump = self._trace is not None and any(self._trace.wants(step - 1))
+        wants_dump = scale_now or (self._trace is not None and any(self._trace.wants(step - 1)))
         if wants_dump and coeff != 1.0:
             self._scale_communicated(was_full, mask, coeff)
             return norm, 1.0

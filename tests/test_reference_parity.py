@@ -551,3 +551,130 @@ def test_replay_reports_equal_on_a_trace_written_by_the_reference(ref, monkeypat
         walk(a, b, "", diffs)
         assert not [d for d in diffs if d[0] not in allowed], (tag, diffs[:10])
         assert len(a["branch_results"]["3"]["per_ratio"]["5.0"]["scores"]) == arms
+
+
+@pytest.mark.skipif(not os.path.exists(os.path.join(REF, "tests", "ref_engine_harness.py")),
+                    reason="no copy of the reference's engine test harness under baseline/_ref/tests")
+def test_shadow_flow_matches_reference_engine(ref, monkeypatch):
+    """Shadow mode on both engines: the stock dense step (decoupled AdamW behind the wrapper surface the
+    reference's shadow step calls, ``sga/engine.py:612-744``) plus the read-only boundary scoring. Same
+    gradient norms, the same support after every boundary (the score reads the post-clip gradient and
+    the upcoming commit's bias corrections), the same cleared gradient buffer, weights to rounding."""
+    import copy
+    import types
+
+    from sga_b200 import config as C
+    from sga_b200.runtime.arena import FlatArena, ParamSpec
+    from sga_b200.runtime.builder import build_engine
+    from sga_b200.runtime.ddp import DataParallel, DDPConfig
+    from sga_b200.runtime.optimizer import FlatOptimizer, OptimizerConfig
+
+    mods = {n: types.ModuleType(n) for n in ("megatron", "megatron.core", "megatron.core.tensor_parallel",
+                                             "megatron.core.transformer", "megatron.core.transformer.module")}
+    mods["megatron.core.tensor_parallel"].param_is_not_tensor_parallel_duplicate = lambda p, g=None: True
+    mods["megatron.core.transformer.module"].param_is_not_shared = lambda p: True
+    for n, m in mods.items():
+        monkeypatch.setitem(sys.modules, n, m)
+    monkeypatch.setenv("SGA_ALLOW_FROZEN_SELECTION", "1")
+    monkeypatch.syspath_prepend(os.path.join(REF, "tests"))
+    ref("sga.engine")
+    H = importlib.import_module("ref_engine_harness")
+
+    class StockOpt(H._FakeMPOpt):
+        def __init__(self, chunk):
+            super().__init__(chunk)
+            self.config = types.SimpleNamespace(clip_grad=1.0, log_num_zeros_in_grad=False)
+            self.optimizer = torch.optim.AdamW(self.main_params, lr=1e-3, betas=(0.9, 0.95), eps=1e-8,
+                                               weight_decay=1e-2)
+
+        def clip_grad_norm(self, clip_grad):
+            total = float(torch.sqrt(sum((mp.grad.float() ** 2).sum() for mp in self.main_params)))
+            c = min(1.0, clip_grad / (total + 1e-6))
+            if c < 1.0:
+                for mp in self.main_params:
+                    mp.grad.data.mul_(c)
+            return total
+
+        def count_zeros(self):
+            return sum(int((mp.grad == 0).sum()) for mp in self.main_params)
+
+        def step_with_ready_grads(self):
+            self.optimizer.step()
+            self._copy_main_params_to_model_params()
+            return True
+
+    def run_reference(combo, extra, steps=14, seed=21):
+        torch.manual_seed(seed)
+        chunk = H._FakeChunk(n_params=3, numel_per=64)
+        mp = StockOpt(chunk)
+        p0 = [p.detach().clone() for p in chunk.params]
+        eng = H._build_engine(combo, extra)
+        eng._dp_cp_group = lambda: None
+        eng.attach(chunk)
+        gen = torch.Generator().manual_seed(seed + 1)
+        grads, log = [], []
+        with H._ReplicaWorld(world=1):
+            for step in range(1, steps + 1):
+                g = torch.randn(chunk.bucket.grad_data.numel(), generator=gen)
+                grads.append(g.clone())
+                chunk.bucket.grad_data += g
+                if not eng.grad_sync(chunk, force_all_reduce=False):
+                    chunk.finish_grad_sync()
+                _ok, gn, _nz = eng.optimizer_step(mp, [chunk], step)
+                mk = eng._bucket_states[0].active_mask_u8
+                log.append((float(gn), None if mk is None else mk.view(-1).to(torch.uint8).clone(),
+                            chunk.bucket.grad_data.clone()))
+                chunk.bucket.grad_data.zero_()  # the stock loop zeroes the buffer between steps
+        return p0, grads, log, torch.cat([m.reshape(-1) for m in mp.main_params])
+
+    def run_ours(combo, extra, p0, grads):
+        kw = {**combo["config"], **combo["selection_params"], **combo["opt_params"], **combo.get("backend_params", {}),
+              "sga_score": combo["score"], "sga_selection": combo["selection"], "sga_optimizer": combo["opt"],
+              "sga_backend": combo["backend"], "sga_enabled": True, **extra}
+        C.set_args(C.make_args(**kw))
+        model = types.SimpleNamespace()
+        model.arena = FlatArena([ParamSpec(f"p{i}", tuple(p.shape), 0, "zeros") for i, p in enumerate(p0)],
+                                bucket_elems=10 ** 9, device="cpu")
+        model.named_parameters = lambda: [(s.name, s.model) for s in model.arena.slots]
+        for s, p in zip(model.arena.slots, p0):
+            s.main.copy_(p)
+        model.arena.sync_model_from_main()
+        ddp = DataParallel(model, transport="local",
+                           ddp_config=DDPConfig(average_in_collective=False, overlap_grad_reduce=False))
+        opt = FlatOptimizer(model.arena, OptimizerConfig(lr=1e-3, weight_decay=1e-2, adam_beta1=0.9, adam_beta2=0.95,
+                                                         adam_eps=1e-8, clip_grad=1.0))
+        eng = build_engine(quiet=True)
+        eng.log_interval = 0
+        eng.attach(ddp)
+        log = []
+        slots = model.arena.slots
+        for step, g in enumerate(grads, 1):
+            off = 0
+            for s in slots:
+                n = s.end - s.start
+                model.arena.main_grad[s.start:s.end] += g[off:off + n]
+                off += n
+            ddp.begin_step()
+            eng.begin_step(ddp, step)
+            if not eng.grad_sync(ddp, False):
+                ddp.finish_grad_sync()
+            _ok, gn, _nz = eng.optimizer_step(opt, [ddp], step)
+            mk = eng._active_mask_arena() if eng._active_support is not None else None
+            log.append((float(gn), None if mk is None else torch.cat([mk[s.start:s.end] for s in slots]).clone(),
+                        torch.cat([model.arena.main_grad[s.start:s.end] for s in slots]).clone()))
+            model.arena.main_grad.zero_()
+        return log, torch.cat([s.main.reshape(-1) for s in slots])
+
+    cases = [(H._UPDATE, {"sga_shadow": True}), (H._ABS_M, {"sga_shadow": True}),
+             ({**H._UPDATE, "score": "coi"}, {"sga_shadow": True}), ({**H._ABS_M, "score": "abs_g"}, {"sga_shadow": True}),
+             (H._ABS_M, {"sga_shadow": True, "sga_shadow_score": False})]
+    for combo, extra in cases:
+        c = copy.deepcopy(combo)
+        tag = (combo["score"], combo["backend"], extra)
+        p0, grads, rlog, rw = run_reference(c, extra)
+        olog, ow = run_ours(c, extra, p0, grads)
+        for (gn, mk, gb), (gn2, mk2, gb2) in zip(rlog, olog):
+            assert abs(gn - gn2) <= 1e-6 * max(gn, 1e-9), tag
+            assert (mk is None) == (mk2 is None) and (mk is None or torch.equal(mk, mk2)), tag
+            assert torch.equal(gb, gb2), tag
+        assert float((rw - ow).abs().max()) <= 5e-6, tag  # torch.optim.AdamW folds the bias corrections differently
