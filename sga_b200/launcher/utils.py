@@ -44,10 +44,14 @@ def parse_hostfile(path: Optional[str]) -> list:
 
 def flatten_dict_to_args(d: dict, ignore=()) -> list:
     """``{"micro_batch_size": 4, "flag": True}`` -> ``["--micro-batch-size", "4", "--flag"]``.
-    ``False`` / ``None`` values are dropped, lists are space-joined arguments."""
+    ``False`` / ``None`` values are dropped, lists are space-joined arguments, nested dicts are flattened
+    in place (``sga/launcher/utils.py:269-290``)."""
     out = []
     for key, val in d.items():
         if key in ignore or val is None or val is False:
+            continue
+        if isinstance(val, dict):  # nested sections (checkpoint:, logging:) flatten into the same flag list
+            out.extend(flatten_dict_to_args(val, ignore))
             continue
         flag = "--" + str(key).replace("_", "-")
         if val is True:

@@ -34,6 +34,9 @@ def test_hostfile_parser(tmp_path):
 def test_flatten_dict_to_args():
     assert U.flatten_dict_to_args({"micro_batch_size": 4, "flag": True, "off": False, "none": None, "xs": [1, 2]}) == \
         ["--micro-batch-size", "4", "--flag", "--xs", "1", "2"]
+    # nested sections flatten in place, in order, with the ignore list applied at every level
+    assert U.flatten_dict_to_args({"a": 1, "logging": {"log_interval": 5, "log_dir": "x", "deep": {"b_c": True}}, "z": 2},
+                                  ignore=("log_dir",)) == ["--a", "1", "--log-interval", "5", "--b-c", "--z", "2"]
 
 
 def test_sga_section_to_flags_and_nulls():
