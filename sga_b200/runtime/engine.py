@@ -733,19 +733,21 @@ class SGAEngine:
     def _log_step(self, step, was_full, reselected, grad_norm) -> None:
         if self.log_interval <= 0 or step % self.log_interval:
             return
-        if was_full:
-            ratio = 1.0
-        elif self.rank_local:
-            ratio = self._ratio
+        # line and record of sga/engine.py:1451-1472: the ratio is the active support's selected fraction
+        # (-1 while there is none, bootstrap and dense steps included), the threshold is the last selection's
+        if self.rank_local:
+            ratio = 1.0 if was_full else self._ratio
+        elif self._active_support is not None and self._active_support.total_elements:
+            ratio = self._active_support.total_selected / self._active_support.total_elements
         else:
-            ratio = self.last_ratio if self.last_ratio is not None else 0.0
+            ratio = -1.0
         gn = float(grad_norm) if grad_norm is not None else float("nan")
         if self._rank != 0:
             return
         thr = getattr(self.selection, "last_threshold", None)
-        extra = f" sel_thresh={thr:.6e}" if (reselected and thr is not None) else ""
-        print(f"[SGA] step={step} phase={'full' if was_full else 'sparse'} ratio={ratio:.6f}{extra} "
-              f"grad_norm={gn:.6f}", flush=True)
+        extra = f" sel_thresh={thr:.3e}" if thr else ""
+        print(f"[SGA] step={step} phase={'full' if was_full else 'sparse'} ratio={ratio:.4f}{extra} "
+              f"grad_norm={gn:.3f}", flush=True)
         if self._metrics_file:
             with open(self._metrics_file, "a") as fh:
                 fh.write(json.dumps({"step": step, "phase": "full" if was_full else "sparse", "ratio": ratio,

@@ -380,10 +380,12 @@ def test_log_line_and_metrics_file(tmp_path, capsys, monkeypatch):
     for step in range(1, 6):
         _step(model, ddp, opt, eng, step)
     out = capsys.readouterr().out
-    assert "[SGA] step=4 phase=full ratio=1.000000 sel_thresh=" in out
     import re
 
-    m = re.search(r"\[SGA\] step=5 phase=sparse ratio=(0\.\d+) grad_norm=\d", out)
+    assert "[SGA] step=1 phase=full ratio=-1.0000 grad_norm=" in out, "no support yet"
+    m4 = re.search(r"\[SGA\] step=4 phase=full ratio=(0\.\d{4}) sel_thresh=\d\.\d{3}e[-+]\d+ grad_norm=\d+\.\d{3}\n", out)
+    assert m4 and abs(float(m4.group(1)) - 0.10) < 0.01, "the boundary line already shows the new support"
+    m = re.search(r"\[SGA\] step=5 phase=sparse ratio=(0\.\d+) sel_thresh=\S+ grad_norm=\d", out)
     assert m and abs(float(m.group(1)) - 0.10) < 0.01
     recs = [json.loads(l) for l in open(tmp_path / "m.jsonl")]
     assert [r["step"] for r in recs] == [1, 2, 3, 4, 5]
