@@ -17,7 +17,8 @@ python -m sga_b200.train_gpt --model llama_tiny --seq-length 512 --micro-batch-s
   --sga-trace-branch-points 8 --sga-trace-window 16
 
 echo "== step 2: fused replay (4 scores x 2 ratios x 3 cycle lengths x fold on/off = 48 cells) =="
-python -m sga_b200.replay --trace-dir "$OUT/trace" --branch-point all --ratios 5,10 --cycle-lens 1,4,8 \
+python -m sga_b200.replay --trace-dir "$OUT/trace" --branch-point all --ratios 5,10 --replay-mode cycle --cycle-lens 2,4,8 \
+  --dense-cache "$OUT/dense_cache" \
   --score-names abs_g,abs_m,coi,update --fold off,on --window 16 --device "$DEVICE" --fused-max-configs 24 \
   --out "$OUT/replay.json"
 python experiments/example/select_best.py "$OUT/replay.json" | tee "$OUT/best.txt"

@@ -16,7 +16,7 @@ def best_arm(report: dict, ratio=None):
     for t0, br in report["branch_results"].items():
         if br.get("state_absent"):
             continue
-        h = str(br["horizon_steps"][-1])
+        h = str(max(int(x) for x in br["horizon_steps"]))  # {horizon: steps replayed} (a list in older reports)
         for r, entry in br["per_ratio"].items():
             if ratio is not None and float(r) != float(ratio):
                 continue
