@@ -129,6 +129,14 @@ variants = {
  "index fold adams": {"sga_optimizer": "adams", "sga_optimizer_residual_mean": True},
  "index writeback": {"sga_backend_emission": "writeback"},
  "index dual": {"sga_optimizer_full_sync_inactive_lr_scale": 0.5, "sga_score": "abs_m"},
+ "exact kth": {"sga_selection_method": "exact", "sga_score": "coi"},
+ "adaptive": {"sga_selection_method": "adaptive"},
+ "hist allreduce": {"sga_selection_topk_histogram_add_global_allreduce": True, "sga_selection_histogram_mode": "exact"},
+ "fast": {"sga_selection_histogram_mode": "fast", "sga_backend_index_slices": 3},
+ "block8": {"sga_selection_block_size": 8, "sga_selection_histogram_mode": "exact", "sga_backend_emission": "writeback"},
+ "always": {"sga_always_sync_layers": ["layers.1."], "sga_backend": "torch_pipelined_mask"},
+ "decoupled": {"sga_cycle_period": 6, "sga_cycle_full_sync_interval": 3,
+               "sga_cycle_decouple_full_sync_interval_and_period": True},
 }
 bad = []
 for name, ov in variants.items():
