@@ -66,6 +66,57 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const __nv_bfloat16* _
   }
 }
 
+// The same row kept in registers: CPL 16-byte chunks per lane (H <= CPL * 256), all loads of the row issued
+// before the first use, the second pass served from registers. Same summation order as the kernel above, so the
+// results are bit-identical.
+template <int CPL>
+__global__ void __launch_bounds__(256) rmsnorm_fwd_reg_kernel(const __nv_bfloat16* __restrict__ x,
+                                                              const __nv_bfloat16* __restrict__ w,
+                                                              __nv_bfloat16* __restrict__ y, float* __restrict__ rstd,
+                                                              long long rows, int H, long long x_stride,
+                                                              long long y_stride, int rows_per_group,
+                                                              long long group_stride_x, long long group_stride_y,
+                                                              float eps) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const long long grp = row / rows_per_group, r = row % rows_per_group;
+  const __nv_bfloat16* xr = x + grp * group_stride_x + r * x_stride;
+  __nv_bfloat16* yr = y + grp * group_stride_y + r * y_stride;
+  const int nch = H >> 3;
+  uint4 raw[CPL];
+#pragma unroll
+  for (int j = 0; j < CPL; ++j) {
+    const int c = lane + 32 * j;
+    raw[j] = c < nch ? *reinterpret_cast<const uint4*>(xr + c * 8) : make_uint4(0u, 0u, 0u, 0u);
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < CPL; ++j) {
+    if (lane + 32 * j < nch) {
+      float f[8];
+      unpack8(raw[j], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+    }
+  }
+  ss = warp_sum(ss);
+  const float rs = rsqrtf(ss / (float)H + eps);
+  if (lane == 0 && rstd) rstd[row] = rs;
+#pragma unroll
+  for (int j = 0; j < CPL; ++j) {
+    const int c = lane + 32 * j;
+    if (c < nch) {
+      float f[8], g[8];
+      unpack8(raw[j], f);
+      unpack8(*reinterpret_cast<const uint4*>(w + c * 8), g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = f[i] * rs * g[i];
+      *reinterpret_cast<uint4*>(yr + c * 8) = pack8(f);
+    }
+  }
+}
+
 // dx = rstd * (dy*w - xhat * mean(dy*w*xhat)); dw partial per CTA.
 // Each warp walks rows (strided by total warps); lanes own column chunks.
 template <int NCH>  // chunks of 8 columns per lane: H <= NCH * 256
@@ -408,9 +459,22 @@ SGA_API int sga_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, 
   if (rows <= 0) return 0;
   if (H & 7) return -5;
   const int wpb = 8;
-  rmsnorm_fwd_kernel<<<(unsigned)((rows + wpb - 1) / wpb), wpb * 32, 0, ST(stream)>>>(
-      (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, rstd, rows, H, x_stride, y_stride,
-      rows_per_group, gsx, gsy, eps);
+  const unsigned grid = (unsigned)((rows + wpb - 1) / wpb);
+  const int cpl = (H / 8 + 31) / 32;  // 16-byte chunks per lane
+#define RF(N)                                                                                                  \
+  rmsnorm_fwd_reg_kernel<N><<<grid, wpb * 32, 0, ST(stream)>>>(                                                 \
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, rstd, rows, H, x_stride, y_stride,   \
+      rows_per_group, gsx, gsy, eps)
+  if (cpl <= 1) RF(1);
+  else if (cpl <= 2) RF(2);
+  else if (cpl <= 4) RF(4);
+  else if (cpl <= 8) RF(8);
+  else if (cpl <= 16) RF(16);
+  else
+    rmsnorm_fwd_kernel<<<grid, wpb * 32, 0, ST(stream)>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
+                                                         (__nv_bfloat16*)y, rstd, rows, H, x_stride, y_stride,
+                                                         rows_per_group, gsx, gsy, eps);
+#undef RF
   return LAUNCH_OK();
 }
 

@@ -101,23 +101,57 @@ __global__ void __launch_bounds__(256) mask_ge_kernel(const float* __restrict__ 
 }
 
 // out[0] += count, out[1] += sum(pos), out[2] += sum((pos % 9973) * (pos % 1009)) over mask-on positions.
+// Sixteen mask bytes per load (the unaligned head and the tail go byte by byte); all-zero words, the common
+// case of a sparse support, cost one test. Integer sums: the result does not depend on the order.
 __global__ void __launch_bounds__(256) mask_stats_kernel(const uint8_t* __restrict__ mask, long long n,
                                                          long long* __restrict__ out) {
   long long c = 0, s1 = 0, s2 = 0;
-  const long long gstride = (long long)gridDim.x * blockDim.x;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gstride) {
-    if (mask[i]) {
-      ++c;
-      s1 += i;
-      s2 += (i % 9973) * (i % 1009);
+  const bool small = n < (1LL << 32);  // 32-bit remainders by constants are a multiply and a shift
+  auto hit = [&](long long pos) {
+    ++c;
+    s1 += pos;
+    if (small) {
+      const uint32_t p = (uint32_t)pos;
+      s2 += (long long)((p % 9973u) * (p % 1009u));
+    } else {
+      s2 += (pos % 9973) * (pos % 1009);
     }
+  };
+  const long long gtid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long gstride = (long long)gridDim.x * blockDim.x;
+  long long head = (16 - (long long)(reinterpret_cast<uintptr_t>(mask) & 15)) & 15;
+  if (head > n) head = n;
+  const long long nvec = (n - head) >> 4;
+  const uint4* v = reinterpret_cast<const uint4*>(mask + head);
+  for (long long j = gtid; j < nvec; j += gstride) {
+    const uint4 q = __ldg(v + j);
+    if ((q.x | q.y | q.z | q.w) == 0u) continue;
+    const uint32_t wds[4] = {q.x, q.y, q.z, q.w};
+    const long long base = head + (j << 4);
+    // one bit per non-zero byte: bit 0 of every byte of the SIMD compare, gathered into the top nibble by a
+    // multiply whose partial products do not overlap; then only the set bits are visited
+    uint32_t bits = 0;
+#pragma unroll
+    for (int w = 0; w < 4; ++w)
+      bits |= (((__vcmpne4(wds[w], 0u) & 0x01010101u) * 0x01020408u) >> 24 & 0xFu) << (4 * w);
+    while (bits) {
+      hit(base + (__ffs(bits) - 1));
+      bits &= bits - 1;
+    }
+  }
+  // byte-wise edges: [0, head) and [head + 16 * nvec, n), at most 30 positions
+  const long long tail0 = head + (nvec << 4);
+  const long long edges = head + (n - tail0);
+  if (gtid < edges) {
+    const long long pos = gtid < head ? gtid : tail0 + (gtid - head);
+    if (mask[pos]) hit(pos);
   }
   for (int o = 16; o > 0; o >>= 1) {
     c += __shfl_xor_sync(0xffffffffu, c, o);
     s1 += __shfl_xor_sync(0xffffffffu, s1, o);
     s2 += __shfl_xor_sync(0xffffffffu, s2, o);
   }
-  if ((threadIdx.x & 31) == 0) {
+  if ((threadIdx.x & 31) == 0 && c) {
     atomicAdd(reinterpret_cast<unsigned long long*>(out + 0), (unsigned long long)c);
     atomicAdd(reinterpret_cast<unsigned long long*>(out + 1), (unsigned long long)s1);
     atomicAdd(reinterpret_cast<unsigned long long*>(out + 2), (unsigned long long)s2);
@@ -378,7 +412,10 @@ SGA_API int sga_mask_ge(const float* x, long long n, int mode, int shift, int bi
 
 SGA_API int sga_mask_stats(const uint8_t* mask, long long n, long long* out3, void* stream) {
   if (n <= 0) return 0;
-  mask_stats_kernel<<<grid_for(n, 256 * 16), 256, 0, ST(stream)>>>(mask, n, out3);
+  // one 16-byte word per thread and iteration; at most eight CTAs per SM, grid-stride beyond that
+  long long blocks = ((n >> 4) + 255) / 256 + 1;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  mask_stats_kernel<<<(unsigned)blocks, 256, 0, ST(stream)>>>(mask, n, out3);
   return LAUNCH_OK();
 }
 

@@ -223,7 +223,18 @@ def bench_attention(small):
         A._IMPL = "auto"
 
 
-CASES = {"attention": bench_attention, "gemm": bench_gemm, "adam": bench_adam, "index_sync": bench_index_sync, "elementwise": bench_elementwise,
+def bench_mask_stats(small):
+    """Support count and position checksums of a byte mask (the consistency checks' kernel): 1 byte per element."""
+    from .. import kernels as K
+
+    n = (64 if small else 512) * 1024 * 1024
+    mask = (torch.rand(n, device="cuda") < 0.01).to(torch.uint8)
+    out = torch.zeros(3, dtype=torch.int64, device="cuda")
+    ms = timed(lambda: K.mask_stats(mask, out), 2 if small else 10, warmup=1)
+    emit("mask_stats_kernel", f"n={n} 1% set", ms, bytes_=float(n))
+
+
+CASES = {"mask_stats": bench_mask_stats, "attention": bench_attention, "gemm": bench_gemm, "adam": bench_adam, "index_sync": bench_index_sync, "elementwise": bench_elementwise,
          "replay": bench_replay}
 
 

@@ -196,6 +196,9 @@ def test_mask_compact_stats(n):
     assert torch.equal(mask2.bool(), KT.abs_bit_key(x, 16) >= 0x3F80)
     st = K.mask_stats(mask)
     assert torch.equal(st.cpu(), KT.mask_stats(mask.cpu()))
+    for off in (1, 7, 15):  # views that start off the 16-byte grid of the vector loads
+        if n > off + 1:
+            assert torch.equal(K.mask_stats(mask[off:]).cpu(), KT.mask_stats(mask[off:].cpu())), off
     idx = torch.full((n,), -1, dtype=torch.int32, device=DEV)
     total = torch.zeros(1, dtype=torch.int64, device=DEV)
     K.compact_mask(mask, idx, total)
