@@ -106,8 +106,9 @@ def load_state(info: TraceInfo, t0: int):
     return blob["meta"], blob["payload"]
 
 
-def load_g(info: TraceInfo, t: int):
-    blob = torch.load(os.path.join(info.dir, f"step_{t:06d}_g.pt"), weights_only=False, mmap=True)
+def load_g(info: TraceInfo, t: int, mmap: bool = True):
+    """``mmap``: tensors are file-backed, so a caller that slices reads only its slice from disk."""
+    blob = torch.load(os.path.join(info.dir, f"step_{t:06d}_g.pt"), weights_only=False, mmap=mmap)
     return blob["meta"], blob["payload"]
 
 

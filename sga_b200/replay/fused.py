@@ -38,7 +38,10 @@ from . import core as RC
 
 # kill switches: unknown values raise so that both arms of an A/B are always reachable
 ENV_KERNEL = "REPLAY_FUSED_KERNEL"      # on | off  (off: PyTorch ops even on CUDA)
-ENV_SELECT = "REPLAY_FUSED_SELECT"      # radix | gather
+ENV_SELECT = "REPLAY_FUSED_SELECT"      # auto | cpu  (cpu: the front block's selections run on host tensors)
+ENV_FRONT_SORT = "REPLAY_FUSED_FRONT_SORT"  # auto | cpu  (cpu: the front block's ranking sorts run on the host)
+ENV_P1_READ = "REPLAY_FUSED_P1_READ"    # mmap | load  (mmap: a shard touches only its slice of every gradient file)
+ENV_S0_PROFILE = "REPLAY_S0_PROFILE"    # 0 | 1  (1: rank 0 prints per-group counters and the phase times)
 ENV_WINDOW_HOST_GIB = "REPLAY_FUSED_WINDOW_HOST_GIB"  # host bytes (GiB, default 8) a shard may spend keeping the
 #                                          window's gradients between the dense arm and the stream
 
@@ -228,7 +231,7 @@ class GPrefetcher:
         self.t.start()
 
     def _load(self, t):
-        return RC.load_g(self.info, t)
+        return RC.load_g(self.info, t, mmap=_switch(ENV_P1_READ, ("mmap", "load"), "mmap") == "mmap")
 
     def _run(self):
         try:
@@ -282,7 +285,7 @@ class FusedGroup:
         self.k = [RC.k_for(n_total, c.ratio_percent) for c in self.cfgs]
         self.numer = {h: [0.0] * R for h in self.horizons}
         self.per_step = []
-        self.stats = {"pass1_s": 0.0, "select_s": 0.0, "pass3_s": 0.0, "selects": 0}
+        self.stats = {"pass1_s": 0.0, "select_s": 0.0, "pass3_s": 0.0, "selects": 0, "h2d_bytes": 0, "host_syncs": 0}
         if self.use_kernel:
             from ..csrc import lib
 
@@ -352,6 +355,8 @@ class FusedGroup:
         plan = self._plan(si, count, inp.lr)
         coef_dense = RC.f32(RC.clip_coef(inp.grad_norm ** 2, self.hp.clip)) if self.hp.clip > 0 else 1.0
         g_dev = inp.g.to(self.device, non_blocking=True)
+        if self.device.type == "cuda":
+            self.stats["h2d_bytes"] += inp.g.numel() * inp.g.element_size()
         st = None
         # ---- pass 1: clip norms
         t0 = time.perf_counter()
@@ -371,6 +376,7 @@ class FusedGroup:
             sums = torch.stack([(self._q_pre(p, g, r).double() ** 2).sum() for r, p in enumerate(plan)])
         self.comms.sum_(sums)
         sums = sums.tolist()
+        self.stats["host_syncs"] += 1
         for p, s in zip(plan, sums):
             p["coef"] = RC.f32(RC.clip_coef(s, self.hp.clip))
         self.stats["pass1_s"] += time.perf_counter() - t0
@@ -408,6 +414,7 @@ class FusedGroup:
             assert rc == 0, rc
             if wden is not None:
                 num = self.comms.sum_(self._out.clone()).tolist()
+                self.stats["host_syncs"] += 1
                 self.numer[h] = num
         else:
             for r, (p, c) in enumerate(zip(plan, self.cfgs)):
@@ -461,6 +468,11 @@ def run_shard(rank, world, trace_dir, t0, configs, window, horizons, device, den
         phases[name] = round(phases.get(name, 0.0) + now - t_phase, 4)
         t_phase = now
 
+    # every A/B switch is read once, before any work: an unknown value refuses the run by name
+    for name, allowed, dflt in ((ENV_KERNEL, ("on", "off"), "on"), (ENV_SELECT, ("auto", "cpu"), "auto"),
+                                (ENV_FRONT_SORT, ("auto", "cpu"), "auto"), (ENV_P1_READ, ("mmap", "load"), "mmap"),
+                                (ENV_S0_PROFILE, ("0", "1"), "0")):
+        _switch(name, allowed, dflt)
     info = RC.discover_trace(trace_dir)
     dev = torch.device(device)
     comms = Comms(rank, world, group, dev)
@@ -530,34 +542,46 @@ def run_shard(rank, world, trace_dir, t0, configs, window, horizons, device, den
     lap("dense_arm")
     # ---- front: branch scores ranked against the label, the window's summed squared gradient-driven step
     front = {}
-    hp_dev = RC.Hyper(wd=wd_vec.to(dev), beta1=hp.beta1, beta2=hp.beta2, eps=hp.eps, clip=hp.clip)
+    # A/B arms of the front block (unknown values raise): selections and / or ranking sorts on host tensors.
+    # Radix selection is integer arithmetic and the sorts are stable, so both arms give the same report.
+    front_sel = _switch(ENV_SELECT, ("auto", "cpu"), "auto")
+    front_sort = _switch(ENV_FRONT_SORT, ("auto", "cpu"), "auto")
+    fdev = dev
+    if front_sel == "cpu" and dev.type != "cpu":
+        if world > 1:
+            raise ValueError(f"{ENV_SELECT}=cpu needs a process group that reduces host tensors: one shard, or --device cpu")
+        fdev = torch.device("cpu")
+    fcomms = comms if fdev == dev else Comms(rank, world, group, fdev)
+    hp_dev = RC.Hyper(wd=wd_vec.to(fdev), beta1=hp.beta1, beta2=hp.beta2, eps=hp.eps, clip=hp.clip)
     score_stats, thresholds, label_stats = {}, {}, {}
     entries = shard_entries(info, lo, hi)
     for opt in optimizers:
         label_sel = {}
-        label_loc = labels[opt].to(dev)
-        label_stats[opt] = shard_stats(label_loc, comms)
+        label_loc = labels[opt].to(fdev)
+        label_stats[opt] = shard_stats(label_loc, fcomms)
         for name in score_names:
-            sc = RC.replay_score(name, w0.to(dev), m0.to(dev), v0.to(dev), g0.to(dev), hp_dev, t0 + 1, opt)
-            score_stats[(name, opt)] = shard_stats(sc.abs(), comms)
+            sc = RC.replay_score(name, w0.to(fdev), m0.to(fdev), v0.to(fdev), g0.to(fdev), hp_dev, t0 + 1, opt)
+            score_stats[(name, opt)] = shard_stats(sc.abs(), fcomms)
             for ratio in ratios:
                 k = RC.k_for(info.numel, ratio)
-                sel_s, th = shard_select(sc, k, comms, return_threshold=True)
+                sel_s, th = shard_select(sc, k, fcomms, return_threshold=True)
                 if semantics == "balanced-histogram":  # the trajectory's rule reports the crossing bin's lower edge
-                    th = shard_select_balanced(sc, k, comms, entries, return_threshold=True)[1]
+                    th = shard_select_balanced(sc, k, fcomms, entries, return_threshold=True)[1]
                 thresholds[(name, ratio, opt)] = th
                 if ratio not in label_sel:
-                    label_sel[ratio] = shard_select(label_loc, k, comms)
+                    label_sel[ratio] = shard_select(label_loc, k, fcomms)
                 sel_l = label_sel[ratio]
                 stats = torch.tensor([float((sel_s & sel_l).sum()), float(label_loc[~sel_s].double().sum()),
                                       float(label_loc.double().sum()), float(sc.abs()[~sel_s].double().sum()),
-                                      float(sc.abs().double().sum())], dtype=torch.float64, device=dev)
-                comms.sum_(stats)
-                got_s = comms.gather_to_root(sc.abs()[sel_s].float())
-                got_l = comms.gather_to_root(label_loc[sel_s].float())
-                ideal = comms.gather_to_root(label_loc[sel_l].float())
+                                      float(sc.abs().double().sum())], dtype=torch.float64, device=fdev)
+                fcomms.sum_(stats)
+                got_s = fcomms.gather_to_root(sc.abs()[sel_s].float())
+                got_l = fcomms.gather_to_root(label_loc[sel_s].float())
+                ideal = fcomms.gather_to_root(label_loc[sel_l].float())
                 if rank == 0:
-                    disc = 1.0 / torch.log2(torch.arange(2, k + 2, dtype=torch.float64, device=dev))
+                    if front_sort == "cpu":
+                        got_s, got_l, ideal = got_s.cpu(), got_l.cpu(), ideal.cpu()
+                    disc = 1.0 / torch.log2(torch.arange(2, k + 2, dtype=torch.float64, device=got_s.device))
                     order = torch.argsort(got_s, descending=True, stable=True)
                     idl = torch.sort(ideal.double(), descending=True).values
                     idcg = float((idl * disc[:idl.numel()]).sum())
@@ -592,6 +616,16 @@ def run_shard(rank, world, trace_dir, t0, configs, window, horizons, device, den
     lap("stream")
     if prof:
         prof[0]["phases_s"] = phases
+        prof[0]["arms"] = {"front_sel": front_sel, "front_sort": front_sort, "kernel": "cuda" if use_kernel else "torch",
+                           "g_read": _switch(ENV_P1_READ, ("mmap", "load"), "mmap")}
+    if _switch(ENV_S0_PROFILE, ("0", "1"), "0") == "1" and rank == 0:
+        for gi, pr in enumerate(prof):
+            busy = pr["pass1_s"] + pr["select_s"] + pr["pass3_s"]
+            print(f"[fused] S0PROFILE group {gi}: configs={pr['configs']} pass1={pr['pass1_s']:.3f}s "
+                  f"select={pr['select_s']:.3f}s ({pr['selects']} selects) pass3={pr['pass3_s']:.3f}s "
+                  f"read={pr['read_s']:.3f}s h2d={pr['h2d_bytes'] / 1e9:.3f}GB host_syncs={pr['host_syncs']} "
+                  f"comm_ops={pr['comm_ops']} coverage={busy / max(phases.get('stream', 0.0), 1e-9):.2f}", flush=True)
+        print(f"[fused] S0PROFILE phases {phases}", flush=True)
     if rank != 0:
         return None
     per_step = []

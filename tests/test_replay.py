@@ -277,3 +277,25 @@ def test_cli_matches_reference_golden_values(tmp_path):
         for (r, sc), val in ndcg.items():  # ranking diagnostics stay on exact top-k under either semantics
             m = per_ratio[r]["scores"][f"{sc}@T4"]
             assert abs(m["ndcg_at_k"] - val) < 2e-8 and abs(m["recall_at_k"] - recall[(r, sc)]) < 1e-5, (sem, r, sc, m)
+
+
+def test_front_block_arms_and_profile_switches(trace, monkeypatch, capsys):
+    """The A/B switches of the replay: unknown values raise; the host arms of the front block, the
+    whole-file read arm and the profile print leave the report unchanged."""
+    cfgs = CONFIGS[:2]
+    base = RF.run_fused_branch(trace, 0, cfgs, 12, [12], score_names=["abs_g", "update"], ratios=[5.0])
+    for name in (RF.ENV_SELECT, RF.ENV_FRONT_SORT, RF.ENV_P1_READ, RF.ENV_S0_PROFILE):
+        monkeypatch.setenv(name, "bogus")
+        with pytest.raises(ValueError, match=name):
+            RF.run_fused_branch(trace, 0, cfgs, 12, [12], score_names=["abs_g"], ratios=[5.0])
+        monkeypatch.delenv(name)
+    monkeypatch.setenv(RF.ENV_SELECT, "cpu")
+    monkeypatch.setenv(RF.ENV_FRONT_SORT, "cpu")
+    monkeypatch.setenv(RF.ENV_P1_READ, "load")
+    monkeypatch.setenv(RF.ENV_S0_PROFILE, "1")
+    other = RF.run_fused_branch(trace, 0, cfgs, 12, [12], score_names=["abs_g", "update"], ratios=[5.0])
+    assert other["front"] == base["front"] and other["results"] == base["results"]
+    arms = other["profile"][0]["arms"]
+    assert arms["front_sel"] == "cpu" and arms["front_sort"] == "cpu" and arms["g_read"] == "load"
+    out = capsys.readouterr().out
+    assert "[fused] S0PROFILE group 0: configs=2" in out and "host_syncs=" in out and "S0PROFILE phases" in out
