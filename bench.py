@@ -222,6 +222,37 @@ def main() -> int:
                "d2h_bytes_per_step": 4 * world, "last_loss": last_loss}
         tr.check()
 
+    # ---- gradient synchronisation: device time of the per-bucket sync launches, outside the timed regions
+    grad_sync = None
+    if tr.tp_size == 1 and tr.pp_size == 1:
+        tr.ddp.time_syncs = True
+        for i in range(2):
+            tr.train_step(tr.host_batch(step_id + K + i))
+        sync_ms = torch.tensor([tr.ddp.sync_device_ms() / 2], dtype=torch.float64, device=dev)
+        tr.ddp.time_syncs = False
+        if world > 1:
+            dist.all_reduce(sync_ms, op=dist.ReduceOp.MAX)
+        if float(sync_ms.item()) > 0.0:
+            grad_sync = {"ms_per_step": float(sync_ms.item()), "buckets": len(tr.model.arena.buckets),
+                         "what": "sum over buckets of the device time of each bucket's sync launch on the "
+                                 "communication stream (event pairs), mean of 2 untimed steps, max over ranks; "
+                                 "runs under the backward pass"}
+    if grad_sync is not None and ns.mode == "sga" and ns.sga_backend == "index":
+        try:
+            hbm = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"]) * 1e9
+        except Exception:
+            hbm = 6.65e12
+        # per bucket: the slower of three passes over the fp32 bucket at the measured copy rate and the
+        # (index, value) payload of the other ranks over NVLink at the measured peer-copy rate (770 GB/s)
+        bound = 0.0
+        for b in tr.model.arena.buckets:
+            n = b.end - b.start
+            k = max(1, round(n * ns.ratio_percent / 100.0))
+            bound += max(3 * 4.0 * n / hbm, (world - 1) * k * 8.0 / 770e9)
+        grad_sync["roofline_ms"] = bound * 1e3
+        grad_sync["frac_of_roofline"] = bound * 1e3 / max(grad_sync["ms_per_step"], 1e-9)
+        grad_sync["roofline"] = "per bucket max(3 x 4 B x n / measured HBM, (W-1) x k x 8 B / 770 GB/s)"
+
     tokens = tr.tokens_per_step() * K
     value = tokens / (ms_total / 1e3)
     baseline = None
@@ -249,7 +280,7 @@ def main() -> int:
                    "l2": "inputs larger than L2 (weights %.1f GB, grads %.1f GB per rank)" % (
                        2e-9 * tr.model.arena.numel, 4e-9 * tr.model.arena.numel),
                    "params": tr.cfg.num_params()},
-        "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
+        "clocks": clocks, "e2e": e2e, "grad_sync": grad_sync, "gpu_launches": int(launches),
         "mfu_bf16_of_measured_burst": None,
     }
     try:

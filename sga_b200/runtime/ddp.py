@@ -112,15 +112,39 @@ class DataParallel:
         if bucket.index in self._synced:
             return
         self._synced.add(bucket.index)
+        timed = getattr(self, "time_syncs", False) and self.device.type == "cuda"
         if self.comm_stream is not None:
             ev = torch.cuda.Event()
             ev.record(torch.cuda.current_stream(self.device))
             self.comm_stream.wait_event(ev)
             with torch.cuda.stream(self.comm_stream):
+                pair = self._timed_pair() if timed else None
                 self.bucket_sync_fn(bucket)
+                if pair is not None:
+                    pair[1].record()
         else:
+            pair = self._timed_pair() if timed else None
             self.bucket_sync_fn(bucket)
+            if pair is not None:
+                pair[1].record()
         self.sync_launches += 1
+
+    def _timed_pair(self):
+        """Event pair around one bucket's synchronisation on the stream it runs on (``time_syncs``)."""
+        pair = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+        pair[0].record()
+        if not hasattr(self, "_sync_events"):
+            self._sync_events = []
+        self._sync_events.append(pair)
+        return pair
+
+    def sync_device_ms(self) -> float:
+        """Sum of the device time of the bucket synchronisations recorded since the last call
+        (their own kernels and library collectives; overlapped with the backward pass in a step)."""
+        torch.cuda.synchronize(self.device)
+        total = sum(a.elapsed_time(b) for a, b in getattr(self, "_sync_events", []))
+        self._sync_events = []
+        return float(total)
 
     def finish_pending(self) -> None:
         """Synchronise every bucket not yet launched and join the comm stream."""
