@@ -120,6 +120,26 @@ class SyntheticTokens:
         return out
 
 
+class _nvtx:
+    """NVTX range around a phase of the step when ``SGA_NVTX=1`` (the launcher's profiler prefix captures
+    ``nvtx,cuda,osrt``); a no-op otherwise."""
+
+    on = os.environ.get("SGA_NVTX", "0") == "1"
+
+    def __init__(self, name: str):
+        self.name = name
+
+    def __enter__(self):
+        if self.on and torch.cuda.is_available():
+            torch.cuda.nvtx.range_push(self.name)
+        return self
+
+    def __exit__(self, *exc):
+        if self.on and torch.cuda.is_available():
+            torch.cuda.nvtx.range_pop()
+        return False
+
+
 class Trainer:
     def __init__(self, args, quiet: bool = False):
         self.args = args
@@ -332,17 +352,21 @@ class Trainer:
                 last = i == self.num_micro - 1
                 if last:
                     arm_last()
-                loss = self.model.forward_backward(tokens, targets, loss_scale=1.0 / self.num_micro,
-                                                   on_param_done=self.ddp.on_param_done if last else None,
-                                                   reduce_replicated=last)
+                with _nvtx(f"micro_batch_{i}"):
+                    loss = self.model.forward_backward(tokens, targets, loss_scale=1.0 / self.num_micro,
+                                                       on_param_done=self.ddp.on_param_done if last else None,
+                                                       reduce_replicated=last)
                 losses.append(loss)
         if self.engine is not None:
-            if not self.engine.grad_sync(self.ddp, False):
-                self.ddp.finish_grad_sync()
-            ok, gn, _nz = self.engine.optimizer_step(self.optimizer, [self.ddp], it)
+            with _nvtx("grad_sync"):
+                if not self.engine.grad_sync(self.ddp, False):
+                    self.ddp.finish_grad_sync()
+            with _nvtx("optimizer_step"):
+                ok, gn, _nz = self.engine.optimizer_step(self.optimizer, [self.ddp], it)
             self.last_grad_norm = gn
         else:
-            self._dense_step()
+            with _nvtx("dense_step"):
+                self._dense_step()
         if self.pipeline is not None:
             # the loss lives on the last stage: hand it to every stage of the replica
             t = torch.stack(losses).mean() if losses else torch.zeros((), dtype=torch.float32, device=self.device)
