@@ -108,7 +108,12 @@ def bench_index_sync(small):
 
     pool = SymmPool(device="cuda:0")
     ch = p2p.PeerChannel(pool)
-    n = 32 * 1024 * 1024
+    for mi in ((32,) if small else (8, 16, 32, 64)):
+        _index_sync_case(pool, ch, p2p, mi * 1024 * 1024, small)
+    pool.close()
+
+
+def _index_sync_case(pool, ch, p2p, n, small):
     k = n // 100
     acc0 = torch.randn(n, device="cuda") * 1e-3
     acc = acc0.clone()
@@ -126,7 +131,6 @@ def bench_index_sync(small):
     ch.check()
     # three reads of the bucket (two radix digits, compaction) + payload write, read-back and scatter
     emit("bucket_index_sync_kernel", f"n={n} k={k} (1 rank)", ms, bytes_=n * 4.0 * 3 + k * 8.0 * 3)
-    pool.close()
 
 
 def bench_elementwise(small):
