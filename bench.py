@@ -228,8 +228,12 @@ def main() -> int:
         tr.ddp.time_syncs = True
         for i in range(2):
             tr.train_step(tr.host_batch(step_id + K + i))
-        sync_ms = torch.tensor([tr.ddp.sync_device_ms() / 2], dtype=torch.float64, device=dev)
         tr.ddp.time_syncs = False
+        try:
+            local_ms = tr.ddp.sync_device_ms() / 2
+        except Exception:  # a rank without a reading still joins the reduction below
+            local_ms = 0.0
+        sync_ms = torch.tensor([local_ms], dtype=torch.float64, device=dev)
         if world > 1:
             dist.all_reduce(sync_ms, op=dist.ReduceOp.MAX)
         if float(sync_ms.item()) > 0.0:
