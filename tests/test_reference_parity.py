@@ -315,7 +315,7 @@ def test_engine_flow_matches_reference_engine(ref, monkeypatch):
     (``tests/test_engine_unit.py:647-730`` there), against this framework's engine on the same
     parameters and the same per-step gradients, for mask- and index-consuming backends across scores,
     both optimizers, the residual fold, the boundary dual lr, every selection method and histogram
-    mode, sliced and block transports, always-synchronised parameters and the decoupled calendar: same full / sparse calendar, bit-identical
+    mode, sliced and block transports, always-synchronised parameters, the decoupled calendar and failed (non-finite) steps: same full / sparse calendar, bit-identical
     residual buffer, weights and gradient norms equal to fp32 rounding (the reference's dense steps
     run ``torch.optim.Adam``, whose operation order differs from the fused form by an ulp)."""
     import copy
@@ -339,10 +339,13 @@ def test_engine_flow_matches_reference_engine(ref, monkeypatch):
     ref("sga.engine")
     H = importlib.import_module("ref_engine_harness")
 
-    def run_reference(combo, steps, seed, extra):
+    def run_reference(combo, steps, seed, extra, bad_steps=()):
         torch.manual_seed(seed)
         chunk = H._FakeChunk(n_params=3, numel_per=64)
         mp = H._FakeMPOpt(chunk)
+        now = {"step": 0}
+        stock_prepare = mp.prepare_grads
+        mp.prepare_grads = lambda: (stock_prepare() or True) if now["step"] in bad_steps else stock_prepare()
         p0 = [p.detach().clone() for p in chunk.params]
         eng = H._build_engine(combo, extra)
         eng.attach(chunk)
@@ -350,16 +353,17 @@ def test_engine_flow_matches_reference_engine(ref, monkeypatch):
         gen = torch.Generator().manual_seed(seed + 1)
         with H._ReplicaWorld(world=1):
             for step in range(1, steps + 1):
+                now["step"] = step
                 g = torch.randn(chunk.bucket.grad_data.numel(), generator=gen)
                 grads.append(g.clone())
                 chunk.bucket.grad_data += g
                 assert eng.grad_sync(chunk, force_all_reduce=False) is True
                 full = bool(eng._step_full)
-                _ok, gn, _nz = eng.optimizer_step(mp, [chunk], step)
-                log.append((step, full, float(gn)))
+                ok, gn, _nz = eng.optimizer_step(mp, [chunk], step)
+                log.append((step, (full, bool(ok)), float(gn) if gn is not None else float("nan")))
         return p0, grads, log, [m.detach().clone() for m in mp.main_params], chunk.bucket.grad_data.clone()
 
-    def run_ours(combo, p0, grads, extra):
+    def run_ours(combo, p0, grads, extra, bad_steps=()):
         kw = {**combo["config"], **combo["selection_params"], **combo["opt_params"], **combo.get("backend_params", {}),
               "sga_score": combo["score"], "sga_selection": combo["selection"], "sga_optimizer": combo["opt"],
               "sga_backend": combo["backend"], "sga_enabled": True, **(extra or {})}
@@ -375,11 +379,15 @@ def test_engine_flow_matches_reference_engine(ref, monkeypatch):
                            ddp_config=DDPConfig(average_in_collective=False, overlap_grad_reduce=False))
         opt = FlatOptimizer(model.arena, OptimizerConfig(lr=1e-3, weight_decay=1e-2, adam_beta1=0.9, adam_beta2=0.95,
                                                          adam_eps=1e-8, clip_grad=1.0))
+        now = {"step": 0}
+        own_prepare = opt.prepare_grads
+        opt.prepare_grads = lambda: True if now["step"] in bad_steps else own_prepare()
         eng = build_engine(quiet=True)
         eng.log_interval = 0
         eng.attach(ddp)
         log = []
         for step, g in enumerate(grads, 1):
+            now["step"] = step
             off = 0
             for s in model.arena.slots:
                 n = s.end - s.start
@@ -390,8 +398,8 @@ def test_engine_flow_matches_reference_engine(ref, monkeypatch):
             if not eng.grad_sync(ddp, False):
                 ddp.finish_grad_sync()
             full = bool(eng._step_full)
-            _ok, gn, _nz = eng.optimizer_step(opt, [ddp], step)
-            log.append((step, full, float(gn.item() if hasattr(gn, "item") else gn)))
+            ok, gn, _nz = eng.optimizer_step(opt, [ddp], step)
+            log.append((step, (full, bool(ok)), float(gn) if gn is not None else float("nan")))
         return (log, [s.main.clone() for s in model.arena.slots],
                 torch.cat([model.arena.main_grad[s.start:s.end] for s in model.arena.slots]))
 
@@ -419,15 +427,20 @@ def test_engine_flow_matches_reference_engine(ref, monkeypatch):
         ({**M, "score": "abs_g"}, {"sga_selection_block_size": 8, "sga_selection_histogram_mode": "exact",
                                    "sga_backend_emission": "writeback"}),
     ]
-    for combo, extra in cases:
+    # a failed step (the optimizer wrapper reports non-finite gradients) on a sparse step and on a boundary:
+    # full clear, the cycle position is consumed, nothing is committed (sga/engine.py:512-521)
+    cases = [(c, e, ()) for c, e in cases] + [(U, None, (5, 9)), (M, None, (5, 9)),
+                                              (M, {"sga_optimizer_residual_mean": True}, (4, 8))]
+    for combo, extra, bad_steps in cases:
         c = copy.deepcopy(combo)
-        tag = (combo["score"], combo["backend"], combo["opt"], extra)
-        p0, grads, rlog, rfinal, rres = run_reference(c, 14, 7, extra)
-        olog, ofinal, ores = run_ours(c, p0, grads, extra)
+        tag = (combo["score"], combo["backend"], combo["opt"], extra, bad_steps)
+        p0, grads, rlog, rfinal, rres = run_reference(c, 14, 7, extra, bad_steps)
+        olog, ofinal, ores = run_ours(c, p0, grads, extra, bad_steps)
         assert [(s, f) for s, f, _ in rlog] == [(s, f) for s, f, _ in olog], tag
+        assert [ok for _, (_, ok), _ in rlog].count(False) == len(bad_steps), tag
         assert torch.equal(rres, ores), ("residual buffer differs", tag)
         for (_, _, a), (_, _, b) in zip(rlog, olog):
-            assert abs(a - b) <= 5e-7 * max(a, 1e-9), tag
+            assert (a != a and b != b) or abs(a - b) <= 5e-7 * max(a, 1e-9), tag
         for a, b in zip(rfinal, ofinal):
             assert float((a - b).abs().max()) <= 3e-7, tag
 
