@@ -7,7 +7,10 @@
 plus ``begin_step`` which, called before the last micro-batch, lets every
 bucket's synchronisation start while the backward pass is still running.
 
-Calendar (1-based steps, ``CycleManager``): a step is FULL when forced, when
+Step numbers are the caller's: the trainer passes the number of completed iterations (0 on the first
+step of a fresh run, K after a resume at K), which is also the number in the log line and in the
+trace file names (``sga/trace.py:37-41``: the dump at step t holds the state with t commits applied).
+Calendar (``CycleManager``): a step is FULL when forced, when
 ``step <= start_iter``, at a cycle boundary ``(step - start) % period == 0``,
 on the decoupled extra grid, or while no support exists. Reselection happens
 only at non-forced boundaries. A full step runs the dense average of every
@@ -374,7 +377,7 @@ class SGAEngine:
         num_zeros = self._count_zeros() if optimizer.config.log_num_zeros_in_grad else None
         # 3b. trace dump slot
         if self._trace is not None:
-            self._trace.maybe_dump(self, optimizer, step - 1, grad_norm)
+            self._trace.maybe_dump(self, optimizer, step, grad_norm)
         # 4. optimizer template
         arena = self._ddp.arena
         next_full = self._cycle.is_full(step + 1)
@@ -443,7 +446,7 @@ class SGAEngine:
         grad_norm, coeff = self._masked_clip_grad_norm(optimizer, True, step, shadow=True, scale_now=reselected)
         num_zeros = self._count_zeros() if optimizer.config.log_num_zeros_in_grad else 0
         if self._trace is not None:
-            self._trace.maybe_dump(self, optimizer, step - 1, grad_norm)
+            self._trace.maybe_dump(self, optimizer, step, grad_norm)
         if reselected:
             self._shadow_reselect(self._refresh_records(optimizer))
         arena = self._ddp.arena
@@ -596,7 +599,7 @@ class SGAEngine:
                 K.clip_coeff(sumsq, 1.0 / world, clip, self._dev["coeff"], self._dev["norm"])
             else:
                 K.clip_coeff(sumsq, 1.0, clip, self._dev["coeff"], self._dev["norm"])
-            wants_dump = scale_now or (self._trace is not None and any(self._trace.wants(step - 1)))
+            wants_dump = scale_now or (self._trace is not None and any(self._trace.wants(step)))
             if wants_dump and clip > 0.0:
                 # the dump slot reads post-clip gradients: scale explicitly, hand the kernel 1.0
                 self._scale_communicated(was_full, mask)
@@ -623,7 +626,7 @@ class SGAEngine:
             c = clip / (norm + 1.0e-6)
             if c < 1.0:
                 coeff = float(torch.tensor(c, dtype=torch.float32).item())
-        wants_dump = scale_now or (self._trace is not None and any(self._trace.wants(step - 1)))
+        wants_dump = scale_now or (self._trace is not None and any(self._trace.wants(step)))
         if wants_dump and coeff != 1.0:
             self._scale_communicated(was_full, mask, coeff)
             return norm, 1.0

@@ -324,8 +324,11 @@ class Trainer:
     def train_step(self, batch: torch.Tensor) -> torch.Tensor:
         """``batch``: ``[num_micro * micro_batch, seq + 1]`` int64 token ids, on the
         host (pinned) or already on the device. Returns the mean loss (device scalar)."""
-        self.iteration += 1
+        # the engine is called with the number of completed iterations, 0 on the first step of a fresh run and K
+        # after a resume at K: the numbering of its step calendar, of the log line and of the trace files
+        # ("dump at step t is the state with exactly t commits applied", sga/trace.py:37-41)
         it = self.iteration
+        self.iteration += 1
         mb = self.args.micro_batch_size
         if batch.device != self.device:
             batch = batch.to(self.device, non_blocking=True)

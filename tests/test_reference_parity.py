@@ -691,3 +691,98 @@ def test_shadow_flow_matches_reference_engine(ref, monkeypatch):
             assert (mk is None) == (mk2 is None) and (mk is None or torch.equal(mk, mk2)), tag
             assert torch.equal(gb, gb2), tag
         assert float((rw - ow).abs().max()) <= 5e-6, tag  # torch.optim.AdamW folds the bias corrections differently
+
+
+@pytest.mark.skipif(not os.path.exists(os.path.join(REF, "tests", "ref_engine_harness.py")),
+                    reason="no copy of the reference's engine test harness under baseline/_ref/tests")
+@pytest.mark.parametrize("async_writer", [False, True])
+def test_trace_files_equal_reference_collector(ref, monkeypatch, tmp_path, async_writer):
+    """Both engines with their trace collectors on over the same run (two branch points, windows that
+    span full and sparse steps): the same file names (the step number is the engine's own step), the
+    same phase tags, bit-identical gradient payloads, weights and moments to an ulp."""
+    import copy
+    import types
+
+    from sga_b200 import config as C
+    from sga_b200.runtime.arena import FlatArena, ParamSpec
+    from sga_b200.runtime.builder import build_engine
+    from sga_b200.runtime.ddp import DataParallel, DDPConfig
+    from sga_b200.runtime.optimizer import FlatOptimizer, OptimizerConfig
+
+    mods = {n: types.ModuleType(n) for n in ("megatron", "megatron.core", "megatron.core.tensor_parallel",
+                                             "megatron.core.transformer", "megatron.core.transformer.module")}
+    mods["megatron.core.tensor_parallel"].param_is_not_tensor_parallel_duplicate = lambda p, g=None: True
+    mods["megatron.core.transformer.module"].param_is_not_shared = lambda p: True
+    for n, m in mods.items():
+        monkeypatch.setitem(sys.modules, n, m)
+    monkeypatch.setenv("SGA_ALLOW_FROZEN_SELECTION", "1")
+    monkeypatch.syspath_prepend(os.path.join(REF, "tests"))
+    ref("sga.engine")
+    H = importlib.import_module("ref_engine_harness")
+    ta, tb = str(tmp_path / "ref"), str(tmp_path / "ours")
+    combo = copy.deepcopy(H._ABS_M)
+    extra = {"sga_trace_branch_points": [3, 7], "sga_trace_window": 3, "sga_trace_async": async_writer}
+
+    torch.manual_seed(3)
+    chunk = H._FakeChunk(n_params=3, numel_per=256)
+    mp = H._FakeMPOpt(chunk)
+    p0 = [p.detach().clone() for p in chunk.params]
+    eng = H._build_engine(combo, {**extra, "sga_trace_dir": ta})
+    eng.attach(chunk)
+    gen = torch.Generator().manual_seed(4)
+    grads = []
+    with H._ReplicaWorld(world=1):
+        for step in range(1, 13):  # the step past the last window drains the asynchronous writer
+            g = torch.randn(chunk.bucket.grad_data.numel(), generator=gen)
+            grads.append(g.clone())
+            chunk.bucket.grad_data += g
+            eng.grad_sync(chunk, force_all_reduce=False)
+            eng.optimizer_step(mp, [chunk], step)
+
+    kw = {**combo["config"], **combo["selection_params"], **combo["opt_params"], **combo.get("backend_params", {}),
+          "sga_score": combo["score"], "sga_selection": combo["selection"], "sga_optimizer": combo["opt"],
+          "sga_backend": combo["backend"], "sga_enabled": True, **extra, "sga_trace_dir": tb}
+    C.set_args(C.make_args(**kw))
+    model = types.SimpleNamespace()
+    model.arena = FlatArena([ParamSpec(f"p{i}", tuple(p.shape), 0, "zeros") for i, p in enumerate(p0)],
+                            bucket_elems=10 ** 9, device="cpu")
+    model.named_parameters = lambda: [(s.name, s.model) for s in model.arena.slots]
+    for s, p in zip(model.arena.slots, p0):
+        s.main.copy_(p)
+    model.arena.sync_model_from_main()
+    ddp = DataParallel(model, transport="local",
+                       ddp_config=DDPConfig(average_in_collective=False, overlap_grad_reduce=False))
+    opt = FlatOptimizer(model.arena, OptimizerConfig(lr=1e-3, weight_decay=1e-2, adam_beta1=0.9, adam_beta2=0.95,
+                                                     adam_eps=1e-8, clip_grad=1.0))
+    ours = build_engine(quiet=True)
+    ours.log_interval = 0
+    ours.attach(ddp)
+    for step, g in enumerate(grads, 1):
+        off = 0
+        for s in model.arena.slots:
+            n = s.end - s.start
+            model.arena.main_grad[s.start:s.end] += g[off:off + n]
+            off += n
+        ddp.begin_step()
+        ours.begin_step(ddp, step)
+        if not ours.grad_sync(ddp, False):
+            ddp.finish_grad_sync()
+        ours.optimizer_step(opt, [ddp], step)
+    ours._trace.close()
+
+    names = sorted(os.listdir(ta))
+    assert names == sorted(os.listdir(tb))
+    assert names == ["catalog.pt"] + sorted([f"step_{t:06d}_g.pt" for t in (3, 4, 5, 7, 8, 9)]
+                                            + [f"step_{t:06d}_state.pt" for t in (3, 7)])
+    for name in names[1:]:
+        a = torch.load(os.path.join(ta, name), weights_only=False)
+        b = torch.load(os.path.join(tb, name), weights_only=False)
+        assert (a["meta"]["step"], a["meta"]["phase"]) == (b["meta"]["step"], b["meta"]["phase"]), name
+        assert abs(a["meta"]["grad_norm"] - b["meta"]["grad_norm"]) <= 1e-6 * a["meta"]["grad_norm"], name
+        if name.endswith("_g.pt"):
+            assert all(torch.equal(a["payload"][k], b["payload"][k]) for k in a["payload"]), name
+        else:
+            assert all(torch.equal(a["payload"]["g"][k], b["payload"]["g"][k]) for k in a["payload"]["g"]), name
+            for part, tol in (("w", 1e-7), ("m", 4e-9), ("v", 4e-9)):  # the reference's dense steps run torch.optim.Adam
+                assert all(float((a["payload"][part][k] - b["payload"][part][k]).abs().max()) <= tol
+                           for k in a["payload"][part]), (name, part)
