@@ -786,3 +786,98 @@ def test_trace_files_equal_reference_collector(ref, monkeypatch, tmp_path, async
             for part, tol in (("w", 1e-7), ("m", 4e-9), ("v", 4e-9)):  # the reference's dense steps run torch.optim.Adam
                 assert all(float((a["payload"][part][k] - b["payload"][part][k]).abs().max()) <= tol
                            for k in a["payload"][part]), (name, part)
+
+
+def test_resume_guard_decisions_equal(ref, monkeypatch, tmp_path):
+    """The reference's resume guard (``sga/train_gpt.py:49-194``; the modules of its external training
+    stack are empty stand-ins, the two checkpoint-path helpers it calls spell Megatron's layout) and this
+    framework's, over stub checkpoints: the same pass / refuse decision in every scenario."""
+    import types
+
+    from sga_b200.config.validation import sga_defaults as our_defaults
+    from sga_b200.runtime import checkpoint as ck
+
+    torch.serialization.add_safe_globals([argparse.Namespace])
+
+    def stand_in(name, **attrs):
+        m = types.ModuleType(name)
+        for k, v in attrs.items():
+            setattr(m, k, v)
+        monkeypatch.setitem(sys.modules, name, m)
+
+    for name in ("pretrain_gpt", "megatron", "megatron.core"):
+        stand_in(name)
+    stand_in("megatron.core.enums", ModelType=None)
+    stand_in("megatron.training", inprocess_restart=None, pretrain=None)
+    stand_in("megatron.training.argument_utils", pretrain_cfg_container_from_args=None)
+    stand_in("megatron.training.arguments", parse_and_validate_args=None)
+    stand_in("gpt_builders", gpt_builder=None)
+    stand_in("model_provider", model_provider=None)
+    stand_in("megatron.training.checkpointing",
+             get_checkpoint_tracker_filename=lambda load: os.path.join(load, "latest_checkpointed_iteration.txt"),
+             get_checkpoint_name=lambda load, it, return_base_dir=False: os.path.join(load, f"iter_{it:07d}"))
+    R = ref("sga.train_gpt")
+    ref_defaults = ref("sga.config.validation").sga_defaults
+
+    def namespace(defaults, **over):
+        a = argparse.Namespace(**defaults)
+        a.train_iters, a.load, a.sga_allow_config_override = 100, None, False
+        for k, v in over.items():
+            setattr(a, k, v)
+        return a
+
+    def save(root, it, saved_args, tracker=True, shard=True, raw=None):
+        os.makedirs(root, exist_ok=True)
+        if tracker:
+            with open(os.path.join(root, "latest_checkpointed_iteration.txt"), "w") as fh:
+                fh.write(str(it) if tracker is True else tracker)
+        if shard:
+            d = os.path.join(root, f"iter_{it:07d}", "mp_rank_00")
+            os.makedirs(d, exist_ok=True)
+            torch.save(raw if raw is not None else {"args": saved_args, "iteration": it},
+                       os.path.join(d, "model_optim_rng.pt"))
+
+    base = dict(sga_enabled=True, sga_score="abs_g", sga_backend="torch_pipelined_index",
+                sga_selection_method="histogram", sga_selection_ratio_percent=10.0, sga_cycle_period=4)
+    pct = {**base, "sga_cycle_start_iter_percent": 10.0}
+    scenarios = {
+        "no tracker": (dict(saved=base, cur=base, tracker=False), "pass"),
+        "same": (dict(saved=base, cur=base), "pass"),
+        "value differs": (dict(saved=base, cur={**base, "sga_cycle_period": 8}), "refuse"),
+        "10 vs 10.0": (dict(saved={**base, "sga_selection_ratio_percent": 10}, cur=base), "refuse"),
+        "release tracker": (dict(saved=base, cur={**base, "sga_cycle_period": 8}, tracker="release"), "pass"),
+        "no shard": (dict(saved=base, cur=base, shard=False), "refuse"),
+        "no saved sga attrs": (dict(saved=None, cur=base), "refuse"),
+        "legacy json era": (dict(saved={**base, "sga_config": "{}"}, cur=base), "refuse"),
+        "retired key": (dict(saved={**base, "sga_old_knob": 3}, cur=base), "refuse"),
+        "override": (dict(saved=base, cur={**base, "sga_cycle_period": 8, "sga_allow_config_override": True}), "pass"),
+        "sga off": (dict(saved=base, cur={**base, "sga_enabled": False, "sga_cycle_period": 8}), "pass"),
+        "percent same": (dict(saved=pct, cur=pct), "pass"),
+        "percent, train_iters changed": (dict(saved={**pct, "train_iters": 50}, cur=pct), "refuse"),
+        "list reordered": (dict(saved={**base, "sga_always_sync_layers": "a,b"},
+                                cur={**base, "sga_always_sync_layers": "b,a"}), "refuse"),
+        "older checkpoint lacks a key": (dict(saved=base, cur=base, drop=["sga_backend_index_slices"]), "pass"),
+        "corrupt shard": (dict(saved=base, cur=base, raw=[1, 2, 3]), "refuse"),
+        "newest iteration decides": (dict(saved=base, cur=base, older={**base, "sga_cycle_period": 8}), "pass"),
+    }
+    for name, (sc, want) in scenarios.items():
+        got = []
+        for side, (defaults, guard) in enumerate(((ref_defaults(), R._sga_resume_guard),
+                                                  (our_defaults(), ck.sga_resume_guard))):
+            root = str(tmp_path / f"{abs(hash(name))}_{side}")
+            saved = argparse.Namespace(train_iters=100) if sc["saved"] is None else namespace(defaults, **sc["saved"])
+            for k in sc.get("drop", []):
+                delattr(saved, k)
+            if "older" in sc:
+                save(root, 100, namespace(defaults, **sc["older"]))
+                save(root, 500, saved, tracker="100\n500")
+            else:
+                save(root, 500, saved, tracker=sc.get("tracker", True), shard=sc.get("shard", True), raw=sc.get("raw"))
+            cur = namespace(defaults, **sc["cur"])
+            cur.load = root
+            try:
+                guard(cur)
+                got.append("pass")
+            except SystemExit:
+                got.append("refuse")
+        assert got == [want, want], (name, got)
