@@ -142,3 +142,15 @@ def test_visibility_probe_refuses_wrong_size(tmp_path):
         launch.confirm_visible(["n0"], str(f), 6, None, "local")
     with pytest.raises(launch.LaunchError):
         launch.confirm_visible(["n0"], str(tmp_path / "missing"), 5, None, "local")
+
+
+@pytest.mark.timeout(900)
+def test_multinode_smoke_script_local_executor(tmp_path):
+    """The cross-node smoke script end to end with local subprocesses standing in for the two nodes."""
+    import subprocess
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    res = subprocess.run(["bash", os.path.join(root, "tests", "smoke_replay_multinode.sh"), "nodeA", "nodeB",
+                          str(tmp_path / "work")], env=dict(os.environ, SGA_LAUNCH_EXECUTOR="local"),
+                         capture_output=True, text=True, timeout=800)
+    assert res.returncode == 0 and "SMOKE PASS" in res.stdout, (res.stdout[-1500:], res.stderr[-1500:])
