@@ -55,6 +55,11 @@ def add_trainer_args(p: argparse.ArgumentParser) -> argparse.ArgumentParser:
     g.add_argument("--clip-grad", type=float, default=1.0)
     g.add_argument("--seed", type=int, default=1234)
     g.add_argument("--data-seed", type=int, default=1234)
+    g.add_argument("--data-path", default=None,
+                   help="pre-tokenised corpus: PREFIX of an indexed-dataset .bin/.idx pair, or a flat token file; "
+                        "default: synthetic uniform token ids")
+    g.add_argument("--data-dtype", choices=("uint16", "int32", "uint32", "int64"), default=None,
+                   help="token dtype of a flat --data-path file (read from the .idx header when there is one)")
     g.add_argument("--log-interval", type=int, default=1)
     g.add_argument("--save", type=str, default=None)
     g.add_argument("--load", type=str, default=None)
@@ -266,7 +271,13 @@ class Trainer:
             self.engine.attach(self.ddp)
             if self.tp is not None or self.pp_size > 1:
                 self.engine.model_parallel_norm = self._tp_norm
-        self.data = SyntheticTokens(self.cfg.vocab, self.cfg.seq_len, args.data_seed, pin=cuda)
+        if getattr(args, "data_path", None):
+            from .data import TokenFile
+
+            self.data = TokenFile(args.data_path, self.cfg.vocab, self.cfg.seq_len, args.data_seed,
+                                  args.global_batch_size, dtype=getattr(args, "data_dtype", None), pin=cuda)
+        else:
+            self.data = SyntheticTokens(self.cfg.vocab, self.cfg.seq_len, args.data_seed, pin=cuda)
         self.iteration = 0
         self._dense = None
         if cuda:

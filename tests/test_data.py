@@ -1,0 +1,72 @@
+"""Token-file data source: index header, windows, seeded order, rank partition, epochs, trainer wiring."""
+import struct
+
+import numpy as np
+import pytest
+import torch
+
+from sga_b200.runtime.data import TokenFile, indexed_dataset_dtype
+from sga_b200.runtime.trainer import Trainer, default_args
+
+
+def _write_pair(prefix, tokens, code=8, dtype=np.uint16):
+    np.asarray(tokens, dtype=dtype).tofile(str(prefix) + ".bin")
+    with open(str(prefix) + ".idx", "wb") as fh:  # header of the indexed-dataset index: magic, version, dtype code
+        fh.write(b"MMIDIDX\x00\x00" + struct.pack("<Q", 1) + struct.pack("<B", code) + struct.pack("<QQ", 1, 1))
+
+
+def test_index_header_and_windows(tmp_path):
+    n, seq = 1000, 16
+    toks = np.arange(n) % 500
+    _write_pair(tmp_path / "corpus", toks)
+    assert indexed_dataset_dtype(str(tmp_path / "corpus.idx")) == np.uint16
+    ds = TokenFile(str(tmp_path / "corpus"), vocab=512, seq_len=seq, seed=7, global_batch=8)
+    assert ds.num_samples == (n - 1) // seq
+    b = ds.batch(0, 0, 8)
+    assert b.shape == (8, seq + 1) and b.dtype == torch.int64
+    starts = set()
+    for row in b:
+        d = (row[1:] - row[:-1]) % 500
+        assert bool((d == 1).all()), "a window is a contiguous run of the stream"
+        starts.add(int(row[0]))
+    assert len(starts) == 8, "distinct windows within a batch"
+    # the order depends on the seed only: two ranks' halves are the one-rank batch, and a resume repeats it
+    again = TokenFile(str(tmp_path / "corpus.bin"), vocab=512, seq_len=seq, seed=7, global_batch=8)
+    assert torch.equal(torch.cat([again.batch(0, 0, 4), again.batch(0, 4, 4)]), b)
+    assert not torch.equal(TokenFile(str(tmp_path / "corpus"), 512, seq, 8, 8).batch(0, 0, 8), b)
+    # an epoch visits every window once; the next epoch reshuffles
+    per_epoch = ds.num_samples
+    seen = [int(ds.batch(s, 0, 1)[0, 0]) for s in range(0, per_epoch * 8, 8)]
+    first = torch.cat([ds.batch(s, 0, 8) for s in range((per_epoch + 7) // 8)])[:per_epoch, 0]
+    assert len(set(first.tolist())) == per_epoch and len(seen) == per_epoch
+
+
+def test_flat_file_dtype_and_vocab_check(tmp_path):
+    np.arange(300, dtype=np.int32).tofile(str(tmp_path / "flat.bin"))
+    ds = TokenFile(str(tmp_path / "flat.bin"), vocab=1000, seq_len=8, seed=1, global_batch=2)
+    assert int(ds.batch(0, 0, 2).max()) < 300
+    with pytest.raises(ValueError, match="outside"):
+        TokenFile(str(tmp_path / "flat.bin"), vocab=100, seq_len=8, seed=1, global_batch=2).batch(0, 0, 37)
+    with pytest.raises(ValueError, match="fewer than one sequence"):
+        TokenFile(str(tmp_path / "flat.bin"), vocab=1000, seq_len=4096, seed=1, global_batch=2)
+    with pytest.raises(FileNotFoundError):
+        TokenFile(str(tmp_path / "absent"), vocab=10, seq_len=8, seed=1, global_batch=2)
+    (tmp_path / "bad.idx").write_bytes(b"not an index")
+    with pytest.raises(ValueError, match="bad magic"):
+        indexed_dataset_dtype(str(tmp_path / "bad.idx"))
+
+
+def test_trainer_reads_the_corpus(tmp_path):
+    tr0 = Trainer(default_args(model="test_tiny", micro_batch_size=2, global_batch_size=4, train_iters=2, device="cpu",
+                               log_interval=0), quiet=True)
+    vocab, seq = tr0.cfg.vocab, tr0.cfg.seq_len
+    tr0.close()
+    g = torch.Generator().manual_seed(0)
+    _write_pair(tmp_path / "c", torch.randint(0, vocab, (seq * 40 + 1,), generator=g).numpy(), code=4, dtype=np.int32)
+    tr = Trainer(default_args(model="test_tiny", micro_batch_size=2, global_batch_size=4, train_iters=2, device="cpu",
+                              log_interval=0, data_path=str(tmp_path / "c")), quiet=True)
+    b = tr.host_batch(0)
+    assert b.shape == (4, seq + 1) and int(b.max()) < vocab
+    loss = tr.train_step(b)
+    assert torch.isfinite(loss)
+    tr.close()
