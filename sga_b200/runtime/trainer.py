@@ -48,6 +48,11 @@ def add_trainer_args(p: argparse.ArgumentParser) -> argparse.ArgumentParser:
     g.add_argument("--global-batch-size", type=int, default=256)
     g.add_argument("--train-iters", type=int, default=10)
     g.add_argument("--lr", type=float, default=3e-4)
+    g.add_argument("--min-lr", type=float, default=0.0)
+    g.add_argument("--lr-decay-style", choices=("constant", "linear", "cosine"), default="constant")
+    g.add_argument("--lr-warmup-iters", type=int, default=0)
+    g.add_argument("--lr-warmup-init", type=float, default=0.0)
+    g.add_argument("--lr-decay-iters", type=int, default=None, help="default: --train-iters")
     g.add_argument("--weight-decay", type=float, default=0.1)
     g.add_argument("--adam-beta1", type=float, default=0.9)
     g.add_argument("--adam-beta2", type=float, default=0.95)
@@ -105,6 +110,29 @@ def init_distributed(device_type: str):
         dist.init_process_group(backend=backend, **kwargs)
     rank = dist.get_rank() if dist.is_initialized() else 0
     return rank, (dist.get_world_size() if dist.is_initialized() else 1)
+
+
+def scheduled_lr(args, done: int) -> float:
+    """Learning rate of the step that follows ``done`` completed iterations: linear warm-up from
+    ``--lr-warmup-init`` over ``--lr-warmup-iters``, then constant, linear or cosine decay to ``--min-lr`` at
+    ``--lr-decay-iters`` (the schedule of the training stack the reference's yamls are written for:
+    ``lr_decay_style`` / ``lr_warmup_iters`` / ``min_lr`` in ``examples/llama3/*.yaml`` there)."""
+    import math
+
+    max_lr, min_lr = float(args.lr), float(getattr(args, "min_lr", 0.0) or 0.0)
+    warm = int(getattr(args, "lr_warmup_iters", 0) or 0)
+    if warm > 0 and done <= warm:
+        init = float(getattr(args, "lr_warmup_init", 0.0) or 0.0)
+        return init + (max_lr - init) * done / warm
+    style = getattr(args, "lr_decay_style", "constant")
+    if style == "constant":
+        return max_lr
+    decay = int(getattr(args, "lr_decay_iters", None) or args.train_iters)
+    if done > decay:
+        return min_lr
+    ratio = (done - warm) / max(decay - warm, 1)
+    coeff = (1.0 - ratio) if style == "linear" else 0.5 * (math.cos(math.pi * ratio) + 1.0)
+    return min_lr + coeff * (max_lr - min_lr)
 
 
 class SyntheticTokens:
@@ -340,6 +368,7 @@ class Trainer:
         # ("dump at step t is the state with exactly t commits applied", sga/trace.py:37-41)
         it = self.iteration
         self.iteration += 1
+        self.optimizer.set_lr(scheduled_lr(self.args, it))
         mb = self.args.micro_batch_size
         if batch.device != self.device:
             batch = batch.to(self.device, non_blocking=True)

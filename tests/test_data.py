@@ -70,3 +70,24 @@ def test_trainer_reads_the_corpus(tmp_path):
     loss = tr.train_step(b)
     assert torch.isfinite(loss)
     tr.close()
+
+
+def test_learning_rate_schedule():
+    from sga_b200.runtime.trainer import scheduled_lr
+
+    a = default_args(lr=1e-3, min_lr=1e-4, lr_decay_style="cosine", lr_warmup_iters=10, train_iters=110)
+    assert scheduled_lr(a, 0) == 0.0 and scheduled_lr(a, 5) == pytest.approx(5e-4) and scheduled_lr(a, 10) == 1e-3
+    assert scheduled_lr(a, 60) == pytest.approx(1e-4 + 0.5 * 9e-4) and scheduled_lr(a, 110) == pytest.approx(1e-4)
+    assert scheduled_lr(a, 500) == 1e-4
+    lin = default_args(lr=1e-3, min_lr=0.0, lr_decay_style="linear", lr_warmup_iters=0, lr_decay_iters=100, train_iters=200)
+    assert scheduled_lr(lin, 25) == pytest.approx(7.5e-4) and scheduled_lr(lin, 150) == 0.0
+    assert scheduled_lr(default_args(lr=3e-4), 12345) == 3e-4
+    # the trainer applies it before every step, and the trace / checkpoint see the scheduled value
+    tr = Trainer(default_args(model="test_tiny", micro_batch_size=2, global_batch_size=2, train_iters=8, device="cpu",
+                              log_interval=0, lr=1e-3, lr_warmup_iters=4), quiet=True)
+    seen = []
+    for s in range(6):
+        tr.train_step(tr.host_batch(s))
+        seen.append(tr.optimizer.param_groups[0]["lr"])
+    assert seen == pytest.approx([0.0, 2.5e-4, 5e-4, 7.5e-4, 1e-3, 1e-3])
+    tr.close()
