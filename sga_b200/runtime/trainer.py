@@ -65,6 +65,11 @@ def add_trainer_args(p: argparse.ArgumentParser) -> argparse.ArgumentParser:
                         "default: synthetic uniform token ids")
     g.add_argument("--data-dtype", choices=("uint16", "int32", "uint32", "int64"), default=None,
                    help="token dtype of a flat --data-path file (read from the .idx header when there is one)")
+    g.add_argument("--eval-interval", type=int, default=0, help="validation loss every N iterations (0: never)")
+    g.add_argument("--eval-iters", type=int, default=10, help="global batches per validation pass")
+    g.add_argument("--eval-data-path", default=None,
+                   help="held-out corpus (same forms as --data-path); default: synthetic ids from another seed, or "
+                        "another window order of --data-path")
     g.add_argument("--log-interval", type=int, default=1)
     g.add_argument("--save", type=str, default=None)
     g.add_argument("--load", type=str, default=None)
@@ -354,6 +359,36 @@ class Trainer:
             dist.all_reduce(sumsq, group=self.pp_group)
 
     # ----------------------------------------------------------------- data
+    @torch.no_grad()
+    def evaluate(self, iters: int) -> float:
+        """Mean token loss over ``iters`` global batches of the validation stream, forward passes only,
+        averaged over the data-parallel ranks. Touches neither gradients nor optimizer state."""
+        if self.pp_size > 1:
+            raise NotImplementedError("validation under pipeline parallelism is not implemented")
+        if getattr(self, "_eval_data", None) is None:
+            a, cuda = self.args, self.device.type == "cuda"
+            path = getattr(a, "eval_data_path", None) or getattr(a, "data_path", None)
+            if path:
+                from .data import TokenFile
+
+                self._eval_data = TokenFile(path, self.cfg.vocab, self.cfg.seq_len, a.data_seed + 7919,
+                                            a.global_batch_size, dtype=getattr(a, "data_dtype", None), pin=cuda)
+            else:
+                self._eval_data = SyntheticTokens(self.cfg.vocab, self.cfg.seq_len, a.data_seed + 7919, pin=cuda)
+        mb, per_rank = self.args.micro_batch_size, self.num_micro * self.args.micro_batch_size
+        total = torch.zeros((), dtype=torch.float32, device=self.device)
+        for step in range(iters):
+            batch = self._eval_data.batch(step, self.dp_rank * per_rank, per_rank).to(self.device, non_blocking=True)
+            for i in range(self.num_micro):
+                chunk = batch[i * mb:(i + 1) * mb]
+                total += self.model.forward_backward(chunk[:, :-1], chunk[:, 1:], backward=False,
+                                                     reduce_replicated=False)
+        total /= max(iters * self.num_micro, 1)
+        if self.dp_world > 1:
+            dist.all_reduce(total, group=self.dp_group)
+            total /= self.dp_world
+        return float(total.item())
+
     def host_batch(self, step: int) -> torch.Tensor:
         """This rank's ``[num_micro * micro_batch, seq + 1]`` token block for ``step`` (pinned host memory)."""
         per_rank = self.num_micro * self.args.micro_batch_size

@@ -44,6 +44,10 @@ def main(argv=None) -> int:
                 gn = float(gn.item()) if hasattr(gn, "item") else (float(gn) if gn is not None else float("nan"))
                 print(f"[train] iteration {it}/{args.train_iters} | loss {lv:.6f} | grad norm {gn:.4f} | "
                       f"{dt * 1e3:.1f} ms/step | {tr.tokens_per_step() / dt:.0f} tokens/s", flush=True)
+        if args.eval_interval and it % args.eval_interval == 0:
+            val = tr.evaluate(args.eval_iters)
+            if tr.rank == 0:
+                print(f"[train] validation loss at iteration {it} | {val:.6f} | {args.eval_iters} batches", flush=True)
         if args.save and args.save_interval and it % args.save_interval == 0:
             ckpt.save_checkpoint(args.save, it, args, tr.model, tr.optimizer, tr.rank, tr.tp_rank, tr.dp_rank, tr.pp_rank, tr.pp_size)
     if args.save:

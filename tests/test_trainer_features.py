@@ -1,4 +1,4 @@
-"""Token-file data source: index header, windows, seeded order, rank partition, epochs, trainer wiring."""
+"""Trainer features around the step: token-file data source, learning-rate schedule, validation pass."""
 import struct
 
 import numpy as np
@@ -91,3 +91,22 @@ def test_learning_rate_schedule():
         seen.append(tr.optimizer.param_groups[0]["lr"])
     assert seen == pytest.approx([0.0, 2.5e-4, 5e-4, 7.5e-4, 1e-3, 1e-3])
     tr.close()
+
+
+def test_validation_pass_leaves_training_state_alone(capsys):
+    tr = Trainer(default_args(model="test_tiny", micro_batch_size=2, global_batch_size=4, train_iters=4, device="cpu",
+                              log_interval=0), quiet=True)
+    tr.train_step(tr.host_batch(0))
+    w, g, m = (t.clone() for t in (tr.model.arena.main_param, tr.model.arena.main_grad, tr.model.arena.exp_avg))
+    v1 = tr.evaluate(2)
+    assert v1 == tr.evaluate(2) and 0.0 < v1 < 20.0
+    assert all(torch.equal(a, b) for a, b in ((w, tr.model.arena.main_param), (g, tr.model.arena.main_grad),
+                                              (m, tr.model.arena.exp_avg)))
+    tr.close()
+    from sga_b200 import train_gpt
+
+    assert train_gpt.main(["--model", "test_tiny", "--micro-batch-size", "2", "--global-batch-size", "2",
+                           "--train-iters", "4", "--device", "cpu", "--log-interval", "0", "--eval-interval", "2",
+                           "--eval-iters", "1"]) == 0
+    out = capsys.readouterr().out
+    assert out.count("validation loss at iteration") == 2
