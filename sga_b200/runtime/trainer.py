@@ -51,7 +51,11 @@ def add_trainer_args(p: argparse.ArgumentParser) -> argparse.ArgumentParser:
     g.add_argument("--min-lr", type=float, default=0.0)
     g.add_argument("--lr-decay-style", choices=("constant", "linear", "cosine"), default="constant")
     g.add_argument("--lr-warmup-iters", type=int, default=0)
+    g.add_argument("--lr-warmup-fraction", type=float, default=None,
+                   help="warm-up length as a fraction of --lr-decay-iters (instead of --lr-warmup-iters)")
     g.add_argument("--lr-warmup-init", type=float, default=0.0)
+    g.add_argument("--exit-interval", type=int, default=0,
+                   help="stop (after saving, with --save) when the iteration count is a multiple of this")
     g.add_argument("--lr-decay-iters", type=int, default=None, help="default: --train-iters")
     g.add_argument("--weight-decay", type=float, default=0.1)
     g.add_argument("--adam-beta1", type=float, default=0.9)
@@ -125,14 +129,19 @@ def scheduled_lr(args, done: int) -> float:
     import math
 
     max_lr, min_lr = float(args.lr), float(getattr(args, "min_lr", 0.0) or 0.0)
+    decay = int(getattr(args, "lr_decay_iters", None) or args.train_iters)
     warm = int(getattr(args, "lr_warmup_iters", 0) or 0)
+    frac = getattr(args, "lr_warmup_fraction", None)
+    if frac is not None:
+        if warm:
+            raise ValueError("give --lr-warmup-iters or --lr-warmup-fraction, not both")
+        warm = int(float(frac) * decay)
     if warm > 0 and done <= warm:
         init = float(getattr(args, "lr_warmup_init", 0.0) or 0.0)
         return init + (max_lr - init) * done / warm
     style = getattr(args, "lr_decay_style", "constant")
     if style == "constant":
         return max_lr
-    decay = int(getattr(args, "lr_decay_iters", None) or args.train_iters)
     if done > decay:
         return min_lr
     ratio = (done - warm) / max(decay - warm, 1)

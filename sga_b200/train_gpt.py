@@ -50,6 +50,14 @@ def main(argv=None) -> int:
                 print(f"[train] validation loss at iteration {it} | {val:.6f} | {args.eval_iters} batches", flush=True)
         if args.save and args.save_interval and it % args.save_interval == 0:
             ckpt.save_checkpoint(args.save, it, args, tr.model, tr.optimizer, tr.rank, tr.tp_rank, tr.dp_rank, tr.pp_rank, tr.pp_size)
+        if args.exit_interval and it % args.exit_interval == 0 and it < args.train_iters:
+            if args.save:
+                ckpt.save_checkpoint(args.save, it, args, tr.model, tr.optimizer, tr.rank, tr.tp_rank, tr.dp_rank, tr.pp_rank, tr.pp_size)
+            if tr.rank == 0:
+                print(f"[train] exiting at iteration {it} (--exit-interval {args.exit_interval})", flush=True)
+            tr.check()
+            tr.close()
+            return 0
     if args.save:
         ckpt.save_checkpoint(args.save, args.train_iters, args, tr.model, tr.optimizer, tr.rank, tr.tp_rank, tr.dp_rank, tr.pp_rank, tr.pp_size)
     tr.check()

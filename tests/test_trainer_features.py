@@ -110,3 +110,20 @@ def test_validation_pass_leaves_training_state_alone(capsys):
                            "--eval-iters", "1"]) == 0
     out = capsys.readouterr().out
     assert out.count("validation loss at iteration") == 2
+
+
+def test_warmup_fraction_and_exit_interval(tmp_path, capsys):
+    from sga_b200 import train_gpt
+    from sga_b200.runtime.trainer import scheduled_lr
+
+    a = default_args(lr=1e-3, lr_decay_style="linear", lr_warmup_fraction=0.1, train_iters=100)
+    assert scheduled_lr(a, 5) == pytest.approx(5e-4) and scheduled_lr(a, 10) == 1e-3
+    with pytest.raises(ValueError, match="not both"):
+        scheduled_lr(default_args(lr=1e-3, lr_warmup_fraction=0.1, lr_warmup_iters=3, train_iters=100), 1)
+    argv = ["--model", "test_tiny", "--micro-batch-size", "2", "--global-batch-size", "2", "--train-iters", "6",
+            "--device", "cpu", "--log-interval", "0", "--save", str(tmp_path), "--exit-interval", "4"]
+    assert train_gpt.main(argv) == 0
+    assert "exiting at iteration 4" in capsys.readouterr().out
+    assert open(tmp_path / "latest_checkpointed_iteration.txt").read().strip() == "4"
+    assert train_gpt.main(argv + ["--load", str(tmp_path)]) == 0   # resumes at 4, runs to 6
+    assert open(tmp_path / "latest_checkpointed_iteration.txt").read().strip() == "6"
