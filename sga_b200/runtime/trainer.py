@@ -44,6 +44,17 @@ def add_trainer_args(p: argparse.ArgumentParser) -> argparse.ArgumentParser:
     g.add_argument("--model", type=str, default="llama3_1b")
     g.add_argument("--seq-length", type=int, default=None)
     g.add_argument("--num-layers", type=int, default=None)
+    # architecture overrides on top of the --model preset, in the vocabulary of the reference's yamls
+    g.add_argument("--hidden-size", type=int, default=None)
+    g.add_argument("--ffn-hidden-size", type=int, default=None)
+    g.add_argument("--num-attention-heads", type=int, default=None)
+    g.add_argument("--num-query-groups", type=int, default=None, help="key/value heads (grouped-query attention)")
+    g.add_argument("--kv-channels", type=int, default=None, help="head dimension (default hidden / heads)")
+    g.add_argument("--padded-vocab-size", type=int, default=None)
+    g.add_argument("--rotary-base", type=float, default=None)
+    g.add_argument("--norm-epsilon", type=float, default=None)
+    g.add_argument("--init-method-std", type=float, default=None)
+    g.add_argument("--qk-layernorm", action="store_true", help="RMSNorm on the per-head queries and keys")
     g.add_argument("--micro-batch-size", type=int, default=4)
     g.add_argument("--global-batch-size", type=int, default=256)
     g.add_argument("--train-iters", type=int, default=10)
@@ -207,7 +218,22 @@ class Trainer:
             over["num_layers"] = args.num_layers
         if args.untie_embeddings_and_output_weights:
             over["tied_embeddings"] = False
+        for flag, field in (("hidden_size", "hidden"), ("ffn_hidden_size", "ffn"), ("num_attention_heads", "n_heads"),
+                            ("num_query_groups", "n_kv_heads"), ("kv_channels", "head_dim"),
+                            ("padded_vocab_size", "vocab"), ("rotary_base", "rope_theta"),
+                            ("norm_epsilon", "norm_eps"), ("init_method_std", "init_std")):
+            if getattr(args, flag, None) is not None:
+                over[field] = getattr(args, flag)
+        if getattr(args, "qk_layernorm", False):
+            over["qk_norm"] = True
+        if ("hidden" in over or "n_heads" in over) and "head_dim" not in over:
+            base = get_config(args.model)
+            over["head_dim"] = over.get("hidden", base.hidden) // over.get("n_heads", base.n_heads)
         self.cfg = get_config(args.model, **over)
+        c = self.cfg
+        if c.n_heads % c.n_kv_heads or c.head_dim % 8 or c.hidden % 8 or c.ffn % 8:
+            raise ValueError(f"model geometry: {c.n_heads} heads must be a multiple of {c.n_kv_heads} key/value heads; "
+                             "head dimension, hidden and FFN sizes must be multiples of 8")
         self.tp_size = max(1, int(args.tensor_model_parallel_size))
         self.pp_size = max(1, int(args.pipeline_model_parallel_size or 1))
         if self.pp_size > 1 and self.tp_size > 1:

@@ -127,3 +127,17 @@ def test_warmup_fraction_and_exit_interval(tmp_path, capsys):
     assert open(tmp_path / "latest_checkpointed_iteration.txt").read().strip() == "4"
     assert train_gpt.main(argv + ["--load", str(tmp_path)]) == 0   # resumes at 4, runs to 6
     assert open(tmp_path / "latest_checkpointed_iteration.txt").read().strip() == "6"
+
+
+def test_architecture_flags_override_the_preset():
+    tr = Trainer(default_args(model="test_tiny", num_layers=1, hidden_size=64, ffn_hidden_size=128,
+                              num_attention_heads=4, num_query_groups=2, padded_vocab_size=320, rotary_base=1e6,
+                              norm_epsilon=1e-6, qk_layernorm=True, micro_batch_size=2, global_batch_size=2,
+                              train_iters=2, device="cpu", log_interval=0), quiet=True)
+    c = tr.cfg
+    assert (c.hidden, c.ffn, c.n_heads, c.n_kv_heads, c.head_dim, c.vocab) == (64, 128, 4, 2, 16, 320)
+    assert c.rope_theta == 1e6 and c.norm_eps == 1e-6 and c.qk_norm and c.num_layers == 1
+    assert torch.isfinite(tr.train_step(tr.host_batch(0)))
+    tr.close()
+    with pytest.raises(ValueError, match="multiple of"):
+        Trainer(default_args(model="test_tiny", num_attention_heads=4, num_query_groups=3, device="cpu"), quiet=True)
