@@ -107,6 +107,30 @@ def add_trainer_args(p: argparse.ArgumentParser) -> argparse.ArgumentParser:
     g.add_argument("--use-distributed-optimizer", action="store_true")
     g.add_argument("--log-num-zeros-in-grad", action="store_true")
     g.add_argument("--sga-allow-config-override", action="store_true")
+    # Flags of the training stack the reference's yamls are written for. This trainer has one choice for each
+    # (bf16 compute with fp32 master weights and gradients, bias-free linears, RMSNorm, rotary positions, SwiGLU,
+    # its own attention kernels, no dropout, pre-tokenised data): the flags are accepted so that such a yaml
+    # launches unchanged, and a value this trainer cannot honour is refused by check_compat_flags.
+    c = p.add_argument_group("accepted for yaml compatibility")
+    for flag in ("--disable-bias-linear", "--use-flash-attn", "--bf16", "--attention-softmax-in-fp32",
+                 "--accumulate-allreduce-grads-in-fp32", "--log-throughput", "--log-params-norm",
+                 "--group-query-attention", "--use-rotary-position-embeddings", "--swiglu"):
+        c.add_argument(flag, action="store_true")
+    c.add_argument("--rerun-mode", default=None)
+    c.add_argument("--data-parallel-sharding-strategy", default=None)
+    c.add_argument("--timing-log-level", type=int, default=None)
+    c.add_argument("--transformer-impl", default=None)
+    c.add_argument("--max-position-embeddings", type=int, default=None)
+    c.add_argument("--normalization", default=None)
+    c.add_argument("--position-embedding-type", default=None)
+    c.add_argument("--attention-dropout", type=float, default=None)
+    c.add_argument("--hidden-dropout", type=float, default=None)
+    c.add_argument("--split", default=None)
+    c.add_argument("--tokenizer-type", default=None)
+    c.add_argument("--tokenizer-model", default=None)
+    c.add_argument("--make-vocab-size-divisible-by", type=int, default=None)
+    c.add_argument("--tensorboard-dir", default=None)
+    c.add_argument("--wandb-save-dir", default=None)
     return p
 
 
@@ -130,6 +154,24 @@ def init_distributed(device_type: str):
         dist.init_process_group(backend=backend, **kwargs)
     rank = dist.get_rank() if dist.is_initialized() else 0
     return rank, (dist.get_world_size() if dist.is_initialized() else 1)
+
+
+def check_compat_flags(args) -> None:
+    """Refuses the values of the compatibility flags that would mean another model or another numerics."""
+    bad = []
+    if args.normalization not in (None, "RMSNorm"):
+        bad.append(f"--normalization {args.normalization} (RMSNorm only)")
+    if args.position_embedding_type not in (None, "rope"):
+        bad.append(f"--position-embedding-type {args.position_embedding_type} (rope only)")
+    for name in ("attention_dropout", "hidden_dropout"):
+        if getattr(args, name) not in (None, 0.0):
+            bad.append(f"--{name.replace('_', '-')} {getattr(args, name)} (no dropout)")
+    if args.data_parallel_sharding_strategy not in (None, "no_shard"):
+        bad.append(f"--data-parallel-sharding-strategy {args.data_parallel_sharding_strategy} (no_shard only)")
+    if args.max_position_embeddings is not None and args.seq_length and args.max_position_embeddings < args.seq_length:
+        bad.append(f"--max-position-embeddings {args.max_position_embeddings} < --seq-length {args.seq_length}")
+    if bad:
+        raise ValueError("not supported by this trainer: " + "; ".join(bad))
 
 
 def scheduled_lr(args, done: int) -> float:
@@ -211,6 +253,8 @@ class Trainer:
         else:
             self.device = torch.device("cpu")
         cuda = self.device.type == "cuda"
+        if hasattr(args, "normalization"):
+            check_compat_flags(args)
         over = {}
         if args.seq_length:
             over["seq_len"] = args.seq_length

@@ -171,3 +171,94 @@ def test_env_and_setup_scripts_check_the_checkout():
         bad = subprocess.run(["bash", "-c", f"cd {d} && export PYTHONPATH={d} && source {root}/env.sh --check"],
                              capture_output=True, text=True)
         assert bad.returncode != 0 and "resolves to" in bad.stderr, bad.stdout + bad.stderr
+
+
+def test_yaml_in_the_reference_vocabulary_launches(tmp_path):
+    """A yaml written for the reference (its training stack's flag names: nested precision / logging /
+    checkpoint / optimizer / lr_scheduler / tokenizer sections, architecture by flags) goes through the
+    launcher unchanged, and the flags it produces train."""
+    import torch
+
+    from sga_b200.runtime.trainer import Trainer, build_parser
+
+    (tmp_path / "ref_style.yaml").write_text(f"""
+experiment:
+  exp_name: ref-style
+  exp_dir: {tmp_path}/exp
+  task: {{type: train, backend: megatron, entrypoint: ./sga/train_gpt.py}}
+  runner: {{type: ssh, nproc_per_node: 1}}
+sga:
+  sga_enabled: true
+  sga_score: abs_m
+  sga_selection_method: histogram
+  sga_selection_histogram_mode: balanced
+  sga_selection_ratio_percent: 10
+  sga_cycle_period: 4
+  sga_backend: torch_pipelined_index
+train:
+  system:
+    rerun_mode: disabled
+    tensor_model_parallel_size: 1
+    pipeline_model_parallel_size: 1
+    disable_bias_linear: true
+    use_flash_attn: true
+    use_distributed_optimizer: false
+    data_parallel_sharding_strategy: no_shard
+    precision: {{bf16: true, attention_softmax_in_fp32: true, accumulate_allreduce_grads_in_fp32: true}}
+    logging: {{timing_log_level: 2, log_interval: 1, log_throughput: true, log_num_zeros_in_grad: true}}
+    checkpoint: {{save_interval: 100000}}
+  model:
+    transformer_impl: transformer_engine
+    num_layers: 1
+    hidden_size: 64
+    ffn_hidden_size: 128
+    num_attention_heads: 4
+    seq_length: 32
+    group_query_attention: true
+    num_query_groups: 2
+    max_position_embeddings: 32
+    norm_epsilon: 1e-5
+    swiglu: true
+    normalization: RMSNorm
+    position_embedding_type: rope
+    rotary_base: 500000
+    untie_embeddings_and_output_weights: true
+    attention_dropout: 0.0
+    hidden_dropout: 0.0
+    clip_grad: 1.0
+    train_iters: 20
+    exit_interval: 10
+    eval_iters: 0
+    eval_interval: 1000
+    micro_batch_size: 1
+    global_batch_size: 2
+    seed: 1234
+    optimizer:
+      weight_decay: 1e-2
+      adam_beta1: 0.9
+      adam_beta2: 0.95
+      lr_scheduler: {{lr: 1.0e-3, min_lr: 1.0e-4, lr_warmup_fraction: 0.1, lr_decay_style: cosine}}
+  data:
+    split: 1
+    tokenizer: {{tokenizer_type: HuggingFaceTokenizer, tokenizer_model: /nowhere, padded_vocab_size: 320,
+                make_vocab_size_divisible_by: 64}}
+""")
+    cfg = load_config(str(tmp_path / "ref_style.yaml"), [])
+    validate_task(cfg)
+    be = B.TrainBackend(cfg)
+    flags = be.train_args
+    for tok in ("--hidden-size", "--lr-warmup-fraction", "--lr-decay-style", "--padded-vocab-size", "--bf16",
+                "--sga-cycle-period", "--exit-interval"):
+        assert tok in flags, tok
+    assert "--use-distributed-optimizer" not in flags, "a false switch is not emitted"
+    args = build_parser().parse_args(flags + ["--device", "cpu", "--model", "test_tiny"])
+    tr = Trainer(args, quiet=True)
+    assert (tr.cfg.hidden, tr.cfg.n_heads, tr.cfg.n_kv_heads, tr.cfg.vocab, tr.cfg.seq_len) == (64, 4, 2, 320, 32)
+    assert not tr.cfg.tied_embeddings
+    for s in range(3):
+        assert torch.isfinite(tr.train_step(tr.host_batch(s)))
+    assert tr.optimizer.param_groups[0]["lr"] == pytest.approx(1e-3)  # warm-up of 2 steps is over
+    tr.close()
+    bad = build_parser().parse_args(flags + ["--device", "cpu", "--model", "test_tiny", "--normalization", "LayerNorm"])
+    with pytest.raises(ValueError, match="RMSNorm only"):
+        Trainer(bad, quiet=True)
