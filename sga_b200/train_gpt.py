@@ -42,7 +42,11 @@ def main(argv=None) -> int:
             if tr.rank == 0:
                 gn = tr.last_grad_norm
                 gn = float(gn.item()) if hasattr(gn, "item") else (float(gn) if gn is not None else float("nan"))
-                print(f"[train] iteration {it}/{args.train_iters} | loss {lv:.6f} | grad norm {gn:.4f} | "
+                extra = ""
+                if getattr(args, "log_params_norm", False):  # this rank's parameters (a shard under TP / PP)
+                    extra += f" | params norm {float(tr.model.arena.main_param.norm()):.4f}"
+                extra += f" | lr {tr.optimizer.param_groups[0]['lr']:.3e}"
+                print(f"[train] iteration {it}/{args.train_iters} | loss {lv:.6f} | grad norm {gn:.4f}{extra} | "
                       f"{dt * 1e3:.1f} ms/step | {tr.tokens_per_step() / dt:.0f} tokens/s", flush=True)
         if args.eval_interval and it % args.eval_interval == 0:
             val = tr.evaluate(args.eval_iters)
