@@ -87,6 +87,27 @@ def save_checkpoint(root: str, iteration: int, args, model, optimizer, rank: int
     return path
 
 
+def sga_state_name(root: str, iteration: int, rank: int) -> str:
+    return os.path.join(checkpoint_dir(root, iteration), f"sga_state_rank{rank:05d}.pt")
+
+
+def save_sga_state(root: str, iteration: int, engine, rank: int) -> str:
+    """Every rank writes its own file: the residual is this rank's unsent gradient mass."""
+    path = sga_state_name(root, iteration, rank)
+    os.makedirs(os.path.dirname(path), exist_ok=True)
+    torch.save(engine.state_dict(), path + ".tmp")
+    os.replace(path + ".tmp", path)
+    return path
+
+
+def load_sga_state(root: str, iteration: int, engine, rank: int) -> bool:
+    path = sga_state_name(root, iteration, rank)
+    if not os.path.exists(path):
+        return False
+    engine.load_state_dict(torch.load(path, map_location="cpu", weights_only=False))
+    return True
+
+
 def load_checkpoint(root: str, model, optimizer, tp_rank: int = 0, pp_rank: int = 0, pp_size: int = 1):
     """Loads the latest checkpoint; returns its iteration (0 when there is none)."""
     it = latest_iteration(root)

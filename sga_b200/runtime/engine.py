@@ -520,6 +520,9 @@ class SGAEngine:
         bucket_masks = self._assemble_bucket_masks(masks, meta)
         if self._support_consistency:
             self._verify_support_consistency(bucket_masks)
+        return self._support_from_bucket_masks(bucket_masks)
+
+    def _support_from_bucket_masks(self, bucket_masks) -> Support:
         x = getattr(self.selection, "block_size", 1)
         if self._idx_pools is None:
             self._idx_pools = [IndexPool(self._ddp.arena.device) for _ in self._bucket_states]
@@ -528,6 +531,49 @@ class SGAEngine:
                           block_spans=(sorted((s, e) for (_p, s, e) in self._bucket_states[i].param_spans)
                                        if x > 1 else None))
             for i, m in enumerate(bucket_masks)])
+
+    # ------------------------------------------------------ continuation state
+    def state_dict(self) -> dict:
+        """What a checkpoint of the optimizer does not hold and a bit-continuous resume needs: this rank's
+        residual (the gradient arena), the active support, the step counter, the calendar's pending forced
+        step and the selection plugin's running state. The reference keeps none of it (its resumed engine
+        cold-starts with dense steps until the next boundary, ``sga/engine.py:488-494``); saving it is opt-in."""
+        arena = self._ddp.arena
+        sel = {f"{where}.{key}": getattr(owner, key) for where, owner, key in self._selection_state_fields()}
+        return {"iter": self._iter, "residual": arena.main_grad.detach().cpu().clone(),
+                "mask": (self._active_mask_arena().detach().cpu().clone() if self._active_support is not None else None),
+                "force_next": bool(getattr(self._cycle, "force_next", False)), "selection": sel,
+                "last_ratio": self.last_ratio}
+
+    def _selection_state_fields(self):
+        """``(where, owner, attribute)`` of the selection plugin's running state: the last threshold on the
+        plugin, the adaptive controller's threshold and warm-up count on its method object."""
+        out = []
+        if "last_threshold" in vars(self.selection):
+            out.append(("plugin", self.selection, "last_threshold"))
+        impl = vars(self.selection).get("_impl")
+        for key in ("tau", "warmup_passed"):
+            if impl is not None and key in vars(impl):
+                out.append(("method", impl, key))
+        return out
+
+    def load_state_dict(self, state: dict) -> None:
+        arena = self._ddp.arena
+        if state["residual"].numel() != arena.main_grad.numel():
+            raise ValueError("saved SGA state belongs to another parameter layout")
+        arena.main_grad.copy_(state["residual"].to(arena.device))
+        self._iter, self._first_step = state["iter"], False
+        self._cycle.force_next = bool(state.get("force_next", False))
+        saved = state.get("selection", {})
+        for where, owner, key in self._selection_state_fields():
+            if f"{where}.{key}" in saved:
+                setattr(owner, key, saved[f"{where}.{key}"])
+        if state.get("mask") is not None:
+            inactive = self._mask_arena_pair()[1 - self._mask_turn]
+            inactive.copy_(state["mask"].to(arena.device))
+            masks = [inactive[bs.arena_start:bs.arena_start + bs.grad_data.numel()] for bs in self._bucket_states]
+            self._activate_support(self._support_from_bucket_masks(masks))
+        self.last_ratio = state.get("last_ratio", self.last_ratio)
 
     def _assemble_bucket_masks(self, masks, meta):
         """Write the per-parameter masks into the inactive arena-wide mask buffer

@@ -107,6 +107,9 @@ def add_trainer_args(p: argparse.ArgumentParser) -> argparse.ArgumentParser:
     g.add_argument("--use-distributed-optimizer", action="store_true")
     g.add_argument("--log-num-zeros-in-grad", action="store_true")
     g.add_argument("--sga-allow-config-override", action="store_true")
+    g.add_argument("--save-sga-state", action="store_true",
+                   help="checkpoints also hold every rank's residual, the active support and the engine's counters, "
+                        "and a resume continues bit for bit instead of cold-starting the cycle")
     # Flags of the training stack the reference's yamls are written for. This trainer has one choice for each
     # (bf16 compute with fp32 master weights and gradients, bias-free linears, RMSNorm, rotary positions, SwiGLU,
     # its own attention kernels, no dropout, pre-tokenised data): the flags are accepted so that such a yaml

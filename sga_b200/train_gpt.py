@@ -17,6 +17,11 @@ from .runtime import checkpoint as ckpt
 from .runtime.trainer import Trainer, build_parser
 
 
+def _save_sga(args, tr, iteration: int) -> None:
+    if args.save and args.save_sga_state and tr.engine is not None:
+        ckpt.save_sga_state(args.save, iteration, tr.engine, tr.rank)
+
+
 def main(argv=None) -> int:
     args = build_parser().parse_args(argv)
     ckpt.sga_resume_guard(args)
@@ -25,9 +30,13 @@ def main(argv=None) -> int:
     if args.load:
         start = ckpt.load_checkpoint(args.load, tr.model, tr.optimizer, tr.tp_rank, tr.pp_rank, tr.pp_size)
         tr.iteration = start
+        warm = bool(start and args.save_sga_state and tr.engine is not None
+                    and ckpt.load_sga_state(args.load, start, tr.engine, tr.rank))
         if tr.rank == 0 and start:
-            print(f"[train] resumed from iteration {start} (the SGA cycle cold-starts: dense steps until the next "
-                  "boundary; discard the first post-resume timing)", flush=True)
+            print(f"[train] resumed from iteration {start} " + (
+                "with the saved residual and support" if warm else
+                "(the SGA cycle cold-starts: dense steps until the next boundary; discard the first post-resume "
+                "timing)"), flush=True)
     cuda = tr.device.type == "cuda"
     t_last = time.perf_counter()
     for it in range(start + 1, args.train_iters + 1):
@@ -54,9 +63,11 @@ def main(argv=None) -> int:
                 print(f"[train] validation loss at iteration {it} | {val:.6f} | {args.eval_iters} batches", flush=True)
         if args.save and args.save_interval and it % args.save_interval == 0:
             ckpt.save_checkpoint(args.save, it, args, tr.model, tr.optimizer, tr.rank, tr.tp_rank, tr.dp_rank, tr.pp_rank, tr.pp_size)
+            _save_sga(args, tr, it)
         if args.exit_interval and it % args.exit_interval == 0 and it < args.train_iters:
             if args.save:
                 ckpt.save_checkpoint(args.save, it, args, tr.model, tr.optimizer, tr.rank, tr.tp_rank, tr.dp_rank, tr.pp_rank, tr.pp_size)
+                _save_sga(args, tr, it)
             if tr.rank == 0:
                 print(f"[train] exiting at iteration {it} (--exit-interval {args.exit_interval})", flush=True)
             tr.check()
@@ -64,6 +75,7 @@ def main(argv=None) -> int:
             return 0
     if args.save:
         ckpt.save_checkpoint(args.save, args.train_iters, args, tr.model, tr.optimizer, tr.rank, tr.tp_rank, tr.dp_rank, tr.pp_rank, tr.pp_size)
+        _save_sga(args, tr, args.train_iters)
     tr.check()
     tr.close()
     return 0

@@ -141,3 +141,44 @@ def test_architecture_flags_override_the_preset():
     tr.close()
     with pytest.raises(ValueError, match="multiple of"):
         Trainer(default_args(model="test_tiny", num_attention_heads=4, num_query_groups=3, device="cpu"), quiet=True)
+
+
+@pytest.mark.parametrize("sga", [
+    dict(sga_score="abs_m", sga_selection_method="histogram", sga_selection_histogram_mode="balanced",
+         sga_backend="torch_pipelined_index", sga_cycle_period=4),
+    dict(sga_score="update", sga_selection_method="adaptive", sga_backend="torch_pipelined_mask", sga_cycle_period=3,
+         sga_optimizer_residual_mean=True),
+    dict(sga_score="abs_g", sga_selection_method="exact", sga_backend="torch_pipelined_index",
+         sga_selection_locality="rank_local", sga_cycle_period=0),
+])
+def test_saved_sga_state_resumes_bit_for_bit(tmp_path, monkeypatch, sga):
+    """With --save-sga-state a run stopped in the middle of a cycle and resumed ends with the weights, moments
+    and residual of the uninterrupted run, bit for bit; without it the resumed engine cold-starts and differs."""
+    from sga_b200 import train_gpt
+
+    monkeypatch.setenv("SGA_ALLOW_FROZEN_SELECTION", "1")
+    flags = ["--model", "test_tiny", "--micro-batch-size", "2", "--global-batch-size", "2", "--device", "cpu",
+             "--log-interval", "0", "--sga-enabled", "true", "--sga-selection-ratio-percent", "10"]
+    for k, v in sga.items():
+        flags += ["--" + k.replace("_", "-"), str(v).lower() if isinstance(v, bool) else str(v)]
+    final, now = {}, {"tag": None}
+    stock_close = Trainer.close
+
+    def close(self):
+        a = self.model.arena
+        final[now["tag"]] = (a.main_param.clone(), a.exp_avg.clone(), a.main_grad.clone())
+        return stock_close(self)
+
+    monkeypatch.setattr(Trainer, "close", close)
+
+    def run(tag, argv):
+        now["tag"] = tag
+        assert train_gpt.main(flags + argv) == 0
+
+    run("whole", ["--train-iters", "11"])
+    for tag, extra in (("warm", ["--save-sga-state"]), ("cold", [])):
+        d = str(tmp_path / tag)
+        run("first_" + tag, ["--train-iters", "6", "--save", d] + extra)
+        run(tag, ["--train-iters", "11", "--load", d] + extra)
+    assert all(torch.equal(a, b) for a, b in zip(final["whole"], final["warm"]))
+    assert not torch.equal(final["whole"][0], final["cold"][0])
