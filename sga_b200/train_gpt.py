@@ -38,6 +38,14 @@ def main(argv=None) -> int:
                 "(the SGA cycle cold-starts: dense steps until the next boundary; discard the first post-resume "
                 "timing)"), flush=True)
     cuda = tr.device.type == "cuda"
+    tb = None
+    if getattr(args, "tensorboard_dir", None) and tr.rank == 0:
+        try:
+            from torch.utils.tensorboard import SummaryWriter
+
+            tb = SummaryWriter(args.tensorboard_dir)
+        except ImportError:
+            print("[train] --tensorboard-dir given but tensorboard is not installed: no scalars are written", flush=True)
     t_last = time.perf_counter()
     for it in range(start + 1, args.train_iters + 1):
         loss = tr.train_step(tr.host_batch(it - 1))
@@ -57,10 +65,16 @@ def main(argv=None) -> int:
                 extra += f" | lr {tr.optimizer.param_groups[0]['lr']:.3e}"
                 print(f"[train] iteration {it}/{args.train_iters} | loss {lv:.6f} | grad norm {gn:.4f}{extra} | "
                       f"{dt * 1e3:.1f} ms/step | {tr.tokens_per_step() / dt:.0f} tokens/s", flush=True)
+                if tb is not None:
+                    for tag, val in (("lm loss", lv), ("grad-norm", gn), ("learning-rate", tr.optimizer.param_groups[0]["lr"]),
+                                     ("iteration-time", dt), ("tokens-per-second", tr.tokens_per_step() / dt)):
+                        tb.add_scalar(tag, val, it)
         if args.eval_interval and it % args.eval_interval == 0:
             val = tr.evaluate(args.eval_iters)
             if tr.rank == 0:
                 print(f"[train] validation loss at iteration {it} | {val:.6f} | {args.eval_iters} batches", flush=True)
+                if tb is not None:
+                    tb.add_scalar("lm loss validation", val, it)
         if args.save and args.save_interval and it % args.save_interval == 0:
             ckpt.save_checkpoint(args.save, it, args, tr.model, tr.optimizer, tr.rank, tr.tp_rank, tr.dp_rank, tr.pp_rank, tr.pp_size)
             _save_sga(args, tr, it)
@@ -70,12 +84,16 @@ def main(argv=None) -> int:
                 _save_sga(args, tr, it)
             if tr.rank == 0:
                 print(f"[train] exiting at iteration {it} (--exit-interval {args.exit_interval})", flush=True)
+            if tb is not None:
+                tb.close()
             tr.check()
             tr.close()
             return 0
     if args.save:
         ckpt.save_checkpoint(args.save, args.train_iters, args, tr.model, tr.optimizer, tr.rank, tr.tp_rank, tr.dp_rank, tr.pp_rank, tr.pp_size)
         _save_sga(args, tr, args.train_iters)
+    if tb is not None:
+        tb.close()
     tr.check()
     tr.close()
     return 0

@@ -182,3 +182,19 @@ def test_saved_sga_state_resumes_bit_for_bit(tmp_path, monkeypatch, sga):
         run(tag, ["--train-iters", "11", "--load", d] + extra)
     assert all(torch.equal(a, b) for a, b in zip(final["whole"], final["warm"]))
     assert not torch.equal(final["whole"][0], final["cold"][0])
+
+
+def test_tensorboard_scalars(tmp_path):
+    pytest.importorskip("tensorboard")
+    from sga_b200 import train_gpt
+
+    assert train_gpt.main(["--model", "test_tiny", "--micro-batch-size", "2", "--global-batch-size", "2",
+                           "--train-iters", "3", "--device", "cpu", "--log-interval", "1", "--tensorboard-dir",
+                           str(tmp_path / "tb"), "--eval-interval", "3", "--eval-iters", "1"]) == 0
+    from tensorboard.backend.event_processing.event_accumulator import EventAccumulator
+
+    acc = EventAccumulator(str(tmp_path / "tb"))
+    acc.Reload()
+    tags = set(acc.Tags()["scalars"])
+    assert {"lm loss", "grad-norm", "learning-rate", "lm loss validation"} <= tags
+    assert [e.step for e in acc.Scalars("lm loss")] == [1, 2, 3]
