@@ -95,6 +95,11 @@ class TrainBackend(BackendBase):
         if ckpt.get("load") and "load" not in system:
             system["load"] = ckpt["load"] if isinstance(ckpt["load"], str) else self.ckpt_dir
         system.pop("checkpoint", None)
+        # scalars go under the experiment directory unless the yaml names another place
+        # (sga/launcher/backend_megatron.py:180-190)
+        logging_cfg = system.get("logging") if isinstance(system.get("logging"), dict) else None
+        if "tensorboard_dir" not in system and not (logging_cfg and logging_cfg.get("tensorboard_dir")):
+            system["tensorboard_dir"] = os.path.join(exp_dir, "tensorboard")
         self.train_args = self._train_args()
 
     def _train_args(self) -> list:

@@ -104,6 +104,7 @@ def test_golden_command_line_and_script_skeleton(tmp_path):
            "--master-port 29512 -m sga_b200.train_gpt" in last
     assert "--sga-enabled true" in last and "--sga-selection-locality rank_local" in last
     assert "--global-batch-size 256" in last and f"--save {tmp_path}/checkpoints" in last
+    assert f"--tensorboard-dir {tmp_path}/tensorboard" in last
     stop = open(stop_sh).read()
     assert "kill" in stop and f"host_0_{host}.pid" in stop
     assert r.launcher.query() == JobStatus.COMPLETED_OR_IDLE
