@@ -1,7 +1,9 @@
 """Launcher: yaml -> flags (dual-form equivalence with the CLI), pre-validation,
 torchrun command line and run-script skeleton, hostfile parsing."""
 import glob
+import json
 import os
+import sys
 
 import pytest
 import yaml
@@ -263,3 +265,19 @@ train:
     bad = build_parser().parse_args(flags + ["--device", "cpu", "--model", "test_tiny", "--normalization", "LayerNorm"])
     with pytest.raises(ValueError, match="RMSNorm only"):
         Trainer(bad, quiet=True)
+
+
+def test_audit_tool(tmp_path, capsys):
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import audit_trainer_args as audit
+
+    out = str(tmp_path / "flags.json")
+    assert audit.main(["check", os.path.join(ROOT, "examples/llama3/train_1b_adamw.yaml"), out]) == 0
+    table = json.load(open(out))
+    assert table["--lr-decay-style"]["choices"] == ["constant", "linear", "cosine"]
+    assert table["--swiglu"]["group"] == "accepted for yaml compatibility"
+    (tmp_path / "bad.yaml").write_text("experiment: {exp_name: x, exp_dir: /tmp/x, task: {type: train}}\n"
+                                       "train: {model: {no_such_flag: 1}}\n")
+    assert audit.main(["check", str(tmp_path / "bad.yaml")]) == 1
+    text = capsys.readouterr().out
+    assert "REFUSED" in text and "--no-such-flag" in text
