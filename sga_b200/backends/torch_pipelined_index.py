@@ -43,6 +43,23 @@ def _ops(t):
     return KT
 
 
+def _score_abs(grad, score):
+    """|score| of every bucket coordinate with the registry formulas (library / CPU path)."""
+    if score is None or score.name == "abs_g":
+        return grad.abs()
+    from ..plugins.scores import compute_score
+
+    out = torch.empty_like(grad)
+    starts = score.span_start.tolist() if score.span_start is not None else [0, grad.numel()]
+    wds = score.span_wd.tolist() if score.span_wd is not None else [0.0]
+    for (s, e), wd in zip(zip(starts[:-1], starts[1:]), wds):
+        out[s:e] = compute_score(score.name, score.w[s:e], score.m[s:e], score.v[s:e], grad[s:e],
+                                 beta1=score.beta1, beta2=score.beta2, eps=score.eps, weight_decay=wd,
+                                 bc1=score.bc1, bc2=score.bc2,
+                                 optimizer="adams" if score.adams else "adamw").abs()
+    return out
+
+
 class TorchPipelinedIndexBackend:
     consumes = "idx"
     inherent_emission = "compact"
@@ -254,18 +271,19 @@ class TorchPipelinedIndexBackend:
         return None
 
     # ---------------------------------------------------------- rank local
-    def sync_rank_local(self, bucket_state, k: int, comm_view, comm_group, world: int) -> None:
-        """Exact per-bucket top-``k`` of ``|grad + residual|`` on this rank, exchange
-        of (int32 index, fp32 value) pairs, rank-ordered sum / world into
-        ``comm_view``; the selected coordinates of the bucket are zeroed."""
+    def sync_rank_local(self, bucket_state, k: int, comm_view, comm_group, world: int, score=None) -> None:
+        """Exact per-bucket top-``k`` of the score (``None``: ``|grad + residual|``; otherwise a
+        ``ScoreInputs`` with the bucket's weights, moments and Adam scalars) on this rank, exchange of
+        (int32 index, fp32 value) pairs, rank-ordered sum / world into ``comm_view``; the selected
+        coordinates of the bucket are zeroed. Coordinates with a zero score are never selected."""
         token = backend_timer.begin()
         try:
-            self._rank_local_impl(bucket_state, k, comm_view, comm_group, world)
+            self._rank_local_impl(bucket_state, k, comm_view, comm_group, world, score)
         finally:
             backend_timer.end(token, "sparse", backend=self.name, emission="rank_local", layout="er",
                               block_size=1, bucket=bucket_state.bucket_id, k=k)
 
-    def _rank_local_impl(self, bs, k, comm_view, comm_group, world):
+    def _rank_local_impl(self, bs, k, comm_view, comm_group, world, score=None):
         grad = bs.grad_data
         n = grad.numel()
         if self.transport == "p2p" or (grad.is_cuda and world == 1 and self.ddp is not None and self.ddp.channels):
@@ -274,18 +292,16 @@ class TorchPipelinedIndexBackend:
             ddp = self.ddp
             ci = bs.bucket_id % len(ddp.channels)
             ch = ddp.channels[ci]
-            kcap = self._kcap
             if ci not in self._slots:
-                self._slots[ci] = ddp.pool.alloc(8 * kcap * ddp.world)
+                self._slots[ci] = p2p.IndexSyncSlots(ddp.pool, self._kcap, self._max_bucket)
             if self._scratch is None:
-                self._scratch = p2p.IndexSyncScratch(ddp.device)
-                self._touched = torch.empty((self._max_bucket + 31) // 32 + 1, dtype=torch.int32, device=ddp.device)
-            p2p.bucket_index_sync_(ch, self._scratch, grad, k, slots=self._slots[ci], kcap=kcap, comm=comm_view,
-                                   touched=self._touched, scale=1.0 / ddp.world, sumsq_out=self.sumsq,
-                                   accumulate=True, max_ctas=ddp.ddp_config.comm_max_ctas)
+                self._scratch = p2p.IndexSyncScratch(ddp.device, self._max_bucket)
+            p2p.bucket_index_sync_(ch, self._scratch, grad, k, slots=self._slots[ci], comm=comm_view,
+                                   scale=1.0 / ddp.world, sumsq_out=self.sumsq, accumulate=True,
+                                   score=score, max_ctas=ddp.ddp_config.comm_max_ctas)
             return
         # library / CPU path: same arithmetic, rank-ordered
-        mask = KT.topk_exact_flat(grad.abs() if not grad.is_cuda else grad.abs(), k)
+        mask = KT.topk_rank_local(_score_abs(grad, score), k)
         idx = KT.compact_mask_idx(mask)
         vals = grad[idx.long()].clone()
         grad[idx.long()] = 0.0

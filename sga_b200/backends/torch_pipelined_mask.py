@@ -161,19 +161,18 @@ class TorchPipelinedMaskBackend:
                 ddp = self.ddp
                 self._ensure_bits()
                 if self._scratch is None:
-                    self._scratch = p2p.IndexSyncScratch(ddp.device)
+                    self._scratch = p2p.IndexSyncScratch(ddp.device, self._max_bucket)
                 ch = ddp.channels[bs.bucket_id % len(ddp.channels)]
                 woff = 4 * self._word_off(bs)
                 nw = (grad.numel() + 31) // 32
-                p2p.bucket_index_sync_(ch, self._scratch, grad, k, slots=None, kcap=0,
-                                       touched=self._bits.view(torch.int32, woff, nw), select_only=True,
-                                       max_ctas=ddp.ddp_config.comm_max_ctas)
+                p2p.bucket_index_sync_(ch, self._scratch, grad, k, bits=self._bits.view(torch.int32, woff, nw),
+                                       select_only=True, max_ctas=ddp.ddp_config.comm_max_ctas)
                 p2p.mask_union_reduce_(ch, ddp.arena.symm_grad, 4 * bs.arena_start, self._bits, woff, self._ubits,
                                        woff, grad.numel(), scale=1.0 / ddp.world, mask_u8=mask_view,
                                        sumsq_out=self.sumsq, accumulate=True, count_out=self.union_count,
                                        max_ctas=ddp.ddp_config.comm_max_ctas)
                 return
-            mask = KT.topk_exact_flat(grad.abs(), k)
+            mask = KT.topk_rank_local(grad.abs(), k)
             if world > 1 and dist.is_initialized():
                 dist.all_reduce(mask, op=dist.ReduceOp.MAX, group=comm_group)
             on = mask > 0

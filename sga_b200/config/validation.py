@@ -281,9 +281,9 @@ def validate_sga_args(args=None) -> None:
             raise ValueError("sga_selection_locality rank_local is refused with sga_shadow true")
         if args.sga_selection_block_size != 1:
             raise ValueError("sga_selection_locality rank_local is element-granular (block_size must be 1)")
-        if args.sga_score not in ("abs_g",):
-            raise ValueError("sga_selection_locality rank_local scores |grad + residual| "
-                             "(spelled sga_score abs_g: the gradient being committed)")
+        if args.sga_score != "abs_g" and args.sga_backend != "torch_pipelined_index":
+            raise ValueError("sga_selection_locality rank_local with the mask backend scores |grad + residual| "
+                             "(spelled sga_score abs_g); update / abs_m / coi need backend torch_pipelined_index")
         if decouple:
             raise ValueError("sga_selection_locality rank_local has no decoupled full-sync grid")
     if not _is_int(args.sga_bucket_elems) or args.sga_bucket_elems < 1024:

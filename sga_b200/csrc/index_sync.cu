@@ -1,0 +1,804 @@
+// Rank-local sparse gradient synchronisation of one bucket: exact top-k of a
+// score over the bucket, (index, value) pairs pushed into every peer's receive
+// area over NVLink peer memory, rank-ordered scatter-add on the receive side.
+//
+// The bucket is read from HBM once. A 1/64 sample (one hashed 16-byte group in
+// every 1 KiB) gives a lower bound of the k-th largest key with a six-sigma
+// margin; one streaming pass keeps every element at or above the bound as a
+// candidate (about 1.1 k of them). Everything that makes the selection exact
+// -- a two-digit radix select over the candidates' 31-bit keys, the index-order
+// tie cut, the per-segment counts and their scan -- touches the candidates
+// only, which stay in L2. If the sample bound turns out too high (fewer than k
+// candidates) a second pass takes every non-zero element, so the result is
+// exact for any input.
+//
+// Every kernel here is an ordinary launch with at most 20 KB of shared memory
+// and 256 threads per CTA, so its CTAs fit beside the persistent GEMM CTAs of
+// the backward pass they overlap with. Nothing waits on another CTA of the same
+// grid: serial steps (histogram scans, prefix sums, flag signalling) are done by
+// whichever CTA takes the last ticket. The only waits are on peers' flags, bounded.
+//
+// Semantics: the selected set is the k coordinates with the largest keys
+// (key = bits of |score| without the sign), ties at the k-th key taken in index
+// order; coordinates whose key is zero are never selected, so a bucket with
+// fewer than k non-zero scores selects exactly those. Scores follow
+// sga/plugins/scores.py:147-269 of the reference (update, abs_g, abs_m, coi),
+// with the gradient being gradient + residual of this rank.
+//
+// Candidates of segment s (8192 elements) live at [s * 8192, s * 8192 + count)
+// of the candidate arrays, so no allocation cursor and no overflow exists; the
+// payload a rank pushes is grouped by segment (offset table pushed with it),
+// and the receiver's CTA for a range of segments adds the ranks' pairs in rank
+// order, which makes the reduced gradient bit-identical on every rank.
+//
+// Replaces sga/kernels.py:63-81 (pack), sga/plugins/selection/_histogram.py and
+// the all-reduce of sga/backends/torch_pipelined_index.py:503-520.
+//
+// Compiled without fast-math and without FMA contraction: the score formulas
+// round operation by operation like their PyTorch reference.
+#include "common.cuh"
+#include "peer.cuh"
+
+namespace sga {
+
+constexpr int IS_SEG = 8192;          // elements per segment (one warp streams a segment)
+constexpr int IS_SEG_PER_RANGE = 4;   // receive-side CTA range: 4 segments = 32768 elements
+constexpr int IS_THREADS = 256;
+constexpr int IS_ABINS = 4096;        // first digit, also the sample's histogram: key >> 19
+constexpr int IS_BBINS = 2048;        // second digit: bits 18..8
+constexpr int IS_FBINS = 1 << 19;     // fine histogram of the low 19 bits inside the crossing first-digit bin
+constexpr int IS_REP = 8;             // replicas of the two coarse global histograms
+
+// Word offsets inside the state block (unsigned[64], zeroed by the host before each bucket).
+enum {
+  ST_TLO = 0, ST_LEVEL, ST_C, ST_SKIP, ST_BA, ST_ABOVE, ST_T, ST_NEED, ST_EQ, ST_ICUT, ST_NSEL, ST_SAMPLES,
+  ST_TICKET0 = 16  // tickets: one word per kernel of the chain
+};
+
+struct ISyncArgs {
+  PeerCtx c;
+  float* acc;            // gradient + residual of this rank
+  const float* w;        // fp32 master weights / moments: only for scores other than abs_g
+  const float* m;
+  const float* v;
+  long long n;
+  int k;
+  int nseg;
+  int score;             // 0 update, 1 abs_g, 2 abs_m, 3 coi
+  int adams;
+  float beta1, omb1, beta2, omb2, bc1, bc2, eps;
+  const int* span_start; // [nspan + 1] parameter spans of the bucket (score update: weight decay per span)
+  const float* span_wd;  // [nspan]
+  int nspan;
+  int gshift;            // the sample takes one 16-byte group in every 2^gshift
+  unsigned* state;
+  unsigned* histA;       // [8][4096] first-digit replicas: zero on entry, zero on exit
+  unsigned* histB;       // [8][2048] second-digit replicas (zero on exit), then [2^19] fine bins (zeroed by the sample)
+  int* cand_idx;         // [nseg * IS_SEG]
+  unsigned* cand_key;
+  float* cand_val;
+  int* segcnt;           // [nseg] candidates per segment
+  int* segsel;           // [nseg] selected per segment
+  int* segeq;            // [nseg] ties at the threshold per segment
+  int* roff;             // [nseg + 1] exclusive scan of segsel
+  float* partials;       // [number of receive ranges]
+  int2* slots[MAXW];     // slots[p]: peer p's pair area [W][kcap]
+  int* hdr[MAXW];        // hdr[p]: peer p's offset tables [W][hstride]
+  int kcap, hstride;
+  float* comm;           // dense staging of the reduced sparse gradient
+  float scale;
+  float* sumsq_out;
+  int accumulate;
+  int zero_selected;
+  unsigned* bits;        // select-only mode: bit mask of the selection (zeroed by the host)
+  unsigned* result;      // [4]: threshold key, ties taken, keys above the threshold, pairs produced
+  int level;             // filter pass: 0 = sample bound, 1 = every non-zero element
+};
+
+__device__ __forceinline__ unsigned key_bits(float x) { return __float_as_uint(x) & 0x7FFFFFFFu; }
+__device__ __forceinline__ unsigned ldv(const unsigned* p) { return *reinterpret_cast<const volatile unsigned*>(p); }
+
+// The CTA that takes the last ticket of a grid sees every other CTA's writes.
+template <bool SYSTEM = false>
+__device__ __forceinline__ bool last_cta(unsigned* ticket) {
+  __shared__ int s_last;
+  if (SYSTEM) __threadfence_system(); else __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned t = atomicAdd(ticket, 1u);
+    s_last = (t == gridDim.x - 1);
+    if (s_last) *ticket = 0;
+  }
+  __syncthreads();
+  if (s_last) __threadfence();
+  return s_last != 0;
+}
+
+// Block-wide exclusive scan of one value per thread (256 threads).
+__device__ __forceinline__ unsigned block_excl_scan256(unsigned v, unsigned* sh, unsigned& total) {
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  unsigned x = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned y = __shfl_up_sync(0xffffffffu, x, o);
+    if (lane >= o) x += y;
+  }
+  __syncthreads();
+  if (lane == 31) sh[wid] = x;
+  __syncthreads();
+  if (wid == 0) {
+    unsigned t = lane < IS_THREADS / 32 ? sh[lane] : 0;
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) {
+      const unsigned y = __shfl_up_sync(0xffffffffu, t, o);
+      if (lane >= o) t += y;
+    }
+    if (lane < IS_THREADS / 32) sh[lane] = t;
+  }
+  __syncthreads();
+  total = sh[IS_THREADS / 32 - 1];
+  const unsigned wp = wid ? sh[wid - 1] : 0;
+  const unsigned r = wp + x - v;
+  __syncthreads();
+  return r;
+}
+
+// Over the sum of `rep` replicas hist[r * nb + i] (global, nb a multiple of 256): the largest bin b
+// whose suffix count (bins >= b) reaches `want`, and the count in bins above it. Returns false when
+// the whole histogram holds fewer than `want`. One CTA; result uniform over its threads.
+__device__ __forceinline__ bool find_suffix_bin(const unsigned* hist, int nb, int rep, unsigned want, unsigned* sh,
+                                                unsigned& bin, unsigned& above) {
+  __shared__ unsigned s_res[2];
+  const int per = nb / IS_THREADS;
+  const int hi = nb - threadIdx.x * per;  // thread t owns [hi - per, hi): descending ownership
+  unsigned mysum = 0;
+  for (int r = 0; r < rep; ++r)
+    for (int i = hi - per; i < hi; ++i) mysum += __ldcg(hist + r * nb + i);
+  unsigned total;
+  const unsigned before = block_excl_scan256(mysum, sh, total);
+  if (threadIdx.x == 0) { s_res[0] = 0xFFFFFFFFu; s_res[1] = 0; }
+  __syncthreads();
+  if (before < want && before + mysum >= want) {
+    unsigned run = before;
+    for (int i = hi - 1; i >= hi - per; --i) {
+      unsigned h = 0;
+      for (int r = 0; r < rep; ++r) h += __ldcg(hist + r * nb + i);
+      if (run + h >= want) { s_res[0] = (unsigned)i; s_res[1] = run; break; }
+      run += h;
+    }
+  }
+  __syncthreads();
+  bin = s_res[0];
+  above = s_res[1];
+  __syncthreads();
+  return bin != 0xFFFFFFFFu;
+}
+
+__device__ __forceinline__ int load4z(const float* __restrict__ p, long long i, long long limit, float (&v)[4]) {
+  if (i + 4 <= limit) {
+    *reinterpret_cast<float4*>(v) = *reinterpret_cast<const float4*>(p + i);
+    return 4;
+  }
+  int lim = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    v[j] = 0.f;
+    if (i + j < limit) { v[j] = p[i + j]; lim = j + 1; }
+  }
+  return lim;
+}
+
+// Weight decay of element i (score update): spans are few, a binary search per 16-byte group.
+__device__ __forceinline__ float wd_of(const ISyncArgs& a, long long i) {
+  int lo = 0, hi = a.nspan - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if ((long long)a.span_start[mid] <= i) lo = mid; else hi = mid - 1;
+  }
+  return a.span_wd[lo];
+}
+
+template <int SCORE>
+__device__ __forceinline__ unsigned score_key(const ISyncArgs& a, float g, float w, float m0, float v0, float wd) {
+  if (SCORE == 1) return key_bits(g);
+  if (SCORE == 2) return key_bits(m0);
+  const float m1 = m0 * a.beta1 + g * a.omb1;
+  const float g2 = (g * a.omb2) * g;
+  float mh, vh;
+  if (a.adams) {
+    mh = m1;
+    vh = (m0 * m0) * a.beta2 + g2;
+  } else {
+    mh = m1 / a.bc1;
+    vh = (v0 * a.beta2 + g2) / a.bc2;
+  }
+  const float u = mh / (sqrtf(vh) + a.eps);
+  if (SCORE == 0) return key_bits(wd * w + u);
+  float u0;
+  if (a.adams) u0 = (m0 * a.beta1) / (sqrtf((m0 * m0) * a.beta2) + a.eps);
+  else u0 = ((m0 * a.beta1) / a.bc1) / (sqrtf((v0 * a.beta2) / a.bc2) + a.eps);
+  return key_bits(u - u0);
+}
+
+// Keys of the four elements from i (lanes past `limit` get key 0, which is never a candidate).
+template <int SCORE>
+__device__ __forceinline__ void keys4(const ISyncArgs& a, long long i, long long limit, float (&g)[4],
+                                      unsigned (&key)[4]) {
+  const int lim = load4z(a.acc, i, limit, g);
+  float w[4] = {0.f, 0.f, 0.f, 0.f}, m[4] = {0.f, 0.f, 0.f, 0.f}, v[4] = {0.f, 0.f, 0.f, 0.f};
+  if (SCORE == 0) load4z(a.w, i, limit, w);
+  if (SCORE != 1) load4z(a.m, i, limit, m);
+  if (SCORE == 0 || SCORE == 3) load4z(a.v, i, limit, v);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float wd = 0.f;
+    if (SCORE == 0 && j < lim) wd = wd_of(a, i + j);
+    key[j] = j < lim ? score_key<SCORE>(a, g[j], w[j], m[j], v[j], wd) : 0u;
+  }
+}
+
+// ------------------------------------------------------------------ sample
+// Histogram (4096 bins of key >> 19) of one hashed 16-byte group in every 2^gshift; the CTA that
+// finishes last turns it into the candidate bound: the lower edge of the bin at which the sample's
+// suffix count reaches the expected share of k plus six standard deviations. With gshift == 0 the
+// histogram covers the whole bucket and the bound is exact. The grid also zeroes the fine
+// histogram of the digit pass that follows.
+template <int SCORE>
+__global__ void __launch_bounds__(IS_THREADS) isync_sample_kernel(const ISyncArgs a) {
+  __shared__ unsigned sh_hist[IS_ABINS];
+  __shared__ unsigned sh_scan[8];
+  for (int i = threadIdx.x; i < IS_ABINS; i += IS_THREADS) sh_hist[i] = 0;
+  {
+    uint4* fine = reinterpret_cast<uint4*>(a.histB + IS_REP * IS_BBINS);
+    for (int i = blockIdx.x * IS_THREADS + threadIdx.x; i < IS_FBINS / 4; i += gridDim.x * IS_THREADS)
+      fine[i] = make_uint4(0, 0, 0, 0);
+  }
+  __syncthreads();
+  const long long n4 = (a.n + 3) >> 2;
+  const long long ngroups = (n4 + (1LL << a.gshift) - 1) >> a.gshift;
+  const long long stride = (long long)gridDim.x * IS_THREADS;
+  for (long long g0 = (long long)blockIdx.x * IS_THREADS + threadIdx.x; g0 < ngroups; g0 += 4 * stride) {
+    float gv[4][4];
+    unsigned key[4][4];
+    int lim[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {  // four independent groups in flight per thread
+      const long long g = g0 + u * stride;
+      const unsigned h = a.gshift ? (((unsigned)g * 2654435761u) >> (32 - a.gshift)) : 0u;
+      const long long q = (g << a.gshift) + h;
+      lim[u] = (g < ngroups && q < n4) ? (int)min(4LL, a.n - q * 4) : 0;
+      if (lim[u] > 0) keys4<SCORE>(a, q * 4, a.n, gv[u], key[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (j < lim[u]) atomicAdd(&sh_hist[key[u][j] >> 19], 1u);
+  }
+  __syncthreads();
+  unsigned* mine = a.histA + (blockIdx.x % IS_REP) * IS_ABINS;
+  for (int i = threadIdx.x; i < IS_ABINS; i += IS_THREADS) {
+    const unsigned c = sh_hist[i];
+    if (c) atomicAdd(&mine[i], c);
+  }
+  if (!last_cta(a.state + ST_TICKET0 + 0)) return;
+  unsigned part = 0;
+  for (int i = threadIdx.x; i < IS_REP * IS_ABINS; i += IS_THREADS) part += __ldcg(a.histA + i);
+  unsigned samples;
+  block_excl_scan256(part, sh_scan, samples);
+  unsigned want = (unsigned)a.k;
+  if (a.gshift) {
+    const float ks = (float)a.k * ((float)samples / (float)a.n);
+    want = (unsigned)ceilf(ks + 6.0f * sqrtf(ks) + 16.0f);
+  }
+  unsigned bin, above;
+  const bool found = find_suffix_bin(a.histA, IS_ABINS, IS_REP, want, sh_scan, bin, above);
+  for (int i = threadIdx.x; i < IS_REP * IS_ABINS / 4; i += IS_THREADS)
+    reinterpret_cast<uint4*>(a.histA)[i] = make_uint4(0, 0, 0, 0);
+  if (threadIdx.x == 0) {
+    a.state[ST_TLO] = found ? (bin << 19) : 0u;
+    a.state[ST_SAMPLES] = samples;
+  }
+}
+
+// ------------------------------------------------------------------ filter
+// The one pass over the bucket. A warp streams a segment (8192 elements, 512 per trip with four
+// 16-byte loads per lane in flight) and appends the elements whose key reaches the bound to the
+// segment's own slice of the candidate arrays; positions come from warp ballots, so there is no
+// atomic, no barrier and no overflow. The candidates' first radix digit (key >> 19) is counted in
+// a shared-memory histogram on the way and flushed into one of eight global replicas (a handful
+// of bins is hot; replicas keep the same-address atomics short). The last CTA either publishes the
+// crossing bin of that digit or, when fewer than k candidates were found under the sample bound,
+// arms level 1 (every non-zero key), which is the next launch and normally returns at once.
+template <int SCORE>
+__global__ void __launch_bounds__(IS_THREADS) isync_filter_kernel(const ISyncArgs a) {
+  __shared__ unsigned sh_hist[IS_ABINS];
+  __shared__ unsigned sh_cnt[IS_THREADS / 32];
+  if (a.level == 1 && ldv(a.state + ST_LEVEL) != 1u) return;
+  unsigned tlo = a.level == 0 ? ldv(a.state + ST_TLO) : 1u;
+  if (tlo < 1u) tlo = 1u;
+  for (int i = threadIdx.x; i < IS_ABINS; i += IS_THREADS) sh_hist[i] = 0;
+  __syncthreads();
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  const unsigned lt = (1u << lane) - 1u;
+  unsigned warp_total = 0;
+  for (long long seg = (long long)blockIdx.x * (IS_THREADS / 32) + wib; seg < a.nseg;
+       seg += (long long)gridDim.x * (IS_THREADS / 32)) {
+    const long long s0 = seg * IS_SEG;
+    const long long s1 = min(a.n, s0 + IS_SEG);
+    int* ci = a.cand_idx + s0;
+    unsigned* ck = a.cand_key + s0;
+    float* cv = a.cand_val + s0;
+    unsigned cnt = 0;
+    for (long long base = s0; base < s1; base += 512) {
+      float g[4][4];
+      unsigned key[4][4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) keys4<SCORE>(a, base + u * 128 + lane * 4, s1, g[u], key[u]);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const bool f0 = key[u][0] >= tlo, f1 = key[u][1] >= tlo, f2 = key[u][2] >= tlo, f3 = key[u][3] >= tlo;
+        if (__ballot_sync(0xffffffffu, f0 | f1 | f2 | f3) == 0u) continue;
+        const int i0 = (int)(base + u * 128 + lane * 4);
+        const bool f[4] = {f0, f1, f2, f3};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const unsigned bal = __ballot_sync(0xffffffffu, f[j]);
+          if (f[j]) {
+            const unsigned pos = cnt + __popc(bal & lt);
+            ci[pos] = i0 + j;
+            ck[pos] = key[u][j];
+            cv[pos] = g[u][j];
+            atomicAdd(&sh_hist[key[u][j] >> 19], 1u);
+          }
+          cnt += __popc(bal);
+        }
+      }
+    }
+    if (lane == 0) a.segcnt[seg] = (int)cnt;
+    warp_total += cnt;
+  }
+  if (lane == 0) sh_cnt[wib] = warp_total;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned t = 0;
+    for (int i = 0; i < IS_THREADS / 32; ++i) t += sh_cnt[i];
+    if (t) atomicAdd(a.state + ST_C, t);
+  }
+  unsigned* mine = a.histA + (blockIdx.x % IS_REP) * IS_ABINS;
+  for (int i = threadIdx.x; i < IS_ABINS; i += IS_THREADS) {
+    const unsigned c = sh_hist[i];
+    if (c) atomicAdd(&mine[i], c);
+  }
+  if (!last_cta(a.state + ST_TICKET0 + 1 + a.level)) return;
+  const unsigned C = ldv(a.state + ST_C), k = (unsigned)a.k;
+  const bool retry = a.level == 0 && C < k && tlo > 1u;
+  unsigned bin = 0, above = 0;
+  bool found = false;
+  if (!retry && C > k) found = find_suffix_bin(a.histA, IS_ABINS, IS_REP, k, sh_cnt, bin, above);
+  for (int i = threadIdx.x; i < IS_REP * IS_ABINS / 4; i += IS_THREADS)
+    reinterpret_cast<uint4*>(a.histA)[i] = make_uint4(0, 0, 0, 0);
+  if (threadIdx.x != 0) return;
+  if (retry) {
+    a.state[ST_LEVEL] = 1u;  // the sample bound was too high: take every non-zero element
+    a.state[ST_C] = 0u;
+  } else if (C <= k) {
+    // no more non-zero keys than k: every candidate is selected
+    a.state[ST_SKIP] = 1u; a.state[ST_T] = 0u; a.state[ST_NEED] = 0u; a.state[ST_EQ] = 0u;
+    a.state[ST_ICUT] = 0x7FFFFFFFu; a.state[ST_ABOVE] = C;
+  } else {
+    if (!found) atomicOr(a.c.err, SGA_ERR_BOUNDS);
+    a.state[ST_BA] = bin;
+    a.state[ST_ABOVE] = above;
+  }
+}
+
+// ------------------------------------------------------------- radix digits
+// The remaining 19 key bits in one pass over the candidates of the crossing bin: an 11-bit digit
+// in replicated global histograms and the full 19 bits in a 512 K-bin histogram (the values are
+// spread over it, so its atomics rarely meet; a warp's equal keys are merged first). The last CTA
+// finds the 11-bit bin, then reads the 256 fine bins under it: the exact k-th key T, the number
+// of keys above it and the number of ties at T to take.
+__global__ void __launch_bounds__(IS_THREADS) isync_digit_kernel(const ISyncArgs a) {
+  __shared__ unsigned sh_scan[8];
+  if (ldv(a.state + ST_SKIP) || ldv(a.state + ST_C) < (unsigned)a.k) return;
+  const unsigned bA = ldv(a.state + ST_BA);
+  unsigned* coarse = a.histB + (blockIdx.x % IS_REP) * IS_BBINS;
+  unsigned* fine = a.histB + IS_REP * IS_BBINS;
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  for (long long seg = (long long)blockIdx.x * (IS_THREADS / 32) + wib; seg < a.nseg;
+       seg += (long long)gridDim.x * (IS_THREADS / 32)) {
+    const long long s0 = seg * IS_SEG;
+    const int cnt = a.segcnt[seg];
+    for (int j0 = 0; j0 < cnt; j0 += 32) {
+      const int j = j0 + lane;
+      unsigned key = 0;
+      if (j < cnt) key = a.cand_key[s0 + j];
+      const bool valid = j < cnt && (key >> 19) == bA;
+      const unsigned act = __ballot_sync(0xffffffffu, valid);
+      if (valid) {
+        const unsigned low = key & 0x7FFFFu;
+        const unsigned peers = __match_any_sync(act, low);
+        if (lane == __ffs(peers) - 1) {
+          const unsigned c = (unsigned)__popc(peers);
+          atomicAdd(&fine[low], c);
+          atomicAdd(&coarse[low >> 8], c);
+        }
+      }
+    }
+  }
+  if (!last_cta(a.state + ST_TICKET0 + 3)) return;
+  const unsigned k = (unsigned)a.k, aboveA = ldv(a.state + ST_ABOVE);
+  unsigned bB, aboveB;
+  if (!find_suffix_bin(a.histB, IS_BBINS, IS_REP, k - aboveA, sh_scan, bB, aboveB)) {
+    if (threadIdx.x == 0) atomicOr(a.c.err, SGA_ERR_BOUNDS);
+    bB = 0; aboveB = 0;
+  }
+  for (int i = threadIdx.x; i < IS_REP * IS_BBINS / 4; i += IS_THREADS)
+    reinterpret_cast<uint4*>(a.histB)[i] = make_uint4(0, 0, 0, 0);
+  // thread t looks at fine bin 255 - t of the crossing 11-bit bin: a descending scan
+  const unsigned mine = __ldcg(fine + (bB << 8) + (255u - threadIdx.x));
+  unsigned total;
+  const unsigned before = block_excl_scan256(mine, sh_scan, total);
+  const unsigned want = k - aboveA - aboveB;
+  if (before < want && before + mine >= want) {
+    const unsigned n_gt = aboveA + aboveB + before, need = k - n_gt;
+    a.state[ST_T] = (bA << 19) | (bB << 8) | (255u - threadIdx.x);
+    a.state[ST_ABOVE] = n_gt;
+    a.state[ST_NEED] = need;
+    a.state[ST_EQ] = mine;
+    a.state[ST_ICUT] = 0x7FFFFFFFu;
+  }
+  if (threadIdx.x == 0 && total < want) atomicOr(a.c.err, SGA_ERR_BOUNDS);
+}
+
+__device__ __forceinline__ bool is_selected(unsigned key, int idx, unsigned T, unsigned icut) {
+  return key > T || (key == T && idx <= (int)icut);  // icut: index of the last tie taken (INT_MAX: all)
+}
+
+// ------------------------------------------------------------------- count
+// Keys above T and ties at T per segment. The last CTA takes the ties in index order (segments
+// are in index order; inside the one segment that is cut, a bitmap finds the index of the last
+// tie taken) and turns the per-segment counts into the payload's offset table.
+__global__ void __launch_bounds__(IS_THREADS) isync_count_kernel(const ISyncArgs a) {
+  __shared__ unsigned sh_scan[8];
+  __shared__ unsigned sh_bm[IS_SEG / 32];
+  __shared__ unsigned sh_cut[3];
+  const unsigned T = ldv(a.state + ST_T);
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  for (long long seg = (long long)blockIdx.x * (IS_THREADS / 32) + wib; seg < a.nseg;
+       seg += (long long)gridDim.x * (IS_THREADS / 32)) {
+    const long long s0 = seg * IS_SEG;
+    const int cnt = a.segcnt[seg];
+    int g = 0, e = 0;
+    for (int j = lane; j < cnt; j += 32) {
+      const unsigned key = a.cand_key[s0 + j];
+      g += key > T;
+      e += key == T;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      g += __shfl_xor_sync(0xffffffffu, g, o);
+      e += __shfl_xor_sync(0xffffffffu, e, o);
+    }
+    if (lane == 0) { a.segsel[seg] = g; a.segeq[seg] = e; }
+  }
+  if (!last_cta(a.state + ST_TICKET0 + 4)) return;
+  const unsigned need = ldv(a.state + ST_NEED);
+  const int per = (a.nseg + IS_THREADS - 1) / IS_THREADS;
+  const int lo = min(a.nseg, (int)threadIdx.x * per), hi = min(a.nseg, lo + per);
+  // ties: the segment where the running count of ties passes `need`
+  unsigned myeq = 0;
+  for (int i = lo; i < hi; ++i) myeq += (unsigned)__ldcg(a.segeq + i);
+  unsigned eq_total;
+  const unsigned eq_before = block_excl_scan256(myeq, sh_scan, eq_total);
+  if (threadIdx.x == 0) { sh_cut[0] = 0xFFFFFFFFu; sh_cut[1] = 0; sh_cut[2] = 0x7FFFFFFFu; }
+  __syncthreads();
+  if (need < eq_total && eq_before <= need && eq_before + myeq > need) {
+    unsigned run = eq_before;
+    for (int i = lo; i < hi; ++i) {
+      const unsigned e = (unsigned)__ldcg(a.segeq + i);
+      if (run + e > need) { sh_cut[0] = (unsigned)i; sh_cut[1] = need - run; break; }  // take need - run of segment i
+      run += e;
+    }
+  }
+  __syncthreads();
+  const unsigned cut_seg = sh_cut[0], cut_take = sh_cut[1];
+  if (cut_seg != 0xFFFFFFFFu) {
+    // bitmap of the cut segment's ties, then the index of its cut_take-th tie (none taken if 0)
+    for (int i = threadIdx.x; i < IS_SEG / 32; i += IS_THREADS) sh_bm[i] = 0;
+    __syncthreads();
+    const long long s0 = (long long)cut_seg * IS_SEG;
+    const int cnt = __ldcg(a.segcnt + cut_seg);
+    for (int j = threadIdx.x; j < cnt; j += IS_THREADS)
+      if (__ldcg(a.cand_key + s0 + j) == T) {
+        const int rel = __ldcg(a.cand_idx + s0 + j) - (int)s0;
+        atomicOr(&sh_bm[rel >> 5], 1u << (rel & 31));
+      }
+    __syncthreads();
+    const unsigned w = sh_bm[threadIdx.x];  // IS_SEG / 32 == IS_THREADS words
+    const unsigned pc = (unsigned)__popc(w);
+    unsigned tot;
+    const unsigned pre = block_excl_scan256(pc, sh_scan, tot);
+    if (cut_take == 0) {
+      if (threadIdx.x == 0) sh_cut[2] = (unsigned)(s0 - 1);  // nothing of this segment (need >= 1, so s0 > 0)
+    } else if (pre < cut_take && pre + pc >= cut_take) {
+      unsigned bits = w;
+      for (unsigned r = pre + 1; r < cut_take; ++r) bits &= bits - 1;
+      sh_cut[2] = (unsigned)s0 + threadIdx.x * 32 + (__ffs(bits) - 1);
+    }
+    __syncthreads();
+  }
+  const unsigned icut = sh_cut[2];
+  // selected per segment = keys above T + the ties taken there
+  unsigned mysum = 0;
+  for (int i = lo; i < hi; ++i) {
+    unsigned s = (unsigned)__ldcg(a.segsel + i);
+    const unsigned e = (unsigned)__ldcg(a.segeq + i);
+    if (cut_seg == 0xFFFFFFFFu) s += need >= eq_total ? e : 0u;
+    else s += (unsigned)i < cut_seg ? e : ((unsigned)i == cut_seg ? cut_take : 0u);
+    a.segsel[i] = (int)s;
+    mysum += s;
+  }
+  unsigned total;
+  unsigned run = block_excl_scan256(mysum, sh_scan, total);
+  for (int i = lo; i < hi; ++i) {
+    a.roff[i] = (int)run;
+    run += (unsigned)a.segsel[i];
+  }
+  if (threadIdx.x == 0) {
+    a.roff[a.nseg] = (int)total;
+    a.state[ST_NSEL] = total;
+    a.state[ST_ICUT] = icut;
+    if (a.result) {
+      a.result[0] = T;
+      a.result[1] = need;
+      a.result[2] = ldv(a.state + ST_ABOVE);
+      a.result[3] = total;
+    }
+    if (total > (unsigned)a.kcap && a.kcap > 0) atomicOr(a.c.err, SGA_ERR_CAPACITY);
+  }
+}
+
+// -------------------------------------------------------------------- emit
+// Push the selected (index, value) pairs, grouped by segment, and the offset table into every
+// rank's receive area (this rank's own included); zero the selected coordinates of the bucket
+// (what stays is the residual). The last CTA raises this rank's "ready" flag on every peer.
+__global__ void __launch_bounds__(IS_THREADS) isync_emit_kernel(const ISyncArgs a) {
+  const PeerCtx& c = a.c;
+  if (c.prev_seq > 0) peer_wait(c, 1, c.prev_seq);  // peers are done reading my previous payload
+  const unsigned T = ldv(a.state + ST_T), icut = ldv(a.state + ST_ICUT);
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  const unsigned lt = (1u << lane) - 1u;
+  for (long long seg = (long long)blockIdx.x * (IS_THREADS / 32) + wib; seg < a.nseg;
+       seg += (long long)gridDim.x * (IS_THREADS / 32)) {
+    const long long s0 = seg * IS_SEG;
+    const int cnt = a.segcnt[seg];
+    int pos0 = a.roff[seg];
+    for (int j0 = 0; j0 < cnt; j0 += 32) {
+      const int j = j0 + lane;
+      bool sel = false;
+      int2 pr = make_int2(0, 0);
+      if (j < cnt) {
+        pr.x = a.cand_idx[s0 + j];
+        pr.y = __float_as_int(a.cand_val[s0 + j]);
+        sel = is_selected(a.cand_key[s0 + j], pr.x, T, icut);
+      }
+      const unsigned bal = __ballot_sync(0xffffffffu, sel);
+      if (sel) {
+        const int pos = pos0 + __popc(bal & lt);
+        if (pos < a.kcap) {
+#pragma unroll
+          for (int r = 0; r < MAXW; ++r)
+            if (r < c.W) a.slots[r][(long long)c.rank * a.kcap + pos] = pr;
+        }
+        if (a.zero_selected) a.acc[pr.x] = 0.f;
+      }
+      pos0 += __popc(bal);
+    }
+  }
+  for (long long i = (long long)blockIdx.x * IS_THREADS + threadIdx.x; i <= a.nseg;
+       i += (long long)gridDim.x * IS_THREADS) {
+    const int off = a.roff[i];
+#pragma unroll
+    for (int r = 0; r < MAXW; ++r)
+      if (r < c.W) a.hdr[r][(long long)c.rank * a.hstride + i] = off;
+  }
+  if (!last_cta<true>(a.state + ST_TICKET0 + 5)) return;
+  if (threadIdx.x < c.W) {
+    __threadfence_system();
+    st_release_sys(c.flags[threadIdx.x] + 0 * 8 + c.rank, c.seq);
+  }
+}
+
+// Select-only form: the selection as a bit mask (zeroed by the host), nothing is exchanged.
+__global__ void __launch_bounds__(IS_THREADS) isync_mask_kernel(const ISyncArgs a) {
+  const unsigned T = ldv(a.state + ST_T), icut = ldv(a.state + ST_ICUT);
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  for (long long seg = (long long)blockIdx.x * (IS_THREADS / 32) + wib; seg < a.nseg;
+       seg += (long long)gridDim.x * (IS_THREADS / 32)) {
+    const long long s0 = seg * IS_SEG;
+    const int cnt = a.segcnt[seg];
+    for (int j = lane; j < cnt; j += 32) {
+      const int idx = a.cand_idx[s0 + j];
+      if (is_selected(a.cand_key[s0 + j], idx, T, icut)) atomicOr(&a.bits[idx >> 5], 1u << (idx & 31));
+    }
+  }
+}
+
+// ------------------------------------------------------------------ reduce
+// One CTA per range of four segments: once every rank's payload has landed, add the ranks' pairs
+// of the range into the dense staging buffer in rank order (each rank lists a coordinate at most
+// once, so a rank's pairs need no atomics), then the squared norm over the coordinates touched.
+// The last CTA adds the per-range partials in index order and raises "done" on every peer.
+__global__ void __launch_bounds__(IS_THREADS) isync_reduce_kernel(const ISyncArgs a) {
+  __shared__ unsigned sh_bm[IS_SEG_PER_RANGE * IS_SEG / 32];
+  __shared__ float red[IS_THREADS];
+  const PeerCtx& c = a.c;
+  peer_wait(c, 0, c.seq);
+  const int nranges = (a.nseg + IS_SEG_PER_RANGE - 1) / IS_SEG_PER_RANGE;
+  const int2* my_slots = a.slots[c.rank];
+  const int* my_hdr = a.hdr[c.rank];
+  for (int range = blockIdx.x; range < nranges; range += gridDim.x) {
+    const int seg0 = range * IS_SEG_PER_RANGE, seg1 = min(a.nseg, seg0 + IS_SEG_PER_RANGE);
+    const long long r0 = (long long)seg0 * IS_SEG, r1 = min(a.n, (long long)seg1 * IS_SEG);
+    for (int i = threadIdx.x; i < IS_SEG_PER_RANGE * IS_SEG / 32; i += IS_THREADS) sh_bm[i] = 0;
+    __syncthreads();
+    for (int r = 0; r < c.W; ++r) {
+      const int lo = __ldcg(my_hdr + (long long)r * a.hstride + seg0);
+      const int hi = __ldcg(my_hdr + (long long)r * a.hstride + seg1);
+      if (lo < 0 || hi < lo || hi > a.kcap) {
+        if (threadIdx.x == 0) atomicOr(c.err, SGA_ERR_BOUNDS);
+      } else {
+        const int2* list = my_slots + (long long)r * a.kcap;
+        for (int j = lo + threadIdx.x; j < hi; j += IS_THREADS) {
+          const int2 pr = __ldcg(list + j);
+          const long long p = pr.x;
+          if (p >= r0 && p < r1) {
+            a.comm[p] = a.comm[p] + __int_as_float(pr.y) * a.scale;
+            atomicOr(&sh_bm[(p - r0) >> 5], 1u << ((p - r0) & 31));
+          } else {
+            atomicOr(c.err, SGA_ERR_BOUNDS);
+          }
+        }
+      }
+      __syncthreads();
+    }
+    float sq = 0.f;
+    for (int w = threadIdx.x; w < IS_SEG_PER_RANGE * IS_SEG / 32; w += IS_THREADS) {
+      unsigned bits = sh_bm[w];
+      while (bits) {
+        const int b = __ffs(bits) - 1;
+        bits &= bits - 1;
+        const float x = a.comm[r0 + w * 32 + b];
+        sq = sq + x * x;
+      }
+    }
+    const float bs = block_sum(sq, red);
+    if (threadIdx.x == 0) a.partials[range] = bs;
+    __syncthreads();
+  }
+  if (!last_cta<true>(a.state + ST_TICKET0 + 6)) return;
+  float t = 0.f;
+  for (int i = threadIdx.x; i < nranges; i += IS_THREADS) t = t + __ldcg(a.partials + i);
+  const float tot = block_sum(t, red);
+  if (threadIdx.x == 0 && a.sumsq_out) a.sumsq_out[0] = a.accumulate ? a.sumsq_out[0] + tot : tot;
+  if (threadIdx.x < c.W) {
+    __threadfence_system();
+    st_release_sys(c.flags[threadIdx.x] + 1 * 8 + c.rank, c.seq);
+  }
+}
+
+}  // namespace sga
+
+using namespace sga;
+
+// Host-side description of one bucket synchronisation (mirrored by a ctypes.Structure).
+struct SgaISyncDesc {
+  void* acc; const void* w; const void* m; const void* v;
+  long long n;
+  int k, score, adams, nspan;
+  float beta1, omb1, beta2, omb2, bc1, bc2, eps, scale;
+  const void* span_start; const void* span_wd;
+  void* state; void* histA; void* histB; void* cand_idx; void* cand_key; void* cand_val;
+  void* segcnt; void* segsel; void* segeq; void* roff; void* partials;
+  void* slots[sga::MAXW]; void* hdr[sga::MAXW];
+  int kcap, hstride;
+  void* comm; void* sumsq_out; void* bits; void* result;
+  long long cand_capacity;   // elements the candidate arrays hold
+  int seg_capacity;          // entries of segcnt / segsel (roff holds one more)
+  int partials_capacity;
+  int accumulate, zero_selected, mode, max_ctas;
+};
+
+template <int SCORE>
+static void launch_select(const ISyncArgs& base, int grid_seg, int grid_sample, cudaStream_t st) {
+  ISyncArgs a = base;
+  isync_sample_kernel<SCORE><<<grid_sample, IS_THREADS, 0, st>>>(a);
+  a.level = 0;
+  isync_filter_kernel<SCORE><<<grid_seg, IS_THREADS, 0, st>>>(a);
+  a.level = 1;
+  isync_filter_kernel<SCORE><<<grid_seg, IS_THREADS, 0, st>>>(a);
+}
+
+// mode 0: select + exchange + reduce into comm. mode 1: select only, bit mask of the selection
+// into `bits` (ceil(n / 32) words). Returns 0, or a negative code before anything was launched.
+SGA_API int sga_index_sync(const SgaPeerDesc* d, const SgaISyncDesc* s, void* stream) {
+  if (d->W > MAXW) return -1;
+  if (s->n <= 0 || s->n >= (1LL << 31) || s->k < 1 || s->k > s->n) return -6;
+  if (s->score < 0 || s->score > 3) return -6;
+  if ((reinterpret_cast<uintptr_t>(s->acc) & 15) != 0) return -9;
+  const int nseg = (int)((s->n + IS_SEG - 1) / IS_SEG);
+  if ((long long)nseg * IS_SEG > s->cand_capacity || nseg > s->seg_capacity) return -7;
+  const int nranges = (nseg + IS_SEG_PER_RANGE - 1) / IS_SEG_PER_RANGE;
+  if (s->mode == 0) {
+    if (s->k > s->kcap || nseg + 1 > s->hstride || nranges > s->partials_capacity || !s->comm) return -7;
+  } else if (!s->bits) {
+    return -6;
+  }
+  if (s->score != 1 && (!s->m || (s->score != 2 && !s->v) || (s->score == 0 && (!s->w || s->nspan < 1)))) return -6;
+  ISyncArgs a;
+  a.c = make_ctx(d);
+  a.acc = reinterpret_cast<float*>(s->acc);
+  a.w = reinterpret_cast<const float*>(s->w);
+  a.m = reinterpret_cast<const float*>(s->m);
+  a.v = reinterpret_cast<const float*>(s->v);
+  a.n = s->n; a.k = s->k; a.nseg = nseg; a.score = s->score; a.adams = s->adams;
+  a.beta1 = s->beta1; a.omb1 = s->omb1; a.beta2 = s->beta2; a.omb2 = s->omb2;
+  a.bc1 = s->bc1; a.bc2 = s->bc2; a.eps = s->eps;
+  a.span_start = reinterpret_cast<const int*>(s->span_start);
+  a.span_wd = reinterpret_cast<const float*>(s->span_wd);
+  a.nspan = s->nspan;
+  a.gshift = s->n > (1LL << 20) ? 6 : 0;
+  a.state = reinterpret_cast<unsigned*>(s->state);
+  a.histA = reinterpret_cast<unsigned*>(s->histA);
+  a.histB = reinterpret_cast<unsigned*>(s->histB);
+  a.cand_idx = reinterpret_cast<int*>(s->cand_idx);
+  a.cand_key = reinterpret_cast<unsigned*>(s->cand_key);
+  a.cand_val = reinterpret_cast<float*>(s->cand_val);
+  a.segcnt = reinterpret_cast<int*>(s->segcnt);
+  a.segsel = reinterpret_cast<int*>(s->segsel);
+  a.segeq = reinterpret_cast<int*>(s->segeq);
+  a.roff = reinterpret_cast<int*>(s->roff);
+  a.partials = reinterpret_cast<float*>(s->partials);
+  for (int i = 0; i < MAXW; ++i) {
+    a.slots[i] = i < d->W ? reinterpret_cast<int2*>(s->slots[i]) : nullptr;
+    a.hdr[i] = i < d->W ? reinterpret_cast<int*>(s->hdr[i]) : nullptr;
+  }
+  a.kcap = s->mode == 0 ? s->kcap : 0;
+  a.hstride = s->hstride;
+  a.comm = reinterpret_cast<float*>(s->comm);
+  a.scale = s->scale;
+  a.sumsq_out = reinterpret_cast<float*>(s->sumsq_out);
+  a.accumulate = s->accumulate; a.zero_selected = s->zero_selected;
+  a.bits = reinterpret_cast<unsigned*>(s->bits);
+  a.result = reinterpret_cast<unsigned*>(s->result);
+  a.level = 0;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int cap = s->max_ctas > 0 ? s->max_ctas : 148 * 8;
+  const int wpc = IS_THREADS / 32;
+  int grid_seg = (nseg + wpc - 1) / wpc;
+  if (grid_seg > cap) grid_seg = cap;
+  const long long ngroups = (((s->n + 3) >> 2) + (1LL << a.gshift) - 1) >> a.gshift;
+  int grid_sample = (int)((ngroups + IS_THREADS * 4 - 1) / (IS_THREADS * 4));
+  if (grid_sample > 148) grid_sample = 148;
+  if (grid_sample < 1) grid_sample = 1;
+  int grid_range = nranges < cap ? nranges : cap;
+  cudaMemsetAsync(a.state, 0, 64 * sizeof(unsigned), st);
+  if (s->mode == 1) cudaMemsetAsync(a.bits, 0, (size_t)((s->n + 31) / 32) * 4, st);
+  switch (s->score) {
+    case 0: launch_select<0>(a, grid_seg, grid_sample, st); break;
+    case 1: launch_select<1>(a, grid_seg, grid_sample, st); break;
+    case 2: launch_select<2>(a, grid_seg, grid_sample, st); break;
+    default: launch_select<3>(a, grid_seg, grid_sample, st); break;
+  }
+  isync_digit_kernel<<<grid_seg, IS_THREADS, 0, st>>>(a);
+  isync_count_kernel<<<grid_seg, IS_THREADS, 0, st>>>(a);
+  if (s->mode == 1) {
+    isync_mask_kernel<<<grid_seg, IS_THREADS, 0, st>>>(a);
+  } else {
+    isync_emit_kernel<<<grid_seg, IS_THREADS, 0, st>>>(a);
+    isync_reduce_kernel<<<grid_range, IS_THREADS, 0, st>>>(a);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

@@ -152,3 +152,13 @@ def topk_exact_flat(score_abs: torch.Tensor, k: int) -> torch.Tensor:
         ties = torch.nonzero(key == thr, as_tuple=False).view(-1)[:need]
         mask[ties] = 1
     return mask
+
+
+def topk_rank_local(score_abs: torch.Tensor, k: int) -> torch.Tensor:
+    """Selection rule of the fused rank-local kernel (``csrc/index_sync.cu``): the exact top-``k``
+    of :func:`topk_exact_flat`, minus the coordinates whose score is exactly zero (a zero carries
+    nothing to send, so a bucket with fewer than ``k`` non-zero scores selects only those)."""
+    mask = topk_exact_flat(score_abs, k)
+    mask[abs_bit_key(score_abs) == 0] = 0
+    return mask
+

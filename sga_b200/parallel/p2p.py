@@ -58,6 +58,14 @@ class PeerChannel:
         d.wait_cycles = self.wait_cycles
         return d
 
+    def peek_desc(self) -> PeerDesc:
+        """Descriptor for a launch that exchanges nothing (no flag is raised or awaited): the
+        channel's sequence number stays where it is."""
+        d = self.next_desc()
+        self.seq -= 1
+        d.seq, d.prev_seq = self.seq, self.seq
+        return d
+
     def norm_slots(self):
         return self.ctrl.ptr_array(256)
 
@@ -98,31 +106,145 @@ def mask_union_reduce_(ch: PeerChannel, grad: SymmBuffer, grad_off: int, bits: S
     _chk(rc, "sga_p2p_mask_union")
 
 
-class IndexSyncScratch:
-    """Per-device scratch of the fused top-k kernel (histograms kept zero between launches)."""
+IS_SEG = 8192           # elements per segment of the candidate arrays (csrc/index_sync.cu)
+IS_SEG_PER_RANGE = 4
+SCORE_CODES = {"update": 0, "abs_g": 1, "abs_m": 2, "coi": 3}
 
-    def __init__(self, device):
-        self.hist1 = torch.zeros(32769, dtype=torch.int32, device=device)
-        self.hist2 = torch.zeros(65536, dtype=torch.int32, device=device)
-        self.cta_gt = torch.zeros(256, dtype=torch.int32, device=device)
-        self.cta_eq = torch.zeros(256, dtype=torch.int32, device=device)
+
+class ISyncDesc(ctypes.Structure):
+    """Mirror of ``SgaISyncDesc`` (csrc/index_sync.cu)."""
+    _fields_ = [("acc", ctypes.c_void_p), ("w", ctypes.c_void_p), ("m", ctypes.c_void_p), ("v", ctypes.c_void_p),
+                ("n", ctypes.c_longlong),
+                ("k", ctypes.c_int), ("score", ctypes.c_int), ("adams", ctypes.c_int), ("nspan", ctypes.c_int),
+                ("beta1", ctypes.c_float), ("omb1", ctypes.c_float), ("beta2", ctypes.c_float),
+                ("omb2", ctypes.c_float), ("bc1", ctypes.c_float), ("bc2", ctypes.c_float), ("eps", ctypes.c_float),
+                ("scale", ctypes.c_float),
+                ("span_start", ctypes.c_void_p), ("span_wd", ctypes.c_void_p),
+                ("state", ctypes.c_void_p), ("histA", ctypes.c_void_p), ("histB", ctypes.c_void_p),
+                ("cand_idx", ctypes.c_void_p), ("cand_key", ctypes.c_void_p), ("cand_val", ctypes.c_void_p),
+                ("segcnt", ctypes.c_void_p), ("segsel", ctypes.c_void_p), ("segeq", ctypes.c_void_p),
+                ("roff", ctypes.c_void_p),
+                ("partials", ctypes.c_void_p),
+                ("slots", ctypes.c_void_p * 8), ("hdr", ctypes.c_void_p * 8),
+                ("kcap", ctypes.c_int), ("hstride", ctypes.c_int),
+                ("comm", ctypes.c_void_p), ("sumsq_out", ctypes.c_void_p), ("bits", ctypes.c_void_p),
+                ("result", ctypes.c_void_p),
+                ("cand_capacity", ctypes.c_longlong), ("seg_capacity", ctypes.c_int),
+                ("partials_capacity", ctypes.c_int),
+                ("accumulate", ctypes.c_int), ("zero_selected", ctypes.c_int), ("mode", ctypes.c_int),
+                ("max_ctas", ctypes.c_int)]
+
+
+def _nseg(n: int) -> int:
+    return (int(n) + IS_SEG - 1) // IS_SEG
+
+
+class IndexSyncScratch:
+    """Per-device work memory of the fused top-k chain, sized for the largest bucket: the
+    candidate arrays hold one entry per bucket element (a segment's candidates live in the
+    segment's own slice, so no input can overflow them), the histograms stay zero between
+    launches. Launches that share a scratch must be ordered on one stream."""
+
+    def __init__(self, device, max_elems: int = 1 << 20):
+        self.device = device
+        self.nseg = _nseg(max_elems)
+        cap = self.nseg * IS_SEG
+        self.capacity = cap
+        self.state = torch.zeros(64, dtype=torch.int32, device=device)
+        self.histA = torch.zeros(8 * 4096, dtype=torch.int32, device=device)
+        self.histB = torch.zeros(8 * 2048 + (1 << 19), dtype=torch.int32, device=device)
+        self.cand_idx = torch.empty(cap, dtype=torch.int32, device=device)
+        self.cand_key = torch.empty(cap, dtype=torch.int32, device=device)
+        self.cand_val = torch.empty(cap, dtype=torch.float32, device=device)
+        self.segcnt = torch.zeros(self.nseg, dtype=torch.int32, device=device)
+        self.segsel = torch.zeros(self.nseg, dtype=torch.int32, device=device)
+        self.segeq = torch.zeros(self.nseg, dtype=torch.int32, device=device)
+        self.roff = torch.zeros(self.nseg + 1, dtype=torch.int32, device=device)
+        self.nranges = (self.nseg + IS_SEG_PER_RANGE - 1) // IS_SEG_PER_RANGE
+        self.partials = torch.zeros(self.nranges, dtype=torch.float32, device=device)
         self.result = torch.zeros(4, dtype=torch.int32, device=device)
 
+    def ensure(self, n: int) -> None:
+        if _nseg(n) > self.nseg:
+            self.__init__(self.device, n)
 
-def bucket_index_sync_(ch: PeerChannel, scratch: IndexSyncScratch, acc: torch.Tensor, k: int, *, slots: SymmBuffer | None,
-                       kcap: int, comm=None, touched: torch.Tensor, scale: float = 1.0, sumsq_out=None,
-                       accumulate=False, select_only=False, zero_selected=True, max_ctas: int = 0) -> None:
-    """Exact top-``k`` of ``|acc|`` + (index, value) exchange + rank-ordered
-    scatter-add into ``comm``. With ``select_only`` only the bit mask of the
-    selection is written to ``touched``."""
-    d = ch.next_desc()
-    rc = lib().sga_bucket_index_sync(ctypes.byref(d), acc.data_ptr(), acc.numel(), int(k), scratch.hist1.data_ptr(),
-                                     scratch.hist2.data_ptr(), scratch.cta_gt.data_ptr(), scratch.cta_eq.data_ptr(),
-                                     slots.ptr_array(0) if slots is not None else None, int(kcap), _p(comm),
-                                     touched.data_ptr(), float(scale), ch.cta_partials.data_ptr(), _p(sumsq_out),
-                                     int(accumulate), int(select_only), int(zero_selected), scratch.result.data_ptr(),
-                                     max_ctas, _st())
-    _chk(rc, "sga_bucket_index_sync")
+
+class IndexSyncSlots:
+    """Receive area of one channel in symmetric memory: per source rank ``kcap`` (index, value)
+    pairs, then per source rank the table of segment offsets into its pairs."""
+
+    def __init__(self, pool: SymmPool, kcap: int, max_elems: int):
+        self.kcap = int(kcap)
+        self.hstride = _nseg(max_elems) + 1
+        self.pairs_bytes = (8 * self.kcap * pool.world + 255) // 256 * 256
+        self.buf: SymmBuffer = pool.alloc(self.pairs_bytes + 4 * self.hstride * pool.world)
+        self.world = pool.world
+
+    def pairs(self, src_rank: int, count: int) -> torch.Tensor:
+        """``[count, 2]`` int32 view of what rank ``src_rank`` pushed here (index, value bits)."""
+        return self.buf.view(torch.int32, 8 * self.kcap * src_rank, 2 * count).view(count, 2)
+
+
+class ScoreInputs:
+    """What the scores other than ``abs_g`` read beside the gradient: the bucket's slices of the
+    fp32 weights and moments, the Adam scalars of the coming commit and, for ``update``, the
+    weight decay of every parameter span of the bucket."""
+
+    def __init__(self, name: str, *, w=None, m=None, v=None, beta1=0.9, beta2=0.999, eps=1e-8, step=1,
+                 adams=False, span_start=None, span_wd=None):
+        self.name, self.w, self.m, self.v = name, w, m, v
+        self.beta1, self.beta2, self.eps, self.adams = float(beta1), float(beta2), float(eps), bool(adams)
+        self.bc1 = 1.0 if adams else 1.0 - self.beta1 ** step
+        self.bc2 = 1.0 if adams else 1.0 - self.beta2 ** step
+        self.span_start, self.span_wd = span_start, span_wd
+
+
+def bucket_index_sync_(ch: PeerChannel, scratch: IndexSyncScratch, acc: torch.Tensor, k: int, *,
+                       slots: IndexSyncSlots | None = None, comm=None, bits: torch.Tensor | None = None,
+                       scale: float = 1.0, sumsq_out=None, accumulate=False, select_only=False, zero_selected=True,
+                       score: ScoreInputs | None = None, max_ctas: int = 0) -> None:
+    """Exact top-``k`` of the score over ``acc`` (default ``|acc|``), exchange of the selected
+    (index, value) pairs with every rank of the channel and rank-ordered scatter-add of all ranks'
+    pairs, times ``scale``, into ``comm``; the selected coordinates of ``acc`` are zeroed. With
+    ``select_only`` nothing is exchanged and the selection's bit mask is written to ``bits``."""
+    n = acc.numel()
+    scratch.ensure(n)
+    d = ch.peek_desc() if select_only else ch.next_desc()
+    s = ISyncDesc()
+    s.acc, s.n, s.k = acc.data_ptr(), n, int(k)
+    s.score = SCORE_CODES[score.name] if score is not None else 1
+    if score is not None:
+        s.w, s.m, s.v = _p(score.w), _p(score.m), _p(score.v)
+        s.adams = int(score.adams)
+        s.beta1, s.omb1, s.beta2, s.omb2 = score.beta1, 1.0 - score.beta1, score.beta2, 1.0 - score.beta2
+        s.bc1, s.bc2, s.eps = score.bc1, score.bc2, score.eps
+        if score.span_start is not None:
+            s.span_start, s.span_wd = score.span_start.data_ptr(), score.span_wd.data_ptr()
+            s.nspan = score.span_wd.numel()
+    s.scale = float(scale)
+    s.state, s.histA, s.histB = scratch.state.data_ptr(), scratch.histA.data_ptr(), scratch.histB.data_ptr()
+    s.cand_idx, s.cand_key, s.cand_val = (scratch.cand_idx.data_ptr(), scratch.cand_key.data_ptr(),
+                                          scratch.cand_val.data_ptr())
+    s.segcnt, s.segsel, s.segeq = scratch.segcnt.data_ptr(), scratch.segsel.data_ptr(), scratch.segeq.data_ptr()
+    s.roff = scratch.roff.data_ptr()
+    s.partials, s.result = scratch.partials.data_ptr(), scratch.result.data_ptr()
+    s.cand_capacity, s.seg_capacity, s.partials_capacity = scratch.capacity, scratch.nseg, scratch.nranges
+    if not select_only:
+        if slots is None or comm is None:
+            raise ValueError("bucket_index_sync_: the exchange needs receive slots and a staging buffer")
+        for r in range(slots.world):
+            s.slots[r] = slots.buf.peer_ptrs[r]
+            s.hdr[r] = slots.buf.peer_ptrs[r] + slots.pairs_bytes
+        s.kcap, s.hstride = slots.kcap, slots.hstride
+        s.comm = comm.data_ptr()
+    else:
+        if bits is None:
+            raise ValueError("bucket_index_sync_: select_only writes the bit mask to `bits`")
+        s.bits = bits.data_ptr()
+    s.sumsq_out = _p(sumsq_out)
+    s.accumulate, s.zero_selected, s.mode, s.max_ctas = int(accumulate), int(zero_selected), int(select_only), max_ctas
+    rc = lib().sga_index_sync(ctypes.byref(d), ctypes.byref(s), _st())
+    _chk(rc, "sga_index_sync")
 
 
 def dense_adamw_ag_(ch: PeerChannel, w, g, m, v, model: SymmBuffer, bucket_start, bucket_len, table, group_lr,

@@ -323,7 +323,8 @@ class SGAEngine:
         if self.rank_local:
             k = self._k_for_bucket(bucket.numel)
             if self.backend.consumes == "idx":
-                self.backend.sync_rank_local(bs, k, arena.comm[bucket.start:bucket.end], ddp.group, ddp.world)
+                self.backend.sync_rank_local(bs, k, arena.comm[bucket.start:bucket.end], ddp.group, ddp.world,
+                                             score=self._rank_local_score(bs, bucket))
             else:
                 self.backend.sync_rank_local(bs, k, self._active_mask_arena()[bucket.start:bucket.end], ddp.group,
                                              ddp.world)
@@ -339,6 +340,35 @@ class SGAEngine:
                 raise SGAEngineError(f"compact-emission backend returned {type(out).__name__} instead of a values "
                                      "Tensor")
             self._compact_values[id(bs)] = out
+
+    def bind_optimizer(self, optimizer) -> None:
+        """The rank-local scores other than ``abs_g`` read the optimizer's hyper-parameters and step
+        counter while the buckets are synchronised, i.e. before ``optimizer_step`` hands it over."""
+        self._optimizer = optimizer
+
+    def _rank_local_score(self, bs, bucket):
+        """Inputs of the fused kernel's score for one bucket (``None`` = ``|grad + residual|``)."""
+        if self.score_name == "abs_g":
+            return None
+        opt = getattr(self, "_optimizer", None)
+        if opt is None:
+            raise SGAEngineError(f"rank-local score '{self.score_name}' reads the optimizer state: call "
+                                 "engine.bind_optimizer(optimizer) after attach")
+        from ..parallel.p2p import ScoreInputs
+
+        arena = self._ddp.arena
+        sl = slice(bucket.start, bucket.end)
+        g0 = opt.param_groups[0]
+        wds = tuple(float(opt.param_groups[slot.spec.group]["weight_decay"]) for (slot, _s, _e) in bs.param_spans)
+        cached = getattr(bs, "_span_cache", None)
+        if cached is None or cached[0] != wds:
+            starts = [s for (_slot, s, _e) in bs.param_spans] + [bucket.numel]
+            cached = (wds, torch.tensor(starts, dtype=torch.int32, device=arena.device),
+                      torch.tensor(wds, dtype=torch.float32, device=arena.device))
+            bs._span_cache = cached
+        return ScoreInputs(self.score_name, w=arena.main_param[sl], m=arena.exp_avg[sl], v=arena.exp_avg_sq[sl],
+                           beta1=g0["betas"][0], beta2=g0["betas"][1], eps=g0["eps"], step=opt.peek_step(),
+                           adams=self.opt.optimizer_name == "adams", span_start=cached[1], span_wd=cached[2])
 
     def grad_sync(self, ddp, force_all_reduce: bool = False) -> bool:
         """True = the engine synchronised every bucket of this chunk."""

@@ -384,6 +384,7 @@ class Trainer:
             self.engine = build_engine(trainer_args=args, quiet=quiet)
             self.engine.log_interval = args.log_interval
             self.engine.attach(self.ddp)
+            self.engine.bind_optimizer(self.optimizer)
             if self.tp is not None or self.pp_size > 1:
                 self.engine.model_parallel_norm = self._tp_norm
         if getattr(args, "data_path", None):

@@ -30,12 +30,14 @@ def peaks():
         return 6.65e12, 1.59e15, "fallback"
 
 
-def timed(fn, iters, warmup=3, flush=None):
+def timed(fn, iters, warmup=3, flush=None, pre=None):
     """Mean device time of ``fn`` over ``iters`` launches. Every launch is bracketed by its own pair
     of events, and the whole series is enqueued before the one synchronisation at the end, so the
     host's launch latency hides behind the previous kernel (or the L2 flush) instead of being timed
     as an idle GPU."""
     for _ in range(warmup):
+        if pre is not None:
+            pre()
         fn()
     torch.cuda.synchronize()
     pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
@@ -43,6 +45,8 @@ def timed(fn, iters, warmup=3, flush=None):
     for s, e in pairs:
         if pad is not None:
             pad.zero_()
+        if pre is not None:
+            pre()  # untimed set-up of the launch (restores its input)
         s.record()
         fn()
         e.record()
@@ -117,20 +121,26 @@ def _index_sync_case(pool, ch, p2p, n, small):
     k = n // 100
     acc0 = torch.randn(n, device="cuda") * 1e-3
     acc = acc0.clone()
-    slots = pool.alloc(8 * k)
+    slots = p2p.IndexSyncSlots(pool, k, n)
     comm = torch.zeros(n, device="cuda")
-    touched = torch.empty((n + 31) // 32, dtype=torch.int32, device="cuda")
-    scratch = p2p.IndexSyncScratch("cuda:0")
+    scratch = p2p.IndexSyncScratch("cuda:0", n)
     sq = torch.zeros(1, device="cuda")
 
-    def run():
-        p2p.bucket_index_sync_(ch, scratch, acc, k, slots=slots, kcap=k, comm=comm, touched=touched, scale=1.0,
-                               sumsq_out=sq)
+    def restore():
+        acc.copy_(acc0)   # the launch zeroes what it selects; also pushes the bucket out of L2
+        comm.zero_()
 
-    ms = timed(run, 2 if small else 10, warmup=1)
+    def run():
+        p2p.bucket_index_sync_(ch, scratch, acc, k, slots=slots, comm=comm, scale=1.0, sumsq_out=sq)
+
+    ms = timed(run, 2 if small else 10, warmup=1, pre=restore)
     ch.check()
-    # three reads of the bucket (two radix digits, compaction) + payload write, read-back and scatter
-    emit("bucket_index_sync_kernel", f"n={n} k={k} (1 rank)", ms, bytes_=n * 4.0 * 3 + k * 8.0 * 3)
+    cands = int(scratch.state[2].item())
+    # bound of the path as the step accounts it: three reads of the bucket + the payload written,
+    # read back and scattered; the chain itself reads the bucket once
+    emit("index_sync chain (sample, filter, digits, count, emit, reduce)", f"n={n} k={k} (1 rank)", ms,
+         bytes_=n * 4.0 * 3 + k * 8.0 * 3, frac_of_one_pass_bound=round((n * 4.0 + k * 8.0 * 3) / (ms / 1e3) / peaks()[0], 3),
+         candidates=cands)
 
 
 def bench_elementwise(small):

@@ -87,32 +87,34 @@ def check_kernels(rank, world, dev):
     exp = torch.where(union.bool(), ref, x)
     assert torch.equal(g, exp), "masked entries must hold the mean, the rest the local value"
     # ---- bucket index sync (exact rank-local top-k, (idx, val) exchange, ordered scatter-add)
-    nb, k = 200003, 2000
-    acc = torch.randn(nb, device=dev) * 1e-3
-    acc[::53] = 0.25  # ties at the top
-    a0 = acc.clone()
-    slots = pool.alloc(8 * k * world)
-    comm = torch.zeros(nb, device=dev)
-    touched = torch.empty((nb + 31) // 32, dtype=torch.int32, device=dev)
-    scratch = p2p.IndexSyncScratch(dev)
-    for rep in range(2):
-        acc.copy_(a0)
-        comm.zero_()
-        dist.barrier()
-        p2p.bucket_index_sync_(ch, scratch, acc, k, slots=slots, kcap=k, comm=comm, touched=touched,
-                               scale=1.0 / world, sumsq_out=sq)
-        torch.cuda.synchronize()
-        ch.check("bucket index sync")
-        mask = KT.topk_exact_flat(a0.abs(), k)
-        idx = KT.compact_mask_idx(mask)
-        vals = a0[idx.long()]
-        assert torch.equal(acc, torch.where(mask.bool(), torch.zeros_like(a0), a0))
-        idxs, valss = gather(idx), gather(vals)
-        refc = torch.zeros(nb, device=dev)
-        for r in range(world):
-            refc.index_add_(0, idxs[r].long(), valss[r] * (1.0 / world))
-        assert torch.equal(comm, refc), "reduced sparse gradient differs from the rank-ordered reference"
-        assert abs(sq.item() - (refc.double() ** 2).sum().item()) <= 1e-4 * max(sq.item(), 1e-30)
+    for nb, k in ((200003, 2000), (3 * (1 << 20) + 5, 40000)):
+        acc = torch.randn(nb, device=dev) * 1e-3
+        acc[::53] = 0.25  # ties at the top
+        a0 = acc.clone()
+        slots = p2p.IndexSyncSlots(pool, k, nb)
+        comm = torch.zeros(nb, device=dev)
+        scratch = p2p.IndexSyncScratch(dev, nb)
+        for rep in range(3):
+            acc.copy_(a0)
+            comm.zero_()
+            # poison the receive area: a pair that survives from an earlier launch or is read before
+            # the peers' payload has landed shows up as NaN in the staging buffer
+            slots.buf.view(torch.int32, 0, 2 * k * world).fill_(0x7FC00000)
+            dist.barrier()
+            p2p.bucket_index_sync_(ch, scratch, acc, k, slots=slots, comm=comm, scale=1.0 / world, sumsq_out=sq)
+            torch.cuda.synchronize()
+            ch.check("bucket index sync")
+            mask = KT.topk_rank_local(a0.abs(), k)
+            idx = KT.compact_mask_idx(mask)
+            vals = a0[idx.long()]
+            assert torch.equal(acc, torch.where(mask.bool(), torch.zeros_like(a0), a0))
+            idxs, valss = gather(idx), gather(vals)
+            refc = torch.zeros(nb, device=dev)
+            for r in range(world):
+                refc.index_add_(0, idxs[r].long(), valss[r] * (1.0 / world))
+            assert not torch.isnan(comm).any(), "a poisoned receive slot reached the staging buffer"
+            assert torch.equal(comm, refc), "reduced sparse gradient differs from the rank-ordered reference"
+            assert abs(sq.item() - (refc.double() ** 2).sum().item()) <= 1e-4 * max(sq.item(), 1e-30)
     dist.barrier()
     pool.close()
 

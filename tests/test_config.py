@@ -227,9 +227,13 @@ def test_block_and_layout_rules(monkeypatch):
 def test_rank_local_rules():
     ok = _enabled(sga_selection_locality="rank_local", sga_selection_method="exact", sga_cycle_period=0)
     C.validate_sga_args(ok)
+    # every score runs inside the fused index kernel; the mask backend keeps |grad + residual|
+    for score in ("abs_m", "update", "coi"):
+        C.validate_sga_args(_enabled(sga_selection_locality="rank_local", sga_score=score,
+                                     sga_selection_method="exact"))
     with pytest.raises(ValueError, match="rank_local"):
         C.validate_sga_args(_enabled(sga_selection_locality="rank_local", sga_score="abs_m",
-                                     sga_selection_method="exact"))
+                                     sga_selection_method="exact", sga_backend="torch_pipelined_mask"))
     with pytest.raises(ValueError, match="sga_shadow"):
         C.validate_sga_args(_enabled(sga_selection_locality="rank_local", sga_shadow=True,
                                      sga_selection_method="exact"))

@@ -136,6 +136,61 @@ def test_cfg1_rank_local_index_sparse_allreduce_world2():
     assert res["drift"] <= 2.5 * res["ref_move"], res
 
 
+def _rank_local_score_worker(rank, world, port, score, out):
+    """Rank-local selection by a score that reads the optimizer state: every step's support must be
+    the exact top-k of the registry formula over (gradient + residual), and the replicas stay equal."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from sga_b200 import kernels_torch as KT
+        from sga_b200.plugins.scores import compute_score
+
+        n_buckets, be = 2, 30000
+        C.set_args(_sga_args(sga_score=score, sga_selection_ratio_percent=2.0))
+        model = _FlatModel(n_buckets, be, seed=0)
+        ddp = DataParallel(model, transport="gloo", ddp_config=DDPConfig(average_in_collective=False,
+                                                                         overlap_grad_reduce=False))
+        opt = FlatOptimizer(model.arena, OptimizerConfig(lr=1e-3, clip_grad=1.0))
+        eng = build_engine(quiet=True)
+        eng.log_interval = 0
+        eng.attach(ddp)
+        eng.bind_optimizer(opt)
+        n = n_buckets * be
+        a = model.arena
+        exact = True
+        for step in range(1, 6):
+            g = torch.Generator().manual_seed(31 * step + rank)
+            a.main_grad[:n] += torch.randn(n, generator=g) * 1e-2
+            before = a.main_grad.clone()
+            st = opt.peek_step()
+            sc = compute_score(score, a.main_param, a.exp_avg, a.exp_avg_sq, before, beta1=0.9, beta2=0.95,
+                               eps=1e-8, weight_decay=0.1, bc1=1 - 0.9 ** st, bc2=1 - 0.95 ** st).abs()
+            eng.begin_step(ddp, step)
+            eng.grad_sync(ddp, False)
+            if not eng._step_full:
+                for b in a.buckets:
+                    k = eng._k_for_bucket(b.numel)
+                    ref = KT.topk_rank_local(sc[b.start:b.end], k).bool()
+                    sent = (before[b.start:b.end] != 0) & (a.main_grad[b.start:b.end] == 0)
+                    exact &= bool(torch.equal(sent, ref))
+            eng.optimizer_step(opt, [ddp], step)
+        w = a.main_param.clone()
+        gathered = [torch.empty_like(w) for _ in range(world)]
+        dist.all_gather(gathered, w)
+        if rank == 0:
+            out.put(dict(exact=exact, replicas_equal=all(torch.equal(gathered[0], x) for x in gathered)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(600)
+@pytest.mark.parametrize("score", ["abs_m", "update", "coi"])
+def test_rank_local_scores_world2(score):
+    res = _spawn(_rank_local_score_worker, 2, score)
+    assert res["exact"], "the support is not the exact top-k of the score"
+    assert res["replicas_equal"]
+
+
 def _shared_worker(rank, world, port, backend_name, out):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)

@@ -254,52 +254,114 @@ def _channel():
     return pool, PeerChannel(pool)
 
 
-@pytest.mark.parametrize("n,k", [(4096, 41), (100000, 1000), ((1 << 20) + 13, 10486), (5000, 5000), (777, 1)])
-def test_bucket_index_sync_single_rank(n, k):
+def _check_index_sync(acc0, k, score=None, score_abs=None, scale=0.5, reps=2):
+    """One rank: selection, payload, residual write-back, staging buffer and norm of the fused
+    rank-local chain against the PyTorch oracle (``score_abs``: |score| per coordinate)."""
+    import numpy as np
+
     from sga_b200.parallel import p2p
 
     KT = _kt()
+    n = acc0.numel()
     pool, ch = _channel()
     try:
-        torch.manual_seed(n)
-        acc = torch.randn(n, device=DEV) * 1e-3
-        acc[::97] = 0.5  # many exact ties at the top
-        ref_mask = KT.topk_exact_flat(acc.abs().cpu(), k).to(DEV)
+        sa = acc0.abs() if score_abs is None else score_abs
+        ref_mask = KT.topk_rank_local(sa, k)
         ref_idx = KT.compact_mask_idx(ref_mask)
-        slots = pool.alloc(8 * k)
+        ksel = ref_idx.numel()
+        slots = p2p.IndexSyncSlots(pool, k, n)
         comm = torch.zeros(n, device=DEV)
-        touched = torch.empty((n + 31) // 32, dtype=torch.int32, device=DEV)
         sq = torch.zeros(1, device=DEV)
-        scratch = p2p.IndexSyncScratch(DEV)
-        a0 = acc.clone()
-        for rep in range(2):  # second launch checks the zero-on-exit scratch invariant
-            acc.copy_(a0)
+        scratch = p2p.IndexSyncScratch(DEV, n)
+        acc = acc0.clone()
+        for rep in range(reps):  # the second launch checks what the first left in the scratch
+            acc.copy_(acc0)
             comm.zero_()
-            p2p.bucket_index_sync_(ch, scratch, acc, k, slots=slots, kcap=k, comm=comm, touched=touched, scale=0.5,
-                                   sumsq_out=sq)
+            p2p.bucket_index_sync_(ch, scratch, acc, k, slots=slots, comm=comm, scale=scale, sumsq_out=sq,
+                                   score=score)
             ch.check()
-            pairs = slots.view(torch.int32, 0, 2 * k).view(k, 2)
-            assert torch.equal(pairs[:, 0], ref_idx), "selected indices differ from exact top-k"
-            vals = pairs[:, 1].contiguous().view(torch.float32)
-            assert torch.equal(vals, a0[ref_idx.long()])
-            exp_acc = torch.where(ref_mask.bool(), torch.zeros_like(a0), a0)
+            assert int(scratch.result[3].item()) == ksel
+            pairs = slots.pairs(0, ksel)
+            order = torch.argsort(pairs[:, 0])
+            assert torch.equal(pairs[order, 0], ref_idx), "selected indices differ from exact top-k"
+            vals = pairs[order, 1].contiguous().view(torch.float32)
+            assert torch.equal(vals, acc0[ref_idx.long()])
+            exp_acc = torch.where(ref_mask.bool(), torch.zeros_like(acc0), acc0)
             assert torch.equal(acc, exp_acc), "residual write-back differs"
-            exp_comm = torch.where(ref_mask.bool(), a0 * 0.5, torch.zeros_like(a0))
+            exp_comm = torch.where(ref_mask.bool(), acc0 * scale, torch.zeros_like(acc0))
             assert torch.equal(comm, exp_comm)
             assert abs(sq.item() - (exp_comm.double() ** 2).sum().item()) <= 1e-4 * max(sq.item(), 1e-30)
-            assert int(scratch.result[3].item()) == k
-        # select-only mode writes the bit mask
-        acc.copy_(a0)
-        p2p.bucket_index_sync_(ch, scratch, acc, k, slots=None, kcap=0, touched=touched, select_only=True)
+        # select-only mode writes the bit mask and leaves the bucket alone
+        acc.copy_(acc0)
+        bits = torch.full(((n + 31) // 32,), -1, dtype=torch.int32, device=DEV)
+        p2p.bucket_index_sync_(ch, scratch, acc, k, bits=bits, select_only=True, score=score)
         ch.check()
-        bits = touched.cpu().numpy().view("uint32")
-        import numpy as np
-
-        un = np.unpackbits(bits.view("uint8"), bitorder="little")[:n]
+        un = np.unpackbits(bits.cpu().numpy().view("uint8"), bitorder="little")[:n]
         assert np.array_equal(un, ref_mask.cpu().numpy())
-        assert torch.equal(acc, a0)
+        assert torch.equal(acc, acc0)
+        return scratch
     finally:
         pool.close()
+
+
+@pytest.mark.parametrize("n,k", [(4096, 41), (100000, 1000), ((1 << 20) + 13, 10486), (5000, 5000), (777, 1),
+                                 (3 * (1 << 20) + 77, 31458)])
+def test_bucket_index_sync_single_rank(n, k):
+    torch.manual_seed(n)
+    acc = torch.randn(n, device=DEV) * 1e-3
+    acc[::97] = 0.5  # many exact ties at the top: the tie cut by index decides
+    _check_index_sync(acc, k)
+
+
+def test_bucket_index_sync_degenerate_inputs():
+    n = (1 << 21) + 5
+    torch.manual_seed(3)
+    # all zeros: nothing is selected
+    _check_index_sync(torch.zeros(n, device=DEV), 2000, reps=1)
+    # fewer non-zero coordinates than k: exactly those
+    acc = torch.zeros(n, device=DEV)
+    acc[torch.randperm(n, device=DEV)[:700]] = torch.randn(700, device=DEV)
+    _check_index_sync(acc, 2000, reps=1)
+    # one magnitude everywhere: the k lowest indices
+    _check_index_sync(torch.full((n,), -0.125, device=DEV), 3000, reps=1)
+    # the hashed 1/64 sample sees only large values (they sit exactly where it looks) and puts the
+    # bound among them, but there are fewer of them than k: the second filter pass over every
+    # non-zero element must take over
+    acc = torch.randn(n, device=DEV) * 1e-6
+    g = torch.arange((n // 4 + 63) // 64, device=DEV, dtype=torch.int64)
+    h = ((g * 2654435761) & 0xFFFFFFFF) >> 26
+    base = ((g << 6) + h) * 4
+    base = base[base + 4 <= n]
+    for j in range(4):
+        acc[base + j] = 1.0 + torch.rand(base.numel(), device=DEV)
+    scratch = _check_index_sync(acc, 100000, reps=1)
+    assert int(scratch.state[1].item()) == 1, "the fallback pass did not run"
+
+
+@pytest.mark.parametrize("name", ["update", "abs_m", "coi"])
+@pytest.mark.parametrize("adams", [False, True])
+def test_bucket_index_sync_scores(name, adams):
+    from sga_b200.parallel import p2p
+    from sga_b200.plugins.scores import compute_score
+
+    n = (1 << 21) + 40
+    torch.manual_seed(11)
+    acc = torch.randn(n, device=DEV) * 1e-3
+    w = torch.randn(n, device=DEV) * 0.02
+    m = torch.randn(n, device=DEV) * 1e-4
+    v = torch.rand(n, device=DEV) * 1e-7
+    starts = [0, 400000, 400004, 1500000, n]
+    wds = [0.1, 0.0, 0.1, 0.0]
+    beta1, beta2, eps, step = 0.9, 0.95, 1e-8, 7
+    inp = p2p.ScoreInputs(name, w=w, m=m, v=v, beta1=beta1, beta2=beta2, eps=eps, step=step, adams=adams,
+                          span_start=torch.tensor(starts, dtype=torch.int32, device=DEV),
+                          span_wd=torch.tensor(wds, dtype=torch.float32, device=DEV))
+    sa = torch.empty_like(acc)
+    for (s, e), wd in zip(zip(starts[:-1], starts[1:]), wds):
+        sa[s:e] = compute_score(name, w[s:e], m[s:e], v[s:e], acc[s:e], beta1=beta1, beta2=beta2, eps=eps,
+                                weight_decay=wd, bc1=inp.bc1, bc2=inp.bc2,
+                                optimizer="adams" if adams else "adamw").abs()
+    _check_index_sync(acc, 20000, score=inp, score_abs=sa, reps=1)
 
 
 def test_p2p_allreduce_and_mask_union_single_rank():
