@@ -127,6 +127,12 @@ def main() -> int:
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel size (with sequence-parallel activations)")
     ap.add_argument("--tp-comm", type=str, default="auto", choices=("auto", "fused", "library"))
     ap.add_argument("--pp", type=int, default=1, help="pipeline stages (untied embeddings; 1F1B over NCCL p2p)")
+    ap.add_argument("--bucket-elems", type=int, default=None,
+                    help="gradient bucket size in elements (default: 128 Mi for the rank-local index mode, whose "
+                         "per-bucket chain of kernels has a fixed cost; the trainer's 16 Mi otherwise)")
+    ap.add_argument("--sga-score", type=str, default="abs_g", choices=("abs_g", "abs_m", "update", "coi"))
+    ap.add_argument("--sga-checks", action="store_true", help="leave the engine's cross-rank checks at their defaults")
+    ap.add_argument("--no-exposed", action="store_true", help="skip the exposed-synchronisation measurement")
     ns = ap.parse_args()
     if ns.impl == "reference":
         return _reference_arm(ns)
@@ -151,10 +157,13 @@ def main() -> int:
     if ns.pp > 1:
         over.update(pipeline_model_parallel_size=ns.pp, untie_embeddings_and_output_weights=True)
     if ns.mode == "sga" and ns.sga_backend == "index":
-        over.update(sga_enabled=True, sga_score="abs_g", sga_selection="topk", sga_selection_method="exact",
+        over.update(sga_enabled=True, sga_score=ns.sga_score, sga_selection="topk", sga_selection_method="exact",
                     sga_selection_ratio_percent=ns.ratio_percent, sga_backend="torch_pipelined_index",
                     sga_optimizer="adamw", sga_selection_locality="rank_local",
-                    sga_cycle_period=ns.cycle_period or 0, sga_cycle_start_iter=0, sga_checks=False)
+                    sga_cycle_period=ns.cycle_period or 0, sga_cycle_start_iter=0,
+                    sga_bucket_elems=ns.bucket_elems or (128 << 20))
+        if not ns.sga_checks:
+            over.update(sga_checks=False)
     elif ns.mode == "sga":
         over.update(sga_enabled=True, sga_score="abs_g", sga_selection="topk", sga_selection_method="histogram",
                     sga_selection_histogram_mode="balanced", sga_selection_ratio_percent=ns.ratio_percent,
@@ -162,6 +171,8 @@ def main() -> int:
                     sga_cycle_start_iter=0, sga_checks=False)
     elif ns.mode == "nccl_baseline":
         over.update(transport="nccl", dense_mode="allreduce")
+    if ns.bucket_elems and "sga_bucket_elems" not in over:
+        over["sga_bucket_elems"] = ns.bucket_elems
     args = default_args(**over)
     tr = Trainer(args, quiet=True)
     rank, world = tr.rank, tr.world
@@ -257,6 +268,31 @@ def main() -> int:
         grad_sync["frac_of_roofline"] = bound * 1e3 / max(grad_sync["ms_per_step"], 1e-9)
         grad_sync["roofline"] = "per bucket max(3 x 4 B x n / measured HBM, (W-1) x k x 8 B / 770 GB/s)"
 
+    # ---- exposed synchronisation: step time minus the same step with every bucket's sync skipped.
+    # Runs last: the skipped steps feed the optimizer nothing, so the weights after them mean nothing.
+    if grad_sync is not None and not ns.no_exposed:
+        def _timed_steps(n, first):
+            barrier()
+            e0.record()
+            for i in range(n):
+                tr.train_step(tr.host_batch(first + i))
+            e1.record()
+            barrier()
+            t = torch.tensor([e0.elapsed_time(e1) / n], dtype=torch.float64, device=dev)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+
+        n_exp = 2
+        with_sync = _timed_steps(n_exp, step_id + K + 2)
+        tr.ddp.null_sync = True
+        without = _timed_steps(n_exp, step_id + K + 4)
+        tr.ddp.null_sync = False
+        grad_sync["exposed_ms_per_step"] = with_sync - without
+        grad_sync["exposed_what"] = ("ms per step with the buckets synchronised minus ms per step with every bucket's "
+                                     "synchronisation skipped (%d + %d untimed-region steps, host-fed batches, max "
+                                     "over ranks); differences below the step-to-step jitter read as zero" % (n_exp, n_exp))
+
     tokens = tr.tokens_per_step() * K
     value = tokens / (ms_total / 1e3)
     baseline = None
@@ -275,12 +311,13 @@ def main() -> int:
         "data": "synthetic uniform token ids (seed 1234), random-init weights N(0, 0.02^2)",
         "config": {"model": tr.cfg.name, "global_batch": args.global_batch_size, "seq_len": tr.cfg.seq_len,
                    "micro_batch": args.micro_batch_size, "parallelism": par, "mode": ns.mode,
-                   "sga": (("score=|g+residual|, per-bucket exact top-%g%%, index backend, residual-aware AdamW"
-                            % ns.ratio_percent) if ns.sga_backend == "index" else
+                   "sga": (("score=%s, per-bucket exact top-%g%%, index backend, residual-aware AdamW"
+                            % ("|g+residual|" if ns.sga_score == "abs_g" else ns.sga_score, ns.ratio_percent)) if ns.sga_backend == "index" else
                            ("score=|g+residual|, shared support top-%g%% (balanced histogram), mask backend, "
                             "dense flush every %d steps, residual-aware AdamW"
                             % (ns.ratio_percent, ns.cycle_period or 4))) if ns.mode == "sga" else None,
-                   "transport": tr.ddp.transport,
+                   "transport": tr.ddp.transport, "bucket_elems": int(getattr(args, "sga_bucket_elems", 0)),
+                   "sharded_optimizer_step": bool(tr.sharded_state),
                    "l2": "inputs larger than L2 (weights %.1f GB, grads %.1f GB per rank)" % (
                        2e-9 * tr.model.arena.numel, 4e-9 * tr.model.arena.numel),
                    "params": tr.cfg.num_params()},

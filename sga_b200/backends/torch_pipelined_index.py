@@ -26,6 +26,8 @@ Contract and knobs follow ``sga/backends/torch_pipelined_index.py:103-520``.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -41,6 +43,9 @@ def _ops(t):
 
         return K
     return KT
+
+
+_DEBUG_SYNC = os.environ.get("SGA_ISYNC_DEBUG", "0") == "1"
 
 
 def _score_abs(grad, score):
@@ -299,6 +304,13 @@ class TorchPipelinedIndexBackend:
             p2p.bucket_index_sync_(ch, self._scratch, grad, k, slots=self._slots[ci], comm=comm_view,
                                    scale=1.0 / ddp.world, sumsq_out=self.sumsq, accumulate=True,
                                    score=score, max_ctas=ddp.ddp_config.comm_max_ctas)
+            if _DEBUG_SYNC:
+                # debugging aid (SGA_ISYNC_DEBUG=1): stop at the first bucket whose chain reports an error
+                torch.cuda.synchronize()
+                code = int(ch.err.item())
+                if code:
+                    raise RuntimeError(f"index sync of bucket {bs.bucket_id} (n={n}, k={k}) set status {code}; "
+                                       f"state words {self._scratch.state[:16].tolist()}")
             return
         # library / CPU path: same arithmetic, rank-ordered
         mask = KT.topk_rank_local(_score_abs(grad, score), k)
@@ -317,5 +329,17 @@ class TorchPipelinedIndexBackend:
             comm_view.index_add_(0, ri.long(), rv * scale)
 
     def configure_rank_local(self, max_bucket_elems: int, max_k: int) -> None:
+        """Sizes of the largest bucket and payload; the receive areas of both channels and the work
+        memory of the top-k chain are allocated here, at attach, so that no step allocates."""
         self._max_bucket = int(max_bucket_elems)
         self._kcap = int(max_k)
+        ddp = self.ddp
+        if ddp is not None and ddp.channels and ddp.device.type == "cuda":
+            from ..parallel import p2p
+
+            for ci in range(len(ddp.channels)):
+                if ci not in self._slots:
+                    self._slots[ci] = p2p.IndexSyncSlots(ddp.pool, self._kcap, self._max_bucket)
+            if self._scratch is None:
+                self._scratch = p2p.IndexSyncScratch(ddp.device, self._max_bucket)
+            torch.cuda.synchronize(ddp.device)

@@ -5,12 +5,17 @@
 // The bucket is read from HBM once. A 1/64 sample (one hashed 16-byte group in
 // every 1 KiB) gives a lower bound of the k-th largest key with a six-sigma
 // margin; one streaming pass keeps every element at or above the bound as a
-// candidate (about 1.1 k of them). Everything that makes the selection exact
-// -- a two-digit radix select over the candidates' 31-bit keys, the index-order
-// tie cut, the per-segment counts and their scan -- touches the candidates
-// only, which stay in L2. If the sample bound turns out too high (fewer than k
-// candidates) a second pass takes every non-zero element, so the result is
-// exact for any input.
+// candidate (1.1 to 1.6 k of them) and counts the candidates' first radix
+// digit (12 bits) on the way. Everything else that makes the selection exact
+// -- the remaining 19 key bits in one pass (11-bit digit + a 512 K-bin fine
+// histogram), the index-order tie cut, the per-segment counts and their scan
+// -- touches the candidates only. If the sample bound turns out too high
+// (fewer than k candidates) a second pass takes every non-zero element, so the
+// result is exact for any input.
+//
+// Chain per bucket: sample, filter, filter (level 1, normally returns at once),
+// digit, count, emit, reduce; each is launched as a programmatic dependent of
+// its predecessor, so its launch latency hides behind the predecessor's tail.
 //
 // Every kernel here is an ordinary launch with at most 20 KB of shared memory
 // and 256 threads per CTA, so its CTAs fit beside the persistent GEMM CTAs of
@@ -38,6 +43,7 @@
 // round operation by operation like their PyTorch reference.
 #include "common.cuh"
 #include "peer.cuh"
+#include <stdlib.h>
 
 namespace sga {
 
@@ -52,6 +58,7 @@ constexpr int IS_REP = 8;             // replicas of the two coarse global histo
 // Word offsets inside the state block (unsigned[64], zeroed by the host before each bucket).
 enum {
   ST_TLO = 0, ST_LEVEL, ST_C, ST_SKIP, ST_BA, ST_ABOVE, ST_T, ST_NEED, ST_EQ, ST_ICUT, ST_NSEL, ST_SAMPLES,
+  ST_TOP, ST_INVLOW,  // first-digit bins in use: highest bin + 1, IS_ABINS - lowest bin (0 = none)
   ST_TICKET0 = 16  // tickets: one word per kernel of the chain
 };
 
@@ -94,6 +101,14 @@ struct ISyncArgs {
   unsigned* result;      // [4]: threshold key, ties taken, keys above the threshold, pairs produced
   int level;             // filter pass: 0 = sample bound, 1 = every non-zero element
 };
+
+// Programmatic dependent launch: every kernel of the chain first lets the next one be scheduled
+// (its CTAs then sit in their own wait until this grid has finished and its writes are visible),
+// then waits for its predecessor. Both are no-ops for a launch without the attribute.
+__device__ __forceinline__ void chain_enter() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
 
 __device__ __forceinline__ unsigned key_bits(float x) { return __float_as_uint(x) & 0x7FFFFFFFu; }
 __device__ __forceinline__ unsigned ldv(const unsigned* p) { return *reinterpret_cast<const volatile unsigned*>(p); }
@@ -143,35 +158,59 @@ __device__ __forceinline__ unsigned block_excl_scan256(unsigned v, unsigned* sh,
   return r;
 }
 
-// Over the sum of `rep` replicas hist[r * nb + i] (global, nb a multiple of 256): the largest bin b
-// whose suffix count (bins >= b) reaches `want`, and the count in bins above it. Returns false when
-// the whole histogram holds fewer than `want`. One CTA; result uniform over its threads.
-__device__ __forceinline__ bool find_suffix_bin(const unsigned* hist, int nb, int rep, unsigned want, unsigned* sh,
-                                                unsigned& bin, unsigned& above) {
+// Over the sum of `rep` replicas hist[r * nb + i] (global): the largest bin b <= top whose suffix
+// count (bins b..top) reaches `want`, and the count in the bins above it. Scans downwards from
+// `top`, 256 bins per round (one per thread, every replica's load in flight at once), and stops at
+// the crossing, so a crossing near the top costs one round. Returns false when bins low..top hold
+// fewer than `want`. One CTA; result uniform over its threads.
+__device__ __forceinline__ bool find_suffix_bin(const unsigned* hist, int nb, int rep, unsigned want, int top, int low,
+                                                unsigned* sh, unsigned& bin, unsigned& above) {
   __shared__ unsigned s_res[2];
-  const int per = nb / IS_THREADS;
-  const int hi = nb - threadIdx.x * per;  // thread t owns [hi - per, hi): descending ownership
-  unsigned mysum = 0;
-  for (int r = 0; r < rep; ++r)
-    for (int i = hi - per; i < hi; ++i) mysum += __ldcg(hist + r * nb + i);
-  unsigned total;
-  const unsigned before = block_excl_scan256(mysum, sh, total);
   if (threadIdx.x == 0) { s_res[0] = 0xFFFFFFFFu; s_res[1] = 0; }
-  __syncthreads();
-  if (before < want && before + mysum >= want) {
-    unsigned run = before;
-    for (int i = hi - 1; i >= hi - per; --i) {
-      unsigned h = 0;
+  unsigned run = 0;
+  for (int hi = top; hi >= low; hi -= IS_THREADS) {
+    const int i = hi - (int)threadIdx.x;
+    unsigned h = 0;
+    if (i >= low)
       for (int r = 0; r < rep; ++r) h += __ldcg(hist + r * nb + i);
-      if (run + h >= want) { s_res[0] = (unsigned)i; s_res[1] = run; break; }
-      run += h;
-    }
+    unsigned total;
+    const unsigned before = run + block_excl_scan256(h, sh, total);
+    if (before < want && before + h >= want) { s_res[0] = (unsigned)i; s_res[1] = before; }
+    __syncthreads();
+    if (s_res[0] != 0xFFFFFFFFu) break;
+    run += total;
   }
   __syncthreads();
   bin = s_res[0];
   above = s_res[1];
   __syncthreads();
   return bin != 0xFFFFFFFFu;
+}
+
+// Flush a CTA's shared first-digit histogram into its global replica and widen the global window
+// of bins in use.
+__device__ __forceinline__ void flush_first_digit(const unsigned* sh_hist, unsigned* replica, unsigned* state) {
+  __shared__ unsigned s_win[2];
+  if (threadIdx.x == 0) { s_win[0] = 0; s_win[1] = 0; }
+  __syncthreads();
+  unsigned top = 0, invlow = 0;
+  for (int i = threadIdx.x; i < IS_ABINS; i += IS_THREADS) {
+    const unsigned c = sh_hist[i];
+    if (c) {
+      atomicAdd(&replica[i], c);
+      top = max(top, (unsigned)i + 1u);
+      invlow = max(invlow, (unsigned)(IS_ABINS - i));
+    }
+  }
+  if (top) { atomicMax(&s_win[0], top); atomicMax(&s_win[1], invlow); }
+  __syncthreads();
+  if (threadIdx.x == 0 && s_win[0]) { atomicMax(state + ST_TOP, s_win[0]); atomicMax(state + ST_INVLOW, s_win[1]); }
+}
+
+// Zero bins low..top of every replica (the last CTA, after its scan).
+__device__ __forceinline__ void zero_window(unsigned* hist, int nb, int rep, int top, int low) {
+  const int w = top - low + 1;
+  for (int i = threadIdx.x; i < w * rep; i += IS_THREADS) hist[(i / w) * nb + low + (i % w)] = 0;
 }
 
 __device__ __forceinline__ int load4z(const float* __restrict__ p, long long i, long long limit, float (&v)[4]) {
@@ -245,6 +284,7 @@ __device__ __forceinline__ void keys4(const ISyncArgs& a, long long i, long long
 // histogram of the digit pass that follows.
 template <int SCORE>
 __global__ void __launch_bounds__(IS_THREADS) isync_sample_kernel(const ISyncArgs a) {
+  chain_enter();
   __shared__ unsigned sh_hist[IS_ABINS];
   __shared__ unsigned sh_scan[8];
   for (int i = threadIdx.x; i < IS_ABINS; i += IS_THREADS) sh_hist[i] = 0;
@@ -276,28 +316,32 @@ __global__ void __launch_bounds__(IS_THREADS) isync_sample_kernel(const ISyncArg
         if (j < lim[u]) atomicAdd(&sh_hist[key[u][j] >> 19], 1u);
   }
   __syncthreads();
-  unsigned* mine = a.histA + (blockIdx.x % IS_REP) * IS_ABINS;
-  for (int i = threadIdx.x; i < IS_ABINS; i += IS_THREADS) {
-    const unsigned c = sh_hist[i];
-    if (c) atomicAdd(&mine[i], c);
+  flush_first_digit(sh_hist, a.histA + (blockIdx.x % IS_REP) * IS_ABINS, a.state);
+  {
+    unsigned mine = 0;  // elements this CTA sampled
+    for (int i = threadIdx.x; i < IS_ABINS; i += IS_THREADS) mine += sh_hist[i];
+    unsigned tot;
+    block_excl_scan256(mine, sh_scan, tot);
+    if (threadIdx.x == 0 && tot) atomicAdd(a.state + ST_SAMPLES, tot);
   }
   if (!last_cta(a.state + ST_TICKET0 + 0)) return;
-  unsigned part = 0;
-  for (int i = threadIdx.x; i < IS_REP * IS_ABINS; i += IS_THREADS) part += __ldcg(a.histA + i);
-  unsigned samples;
-  block_excl_scan256(part, sh_scan, samples);
+  const unsigned samples = ldv(a.state + ST_SAMPLES);
   unsigned want = (unsigned)a.k;
   if (a.gshift) {
     const float ks = (float)a.k * ((float)samples / (float)a.n);
     want = (unsigned)ceilf(ks + 6.0f * sqrtf(ks) + 16.0f);
   }
-  unsigned bin, above;
-  const bool found = find_suffix_bin(a.histA, IS_ABINS, IS_REP, want, sh_scan, bin, above);
-  for (int i = threadIdx.x; i < IS_REP * IS_ABINS / 4; i += IS_THREADS)
-    reinterpret_cast<uint4*>(a.histA)[i] = make_uint4(0, 0, 0, 0);
+  const int top = (int)ldv(a.state + ST_TOP) - 1, low = IS_ABINS - (int)ldv(a.state + ST_INVLOW);
+  unsigned bin = 0, above = 0;
+  bool found = false;
+  if (top >= 0) {
+    found = find_suffix_bin(a.histA, IS_ABINS, IS_REP, want, top, low, sh_scan, bin, above);
+    zero_window(a.histA, IS_ABINS, IS_REP, top, low);
+  }
   if (threadIdx.x == 0) {
     a.state[ST_TLO] = found ? (bin << 19) : 0u;
-    a.state[ST_SAMPLES] = samples;
+    a.state[ST_TOP] = 0u;
+    a.state[ST_INVLOW] = 0u;
   }
 }
 
@@ -312,6 +356,7 @@ __global__ void __launch_bounds__(IS_THREADS) isync_sample_kernel(const ISyncArg
 // arms level 1 (every non-zero key), which is the next launch and normally returns at once.
 template <int SCORE>
 __global__ void __launch_bounds__(IS_THREADS) isync_filter_kernel(const ISyncArgs a) {
+  chain_enter();
   __shared__ unsigned sh_hist[IS_ABINS];
   __shared__ unsigned sh_cnt[IS_THREADS / 32];
   if (a.level == 1 && ldv(a.state + ST_LEVEL) != 1u) return;
@@ -320,7 +365,7 @@ __global__ void __launch_bounds__(IS_THREADS) isync_filter_kernel(const ISyncArg
   for (int i = threadIdx.x; i < IS_ABINS; i += IS_THREADS) sh_hist[i] = 0;
   __syncthreads();
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
-  const unsigned lt = (1u << lane) - 1u;
+  constexpr int U = SCORE == 1 ? 8 : 4;  // 16-byte loads in flight per lane and array
   unsigned warp_total = 0;
   for (long long seg = (long long)blockIdx.x * (IS_THREADS / 32) + wib; seg < a.nseg;
        seg += (long long)gridDim.x * (IS_THREADS / 32)) {
@@ -330,29 +375,46 @@ __global__ void __launch_bounds__(IS_THREADS) isync_filter_kernel(const ISyncArg
     unsigned* ck = a.cand_key + s0;
     float* cv = a.cand_val + s0;
     unsigned cnt = 0;
-    for (long long base = s0; base < s1; base += 512) {
-      float g[4][4];
-      unsigned key[4][4];
+    for (long long base = s0; base < s1; base += U * 128) {
+      float g[U][4];
+      unsigned key[U][4];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) keys4<SCORE>(a, base + u * 128 + lane * 4, s1, g[u], key[u]);
+      for (int u = 0; u < U; ++u) {
+        if (SCORE == 1) load4z(a.acc, base + u * 128 + lane * 4, s1, g[u]);  // the key is the value's own bits
+        else keys4<SCORE>(a, base + u * 128 + lane * 4, s1, g[u], key[u]);
+      }
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const bool f0 = key[u][0] >= tlo, f1 = key[u][1] >= tlo, f2 = key[u][2] >= tlo, f3 = key[u][3] >= tlo;
-        if (__ballot_sync(0xffffffffu, f0 | f1 | f2 | f3) == 0u) continue;
-        const int i0 = (int)(base + u * 128 + lane * 4);
-        const bool f[4] = {f0, f1, f2, f3};
+      for (int u = 0; u < U; ++u) {
+        if (SCORE == 1) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const unsigned bal = __ballot_sync(0xffffffffu, f[j]);
-          if (f[j]) {
-            const unsigned pos = cnt + __popc(bal & lt);
-            ci[pos] = i0 + j;
-            ck[pos] = key[u][j];
-            cv[pos] = g[u][j];
-            atomicAdd(&sh_hist[key[u][j] >> 19], 1u);
-          }
-          cnt += __popc(bal);
+          for (int j = 0; j < 4; ++j) key[u][j] = key_bits(g[u][j]);
         }
+        const bool f0 = key[u][0] >= tlo, f1 = key[u][1] >= tlo, f2 = key[u][2] >= tlo, f3 = key[u][3] >= tlo;
+        const int c = (int)f0 + (int)f1 + (int)f2 + (int)f3;
+        const unsigned bal = __ballot_sync(0xffffffffu, c != 0);
+        if (bal == 0u) continue;
+        // about two of a warp's 128 elements qualify: a warp scan of the per-lane counts places them
+        int incl = c;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int y = __shfl_up_sync(0xffffffffu, incl, o);
+          if (lane >= o) incl += y;
+        }
+        if (c) {
+          unsigned pos = cnt + (unsigned)(incl - c);
+          const int i0 = (int)(base + u * 128 + lane * 4);
+          const bool f[4] = {f0, f1, f2, f3};
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (f[j]) {
+              ci[pos] = i0 + j;
+              ck[pos] = key[u][j];
+              cv[pos] = g[u][j];
+              atomicAdd(&sh_hist[key[u][j] >> 19], 1u);
+              ++pos;
+            }
+        }
+        cnt += (unsigned)__shfl_sync(0xffffffffu, incl, 31);
       }
     }
     if (lane == 0) a.segcnt[seg] = (int)cnt;
@@ -365,19 +427,18 @@ __global__ void __launch_bounds__(IS_THREADS) isync_filter_kernel(const ISyncArg
     for (int i = 0; i < IS_THREADS / 32; ++i) t += sh_cnt[i];
     if (t) atomicAdd(a.state + ST_C, t);
   }
-  unsigned* mine = a.histA + (blockIdx.x % IS_REP) * IS_ABINS;
-  for (int i = threadIdx.x; i < IS_ABINS; i += IS_THREADS) {
-    const unsigned c = sh_hist[i];
-    if (c) atomicAdd(&mine[i], c);
-  }
+  flush_first_digit(sh_hist, a.histA + (blockIdx.x % IS_REP) * IS_ABINS, a.state);
   if (!last_cta(a.state + ST_TICKET0 + 1 + a.level)) return;
   const unsigned C = ldv(a.state + ST_C), k = (unsigned)a.k;
   const bool retry = a.level == 0 && C < k && tlo > 1u;
+  const int top = (int)ldv(a.state + ST_TOP) - 1, low = IS_ABINS - (int)ldv(a.state + ST_INVLOW);
   unsigned bin = 0, above = 0;
   bool found = false;
-  if (!retry && C > k) found = find_suffix_bin(a.histA, IS_ABINS, IS_REP, k, sh_cnt, bin, above);
-  for (int i = threadIdx.x; i < IS_REP * IS_ABINS / 4; i += IS_THREADS)
-    reinterpret_cast<uint4*>(a.histA)[i] = make_uint4(0, 0, 0, 0);
+  if (top >= 0) {
+    if (!retry && C > k) found = find_suffix_bin(a.histA, IS_ABINS, IS_REP, k, top, low, sh_cnt, bin, above);
+    zero_window(a.histA, IS_ABINS, IS_REP, top, low);
+  }
+  if (threadIdx.x == 0) { a.state[ST_TOP] = 0u; a.state[ST_INVLOW] = 0u; }
   if (threadIdx.x != 0) return;
   if (retry) {
     a.state[ST_LEVEL] = 1u;  // the sample bound was too high: take every non-zero element
@@ -400,6 +461,7 @@ __global__ void __launch_bounds__(IS_THREADS) isync_filter_kernel(const ISyncArg
 // finds the 11-bit bin, then reads the 256 fine bins under it: the exact k-th key T, the number
 // of keys above it and the number of ties at T to take.
 __global__ void __launch_bounds__(IS_THREADS) isync_digit_kernel(const ISyncArgs a) {
+  chain_enter();
   __shared__ unsigned sh_scan[8];
   if (ldv(a.state + ST_SKIP) || ldv(a.state + ST_C) < (unsigned)a.k) return;
   const unsigned bA = ldv(a.state + ST_BA);
@@ -430,7 +492,7 @@ __global__ void __launch_bounds__(IS_THREADS) isync_digit_kernel(const ISyncArgs
   if (!last_cta(a.state + ST_TICKET0 + 3)) return;
   const unsigned k = (unsigned)a.k, aboveA = ldv(a.state + ST_ABOVE);
   unsigned bB, aboveB;
-  if (!find_suffix_bin(a.histB, IS_BBINS, IS_REP, k - aboveA, sh_scan, bB, aboveB)) {
+  if (!find_suffix_bin(a.histB, IS_BBINS, IS_REP, k - aboveA, IS_BBINS - 1, 0, sh_scan, bB, aboveB)) {
     if (threadIdx.x == 0) atomicOr(a.c.err, SGA_ERR_BOUNDS);
     bB = 0; aboveB = 0;
   }
@@ -457,14 +519,17 @@ __device__ __forceinline__ bool is_selected(unsigned key, int idx, unsigned T, u
 }
 
 // ------------------------------------------------------------------- count
-// Keys above T and ties at T per segment. The last CTA takes the ties in index order (segments
-// are in index order; inside the one segment that is cut, a bitmap finds the index of the last
-// tie taken) and turns the per-segment counts into the payload's offset table.
+// Selected per segment, then (last CTA) the payload's offset table. When every tie at T is taken
+// (nearly always) a segment's count is final at once. Otherwise the ties are taken in index order:
+// segments are in index order, and inside the one segment that is cut a bitmap of its ties gives
+// the index of the last tie taken.
 __global__ void __launch_bounds__(IS_THREADS) isync_count_kernel(const ISyncArgs a) {
+  chain_enter();
   __shared__ unsigned sh_scan[8];
   __shared__ unsigned sh_bm[IS_SEG / 32];
   __shared__ unsigned sh_cut[3];
-  const unsigned T = ldv(a.state + ST_T);
+  const unsigned T = ldv(a.state + ST_T), need = ldv(a.state + ST_NEED), eq_total = ldv(a.state + ST_EQ);
+  const bool all_ties = need >= eq_total;
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
   for (long long seg = (long long)blockIdx.x * (IS_THREADS / 32) + wib; seg < a.nseg;
        seg += (long long)gridDim.x * (IS_THREADS / 32)) {
@@ -481,82 +546,102 @@ __global__ void __launch_bounds__(IS_THREADS) isync_count_kernel(const ISyncArgs
       g += __shfl_xor_sync(0xffffffffu, g, o);
       e += __shfl_xor_sync(0xffffffffu, e, o);
     }
-    if (lane == 0) { a.segsel[seg] = g; a.segeq[seg] = e; }
+    if (lane == 0) {
+      a.segsel[seg] = all_ties ? g + e : g;
+      if (!all_ties) a.segeq[seg] = e;
+    }
   }
   if (!last_cta(a.state + ST_TICKET0 + 4)) return;
-  const unsigned need = ldv(a.state + ST_NEED);
-  const int per = (a.nseg + IS_THREADS - 1) / IS_THREADS;
-  const int lo = min(a.nseg, (int)threadIdx.x * per), hi = min(a.nseg, lo + per);
-  // ties: the segment where the running count of ties passes `need`
-  unsigned myeq = 0;
-  for (int i = lo; i < hi; ++i) myeq += (unsigned)__ldcg(a.segeq + i);
-  unsigned eq_total;
-  const unsigned eq_before = block_excl_scan256(myeq, sh_scan, eq_total);
-  if (threadIdx.x == 0) { sh_cut[0] = 0xFFFFFFFFu; sh_cut[1] = 0; sh_cut[2] = 0x7FFFFFFFu; }
-  __syncthreads();
-  if (need < eq_total && eq_before <= need && eq_before + myeq > need) {
-    unsigned run = eq_before;
+  unsigned icut = 0x7FFFFFFFu;
+  if (!all_ties) {
+    // the segment where the running count of ties passes `need`, and how many of its ties are taken
+    const int per = (a.nseg + IS_THREADS - 1) / IS_THREADS;
+    const int lo = min(a.nseg, (int)threadIdx.x * per), hi = min(a.nseg, lo + per);
+    unsigned myeq = 0;
+    for (int i = lo; i < hi; ++i) myeq += (unsigned)__ldcg(a.segeq + i);
+    unsigned tot;
+    const unsigned eq_before = block_excl_scan256(myeq, sh_scan, tot);
+    if (threadIdx.x == 0) { sh_cut[0] = (unsigned)a.nseg; sh_cut[1] = 0; sh_cut[2] = 0x7FFFFFFFu; }
+    __syncthreads();
+    if (eq_before <= need && eq_before + myeq > need) {
+      unsigned run = eq_before;
+      for (int i = lo; i < hi; ++i) {
+        const unsigned e = (unsigned)__ldcg(a.segeq + i);
+        if (run + e > need) { sh_cut[0] = (unsigned)i; sh_cut[1] = need - run; break; }
+        run += e;
+      }
+    }
+    __syncthreads();
+    const unsigned cut_seg = sh_cut[0], cut_take = sh_cut[1];
+    if (cut_seg < (unsigned)a.nseg) {
+      for (int i = threadIdx.x; i < IS_SEG / 32; i += IS_THREADS) sh_bm[i] = 0;
+      __syncthreads();
+      const long long s0 = (long long)cut_seg * IS_SEG;
+      const int cnt = __ldcg(a.segcnt + cut_seg);
+      for (int j = threadIdx.x; j < cnt; j += IS_THREADS)
+        if (__ldcg(a.cand_key + s0 + j) == T) {
+          const int rel = __ldcg(a.cand_idx + s0 + j) - (int)s0;
+          atomicOr(&sh_bm[rel >> 5], 1u << (rel & 31));
+        }
+      __syncthreads();
+      const unsigned w = sh_bm[threadIdx.x];  // IS_SEG / 32 == IS_THREADS words
+      const unsigned pc = (unsigned)__popc(w);
+      const unsigned pre = block_excl_scan256(pc, sh_scan, tot);
+      if (cut_take == 0) {
+        if (threadIdx.x == 0) sh_cut[2] = (unsigned)(s0 - 1);  // nothing of this segment (need >= 1, so s0 > 0)
+      } else if (pre < cut_take && pre + pc >= cut_take) {
+        unsigned bits = w;
+        for (unsigned r = pre + 1; r < cut_take; ++r) bits &= bits - 1;
+        sh_cut[2] = (unsigned)s0 + threadIdx.x * 32 + (__ffs(bits) - 1);
+      }
+      __syncthreads();
+    }
+    icut = sh_cut[2];
     for (int i = lo; i < hi; ++i) {
       const unsigned e = (unsigned)__ldcg(a.segeq + i);
-      if (run + e > need) { sh_cut[0] = (unsigned)i; sh_cut[1] = need - run; break; }  // take need - run of segment i
-      run += e;
+      const unsigned take = (unsigned)i < cut_seg ? e : ((unsigned)i == cut_seg ? cut_take : 0u);
+      a.segsel[i] = __ldcg(a.segsel + i) + (int)take;
     }
-  }
-  __syncthreads();
-  const unsigned cut_seg = sh_cut[0], cut_take = sh_cut[1];
-  if (cut_seg != 0xFFFFFFFFu) {
-    // bitmap of the cut segment's ties, then the index of its cut_take-th tie (none taken if 0)
-    for (int i = threadIdx.x; i < IS_SEG / 32; i += IS_THREADS) sh_bm[i] = 0;
     __syncthreads();
-    const long long s0 = (long long)cut_seg * IS_SEG;
-    const int cnt = __ldcg(a.segcnt + cut_seg);
-    for (int j = threadIdx.x; j < cnt; j += IS_THREADS)
-      if (__ldcg(a.cand_key + s0 + j) == T) {
-        const int rel = __ldcg(a.cand_idx + s0 + j) - (int)s0;
-        atomicOr(&sh_bm[rel >> 5], 1u << (rel & 31));
+  }
+  // exclusive scan of the per-segment counts, 4096 segments per round, 16 per thread
+  unsigned carry = 0;
+  for (int t0 = 0; t0 < a.nseg; t0 += IS_THREADS * 16) {
+    const int i0 = t0 + (int)threadIdx.x * 16;
+    int v[16];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int i = i0 + q * 4;
+      if (i + 4 <= a.nseg) {
+        *reinterpret_cast<int4*>(v + q * 4) = __ldcg(reinterpret_cast<const int4*>(a.segsel + i));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[q * 4 + j] = i + j < a.nseg ? __ldcg(a.segsel + i + j) : 0;
       }
-    __syncthreads();
-    const unsigned w = sh_bm[threadIdx.x];  // IS_SEG / 32 == IS_THREADS words
-    const unsigned pc = (unsigned)__popc(w);
-    unsigned tot;
-    const unsigned pre = block_excl_scan256(pc, sh_scan, tot);
-    if (cut_take == 0) {
-      if (threadIdx.x == 0) sh_cut[2] = (unsigned)(s0 - 1);  // nothing of this segment (need >= 1, so s0 > 0)
-    } else if (pre < cut_take && pre + pc >= cut_take) {
-      unsigned bits = w;
-      for (unsigned r = pre + 1; r < cut_take; ++r) bits &= bits - 1;
-      sh_cut[2] = (unsigned)s0 + threadIdx.x * 32 + (__ffs(bits) - 1);
     }
-    __syncthreads();
-  }
-  const unsigned icut = sh_cut[2];
-  // selected per segment = keys above T + the ties taken there
-  unsigned mysum = 0;
-  for (int i = lo; i < hi; ++i) {
-    unsigned s = (unsigned)__ldcg(a.segsel + i);
-    const unsigned e = (unsigned)__ldcg(a.segeq + i);
-    if (cut_seg == 0xFFFFFFFFu) s += need >= eq_total ? e : 0u;
-    else s += (unsigned)i < cut_seg ? e : ((unsigned)i == cut_seg ? cut_take : 0u);
-    a.segsel[i] = (int)s;
-    mysum += s;
-  }
-  unsigned total;
-  unsigned run = block_excl_scan256(mysum, sh_scan, total);
-  for (int i = lo; i < hi; ++i) {
-    a.roff[i] = (int)run;
-    run += (unsigned)a.segsel[i];
+    unsigned mysum = 0;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) mysum += (unsigned)v[j];
+    unsigned tot;
+    unsigned run = carry + block_excl_scan256(mysum, sh_scan, tot);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      if (i0 + j < a.nseg) a.roff[i0 + j] = (int)run;
+      run += (unsigned)v[j];
+    }
+    carry += tot;
   }
   if (threadIdx.x == 0) {
-    a.roff[a.nseg] = (int)total;
-    a.state[ST_NSEL] = total;
+    a.roff[a.nseg] = (int)carry;
+    a.state[ST_NSEL] = carry;
     a.state[ST_ICUT] = icut;
     if (a.result) {
       a.result[0] = T;
       a.result[1] = need;
       a.result[2] = ldv(a.state + ST_ABOVE);
-      a.result[3] = total;
+      a.result[3] = carry;
     }
-    if (total > (unsigned)a.kcap && a.kcap > 0) atomicOr(a.c.err, SGA_ERR_CAPACITY);
+    if (carry > (unsigned)a.kcap && a.kcap > 0) atomicOr(a.c.err, SGA_ERR_CAPACITY);
   }
 }
 
@@ -565,6 +650,7 @@ __global__ void __launch_bounds__(IS_THREADS) isync_count_kernel(const ISyncArgs
 // rank's receive area (this rank's own included); zero the selected coordinates of the bucket
 // (what stays is the residual). The last CTA raises this rank's "ready" flag on every peer.
 __global__ void __launch_bounds__(IS_THREADS) isync_emit_kernel(const ISyncArgs a) {
+  chain_enter();
   const PeerCtx& c = a.c;
   if (c.prev_seq > 0) peer_wait(c, 1, c.prev_seq);  // peers are done reading my previous payload
   const unsigned T = ldv(a.state + ST_T), icut = ldv(a.state + ST_ICUT);
@@ -613,6 +699,7 @@ __global__ void __launch_bounds__(IS_THREADS) isync_emit_kernel(const ISyncArgs 
 
 // Select-only form: the selection as a bit mask (zeroed by the host), nothing is exchanged.
 __global__ void __launch_bounds__(IS_THREADS) isync_mask_kernel(const ISyncArgs a) {
+  chain_enter();
   const unsigned T = ldv(a.state + ST_T), icut = ldv(a.state + ST_ICUT);
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
   for (long long seg = (long long)blockIdx.x * (IS_THREADS / 32) + wib; seg < a.nseg;
@@ -632,6 +719,7 @@ __global__ void __launch_bounds__(IS_THREADS) isync_mask_kernel(const ISyncArgs 
 // once, so a rank's pairs need no atomics), then the squared norm over the coordinates touched.
 // The last CTA adds the per-range partials in index order and raises "done" on every peer.
 __global__ void __launch_bounds__(IS_THREADS) isync_reduce_kernel(const ISyncArgs a) {
+  chain_enter();
   __shared__ unsigned sh_bm[IS_SEG_PER_RANGE * IS_SEG / 32];
   __shared__ float red[IS_THREADS];
   const PeerCtx& c = a.c;
@@ -711,14 +799,30 @@ struct SgaISyncDesc {
   int accumulate, zero_selected, mode, max_ctas;
 };
 
+// Launch one kernel of the chain; `dependent` lets it be scheduled while its predecessor (the
+// previous kernel on the stream) is still running.
+static void launch_chain(void (*kern)(const ISyncArgs), int grid, cudaStream_t st, const ISyncArgs& a, bool dependent) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(IS_THREADS);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = dependent ? 1 : 0;
+  cudaLaunchKernelEx(&cfg, kern, a);
+}
+
 template <int SCORE>
-static void launch_select(const ISyncArgs& base, int grid_seg, int grid_sample, cudaStream_t st) {
+static void launch_select(const ISyncArgs& base, int grid_seg, int grid_sample, cudaStream_t st, bool pdl) {
   ISyncArgs a = base;
-  isync_sample_kernel<SCORE><<<grid_sample, IS_THREADS, 0, st>>>(a);
+  launch_chain(isync_sample_kernel<SCORE>, grid_sample, st, a, false);  // follows a memset, not a kernel
   a.level = 0;
-  isync_filter_kernel<SCORE><<<grid_seg, IS_THREADS, 0, st>>>(a);
+  launch_chain(isync_filter_kernel<SCORE>, grid_seg, st, a, pdl);
   a.level = 1;
-  isync_filter_kernel<SCORE><<<grid_seg, IS_THREADS, 0, st>>>(a);
+  launch_chain(isync_filter_kernel<SCORE>, grid_seg, st, a, pdl);
 }
 
 // mode 0: select + exchange + reduce into comm. mode 1: select only, bit mask of the selection
@@ -784,21 +888,22 @@ SGA_API int sga_index_sync(const SgaPeerDesc* d, const SgaISyncDesc* s, void* st
   if (grid_sample > 148) grid_sample = 148;
   if (grid_sample < 1) grid_sample = 1;
   int grid_range = nranges < cap ? nranges : cap;
+  static const bool pdl = [] { const char* e = getenv("SGA_ISYNC_PDL"); return !(e && e[0] == '0'); }();
   cudaMemsetAsync(a.state, 0, 64 * sizeof(unsigned), st);
   if (s->mode == 1) cudaMemsetAsync(a.bits, 0, (size_t)((s->n + 31) / 32) * 4, st);
   switch (s->score) {
-    case 0: launch_select<0>(a, grid_seg, grid_sample, st); break;
-    case 1: launch_select<1>(a, grid_seg, grid_sample, st); break;
-    case 2: launch_select<2>(a, grid_seg, grid_sample, st); break;
-    default: launch_select<3>(a, grid_seg, grid_sample, st); break;
+    case 0: launch_select<0>(a, grid_seg, grid_sample, st, pdl); break;
+    case 1: launch_select<1>(a, grid_seg, grid_sample, st, pdl); break;
+    case 2: launch_select<2>(a, grid_seg, grid_sample, st, pdl); break;
+    default: launch_select<3>(a, grid_seg, grid_sample, st, pdl); break;
   }
-  isync_digit_kernel<<<grid_seg, IS_THREADS, 0, st>>>(a);
-  isync_count_kernel<<<grid_seg, IS_THREADS, 0, st>>>(a);
+  launch_chain(isync_digit_kernel, grid_seg, st, a, pdl);
+  launch_chain(isync_count_kernel, grid_seg, st, a, pdl);
   if (s->mode == 1) {
-    isync_mask_kernel<<<grid_seg, IS_THREADS, 0, st>>>(a);
+    launch_chain(isync_mask_kernel, grid_seg, st, a, pdl);
   } else {
-    isync_emit_kernel<<<grid_seg, IS_THREADS, 0, st>>>(a);
-    isync_reduce_kernel<<<grid_range, IS_THREADS, 0, st>>>(a);
+    launch_chain(isync_emit_kernel, grid_seg, st, a, pdl);
+    launch_chain(isync_reduce_kernel, grid_range, st, a, pdl);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

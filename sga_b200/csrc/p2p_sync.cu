@@ -281,6 +281,10 @@ SGA_API int sga_symm_alloc(long long bytes, void** out) {
     return -(int)e;
   }
   e = cudaMemset(*out, 0, (size_t)bytes);
+  if (e != cudaSuccess) return -(int)e;
+  // The fill runs on the default stream, which non-blocking streams do not wait for: finish it here,
+  // so that no kernel on another stream can write the new buffer before it has been zeroed.
+  e = cudaDeviceSynchronize();
   return e == cudaSuccess ? 0 : -(int)e;
 }
 SGA_API int sga_symm_free(void* p) { return cudaFree(p) == cudaSuccess ? 0 : -1; }

@@ -54,3 +54,5 @@ class OptContext:
     mask_arena: object = None          # uint8 [arena.numel]: active support mask of every bucket
     grad_source: str = "grad"          # 'grad' | 'comm' (rank-local index mode reads the staging arena)
     emit: bool = True                  # full step: write the score into the grad buffer
+    sharded: object = None             # ShardedStep: every rank updates the bucket slices it owns and pushes
+                                       # the bf16 parameters to its peers (None: replicated update)

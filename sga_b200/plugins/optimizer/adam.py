@@ -71,7 +71,24 @@ class _SgaAdamBase:
         eps = g0["eps"]
         coeff = ctx.apply_coeff
         src = arena.comm if ctx.grad_source == "comm" else arena.main_grad
-        if arena.device.type == "cuda":
+        if ctx.sharded is not None:
+            # Every rank holds the same gradient here (the all-reduced bucket on a full step, the
+            # rank-ordered sum of all ranks' pairs on a sparse one), so the update can be cut like the
+            # dense step's: 1 / W of the weights and moments per rank, bf16 copies stored to every peer.
+            if emit is not None or mask is not None or lr_scale != 1.0:
+                raise NotImplementedError("the sharded step covers the rank-local index mode (no score emission, "
+                                          "no mask, no boundary dual lr)")
+            coeff_t = coeff if isinstance(coeff, torch.Tensor) else (
+                None if coeff == 1.0 else torch.tensor([coeff], dtype=torch.float32, device=arena.device))
+            ctx.sharded.step(arena, src, opt, beta1=beta1, beta2=beta2, eps=eps, step=step, coeff=coeff_t,
+                             adams=self.adams)
+            if clear:
+                src.zero_()   # the replicated kernel clears what it consumed in the same pass; here only a slice is read
+            if fold:
+                from ... import kernels as K
+
+                K.scale_(arena.main_grad, None, 1.0 / float(ctx.fold_window))
+        elif arena.device.type == "cuda":
             from ... import kernels as K
 
             coeff_t = None

@@ -61,11 +61,22 @@ def latest_iteration(root: str):
     return max(its) if its else None
 
 
+def write_tracker(root: str, iteration: int) -> None:
+    """Point ``latest_checkpointed_iteration.txt`` at ``iteration``. With several writers (tensor /
+    pipeline shards, per-rank SGA state files) call it on one rank, after a barrier that follows
+    every writer's last file, so that the tracker never names a checkpoint that is still incomplete."""
+    os.makedirs(root, exist_ok=True)
+    with open(tracker_path(root) + ".tmp", "w") as fh:
+        fh.write(str(iteration))
+    os.replace(tracker_path(root) + ".tmp", tracker_path(root))
+
+
 def save_checkpoint(root: str, iteration: int, args, model, optimizer, rank: int = 0, tp_rank: int = 0,
-                    dp_rank: int | None = None, pp_rank: int = 0, pp_size: int = 1) -> str:
-    """The first data-parallel replica writes (every replica holds the same state): one
-    ``mp_rank_XX[_YYY]`` file per tensor-parallel rank (and pipeline stage), the tracker by the
-    first of them."""
+                    dp_rank: int | None = None, pp_rank: int = 0, pp_size: int = 1, tracker: bool = True) -> str:
+    """The first data-parallel replica writes (every replica holds the same state; a run whose
+    optimizer state lives in per-rank owner slices gathers it first, ``Trainer.gather_optimizer_state``):
+    one ``mp_rank_XX[_YYY]`` file per tensor-parallel rank (and pipeline stage). ``tracker`` false leaves
+    the tracker file to the caller (``write_tracker`` after a barrier)."""
     path = checkpoint_name(root, iteration, tp_rank, pp_rank, pp_size)
     if (dp_rank if dp_rank is not None else rank) != 0:
         return path
@@ -80,10 +91,8 @@ def save_checkpoint(root: str, iteration: int, args, model, optimizer, rank: int
     tmp = path + ".tmp"
     torch.save(state, tmp)
     os.replace(tmp, path)
-    if tp_rank == 0 and pp_rank == 0:
-        with open(tracker_path(root) + ".tmp", "w") as fh:
-            fh.write(str(iteration))
-        os.replace(tracker_path(root) + ".tmp", tracker_path(root))
+    if tracker and tp_rank == 0 and pp_rank == 0:
+        write_tracker(root, iteration)
     return path
 
 
@@ -106,6 +115,23 @@ def load_sga_state(root: str, iteration: int, engine, rank: int) -> bool:
         return False
     engine.load_state_dict(torch.load(path, map_location="cpu", weights_only=False))
     return True
+
+
+def sga_state_present_everywhere(root: str, iteration: int, rank: int, device=None) -> bool:
+    """True only when every rank finds its own SGA state file: a warm resume on some ranks and a
+    cold start on others would issue mismatched collectives."""
+    import torch.distributed as dist
+
+    here = os.path.exists(sga_state_name(root, iteration, rank))
+    if not (dist.is_available() and dist.is_initialized()):
+        return here
+    dev = device if (device is not None and dist.get_backend() == "nccl") else "cpu"
+    flag = torch.tensor([1 if here else 0], dtype=torch.int32, device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    ok = bool(flag.item())
+    if here and not ok and rank == 0:
+        print("[train] some rank has no saved SGA state: every rank cold-starts its cycle", flush=True)
+    return ok
 
 
 def load_checkpoint(root: str, model, optimizer, tp_rank: int = 0, pp_rank: int = 0, pp_size: int = 1):

@@ -62,7 +62,9 @@ class DataParallel:
         self.channels = []
         self.comm_stream = None
         if cuda:
-            self.comm_stream = torch.cuda.Stream(device=self.device)
+            # high priority: a bucket's short synchronisation kernels take the SM resources that the
+            # long GEMMs of the backward pass leave free as soon as they are launched
+            self.comm_stream = torch.cuda.Stream(device=self.device, priority=-1)
         if transport == "p2p":
             from ..parallel.p2p import PeerChannel
 
@@ -75,6 +77,7 @@ class DataParallel:
         self._slot_bucket = {id(s): s.bucket for s in self.arena.slots}
         self._bucket_nparams = [len(b.slots) for b in self.arena.buckets]
         self.sync_launches = 0
+        self.null_sync = False   # measurement switch: skip the buckets' synchronisation work (see bench.py)
 
     # ------------------------------------------------------- structure
     @property
@@ -112,6 +115,8 @@ class DataParallel:
         if bucket.index in self._synced:
             return
         self._synced.add(bucket.index)
+        if self.null_sync:
+            return
         timed = getattr(self, "time_syncs", False) and self.device.type == "cuda"
         if self.comm_stream is not None:
             ev = torch.cuda.Event()

@@ -69,6 +69,27 @@ class BucketState:
         self.active_mask_u8 = None
 
 
+class ShardedStep:
+    """Sharded form of the optimizer step over the peer-memory transport: one launch updates, on every
+    rank, the slice of each bucket that the rank owns (the cut of ``csrc/dense_sync.cu``) and stores
+    the bf16 parameters into every rank's model arena. The fp32 weights and moments outside a rank's
+    slices go stale; ``Trainer.gather_optimizer_state`` rebuilds the replicated layout on demand."""
+
+    def __init__(self, ddp):
+        arena = ddp.arena
+        self.ddp = ddp
+        self.bucket_start = torch.tensor([b.start for b in arena.buckets], dtype=torch.int64, device=arena.device)
+        self.bucket_len = torch.tensor([b.numel for b in arena.buckets], dtype=torch.int64, device=arena.device)
+
+    def step(self, arena, grad, opt, *, beta1, beta2, eps, step, coeff, adams) -> None:
+        from ..parallel import p2p
+
+        p2p.dense_adamw_ag_(self.ddp.channels[0], arena.main_param, grad, arena.exp_avg, arena.exp_avg_sq,
+                            arena.symm_model, self.bucket_start, self.bucket_len, arena.segment_table(),
+                            opt.group_lr(), opt.group_wd(), beta1=beta1, beta2=beta2, eps=eps, step=step,
+                            coeff=coeff, adams=adams, max_ctas=self.ddp.ddp_config.comm_max_ctas)
+
+
 class SelectionContext:
     """What a selector sees: the eligible score views, the comm group and the
     warm-up target its own hook implied."""
@@ -226,6 +247,15 @@ class SGAEngine:
             self.backend.configure_rank_local(max_b, max_k)
             if self.backend.consumes == "idx" and arena.comm is None:
                 arena.comm = torch.zeros(arena.numel, dtype=torch.float32, device=arena.device)
+        # Sharded optimizer step: possible when every rank ends the sync with the same gradient and
+        # nothing reads another rank's share of the weights or moments: rank-local index mode with the
+        # |grad + residual| score, peer-memory transport, no model parallelism, no trace dumps.
+        want = os.environ.get("SGA_SHARDED_STEP", "auto")
+        self.sharded = None
+        if (want != "0" and self.rank_local and self.backend.consumes == "idx" and self.score_name == "abs_g"
+                and getattr(ddp, "transport", None) == "p2p" and ddp.world > 1 and arena.symm_model is not None
+                and self._trace is None and self.model_parallel_norm is None and not self._shadow):
+            self.sharded = ShardedStep(ddp)
         if arena.device.type == "cuda":
             z = lambda dt: torch.zeros(1, dtype=dt, device=arena.device)  # noqa: E731
             self._dev = {"sumsq": z(torch.float32), "coeff": torch.ones(1, dtype=torch.float32, device=arena.device),
@@ -421,7 +451,7 @@ class SGAEngine:
             mask_arena=(self._active_mask_arena() if self._mask_in_use(was_full) else None),
             grad_source=("comm" if (self.rank_local and not was_full and self.backend.consumes == "idx")
                          else "grad"),
-            emit=not self.rank_local)
+            emit=not self.rank_local, sharded=self.sharded if self.model_parallel_norm is None else None)
         if was_full:
             self.opt.full_step(ctx)
         else:

@@ -285,6 +285,9 @@ class Trainer:
         self.pp_size = max(1, int(args.pipeline_model_parallel_size or 1))
         if self.pp_size > 1 and self.tp_size > 1:
             raise NotImplementedError("pipeline stages combined with tensor parallelism are not built")
+        if self.pp_size > 1 and int(getattr(args, "eval_interval", 0) or 0) > 0:
+            raise NotImplementedError("--eval-interval with pipeline stages: the validation pass has no "
+                                      "forward-only pipeline schedule; run validation without pipeline parallelism")
         mp = self.tp_size * self.pp_size
         assert self.world % mp == 0, "world size must be a multiple of tensor-parallel x pipeline-parallel size"
         self.dp_world = self.world // mp
@@ -324,6 +327,13 @@ class Trainer:
         if transport == "auto" and sga_t != "auto":
             transport = sga_t
         self.pool = None
+        if cuda and transport == "auto" and self.dp_world > 1 and not self._dp_group_on_one_host():
+            # peer-mapped memory (CUDA IPC) covers one NVSwitch domain: a data-parallel group that spans
+            # hosts, or has more than 8 ranks, takes the library collectives
+            transport = "nccl"
+            if self.rank == 0 and not quiet:
+                print("[train] the data-parallel group spans hosts (or more than 8 ranks): transport nccl, "
+                      "dense steps by all-reduce", flush=True)
         if cuda and transport in ("auto", "p2p"):
             from ..parallel.symm import SymmPool
 
@@ -383,10 +393,10 @@ class Trainer:
         if self.sga:
             self.engine = build_engine(trainer_args=args, quiet=quiet)
             self.engine.log_interval = args.log_interval
-            self.engine.attach(self.ddp)
-            self.engine.bind_optimizer(self.optimizer)
             if self.tp is not None or self.pp_size > 1:
                 self.engine.model_parallel_norm = self._tp_norm
+            self.engine.attach(self.ddp)
+            self.engine.bind_optimizer(self.optimizer)
         if getattr(args, "data_path", None):
             from .data import TokenFile
 
@@ -471,6 +481,45 @@ class Trainer:
             dist.all_reduce(total, group=self.dp_group)
             total /= self.dp_world
         return float(total.item())
+
+    def _dp_group_on_one_host(self) -> bool:
+        import socket
+
+        if self.dp_world > 8:
+            return False
+        names = [None] * self.dp_world
+        dist.all_gather_object(names, socket.gethostname(), group=self.dp_group)
+        return len(set(names)) == 1
+
+    # ------------------------------------------------- sharded optimizer state
+    @property
+    def sharded_state(self) -> bool:
+        """True when each data-parallel rank keeps the fp32 weights and moments only for the slice
+        of every bucket it owns (the fused dense step, and the sharded SGA step)."""
+        if self.engine is not None:
+            return bool(getattr(self.engine, "sharded", False))
+        return self._fused_dense() and self.dp_world > 1
+
+    def gather_optimizer_state(self) -> None:
+        """All-gather the owner slices of the fp32 weights and both moments over the data-parallel
+        group, so that every rank holds the whole replicated state again (what a checkpoint, a trace
+        dump or a parameter norm reads). The cut is the update kernel's: a bucket of n elements is
+        split at 16-byte granularity into ``dp`` equal slices, slice r owned by rank r."""
+        if not self.sharded_state or self.dp_world == 1:
+            return
+        arena = self.model.arena
+        W, r = self.dp_world, self.dp_rank
+        for b in arena.buckets:
+            n4 = (b.numel + 3) // 4
+            per = (n4 + W - 1) // W * 4
+            lo, hi = min(b.numel, per * r), min(b.numel, per * (r + 1))
+            for t in (arena.main_param, arena.exp_avg, arena.exp_avg_sq):
+                view = t[b.start:b.end]
+                stage = torch.zeros(per, dtype=t.dtype, device=t.device)
+                stage[:hi - lo].copy_(view[lo:hi])
+                full = torch.empty(per * W, dtype=t.dtype, device=t.device)
+                dist.all_gather_into_tensor(full, stage, group=self.dp_group)
+                view.copy_(full[:b.numel])
 
     def host_batch(self, step: int) -> torch.Tensor:
         """This rank's ``[num_micro * micro_batch, seq + 1]`` token block for ``step`` (pinned host memory)."""

@@ -17,9 +17,20 @@ from .runtime import checkpoint as ckpt
 from .runtime.trainer import Trainer, build_parser
 
 
-def _save_sga(args, tr, iteration: int) -> None:
-    if args.save and args.save_sga_state and tr.engine is not None:
+def _save(args, tr, iteration: int) -> None:
+    """One complete checkpoint: owner slices of the optimizer state gathered, every shard and every
+    rank's SGA state file written, and only then (after a barrier) the tracker."""
+    import torch.distributed as dist
+
+    tr.gather_optimizer_state()
+    ckpt.save_checkpoint(args.save, iteration, args, tr.model, tr.optimizer, tr.rank, tr.tp_rank, tr.dp_rank,
+                         tr.pp_rank, tr.pp_size, tracker=False)
+    if args.save_sga_state and tr.engine is not None:
         ckpt.save_sga_state(args.save, iteration, tr.engine, tr.rank)
+    if dist.is_available() and dist.is_initialized():
+        dist.barrier()
+    if tr.rank == 0:
+        ckpt.write_tracker(args.save, iteration)
 
 
 def main(argv=None) -> int:
@@ -31,6 +42,7 @@ def main(argv=None) -> int:
         start = ckpt.load_checkpoint(args.load, tr.model, tr.optimizer, tr.tp_rank, tr.pp_rank, tr.pp_size)
         tr.iteration = start
         warm = bool(start and args.save_sga_state and tr.engine is not None
+                    and ckpt.sga_state_present_everywhere(args.load, start, tr.rank, tr.device)
                     and ckpt.load_sga_state(args.load, start, tr.engine, tr.rank))
         if tr.rank == 0 and start:
             print(f"[train] resumed from iteration {start} " + (
@@ -61,7 +73,8 @@ def main(argv=None) -> int:
                 gn = float(gn.item()) if hasattr(gn, "item") else (float(gn) if gn is not None else float("nan"))
                 extra = ""
                 if getattr(args, "log_params_norm", False):  # this rank's parameters (a shard under TP / PP)
-                    extra += f" | params norm {float(tr.model.arena.main_param.norm()):.4f}"
+                    # the bf16 copies are complete on every rank; the fp32 masters may live in owner slices
+                    extra += f" | params norm {float(tr.model.arena.model_param.float().norm()):.4f}"
                 extra += f" | lr {tr.optimizer.param_groups[0]['lr']:.3e}"
                 print(f"[train] iteration {it}/{args.train_iters} | loss {lv:.6f} | grad norm {gn:.4f}{extra} | "
                       f"{dt * 1e3:.1f} ms/step | {tr.tokens_per_step() / dt:.0f} tokens/s", flush=True)
@@ -76,12 +89,10 @@ def main(argv=None) -> int:
                 if tb is not None:
                     tb.add_scalar("lm loss validation", val, it)
         if args.save and args.save_interval and it % args.save_interval == 0:
-            ckpt.save_checkpoint(args.save, it, args, tr.model, tr.optimizer, tr.rank, tr.tp_rank, tr.dp_rank, tr.pp_rank, tr.pp_size)
-            _save_sga(args, tr, it)
+            _save(args, tr, it)
         if args.exit_interval and it % args.exit_interval == 0 and it < args.train_iters:
             if args.save:
-                ckpt.save_checkpoint(args.save, it, args, tr.model, tr.optimizer, tr.rank, tr.tp_rank, tr.dp_rank, tr.pp_rank, tr.pp_size)
-                _save_sga(args, tr, it)
+                _save(args, tr, it)
             if tr.rank == 0:
                 print(f"[train] exiting at iteration {it} (--exit-interval {args.exit_interval})", flush=True)
             if tb is not None:
@@ -90,8 +101,7 @@ def main(argv=None) -> int:
             tr.close()
             return 0
     if args.save:
-        ckpt.save_checkpoint(args.save, args.train_iters, args, tr.model, tr.optimizer, tr.rank, tr.tp_rank, tr.dp_rank, tr.pp_rank, tr.pp_size)
-        _save_sga(args, tr, args.train_iters)
+        _save(args, tr, args.train_iters)
     if tb is not None:
         tb.close()
     tr.check()

@@ -164,6 +164,111 @@ def check_trainer(rank, world, dev):
     return final
 
 
+def _run_steps(args, steps, batches=None):
+    from sga_b200.runtime.trainer import Trainer
+
+    tr = Trainer(args, quiet=True)
+    losses = [float(tr.train_step(tr.host_batch(s if batches is None else batches[s])).item()) for s in range(steps)]
+    tr.check()
+    return tr, losses
+
+
+def check_trajectories(rank, world, dev):
+    """The same configuration over the peer-memory kernels and over the library collectives must give
+    the same loss trajectory up to the order of the fp32 / bf16 sums: SGA rank-local index mode and
+    the dense step, 20 steps each."""
+    from sga_b200.runtime.trainer import default_args
+
+    common = dict(model="test_tiny", micro_batch_size=2, global_batch_size=4 * world, train_iters=20, lr=1e-3,
+                  sga_bucket_elems=30000, log_interval=0)
+    sga = dict(sga_enabled=True, sga_score="abs_g", sga_selection_method="exact", sga_selection_ratio_percent=2.0,
+               sga_backend="torch_pipelined_index", sga_selection_locality="rank_local", sga_cycle_period=0)
+    out = {}
+    for name, kw in (("sga_p2p", dict(sga, transport="p2p")), ("sga_nccl", dict(sga, transport="nccl")),
+                     ("dense_p2p", dict(transport="p2p")), ("dense_nccl", dict(transport="nccl"))):
+        tr, losses = _run_steps(default_args(**common, **kw), 20)
+        out[name] = losses
+        tr.close()
+        dist.barrier()
+    for a, b in (("sga_p2p", "sga_nccl"), ("dense_p2p", "dense_nccl")):
+        worst = max(abs(x - y) / max(abs(y), 1e-6) for x, y in zip(out[a], out[b]))
+        assert worst < 1e-3, f"{a} vs {b}: loss trajectories differ by {worst:.2e} relative: {out[a]} {out[b]}"
+    return out
+
+
+def check_sharded_step(rank, world, dev):
+    """The sharded SGA step (each rank updates the bucket slices it owns, bf16 parameters pushed to the
+    peers) against the replicated one: bit-identical bf16 parameters, and after the gather bit-identical
+    fp32 weights and moments."""
+    from sga_b200.runtime.trainer import default_args
+
+    kw = dict(model="test_tiny", micro_batch_size=2, global_batch_size=4 * world, train_iters=8, lr=1e-3,
+              sga_bucket_elems=30000, log_interval=0, sga_enabled=True, sga_score="abs_g",
+              sga_selection_method="exact", sga_selection_ratio_percent=2.0, sga_backend="torch_pipelined_index",
+              sga_selection_locality="rank_local", sga_cycle_period=3)
+    got = {}
+    for mode in ("1", "0"):
+        os.environ["SGA_SHARDED_STEP"] = mode
+        tr, losses = _run_steps(default_args(**kw), 8)
+        assert tr.sharded_state == (mode == "1" and world > 1)
+        tr.gather_optimizer_state()
+        a = tr.model.arena
+        got[mode] = (losses, a.model_param.clone(), a.main_param.clone(), a.exp_avg.clone(), a.exp_avg_sq.clone())
+        tr.close()
+        dist.barrier()
+    os.environ.pop("SGA_SHARDED_STEP")
+    assert got["1"][0] == got["0"][0], (got["1"][0], got["0"][0])
+    for i, what in ((1, "bf16 parameters"), (2, "fp32 weights"), (3, "exp_avg"), (4, "exp_avg_sq")):
+        assert torch.equal(got["1"][i], got["0"][i]), f"sharded vs replicated step: {what} differ"
+
+
+def check_resume(rank, world, dev):
+    """Checkpoint of a run whose optimizer state lives in owner slices (fused dense step, sharded SGA
+    step): save at step 3, resume in a fresh trainer, continue; bit-identical with the uninterrupted run."""
+    import tempfile
+
+    from sga_b200.runtime import checkpoint as ckpt
+    from sga_b200.runtime.trainer import Trainer, default_args
+
+    root = [tempfile.mkdtemp(prefix="sga_resume_") if rank == 0 else None]
+    dist.broadcast_object_list(root, src=0)
+    base = dict(model="test_tiny", micro_batch_size=2, global_batch_size=4 * world, train_iters=6, lr=1e-3,
+                sga_bucket_elems=30000, log_interval=0)
+    for name, kw in (("dense_fused", dict()),):
+        args = default_args(**base, **kw)
+        full, _ = _run_steps(args, 6)
+        full.gather_optimizer_state()
+        ref = (full.model.arena.model_param.clone(), full.model.arena.main_param.clone(),
+               full.model.arena.exp_avg.clone())
+        full.close()
+        dist.barrier()
+        first, _ = _run_steps(args, 3)
+        assert first.sharded_state == (world > 1)
+        d = os.path.join(root[0], name)
+        first.gather_optimizer_state()
+        ckpt.save_checkpoint(d, 3, args, first.model, first.optimizer, first.rank, first.tp_rank, first.dp_rank,
+                             first.pp_rank, first.pp_size, tracker=False)
+        dist.barrier()
+        if rank == 0:
+            ckpt.write_tracker(d, 3)
+        dist.barrier()
+        first.close()
+        second = Trainer(args, quiet=True)
+        it = ckpt.load_checkpoint(d, second.model, second.optimizer)
+        assert it == 3
+        second.iteration = it
+        for s in range(3, 6):
+            second.train_step(second.host_batch(s))
+        second.check()
+        second.gather_optimizer_state()
+        a = second.model.arena
+        assert torch.equal(a.model_param, ref[0]), f"{name}: resumed bf16 parameters differ"
+        assert torch.equal(a.main_param, ref[1]), f"{name}: resumed fp32 weights differ"
+        assert torch.equal(a.exp_avg, ref[2]), f"{name}: resumed moments differ"
+        second.close()
+        dist.barrier()
+
+
 def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
@@ -172,6 +277,9 @@ def main():
     rank, world = dist.get_rank(), dist.get_world_size()
     check_kernels(rank, world, dev)
     final = check_trainer(rank, world, dev)
+    check_sharded_step(rank, world, dev)
+    check_resume(rank, world, dev)
+    final.update(check_trajectories(rank, world, dev))
     dist.barrier()
     if rank == 0:
         for k, v in final.items():

@@ -1,7 +1,7 @@
-"""Multi-GPU tests: launches ``dist_gpu_worker.py`` under torchrun on the GPUs
-of this box (2 when more are visible, to keep the run short). NVLS is switched
-off in NCCL for these child processes and the framework's own kernels use
-plain peer loads and stores."""
+"""Multi-GPU tests: launches the workers under torchrun on the GPUs of this box: 2 ranks by
+default, ``SGA_TEST_RANKS`` of them (2, 4 or 8) when set and that many GPUs are visible. NVLS is
+switched off in NCCL for these child processes and the framework's own kernels use plain peer
+loads and stores."""
 import os
 import subprocess
 import sys
@@ -11,6 +11,7 @@ import torch
 
 pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
+RANKS = int(os.environ.get("SGA_TEST_RANKS", "2"))
 
 
 def _run(nproc, timeout=600, worker="dist_gpu_worker.py", port=29741):
@@ -21,10 +22,10 @@ def _run(nproc, timeout=600, worker="dist_gpu_worker.py", port=29741):
 
 
 @pytest.mark.timeout(900)
-def test_peer_kernels_and_trainer_two_gpus():
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs at least 2 GPUs")
-    res = _run(2)
+def test_peer_kernels_and_trainer_multi_gpu():
+    if torch.cuda.device_count() < RANKS:
+        pytest.skip(f"needs at least {RANKS} GPUs")
+    res = _run(RANKS)
     assert res.returncode == 0 and "DIST_GPU_OK" in res.stdout, res.stdout[-3000:] + "\n" + res.stderr[-6000:]
 
 

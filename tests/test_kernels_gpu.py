@@ -254,7 +254,7 @@ def _channel():
     return pool, PeerChannel(pool)
 
 
-def _check_index_sync(acc0, k, score=None, score_abs=None, scale=0.5, reps=2):
+def _check_index_sync(acc0, k, score=None, score_abs=None, scale=0.5, reps=2, max_ctas=0):
     """One rank: selection, payload, residual write-back, staging buffer and norm of the fused
     rank-local chain against the PyTorch oracle (``score_abs``: |score| per coordinate)."""
     import numpy as np
@@ -278,7 +278,7 @@ def _check_index_sync(acc0, k, score=None, score_abs=None, scale=0.5, reps=2):
             acc.copy_(acc0)
             comm.zero_()
             p2p.bucket_index_sync_(ch, scratch, acc, k, slots=slots, comm=comm, scale=scale, sumsq_out=sq,
-                                   score=score)
+                                   score=score, max_ctas=max_ctas)
             ch.check()
             assert int(scratch.result[3].item()) == ksel
             pairs = slots.pairs(0, ksel)
@@ -294,7 +294,7 @@ def _check_index_sync(acc0, k, score=None, score_abs=None, scale=0.5, reps=2):
         # select-only mode writes the bit mask and leaves the bucket alone
         acc.copy_(acc0)
         bits = torch.full(((n + 31) // 32,), -1, dtype=torch.int32, device=DEV)
-        p2p.bucket_index_sync_(ch, scratch, acc, k, bits=bits, select_only=True, score=score)
+        p2p.bucket_index_sync_(ch, scratch, acc, k, bits=bits, select_only=True, score=score, max_ctas=max_ctas)
         ch.check()
         un = np.unpackbits(bits.cpu().numpy().view("uint8"), bitorder="little")[:n]
         assert np.array_equal(un, ref_mask.cpu().numpy())
@@ -311,6 +311,16 @@ def test_bucket_index_sync_single_rank(n, k):
     acc = torch.randn(n, device=DEV) * 1e-3
     acc[::97] = 0.5  # many exact ties at the top: the tie cut by index decides
     _check_index_sync(acc, k)
+
+
+@pytest.mark.parametrize("max_ctas", [1, 5])
+def test_bucket_index_sync_few_ctas(max_ctas):
+    """A grid far smaller than the bucket: every warp walks many segments, every CTA many ranges."""
+    n = 5 * (1 << 20) + 3
+    torch.manual_seed(max_ctas)
+    acc = torch.randn(n, device=DEV) * 1e-3
+    acc[::1013] = -0.75
+    _check_index_sync(acc, 60000, max_ctas=max_ctas)
 
 
 def test_bucket_index_sync_degenerate_inputs():
