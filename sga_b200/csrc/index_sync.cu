@@ -54,6 +54,7 @@ constexpr int IS_ABINS = 4096;        // first digit, also the sample's histogra
 constexpr int IS_BBINS = 2048;        // second digit: bits 18..8
 constexpr int IS_FBINS = 1 << 19;     // fine histogram of the low 19 bits inside the crossing first-digit bin
 constexpr int IS_REP = 8;             // replicas of the two coarse global histograms
+constexpr int IS_WBINS = 1024;        // the filter's shared-memory window of first-digit bins (4 KB: its CTAs fit beside a GEMM CTA)
 
 // Word offsets inside the state block (unsigned[64], zeroed by the host before each bucket).
 enum {
@@ -99,7 +100,6 @@ struct ISyncArgs {
   int zero_selected;
   unsigned* bits;        // select-only mode: bit mask of the selection (zeroed by the host)
   unsigned* result;      // [4]: threshold key, ties taken, keys above the threshold, pairs produced
-  int level;             // filter pass: 0 = sample bound, 1 = every non-zero element
 };
 
 // Programmatic dependent launch: every kernel of the chain first lets the next one be scheduled
@@ -189,14 +189,17 @@ __device__ __forceinline__ bool find_suffix_bin(const unsigned* hist, int nb, in
 
 // Flush a CTA's shared first-digit histogram into its global replica and widen the global window
 // of bins in use.
-__device__ __forceinline__ void flush_first_digit(const unsigned* sh_hist, unsigned* replica, unsigned* state) {
+// sh_hist[i] counts absolute bin min(first + i, IS_ABINS - 1).
+__device__ __forceinline__ void flush_first_digit(const unsigned* sh_hist, int nbins, int first, unsigned* replica,
+                                                  unsigned* state) {
   __shared__ unsigned s_win[2];
   if (threadIdx.x == 0) { s_win[0] = 0; s_win[1] = 0; }
   __syncthreads();
   unsigned top = 0, invlow = 0;
-  for (int i = threadIdx.x; i < IS_ABINS; i += IS_THREADS) {
-    const unsigned c = sh_hist[i];
+  for (int j = threadIdx.x; j < nbins; j += IS_THREADS) {
+    const unsigned c = sh_hist[j];
     if (c) {
+      const int i = min(first + j, IS_ABINS - 1);
       atomicAdd(&replica[i], c);
       top = max(top, (unsigned)i + 1u);
       invlow = max(invlow, (unsigned)(IS_ABINS - i));
@@ -276,6 +279,16 @@ __device__ __forceinline__ void keys4(const ISyncArgs& a, long long i, long long
   }
 }
 
+// Value and key of the single element i (the filter re-reads its few hits).
+template <int SCORE>
+__device__ __forceinline__ void key1(const ISyncArgs& a, long long i, float& g, unsigned& key) {
+  g = a.acc[i];
+  const float w = SCORE == 0 ? a.w[i] : 0.f;
+  const float m = SCORE != 1 ? a.m[i] : 0.f;
+  const float v = (SCORE == 0 || SCORE == 3) ? a.v[i] : 0.f;
+  key = score_key<SCORE>(a, g, w, m, v, SCORE == 0 ? wd_of(a, i) : 0.f);
+}
+
 // ------------------------------------------------------------------ sample
 // Histogram (4096 bins of key >> 19) of one hashed 16-byte group in every 2^gshift; the CTA that
 // finishes last turns it into the candidate bound: the lower edge of the bin at which the sample's
@@ -316,7 +329,7 @@ __global__ void __launch_bounds__(IS_THREADS) isync_sample_kernel(const ISyncArg
         if (j < lim[u]) atomicAdd(&sh_hist[key[u][j] >> 19], 1u);
   }
   __syncthreads();
-  flush_first_digit(sh_hist, a.histA + (blockIdx.x % IS_REP) * IS_ABINS, a.state);
+  flush_first_digit(sh_hist, IS_ABINS, 0, a.histA + (blockIdx.x % IS_REP) * IS_ABINS, a.state);
   {
     unsigned mine = 0;  // elements this CTA sampled
     for (int i = threadIdx.x; i < IS_ABINS; i += IS_THREADS) mine += sh_hist[i];
@@ -354,15 +367,22 @@ __global__ void __launch_bounds__(IS_THREADS) isync_sample_kernel(const ISyncArg
 // of bins is hot; replicas keep the same-address atomics short). The last CTA either publishes the
 // crossing bin of that digit or, when fewer than k candidates were found under the sample bound,
 // arms level 1 (every non-zero key), which is the next launch and normally returns at once.
-template <int SCORE>
+template <int SCORE, int LEVEL>
 __global__ void __launch_bounds__(IS_THREADS) isync_filter_kernel(const ISyncArgs a) {
   chain_enter();
-  __shared__ unsigned sh_hist[IS_ABINS];
+  constexpr int HBINS = LEVEL == 0 ? IS_WBINS : IS_ABINS;
+  __shared__ unsigned sh_hist[HBINS];
   __shared__ unsigned sh_cnt[IS_THREADS / 32];
-  if (a.level == 1 && ldv(a.state + ST_LEVEL) != 1u) return;
-  unsigned tlo = a.level == 0 ? ldv(a.state + ST_TLO) : 1u;
+  if (LEVEL == 1 && ldv(a.state + ST_LEVEL) != 1u) return;
+  unsigned tlo = LEVEL == 0 ? ldv(a.state + ST_TLO) : 1u;
   if (tlo < 1u) tlo = 1u;
-  for (int i = threadIdx.x; i < IS_ABINS; i += IS_THREADS) sh_hist[i] = 0;
+  // Level 0 counts the first digit in a shared window of 1024 bins from the bound's bin (64 binades:
+  // what lies above lands in the window's last bin, and a crossing found there sends the bucket to
+  // level 1), which keeps its shared memory at 4 KB. Level 1, the rare exact fallback, takes the
+  // whole range of 4096 bins.
+  const unsigned b_lo = LEVEL == 0 ? (tlo >> 19) : 0u;
+  unsigned* replica = a.histA + (blockIdx.x % IS_REP) * IS_ABINS;
+  for (int i = threadIdx.x; i < HBINS; i += IS_THREADS) sh_hist[i] = 0;
   __syncthreads();
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
   constexpr int U = SCORE == 1 ? 8 : 4;  // 16-byte loads in flight per lane and array
@@ -376,45 +396,61 @@ __global__ void __launch_bounds__(IS_THREADS) isync_filter_kernel(const ISyncArg
     float* cv = a.cand_val + s0;
     unsigned cnt = 0;
     for (long long base = s0; base < s1; base += U * 128) {
-      float g[U][4];
-      unsigned key[U][4];
+      // One trip: U rows of 128 elements. Every lane first collects a bit mask of its qualifying
+      // elements over the whole trip (bit u * 4 + j), with no warp-wide step per row; the trip's
+      // few hits (about 1.5 % of its elements) are then placed by one warp scan and written by a
+      // loop that runs once per hit of the busiest lane, re-reading the value through L1.
+      const bool whole = base + U * 128 <= s1;  // every lane's loads lie inside the segment
+      unsigned M = 0;
+      if (SCORE == 1) {
+        float g[U][4];
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        if (SCORE == 1) load4z(a.acc, base + u * 128 + lane * 4, s1, g[u]);  // the key is the value's own bits
-        else keys4<SCORE>(a, base + u * 128 + lane * 4, s1, g[u], key[u]);
+        for (int u = 0; u < U; ++u) {
+          const long long i = base + u * 128 + lane * 4;
+          if (whole) *reinterpret_cast<float4*>(g[u]) = *reinterpret_cast<const float4*>(a.acc + i);
+          else load4z(a.acc, i, s1, g[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) M |= (key_bits(g[u][j]) >= tlo ? 1u : 0u) << (u * 4 + j);
+      } else {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          float g[4];
+          unsigned key[4];
+          keys4<SCORE>(a, base + u * 128 + lane * 4, s1, g, key);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) M |= (key[j] >= tlo ? 1u : 0u) << (u * 4 + j);
+        }
       }
+      if (__ballot_sync(0xffffffffu, M != 0u) == 0u) continue;
+      const int c = __popc(M);
+      int incl = c;
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
+      for (int o = 1; o < 32; o <<= 1) {
+        const int y = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += y;
+      }
+      unsigned pos = cnt + (unsigned)(incl - c);
+      cnt += (unsigned)__shfl_sync(0xffffffffu, incl, 31);
+      while (M) {
+        const int bit = __ffs(M) - 1;
+        M &= M - 1;
+        const long long i = base + (bit >> 2) * 128 + lane * 4 + (bit & 3);
+        float val;
+        unsigned kk;
         if (SCORE == 1) {
-#pragma unroll
-          for (int j = 0; j < 4; ++j) key[u][j] = key_bits(g[u][j]);
+          val = a.acc[i];
+          kk = key_bits(val);
+        } else {
+          key1<SCORE>(a, i, val, kk);
         }
-        const bool f0 = key[u][0] >= tlo, f1 = key[u][1] >= tlo, f2 = key[u][2] >= tlo, f3 = key[u][3] >= tlo;
-        const int c = (int)f0 + (int)f1 + (int)f2 + (int)f3;
-        const unsigned bal = __ballot_sync(0xffffffffu, c != 0);
-        if (bal == 0u) continue;
-        // about two of a warp's 128 elements qualify: a warp scan of the per-lane counts places them
-        int incl = c;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-          const int y = __shfl_up_sync(0xffffffffu, incl, o);
-          if (lane >= o) incl += y;
-        }
-        if (c) {
-          unsigned pos = cnt + (unsigned)(incl - c);
-          const int i0 = (int)(base + u * 128 + lane * 4);
-          const bool f[4] = {f0, f1, f2, f3};
-#pragma unroll
-          for (int j = 0; j < 4; ++j)
-            if (f[j]) {
-              ci[pos] = i0 + j;
-              ck[pos] = key[u][j];
-              cv[pos] = g[u][j];
-              atomicAdd(&sh_hist[key[u][j] >> 19], 1u);
-              ++pos;
-            }
-        }
-        cnt += (unsigned)__shfl_sync(0xffffffffu, incl, 31);
+        ci[pos] = (int)i;
+        ck[pos] = kk;
+        cv[pos] = val;
+        atomicAdd(&sh_hist[min((kk >> 19) - b_lo, (unsigned)(HBINS - 1))], 1u);
+        ++pos;
       }
     }
     if (lane == 0) a.segcnt[seg] = (int)cnt;
@@ -427,15 +463,17 @@ __global__ void __launch_bounds__(IS_THREADS) isync_filter_kernel(const ISyncArg
     for (int i = 0; i < IS_THREADS / 32; ++i) t += sh_cnt[i];
     if (t) atomicAdd(a.state + ST_C, t);
   }
-  flush_first_digit(sh_hist, a.histA + (blockIdx.x % IS_REP) * IS_ABINS, a.state);
-  if (!last_cta(a.state + ST_TICKET0 + 1 + a.level)) return;
+  flush_first_digit(sh_hist, HBINS, (int)b_lo, replica, a.state);
+  if (!last_cta(a.state + ST_TICKET0 + 1 + LEVEL)) return;
   const unsigned C = ldv(a.state + ST_C), k = (unsigned)a.k;
-  const bool retry = a.level == 0 && C < k && tlo > 1u;
+  bool retry = LEVEL == 0 && C < k && tlo > 1u;
   const int top = (int)ldv(a.state + ST_TOP) - 1, low = IS_ABINS - (int)ldv(a.state + ST_INVLOW);
   unsigned bin = 0, above = 0;
   bool found = false;
   if (top >= 0) {
     if (!retry && C > k) found = find_suffix_bin(a.histA, IS_ABINS, IS_REP, k, top, low, sh_cnt, bin, above);
+    // a crossing in the window's last bin is a crossing somewhere above the window
+    if (LEVEL == 0 && found && bin == b_lo + IS_WBINS - 1 && bin < IS_ABINS - 1) retry = true;
     zero_window(a.histA, IS_ABINS, IS_REP, top, low);
   }
   if (threadIdx.x == 0) { a.state[ST_TOP] = 0u; a.state[ST_INVLOW] = 0u; }
@@ -819,10 +857,8 @@ template <int SCORE>
 static void launch_select(const ISyncArgs& base, int grid_seg, int grid_sample, cudaStream_t st, bool pdl) {
   ISyncArgs a = base;
   launch_chain(isync_sample_kernel<SCORE>, grid_sample, st, a, false);  // follows a memset, not a kernel
-  a.level = 0;
-  launch_chain(isync_filter_kernel<SCORE>, grid_seg, st, a, pdl);
-  a.level = 1;
-  launch_chain(isync_filter_kernel<SCORE>, grid_seg, st, a, pdl);
+  launch_chain(isync_filter_kernel<SCORE, 0>, grid_seg, st, a, pdl);
+  launch_chain(isync_filter_kernel<SCORE, 1>, grid_seg, st, a, pdl);
 }
 
 // mode 0: select + exchange + reduce into comm. mode 1: select only, bit mask of the selection
@@ -877,7 +913,6 @@ SGA_API int sga_index_sync(const SgaPeerDesc* d, const SgaISyncDesc* s, void* st
   a.accumulate = s->accumulate; a.zero_selected = s->zero_selected;
   a.bits = reinterpret_cast<unsigned*>(s->bits);
   a.result = reinterpret_cast<unsigned*>(s->result);
-  a.level = 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int cap = s->max_ctas > 0 ? s->max_ctas : 148 * 8;
   const int wpc = IS_THREADS / 32;
