@@ -168,13 +168,10 @@ class TorchPipelinedIndexBackend:
     # ------------------------------------------------------ shared support
     def allreduce_sparse(self, grad_data, support, comm_group, gradient_scaling_factor, reduce_op, key,
                          bucket_state=None):
-        token = backend_timer.begin()
-        try:
+        with backend_timer.region("sparse", backend=self.name, emission=self.emission, layout=self.layout,
+                                  block_size=getattr(support, "block_size", None), bucket=key,
+                                  k=getattr(support, "n_selected", None)):
             return self._impl(grad_data, support, comm_group, gradient_scaling_factor, reduce_op, key, bucket_state)
-        finally:
-            backend_timer.end(token, "sparse", backend=self.name, emission=self.emission, layout=self.layout,
-                              block_size=getattr(support, "block_size", None), bucket=key,
-                              k=getattr(support, "n_selected", None))
 
     def _impl(self, grad_data, support, comm_group, factor_in, reduce_op, key, bucket_state):
         if grad_data.numel() >= 2 ** 31:
@@ -281,12 +278,9 @@ class TorchPipelinedIndexBackend:
         ``ScoreInputs`` with the bucket's weights, moments and Adam scalars) on this rank, exchange of
         (int32 index, fp32 value) pairs, rank-ordered sum / world into ``comm_view``; the selected
         coordinates of the bucket are zeroed. Coordinates with a zero score are never selected."""
-        token = backend_timer.begin()
-        try:
+        with backend_timer.region("sparse", backend=self.name, emission="rank_local", layout="er", block_size=1,
+                                  bucket=bucket_state.bucket_id, k=k):
             self._rank_local_impl(bucket_state, k, comm_view, comm_group, world, score)
-        finally:
-            backend_timer.end(token, "sparse", backend=self.name, emission="rank_local", layout="er",
-                              block_size=1, bucket=bucket_state.bucket_id, k=k)
 
     def _rank_local_impl(self, bs, k, comm_view, comm_group, world, score=None):
         grad = bs.grad_data

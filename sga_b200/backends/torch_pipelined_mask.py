@@ -96,12 +96,9 @@ class TorchPipelinedMaskBackend:
     # ------------------------------------------------------ shared support
     def allreduce_sparse(self, grad_data, support, comm_group, gradient_scaling_factor, reduce_op, key=None,
                          bucket_state=None) -> None:
-        token = backend_timer.begin()
-        try:
+        with backend_timer.region("sparse", backend=self.name, layout="mask", block_size=None, bucket=key,
+                                  k=getattr(support, "n_selected", None)):
             return self._impl(grad_data, support, comm_group, gradient_scaling_factor, reduce_op, key, bucket_state)
-        finally:
-            backend_timer.end(token, "sparse", backend=self.name, layout="mask", block_size=None, bucket=key,
-                              k=getattr(support, "n_selected", None))
 
     def _impl(self, grad_data, support, comm_group, factor_in, reduce_op, key, bs):
         scale_payload = reduce_op == dist.ReduceOp.SUM and factor_in != 1.0
@@ -152,8 +149,8 @@ class TorchPipelinedMaskBackend:
         """Per-rank exact top-``k`` mask, OR across ranks, reduction (mean) of the
         union's entries in place in the bucket; ``mask_view`` receives the
         union as uint8."""
-        token = backend_timer.begin()
-        try:
+        with backend_timer.region("sparse", backend=self.name, layout="mask", block_size=None, bucket=bs.bucket_id,
+                                  k=k):
             grad = bs.grad_data
             if self.transport == "p2p" or (grad.is_cuda and self.ddp is not None and self.ddp.channels):
                 from ..parallel import p2p
@@ -181,6 +178,4 @@ class TorchPipelinedMaskBackend:
                 dist.all_reduce(sel, op=dist.ReduceOp.SUM, group=comm_group)
             grad[on] = sel * (1.0 / world)
             mask_view.copy_(mask)
-        finally:
-            backend_timer.end(token, "sparse", backend=self.name, layout="mask", block_size=None,
-                              bucket=bs.bucket_id, k=k)
+

@@ -35,7 +35,13 @@
  * Semantics are those of sga_compact_mask(): idx_out receives the ascending
  * positions of the non-zero bytes of mask[0..n), *total_out their number;
  * positions beyond cap are dropped and SGA_ERR_CAPACITY (16) is OR-ed into
- * *err. mask bytes must be 0 or 1. Returns 0 on success.
+ * *err. mask bytes must be 0 or 1. Returns 0 on success. With n <= 0 the call
+ * returns 0 at once and writes nothing, *total_out included.
+ *
+ * Alignment. The kernels read the mask 16 bytes at a time, so mask must start
+ * on a 16-byte boundary (a pointer from cudaMalloc does; an odd offset into a
+ * larger buffer may not). A misaligned mask is refused with
+ * SGA_COMPACT_NOALLOC_E_ALIGN before anything is launched.
  */
 #ifndef SGA_COMPACT_NOALLOC_H
 #define SGA_COMPACT_NOALLOC_H
@@ -48,6 +54,7 @@
 #define SGA_COMPACT_NOALLOC_E_TOO_LARGE (-8) /* n exceeds SGA_COMPACT_NOALLOC_MAX_ELEMS */
 #define SGA_COMPACT_NOALLOC_E_SETUP (-9)     /* the work array's device address could not be resolved */
 #define SGA_COMPACT_NOALLOC_E_LAUNCH (-4)    /* a kernel launch failed */
+#define SGA_COMPACT_NOALLOC_E_ALIGN (-10)    /* mask does not start on a 16-byte boundary */
 
 #ifdef __cplusplus
 extern "C" {

@@ -426,6 +426,7 @@ SGA_API int sga_compact_mask(const uint8_t* mask, long long n, int* block_counts
                              long long* total_out, int* err, void* stream) {
   if (n <= 0) return 0;
   if (n >= (1LL << 31)) return -6;
+  if ((reinterpret_cast<uintptr_t>(mask) & 15) != 0) return -10;  // the kernels read the mask 16 bytes at a time
   const int nb = (int)((n + CP_TILE - 1) / CP_TILE);
   compact_count_kernel<<<nb, CP_THREADS, 0, ST(stream)>>>(mask, n, block_counts);
   scan_counts_kernel<<<1, 1024, 0, ST(stream)>>>(block_counts, nb, total_out);
@@ -565,6 +566,11 @@ SGA_API int sga_compact_mask_noalloc(const uint8_t* mask, long long n, int* idx_
             "use sga_compact_mask with your own work array\n",
             n, (long long)SGA_COMPACT_NOALLOC_MAX_ELEMS);
     return SGA_COMPACT_NOALLOC_E_TOO_LARGE;
+  }
+  if ((reinterpret_cast<uintptr_t>(mask) & 15) != 0) {
+    fprintf(stderr, "sga_compact_mask_noalloc: the mask must start on a 16-byte boundary (got %p)\n",
+            static_cast<const void*>(mask));
+    return SGA_COMPACT_NOALLOC_E_ALIGN;
   }
   int rc = 0;
   int* counts = noalloc_scratch_for_current_device(&rc);

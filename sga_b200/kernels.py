@@ -239,6 +239,8 @@ def mask_stats(mask, out3=None):
 
 def compact_mask(mask, idx_out, total_out, err=None):
     n = mask.numel()
+    if mask.data_ptr() % 16:
+        mask = mask.clone()  # the kernels read 16 bytes at a time; a view at an odd offset is copied
     scratch = torch.empty((n + 4095) // 4096, dtype=torch.int32, device=mask.device)
     _chk(lib().sga_compact_mask(mask.data_ptr(), n, scratch.data_ptr(), idx_out.data_ptr(), idx_out.numel(),
                                 total_out.data_ptr(), _p(err), _st()), "sga_compact_mask")

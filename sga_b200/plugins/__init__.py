@@ -1,70 +1,75 @@
-"""Plugin registries for the three class-valued axes (selection, optimizer,
-backend) and the shared ``auto`` resolutions of emission and layout.
+"""Name -> class tables of the three class-valued plugin axes (selection,
+optimizer, backend) and the two ``auto`` resolutions shared by validation and
+the backends. The score axis is data, not classes (``plugins/scores.py``).
 
-The score axis is data, not classes (``plugins/scores.py``). Mirrors
-``sga/plugins/__init__.py:57-153``.
+A table is filled lazily with the built-in plugins the first time it is asked
+for a name; a name registered earlier (by a test or an extension) is kept.
+Public surface as in ``sga/plugins/__init__.py:57-153``: ``register_*``,
+``build_*``, ``plugin_class``, ``resolve_emission``, ``resolve_layout``.
 """
 from __future__ import annotations
 
-_SELECTIONS: dict = {}
-_OPTIMIZERS: dict = {}
-_BACKENDS: dict = {}
-_REGISTRIES = {"selection": _SELECTIONS, "optimizer": _OPTIMIZERS, "backend": _BACKENDS}
+import importlib
+
+# axis -> {name: class}
+_TABLES: dict = {"selection": {}, "optimizer": {}, "backend": {}}
+
+# axis -> {name: (module relative to this package's parent, attribute)}: the built-ins
+_BUILTIN = {
+    "selection": {"topk": ("plugins.selection.topk", "TopkSelection")},
+    "optimizer": {"adamw": ("plugins.optimizer.adam", "SgaAdamW"), "adams": ("plugins.optimizer.adam", "SgaAdamS")},
+    "backend": {"torch_pipelined_index": ("backends.torch_pipelined_index", "TorchPipelinedIndexBackend"),
+                "torch_pipelined_mask": ("backends.torch_pipelined_mask", "TorchPipelinedMaskBackend"),
+                "nccl_pipelined_index": ("backends.nccl_pipelined_index", "NcclPipelinedIndexBackend")},
+}
 
 
 def resolve_emission(value, inherent):
-    """``None`` / ``auto`` -> the backend's inherent form; explicit values win."""
-    return inherent if value in (None, "auto") else value
+    """An explicit emission wins; ``None`` / ``auto`` means the backend's own form."""
+    return value if value not in (None, "auto") else inherent
 
 
 def resolve_layout(layout, block_size):
-    """``auto`` -> ``er`` for element-granular selection, ``bb`` for blocks."""
+    """An explicit layout wins; ``auto`` is ``er`` for single elements and ``bb`` for blocks."""
     if layout not in (None, "auto"):
         return layout
-    return "er" if block_size == 1 else "bb"
+    return "bb" if block_size != 1 else "er"
 
 
-def _register(reg, axis, name, cls):
-    if name in reg:
+def _add(axis: str, name: str, cls) -> None:
+    table = _TABLES[axis]
+    if name in table:
         raise ValueError(f"Duplicate {axis} registration for '{name}'")
-    reg[name] = cls
+    table[name] = cls
 
 
 def register_selection(name, cls):
-    _register(_SELECTIONS, "selection", name, cls)
+    _add("selection", name, cls)
 
 
 def register_optimizer(name, cls):
-    _register(_OPTIMIZERS, "optimizer", name, cls)
+    _add("optimizer", name, cls)
 
 
 def register_backend_plugin(name, cls):
-    _register(_BACKENDS, "backend", name, cls)
+    _add("backend", name, cls)
 
 
 def register_default_plugins() -> None:
-    """Idempotent; a name a test registered first is never overwritten."""
-    from ..backends.nccl_pipelined_index import NcclPipelinedIndexBackend
-    from ..backends.torch_pipelined_index import TorchPipelinedIndexBackend
-    from ..backends.torch_pipelined_mask import TorchPipelinedMaskBackend
-    from .optimizer.adam import SgaAdamS, SgaAdamW
-    from .selection.topk import TopkSelection
-
-    _SELECTIONS.setdefault("topk", TopkSelection)
-    _OPTIMIZERS.setdefault("adamw", SgaAdamW)
-    _OPTIMIZERS.setdefault("adams", SgaAdamS)
-    _BACKENDS.setdefault("torch_pipelined_index", TorchPipelinedIndexBackend)
-    _BACKENDS.setdefault("torch_pipelined_mask", TorchPipelinedMaskBackend)
-    _BACKENDS.setdefault("nccl_pipelined_index", NcclPipelinedIndexBackend)
+    """Import the built-in plugins into the tables (idempotent; existing names are kept)."""
+    root = __name__.rsplit(".", 1)[0]
+    for axis, names in _BUILTIN.items():
+        for name, (module, attr) in names.items():
+            if name not in _TABLES[axis]:
+                _TABLES[axis][name] = getattr(importlib.import_module(f"{root}.{module}"), attr)
 
 
 def plugin_class(axis: str, name: str):
-    registry = _REGISTRIES[axis]
     register_default_plugins()
-    try:
-        return registry[name]
-    except KeyError:
-        raise ValueError(f"Unknown SGA {axis} plugin '{name}'. Registered: {sorted(registry)}") from None
+    table = _TABLES[axis]
+    if name not in table:
+        raise ValueError(f"Unknown SGA {axis} plugin '{name}'. Registered: {sorted(table)}")
+    return table[name]
 
 
 def build_selection(name):

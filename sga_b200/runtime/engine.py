@@ -310,7 +310,7 @@ class SGAEngine:
         step = self._iter + 1
         if self._decided_step == step:
             return self._step_full
-        backend_timer.set_iter(step)
+        backend_timer.at_step(step)
         forced = bool(force_all_reduce) or self._cycle.force_next
         if self._cycle.force_next:
             self._cycle.force_next = False
@@ -341,7 +341,7 @@ class SGAEngine:
         if self._first_step and iteration is not None:
             self._iter = iteration - 1
         full = self._decide(force_all_reduce)
-        if backend_timer.active():
+        if backend_timer.enabled():
             ddp.disarm()
             return
         ddp.arm(None if full else self._sparse_bucket_sync)
@@ -599,23 +599,12 @@ class SGAEngine:
         step and the selection plugin's running state. The reference keeps none of it (its resumed engine
         cold-starts with dense steps until the next boundary, ``sga/engine.py:488-494``); saving it is opt-in."""
         arena = self._ddp.arena
-        sel = {f"{where}.{key}": getattr(owner, key) for where, owner, key in self._selection_state_fields()}
+        hook = getattr(self.selection, "state_dict", None)
+        sel = hook() if callable(hook) else {}
         return {"iter": self._iter, "residual": arena.main_grad.detach().cpu().clone(),
                 "mask": (self._active_mask_arena().detach().cpu().clone() if self._active_support is not None else None),
                 "force_next": bool(getattr(self._cycle, "force_next", False)), "selection": sel,
                 "last_ratio": self.last_ratio}
-
-    def _selection_state_fields(self):
-        """``(where, owner, attribute)`` of the selection plugin's running state: the last threshold on the
-        plugin, the adaptive controller's threshold and warm-up count on its method object."""
-        out = []
-        if "last_threshold" in vars(self.selection):
-            out.append(("plugin", self.selection, "last_threshold"))
-        impl = vars(self.selection).get("_impl")
-        for key in ("tau", "warmup_passed"):
-            if impl is not None and key in vars(impl):
-                out.append(("method", impl, key))
-        return out
 
     def load_state_dict(self, state: dict) -> None:
         arena = self._ddp.arena
@@ -624,10 +613,9 @@ class SGAEngine:
         arena.main_grad.copy_(state["residual"].to(arena.device))
         self._iter, self._first_step = state["iter"], False
         self._cycle.force_next = bool(state.get("force_next", False))
-        saved = state.get("selection", {})
-        for where, owner, key in self._selection_state_fields():
-            if f"{where}.{key}" in saved:
-                setattr(owner, key, saved[f"{where}.{key}"])
+        hook = getattr(self.selection, "load_state_dict", None)
+        if callable(hook) and state.get("selection"):
+            hook(state["selection"])
         if state.get("mask") is not None:
             inactive = self._mask_arena_pair()[1 - self._mask_turn]
             inactive.copy_(state["mask"].to(arena.device))

@@ -387,9 +387,9 @@ class Trainer:
         if getattr(args, "sga_backend_timer", None):
             from ..utils import backend_timer
 
-            if not backend_timer.active():
-                backend_timer.configure(args.sga_backend_timer, self.rank)
-            backend_timer.install_fullsync_wrap()
+            if not backend_timer.enabled():
+                backend_timer.enable(args.sga_backend_timer, self.rank)
+            backend_timer.time_full_syncs()
         if self.sga:
             self.engine = build_engine(trainer_args=args, quiet=quiet)
             self.engine.log_interval = args.log_interval

@@ -1,132 +1,141 @@
-"""Isolated timing of the communication regions (a breakdown instrument).
+"""Isolated timing of the communication regions: a breakdown instrument, never
+a throughput number.
 
-Off (the default) costs one ``None`` check per call site. On, every region is
-bracketed by a device synchronisation at ``begin`` and an event synchronise on
-the calling stream at ``end``, and one JSON line per region goes to
-``<dir>/backend_timer_rank{R}.jsonl``::
+``--sga-backend-timer <dir>`` switches it on. A timed region is a ``with``
+block::
 
-    {"phase": "sparse"|"prescale"|"fullsync", "wall_ms", "device_ms", "rank",
-     "iter", "seq", "ts", ["error"], "backend", ...}
+    with backend_timer.region("sparse", backend=name, bucket=i, k=k):
+        ... launch the bucket's synchronisation ...
 
-``device_ms`` is the CUDA-event time of the region on the calling stream (not
-in the reference's schema; ``wall_ms`` is). The brackets serialise the step
-and destroy overlap on purpose: these are isolated durations, never
-throughput. Refused with overlapped gradient reduction.
-Schema and discipline: ``sga/backend_timer.py:1-200``.
+Entering drains the device (so the region starts on an idle GPU), leaving
+records a CUDA event on the calling stream and waits for it; one JSON line per
+region is appended to ``<dir>/backend_timer_rank{R}.jsonl``::
+
+    {"phase": "sparse" | "prescale" | "fullsync", "wall_ms", "rank", "iter",
+     "seq", "ts", ["error"], "backend", ... , ["device_ms"]}
+
+which is the record of ``sga/backend_timer.py:116-155`` plus ``device_ms``, the
+CUDA-event duration of the region on its stream. The brackets serialise the
+step and destroy every overlap on purpose. Switched off (the default) a region
+costs one ``None`` test. Dense full syncs are timed by wrapping the
+data-parallel chunk class's ``finish_grad_sync`` (``time_full_syncs``), which
+is refused together with overlapped gradient reduction: an overlapped sync
+never passes through that method.
 """
 from __future__ import annotations
 
+import contextlib
 import functools
 import json
 import os
-import sys
 import time
 
 import torch
 
-_STATE = None
 
+class BackendTimer:
+    """One rank's recorder: the open JSONL file, the current step and the running sequence number."""
 
-class _TimerState:
-    def __init__(self, out_dir, rank):
-        self.out_dir = out_dir
-        self.rank = rank
-        self.iter = None
-        self.seq = 0
+    def __init__(self, out_dir: str, rank: int):
+        if not isinstance(out_dir, str) or not out_dir.strip():
+            raise ValueError(f"sga_backend_timer must be a non-empty output directory path (got {out_dir!r})")
         os.makedirs(out_dir, exist_ok=True)
-        self.fh = open(os.path.join(out_dir, f"backend_timer_rank{rank}.jsonl"), "a", buffering=1)
+        self.out_dir, self.rank = out_dir, rank
+        self.step = None
+        self.seq = 0
+        self.path = os.path.join(out_dir, f"backend_timer_rank{rank}.jsonl")
+        self._fh = open(self.path, "a", buffering=1)
 
-    def write(self, record):
-        self.seq += 1
-        self.fh.write(json.dumps(record, sort_keys=True) + "\n")
+    def close(self) -> None:
+        self._fh.close()
+
+    @contextlib.contextmanager
+    def region(self, phase: str, **fields):
+        cuda = torch.cuda.is_available()
+        start = None
+        if cuda:
+            torch.cuda.synchronize()
+            start = torch.cuda.Event(enable_timing=True)
+            start.record(torch.cuda.current_stream())
+        t0 = time.perf_counter()
+        failed = False
+        try:
+            yield
+        except BaseException:
+            failed = True
+            raise
+        finally:
+            device_ms = None
+            if start is not None:
+                stop = torch.cuda.Event(enable_timing=True)
+                stop.record(torch.cuda.current_stream())
+                stop.synchronize()
+                device_ms = round(start.elapsed_time(stop), 6)
+            rec = {"phase": phase, "wall_ms": round((time.perf_counter() - t0) * 1e3, 6), "rank": self.rank,
+                   "iter": self.step, "seq": self.seq, "ts": round(time.time(), 6)}
+            if device_ms is not None:
+                rec["device_ms"] = device_ms
+            if failed:
+                rec["error"] = True
+            rec.update(fields)
+            self.seq += 1
+            self._fh.write(json.dumps(rec, sort_keys=True) + "\n")
 
 
-def active() -> bool:
-    return _STATE is not None
+_timer: BackendTimer | None = None
+_NO_REGION = contextlib.nullcontext()
 
 
-def configure(out_dir, rank) -> None:
-    global _STATE
-    if _STATE is not None:
-        raise RuntimeError(f"sga_backend_timer already configured for rank {_STATE.rank} ({_STATE.out_dir!r})")
-    if not isinstance(out_dir, str) or not out_dir.strip():
-        raise ValueError(f"sga_backend_timer must be a non-empty output directory path (got {out_dir!r})")
-    _STATE = _TimerState(out_dir, rank)
-    print(f"[SGA] backend_timer active: rank {rank} -> {_STATE.fh.name} (isolated comm timing; not e2e numbers)",
+def enabled() -> bool:
+    return _timer is not None
+
+
+def enable(out_dir, rank) -> None:
+    global _timer
+    if _timer is not None:
+        raise RuntimeError(f"sga_backend_timer already configured for rank {_timer.rank} ({_timer.out_dir!r})")
+    _timer = BackendTimer(out_dir, rank)
+    print(f"[SGA] backend_timer active: rank {rank} -> {_timer.path} (isolated comm timing; not e2e numbers)",
           flush=True)
 
 
-def set_iter(step) -> None:
-    if _STATE is not None:
-        _STATE.iter = step
+def disable() -> None:
+    global _timer
+    if _timer is not None:
+        _timer.close()
+        _timer = None
 
 
-def reset() -> None:
-    global _STATE
-    if _STATE is not None:
-        _STATE.fh.close()
-        _STATE = None
+def at_step(step) -> None:
+    if _timer is not None:
+        _timer.step = step
 
 
-def begin():
-    if _STATE is None:
-        return None
-    ev = None
-    if torch.cuda.is_available():
-        torch.cuda.synchronize()
-        ev = torch.cuda.Event(enable_timing=True)
-        ev.record(torch.cuda.current_stream())
-    return (time.perf_counter(), ev)
+def region(phase: str, **fields):
+    """Context manager around one communication region; a no-op while the timer is off."""
+    return _NO_REGION if _timer is None else _timer.region(phase, **fields)
 
 
-def end(token, phase, **fields) -> None:
-    if token is None or _STATE is None:
+def time_full_syncs(chunk_cls=None) -> None:
+    """Time the dense full sync of ``chunk_cls`` (default: this framework's ``DataParallel``) as the
+    ``fullsync`` phase by wrapping its ``finish_grad_sync`` once. Does nothing while the timer is off."""
+    if _timer is None:
         return
-    t0, ev0 = token
-    device_ms = None
-    if ev0 is not None:
-        ev1 = torch.cuda.Event(enable_timing=True)
-        ev1.record(torch.cuda.current_stream())
-        ev1.synchronize()
-        device_ms = round(ev0.elapsed_time(ev1), 6)
-    record = {"phase": phase, "wall_ms": round((time.perf_counter() - t0) * 1e3, 6), "rank": _STATE.rank,
-              "iter": _STATE.iter, "seq": _STATE.seq, "ts": round(time.time(), 6)}
-    if device_ms is not None:
-        record["device_ms"] = device_ms
-    if sys.exc_info()[0] is not None:
-        record["error"] = True
-    record.update(fields)
-    _STATE.write(record)
-
-
-def wrap_finish_grad_sync(chunk_cls) -> None:
-    """Class-level wrap of ``finish_grad_sync`` (the ``fullsync`` phase). Idempotent."""
-    marker = "_sga_backend_timer"
-    orig = getattr(chunk_cls, "finish_grad_sync")
-    if getattr(orig, marker, False):
+    if chunk_cls is None:
+        from ..runtime.ddp import DataParallel as chunk_cls
+    inner = chunk_cls.finish_grad_sync
+    if getattr(inner, "_timed_as_fullsync", False):
         return
 
-    @functools.wraps(orig)
+    @functools.wraps(inner)
     def finish_grad_sync(self, *args, **kwargs):
-        if _STATE is None:
-            return orig(self, *args, **kwargs)
-        cfg = getattr(self, "ddp_config", None)
-        if getattr(cfg, "overlap_grad_reduce", False):
+        if _timer is None:
+            return inner(self, *args, **kwargs)
+        if getattr(getattr(self, "ddp_config", None), "overlap_grad_reduce", False):
             raise RuntimeError("sga_backend_timer refuses overlap_grad_reduce=true: overlapped grad sync bypasses "
                                "finish_grad_sync, so the fullsync phase would record nothing real")
-        token = begin()
-        try:
-            return orig(self, *args, **kwargs)
-        finally:
-            end(token, "fullsync", backend="ddp", bucket=None)
+        with _timer.region("fullsync", backend="ddp", bucket=None):
+            return inner(self, *args, **kwargs)
 
-    setattr(finish_grad_sync, marker, True)
+    finish_grad_sync._timed_as_fullsync = True
     chunk_cls.finish_grad_sync = finish_grad_sync
-
-
-def install_fullsync_wrap() -> None:
-    if _STATE is None:
-        return
-    from ..runtime.ddp import DataParallel
-
-    wrap_finish_grad_sync(DataParallel)

@@ -13,9 +13,9 @@ from sga_b200.utils import backend_timer as BT
 
 @pytest.fixture(autouse=True)
 def _clean():
-    BT.reset()
+    BT.disable()
     yield
-    BT.reset()
+    BT.disable()
 
 
 def _records(d, rank=0):
@@ -23,22 +23,24 @@ def _records(d, rank=0):
         return [json.loads(line) for line in fh if line.strip()]
 
 
-def test_off_is_inert():
-    assert not BT.active()
-    assert BT.begin() is None
-    BT.end(None, "sparse")  # no state, no file, no error
-    BT.set_iter(3)
+def test_off_is_inert(tmp_path):
+    assert not BT.enabled()
+    with BT.region("sparse", backend="x"):  # no state, no file, no error
+        pass
+    BT.at_step(3)
+    BT.time_full_syncs()
+    assert not os.listdir(tmp_path)
 
 
 def test_records_schema_and_sequence(tmp_path):
     d = str(tmp_path / "timer")
-    BT.configure(d, 2)
-    assert BT.active()
-    BT.set_iter(7)
-    tok = BT.begin()
-    BT.end(tok, "sparse", backend="torch_pipelined_index", bucket=4, nbytes=128)
-    tok = BT.begin()
-    BT.end(tok, "prescale", backend="torch_pipelined_index", bucket=4)
+    BT.enable(d, 2)
+    assert BT.enabled()
+    BT.at_step(7)
+    with BT.region("sparse", backend="torch_pipelined_index", bucket=4, nbytes=128):
+        pass
+    with BT.region("prescale", backend="torch_pipelined_index", bucket=4):
+        pass
     recs = _records(d, rank=2)
     assert [r["phase"] for r in recs] == ["sparse", "prescale"]
     assert [r["seq"] for r in recs] == [0, 1]
@@ -47,21 +49,19 @@ def test_records_schema_and_sequence(tmp_path):
     assert recs[0]["nbytes"] == 128 and recs[0]["bucket"] == 4
 
 
-def test_configure_twice_and_bad_path_refused(tmp_path):
+def test_enable_twice_and_bad_path_refused(tmp_path):
     with pytest.raises(ValueError):
-        BT.configure("  ", 0)
-    BT.configure(str(tmp_path), 0)
+        BT.enable("  ", 0)
+    BT.enable(str(tmp_path), 0)
     with pytest.raises(RuntimeError, match="already configured"):
-        BT.configure(str(tmp_path), 0)
+        BT.enable(str(tmp_path), 0)
 
 
-def test_error_inside_region_is_marked(tmp_path):
-    BT.configure(str(tmp_path), 0)
-    tok = BT.begin()
-    try:
-        raise OSError("link down")
-    except OSError:
-        BT.end(tok, "sparse", backend="x")
+def test_error_inside_region_is_marked_and_propagates(tmp_path):
+    BT.enable(str(tmp_path), 0)
+    with pytest.raises(OSError, match="link down"):
+        with BT.region("sparse", backend="x"):
+            raise OSError("link down")
     assert _records(str(tmp_path))[0]["error"] is True
 
 
@@ -77,19 +77,24 @@ def test_fullsync_wrap_refuses_overlap_and_is_idempotent(tmp_path):
             Chunk.calls += 1
             return "done"
 
-    BT.wrap_finish_grad_sync(Chunk)
+    plain = Chunk.finish_grad_sync
+    BT.time_full_syncs(Chunk)
+    assert Chunk.finish_grad_sync is plain  # timer off: the class is left alone
+    BT.enable(str(tmp_path), 0)
+    BT.time_full_syncs(Chunk)
     first = Chunk.finish_grad_sync
-    BT.wrap_finish_grad_sync(Chunk)
-    assert Chunk.finish_grad_sync is first  # wrapped once
+    BT.time_full_syncs(Chunk)
+    assert Chunk.finish_grad_sync is first and first is not plain  # wrapped once
     c = Chunk()
-    assert c.finish_grad_sync() == "done"  # timer off: straight through
-    BT.configure(str(tmp_path), 0)
     with pytest.raises(RuntimeError, match="overlap_grad_reduce"):
         c.finish_grad_sync()
     Cfg.overlap_grad_reduce = False
     assert c.finish_grad_sync() == "done"
     recs = _records(str(tmp_path))
     assert len(recs) == 1 and recs[0]["phase"] == "fullsync" and recs[0]["backend"] == "ddp"
+    BT.disable()
+    assert c.finish_grad_sync() == "done"  # switched off again: straight through, nothing recorded
+    assert len(_records(str(tmp_path))) == 1
 
 
 def test_trainer_writes_sparse_and_fullsync_regions(tmp_path):

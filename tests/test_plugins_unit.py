@@ -11,7 +11,7 @@ from sga_b200 import kernels_torch as KT
 from sga_b200.plugins import (plugin_class, register_backend_plugin, resolve_emission, resolve_layout)
 from sga_b200.plugins.optimizer.reference import grad_correct_torch
 from sga_b200.plugins.scores import compute_score, get_score_spec, register_score, score_names, ScoreSpec
-from sga_b200.plugins.selection import _adaptive as AD
+from sga_b200.plugins.selection import threshold as AD
 from sga_b200.plugins.selection import _histogram as H
 from sga_b200.plugins.selection._exact import select_masks_exact_kthvalue
 from sga_b200.support import (BucketSupport, IndexPool, Support, block_desc_from_mask, block_idx_from_mask,
@@ -200,10 +200,10 @@ def test_block_selection():
 def test_adaptive_controller_lifecycle():
     views = [_adversarial("normal", 50000, 9)]
     n = 50000
-    ad = AD.AdaptiveTau(10.0, 2, "balanced")
+    ad = AD.AdaptiveThresholdSelect(10.0, 2, "balanced")
     assert ad.warmup_sync_target(0, 4) == 1 and ad.warmup_sync_target(100, 4) == 0
-    assert AD.AdaptiveTau(10.0, None, "fast").warmup_sync_target(0, 4) is None
-    assert AD.AdaptiveTau(10.0, 5, "fast").warmup_sync_target(0, 4) == 4
+    assert AD.AdaptiveThresholdSelect(10.0, None, "fast").warmup_sync_target(0, 4) is None
+    assert AD.AdaptiveThresholdSelect(10.0, 5, "fast").warmup_sync_target(0, 4) == 4
     thr0, m0 = ad.select(views, n // 10, None, None)
     assert ad.warmup_passed == 1 and ad.tau == thr0
     ad.select(views, n // 10, None, None)
@@ -212,24 +212,24 @@ def test_adaptive_controller_lifecycle():
     used, masks = ad.select(views, n // 10, None, None)      # persistent tau from here on
     assert used == tau and torch.equal(masks[0], (views[0].abs() >= tau).to(torch.uint8))
     # outside the dead band the threshold moves by (measured/target)^0.5, clamped
-    assert AD.adapt_threshold(1.0, 0.105, 0.10) == 1.0
-    assert math.isclose(AD.adapt_threshold(1.0, 0.20, 0.10), 1.15)
-    assert math.isclose(AD.adapt_threshold(1.0, 0.02, 0.10), 0.9)
-    assert math.isclose(AD.adapt_threshold(2.0, 0.12, 0.10), 2.0 * math.sqrt(1.2))
+    assert AD.step_threshold(1.0, 0.105, 0.10) == 1.0
+    assert math.isclose(AD.step_threshold(1.0, 0.20, 0.10), 1.15)
+    assert math.isclose(AD.step_threshold(1.0, 0.02, 0.10), 0.9)
+    assert math.isclose(AD.step_threshold(2.0, 0.12, 0.10), 2.0 * math.sqrt(1.2))
     # collapse: a zero measured ratio re-bootstraps, clamped to the smallest positive edge
     ad.tau = 1e9
     thr, _ = ad.select(views, n // 10, None, None)
     assert 0 < thr < 1.0
     # a warm-up select that misses the band resets the consecutive count (fast over-selects here)
-    miss = AD.AdaptiveTau(10.0, 2, "fast")
+    miss = AD.AdaptiveThresholdSelect(10.0, 2, "fast")
     miss.warmup_passed = 1
     _, mm = miss.select(views, n // 10, None, None)
     measured = int(mm[0].sum()) / n
     assert miss.warmup_passed == (2 if abs(measured - 0.10) <= 0.01 else 0)
     zero = [torch.zeros(1000)]
-    ad2 = AD.AdaptiveTau(10.0, 1, "fast")
+    ad2 = AD.AdaptiveThresholdSelect(10.0, 1, "fast")
     t, _ = ad2.select(zero, 100, None, None)
-    assert t == AD.tau_floor("fast") > 0.0
+    assert t == AD.smallest_threshold("fast") > 0.0
 
 
 def test_topk_plugin_k_and_rank_gate():

@@ -237,7 +237,7 @@ def test_selection_plugins_bitwise(ref):
     R_hist = ref("sga.plugins.selection._histogram").select_masks_histogram
     R_ex = ref("sga.plugins.selection._exact").select_masks_exact_kthvalue
     RA = ref("sga.plugins.selection._adaptive").AdaptiveTau
-    from sga_b200.plugins.selection._adaptive import AdaptiveTau as MA
+    from sga_b200.plugins.selection.threshold import AdaptiveThresholdSelect as MA
     from sga_b200.plugins.selection._exact import select_masks_exact_kthvalue as M_ex
     from sga_b200.plugins.selection._histogram import select_masks_histogram as M_hist
 

@@ -74,3 +74,15 @@ def test_noalloc_refuses_masks_beyond_its_limit():
     assert rc == E_TOO_LARGE
     x = torch.ones(4, device=DEV)
     assert float(x.sum().item()) == 4.0
+
+
+def test_noalloc_refuses_a_mask_off_the_16_byte_boundary():
+    fn, _ = _lib()
+    buf = torch.zeros(4096 + 16, dtype=torch.uint8, device=DEV)
+    idx = torch.empty(64, dtype=torch.int32, device=DEV)
+    tot = torch.zeros(1, dtype=torch.int64, device=DEV)
+    # refused on the host before any launch: a misaligned 16-byte load would fault the context
+    rc = fn(buf.data_ptr() + 3, 4096, idx.data_ptr(), 64, tot.data_ptr(), None, None)
+    assert rc == -10
+    torch.cuda.synchronize()
+    assert int(tot.item()) == 0
