@@ -7,10 +7,15 @@ private communicator and stream,
 ``sga/backends/nccl_pipelined_index.py:133-669``). Here the same contract --
 "given the dense fp32 bucket and the sorted support, leave the reduced values
 at the support positions" -- is one fused peer-memory kernel
-(``sga_p2p_allreduce`` with its pack prologue and scatter epilogue), so there
-is no library fork to load. The block form takes packed ``head | tail_len``
-descriptors: a descriptor's run is ``tail_len`` elements when non-zero, else
-a whole block.
+(``sga_p2p_allreduce``), so there is no library fork to load.
+
+Block form (``layout bb``): the support travels as packed ``head | tail_len``
+descriptors, built on the device (``csrc/select.cu``), and the kernel itself
+follows them: every descriptor is a run of 16 to 256 bytes that is gathered
+into the payload, reduced across the ranks and scattered back with 128-bit
+loads and stores; nothing is expanded to element indices. On the library
+transports (``nccl`` / ``gloo``, and CPU) the descriptors are expanded once per
+cycle and the element path of the parent backend carries them.
 
 Kept, like the reference's, as a separately named backend with its own
 runtime probe; refuses resume unless ``SGA_ALLOW_RESUME_PIPELINED=1``.
@@ -65,41 +70,63 @@ class NcclPipelinedIndexBackend(TorchPipelinedIndexBackend):
             raise ValueError("nccl_pipelined_index refuses to resume from a checkpoint "
                              f"(set {ENV_ALLOW_RESUME_PIPELINED}=1 to override)")
 
+    def _runs(self, sup):
+        """Payload elements of a block-form bucket: whole blocks, the last one of a span zero-padded."""
+        return sup.block_desc.numel() * sup.block_size
+
     def on_support_activated(self, support, bucket_states) -> None:
         self._desc_idx = {}
-        for bs, sup in zip(bucket_states, support.buckets):
-            if sup.block_size > 1 and self._layout_for(sup) == "bb":
-                self._desc_idx[id(sup)] = expand_descriptors(sup.block_desc, sup.block_size)
-        if self.transport != "p2p":
-            return
+        p2p = self.transport == "p2p"
         offs, total = {}, 0
         for bs, sup in zip(bucket_states, support.buckets):
-            k = self._desc_idx[id(sup)].numel() if id(sup) in self._desc_idx else sup.num_selected()
+            blocks = sup.block_size > 1 and self._layout_for(sup) == "bb"
+            if blocks and not p2p:
+                self._desc_idx[id(sup)] = expand_descriptors(sup.block_desc, sup.block_size)
+            k = self._runs(sup) if blocks else sup.num_selected()
             offs[id(bs)] = total
             total += (k + 63) // 64 * 64
+        if not p2p:
+            return
         self._payload_off = offs
         need = 4 * max(total, 64)
         if self._payload is None or self._payload.nbytes < need:
             self._payload = self.ddp.pool.alloc(need + need // 4)
 
     def _impl(self, grad_data, support, comm_group, factor_in, reduce_op, key, bucket_state):
-        if self._layout_for(support) == "bb":
-            idx = self._desc_idx.get(id(support))
-            if idx is None:
-                idx = expand_descriptors(support.block_desc, support.block_size)
+        if self._layout_for(support) != "bb":
+            return super()._impl(grad_data, support, comm_group, factor_in, reduce_op, key, bucket_state)
+        if self.transport == "p2p":
+            from ..parallel import p2p
 
-            class _View:
-                pass
+            desc = support.block_desc
+            if desc.numel() == 0:
+                return None
+            ddp = self.ddp
+            avg = reduce_op == dist.ReduceOp.AVG
+            factor = float(factor_in) if (reduce_op == dist.ReduceOp.SUM and factor_in != 1.0) else 1.0
+            ch = ddp.channels[key % len(ddp.channels)] if isinstance(key, int) else ddp.channels[0]
+            p2p.allreduce_(ch, self._payload, 4 * self._payload_off[id(bucket_state)], self._runs(support),
+                           scale=(1.0 / ddp.world) if avg else 1.0, grad=grad_data, idx=desc, factor=factor,
+                           pack=True, zero_after_pack=False, scatter=True, block_x=int(support.block_size),
+                           sumsq_out=self.sumsq, accumulate=True, max_ctas=ddp.ddp_config.comm_max_ctas)
+            return None
+        idx = self._desc_idx.get(id(support))
+        if idx is None:
+            idx = expand_descriptors(support.block_desc, support.block_size)
+        view = _ElementView(idx, grad_data.numel())
+        saved_layout, self.layout = self.layout, "er"
+        try:
+            return super()._impl(grad_data, view, comm_group, factor_in, reduce_op, key, bucket_state)
+        finally:
+            self.layout = saved_layout
 
-            view = _View()
-            view.idx = idx
-            view.block_size = 1
-            view.split = int(torch.searchsorted(idx, grad_data.numel() // 2).item()) if idx.numel() else 0
-            view.n_selected = idx.numel()
-            saved_layout = self.layout
-            self.layout = "er"
-            try:
-                return super()._impl(grad_data, view, comm_group, factor_in, reduce_op, key, bucket_state)
-            finally:
-                self.layout = saved_layout
-        return super()._impl(grad_data, support, comm_group, factor_in, reduce_op, key, bucket_state)
+
+class _ElementView:
+    """What the element path of the parent backend reads from a support, over expanded descriptors."""
+
+    block_size = 1
+
+    def __init__(self, idx: torch.Tensor, n: int):
+        self.idx = idx
+        self.n_selected = idx.numel()
+        self.split = int(torch.searchsorted(idx, n // 2).item()) if idx.numel() else 0

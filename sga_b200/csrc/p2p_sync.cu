@@ -36,6 +36,9 @@ struct AllreduceArgs {
   const int* idx;
   float factor;
   int do_pack, zero_after_pack, do_scatter;
+  int block_x;  // 0: idx holds element positions. > 0: idx holds packed `head | tail_len` descriptors of
+                // block_x-element runs (a power of two >= 4, heads block_x-aligned) and the payload is
+                // n / block_x whole blocks, moved 16 bytes at a time
   int rs_only;  // reduce-scatter only: the owner keeps the reduced slice, nothing is written to peers
   float* norm_slots[MAXW];
   float* cta_partials;
@@ -50,7 +53,33 @@ __global__ void __launch_bounds__(512) p2p_allreduce_kernel(const AllreduceArgs 
   const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long nth = (long long)gridDim.x * blockDim.x;
   float* mine = a.buf[c.rank];
-  if (a.do_pack) {
+  if (a.do_pack && a.block_x > 0) {
+    // descriptor wire form: runs of 16 to 256 bytes, gathered with 128-bit loads and stores
+    const int x = a.block_x;
+    for (long long q = tid; q * 4 < a.n; q += nth) {
+      const long long i = q * 4;
+      const int d = a.idx[i / x];
+      const int off = (int)(i % x);
+      const int head = d & ~(x - 1), tail = d & (x - 1);
+      const int run = tail ? tail : x;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      float* src = a.grad + head + off;
+      if (off + 4 <= run) {
+        v = *reinterpret_cast<const float4*>(src);
+        if (a.zero_after_pack) *reinterpret_cast<float4*>(src) = make_float4(0.f, 0.f, 0.f, 0.f);
+      } else {
+        float t[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int j = 0; j < 4 && off + j < run; ++j) {
+          t[j] = src[j];
+          if (a.zero_after_pack) src[j] = 0.f;
+        }
+        v = make_float4(t[0], t[1], t[2], t[3]);
+      }
+      v.x *= a.factor; v.y *= a.factor; v.z *= a.factor; v.w *= a.factor;
+      *reinterpret_cast<float4*>(mine + i) = v;
+    }
+    __threadfence_system();
+  } else if (a.do_pack) {
     for (long long i = tid; i < a.n; i += nth) {
       const int p = a.idx[i];
       const float v = a.grad[p];
@@ -105,7 +134,22 @@ __global__ void __launch_bounds__(512) p2p_allreduce_kernel(const AllreduceArgs 
   publish_norm(c, a.cta_partials, a.norm_slots);
   peer_signal(c, 1);
   peer_wait(c, 1, c.seq);
-  if (a.do_scatter) {
+  if (a.do_scatter && a.block_x > 0) {
+    const int x = a.block_x;
+    for (long long q = tid; q * 4 < a.n; q += nth) {
+      const long long i = q * 4;
+      const int d = a.idx[i / x];
+      const int off = (int)(i % x);
+      const int head = d & ~(x - 1), tail = d & (x - 1);
+      const int run = tail ? tail : x;
+      float* dst = a.grad + head + off;
+      if (off + 4 <= run) {
+        *reinterpret_cast<float4*>(dst) = *reinterpret_cast<const float4*>(mine + i);
+      } else {
+        for (int j = 0; j < 4 && off + j < run; ++j) dst[j] = mine[i + j];
+      }
+    }
+  } else if (a.do_scatter) {
     for (long long i = tid; i < a.n; i += nth) a.grad[a.idx[i]] = mine[i];
   }
   collect_norm(c, a.norm_slots, a.sumsq_out, a.accumulate);
@@ -226,7 +270,7 @@ using namespace sga;
 
 SGA_API int sga_p2p_allreduce(const SgaPeerDesc* d, void* const* bufs, long long n, float scale, float* grad,
                               const int* idx, float factor, int do_pack, int zero_after_pack, int do_scatter,
-                              int rs_only, void* const* norm_slots, float* cta_partials, float* sumsq_out, int accumulate,
+                              int block_x, int rs_only, void* const* norm_slots, float* cta_partials, float* sumsq_out, int accumulate,
                               int max_ctas, void* stream) {
   if (d->W > MAXW) return -1;
   AllreduceArgs a;
@@ -236,7 +280,11 @@ SGA_API int sga_p2p_allreduce(const SgaPeerDesc* d, void* const* bufs, long long
     a.norm_slots[i] = i < d->W ? reinterpret_cast<float*>(norm_slots[i]) : nullptr;
   }
   a.n = n; a.scale = scale; a.grad = grad; a.idx = idx; a.factor = factor;
+  if (block_x != 0) {
+    if (block_x < 4 || (block_x & (block_x - 1)) || n % block_x || (reinterpret_cast<uintptr_t>(grad) & 15)) return -6;
+  }
   a.do_pack = do_pack; a.zero_after_pack = zero_after_pack; a.do_scatter = do_scatter; a.rs_only = rs_only;
+  a.block_x = block_x;
   a.cta_partials = cta_partials; a.sumsq_out = sumsq_out; a.accumulate = accumulate;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   cudaMemsetAsync(a.c.grid_counter, 0, sizeof(int), st);

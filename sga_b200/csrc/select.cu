@@ -360,6 +360,65 @@ __global__ void expand_blocks_kernel(const uint8_t* __restrict__ bmask, long lon
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gstride) mask[i] = bmask[i / X];
 }
 
+// ------------------------------------------------------------ block forms
+// Blocks of X elements tile every parameter span from its start and never cross a span boundary.
+// Block b belongs to the span s with span_boff[s] <= b < span_boff[s + 1]; its head is
+// span_start[s] + (b - span_boff[s]) * X and it is span_end[s] - head long when that is below X.
+// block_flags_kernel writes, per block, 1 when any of its elements is selected, and counts the
+// blocks that are selected only in part (the descriptor wire form moves whole runs and refuses
+// those). The flags then go through the mask compaction above; block_heads_kernel turns the
+// surviving block numbers into heads or packed `head | tail_len` descriptors.
+// Replaces the per-span loops of sga/support.py:102-206.
+__device__ __forceinline__ int span_of_block(const long long* __restrict__ span_boff, int nspan, long long b) {
+  int lo = 0, hi = nspan - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (span_boff[mid] <= b) lo = mid; else hi = mid - 1;
+  }
+  return lo;
+}
+
+__global__ void block_flags_kernel(const uint8_t* __restrict__ mask, const long long* __restrict__ span_start,
+                                   const long long* __restrict__ span_end, const long long* __restrict__ span_boff,
+                                   int nspan, int X, long long nblocks, uint8_t* __restrict__ flags,
+                                   unsigned long long* __restrict__ partial) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x; b < nblocks; b += stride) {
+    const int s = span_of_block(span_boff, nspan, b);
+    const long long head = span_start[s] + (b - span_boff[s]) * X;
+    const int len = (int)min((long long)X, span_end[s] - head);
+    int on = 0;
+    if (len == X && X % 4 == 0 && (head & 3) == 0) {
+      for (int i = 0; i < X; i += 4) {
+        const uchar4 m = *reinterpret_cast<const uchar4*>(mask + head + i);
+        on += (m.x != 0) + (m.y != 0) + (m.z != 0) + (m.w != 0);
+      }
+    } else {
+      for (int i = 0; i < len; ++i) on += mask[head + i] != 0;
+    }
+    flags[b] = on ? 1 : 0;
+    if (on && on < len && partial) atomicAdd(partial, 1ULL);
+  }
+}
+
+__global__ void block_heads_kernel(const int* __restrict__ block_ids, long long kb,
+                                   const long long* __restrict__ span_start, const long long* __restrict__ span_end,
+                                   const long long* __restrict__ span_boff, int nspan, int X, int as_desc,
+                                   int* __restrict__ out) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x; j < kb; j += stride) {
+    const long long b = block_ids[j];
+    const int s = span_of_block(span_boff, nspan, b);
+    const long long head = span_start[s] + (b - span_boff[s]) * X;
+    long long v = head;
+    if (as_desc) {
+      const long long len = min((long long)X, span_end[s] - head);
+      v = head | (len < X ? len : 0);
+    }
+    out[j] = (int)v;
+  }
+}
+
 static inline int grid_for(long long n, int per_block, int cap = 148 * 8) {
   long long b = (n + per_block - 1) / per_block;
   if (b < 1) b = 1;
@@ -431,6 +490,28 @@ SGA_API int sga_compact_mask(const uint8_t* mask, long long n, int* block_counts
   compact_count_kernel<<<nb, CP_THREADS, 0, ST(stream)>>>(mask, n, block_counts);
   scan_counts_kernel<<<1, 1024, 0, ST(stream)>>>(block_counts, nb, total_out);
   compact_scatter_kernel<<<nb, CP_THREADS, 0, ST(stream)>>>(mask, n, block_counts, idx_out, cap, err);
+  return LAUNCH_OK();
+}
+
+// Per-block "any element selected" flags over the spans' block tiling; *partial (nullable, zeroed by
+// the caller) counts blocks that are selected only in part.
+SGA_API int sga_block_flags(const uint8_t* mask, const long long* span_start, const long long* span_end,
+                            const long long* span_boff, int nspan, int X, long long nblocks, uint8_t* flags,
+                            unsigned long long* partial, void* stream) {
+  if (nblocks <= 0) return 0;
+  if (nspan < 1 || X < 1) return -6;
+  block_flags_kernel<<<grid_for(nblocks, 256), 256, 0, ST(stream)>>>(mask, span_start, span_end, span_boff, nspan, X,
+                                                                    nblocks, flags, partial);
+  return LAUNCH_OK();
+}
+
+// Ascending block numbers -> block heads (as_desc = 0) or packed head | tail_len descriptors (1).
+SGA_API int sga_block_heads(const int* block_ids, long long kb, const long long* span_start,
+                            const long long* span_end, const long long* span_boff, int nspan, int X, int as_desc,
+                            int* out, void* stream) {
+  if (kb <= 0) return 0;
+  block_heads_kernel<<<grid_for(kb, 256), 256, 0, ST(stream)>>>(block_ids, kb, span_start, span_end, span_boff, nspan,
+                                                              X, as_desc, out);
   return LAUNCH_OK();
 }
 

@@ -29,6 +29,8 @@ register_sigs({
     "sga_mask_stats": [_P, _L, _P, _P],
     "sga_compact_mask": [_P, _L, _P, _P, _L, _P, _P, _P],
     "sga_dir_table": [_P, _L, _P, _I, _P],
+    "sga_block_flags": [_P, _P, _P, _P, _I, _I, _L, _P, _P, _P],
+    "sga_block_heads": [_P, _L, _P, _P, _P, _I, _I, _I, _P, _P],
     "sga_pack": [_P, _P, _L, _P, _F, _I, _I, _P],
     "sga_scatter": [_P, _P, _P, _L, _I, _P],
     "sga_gather_blocks": [_P, _P, _P, _L, _I, _L, _P, _F, _I, _I, _P],
@@ -50,7 +52,7 @@ register_sigs({
     "sga_ipc_get_handle": [_P, _P],
     "sga_ipc_open": [_P, _P],
     "sga_ipc_close": [_P],
-    "sga_p2p_allreduce": [_P, _P, _L, _F, _P, _P, _F, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P],
+    "sga_p2p_allreduce": [_P, _P, _L, _F, _P, _P, _F, _I, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P],
     "sga_p2p_mask_union": [_P, _P, _P, _P, _L, _F, _P, _P, _P, _P, _I, _P, _I, _P],
     "sga_index_sync": [_P, _P, _P],
     "sga_dense_adamw_ag": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _P, _P, _I, _P, _F, _F, _F, _F, _F, _F, _F,
@@ -244,6 +246,43 @@ def compact_mask(mask, idx_out, total_out, err=None):
     scratch = torch.empty((n + 4095) // 4096, dtype=torch.int32, device=mask.device)
     _chk(lib().sga_compact_mask(mask.data_ptr(), n, scratch.data_ptr(), idx_out.data_ptr(), idx_out.numel(),
                                 total_out.data_ptr(), _p(err), _st()), "sga_compact_mask")
+
+
+class SpanTable:
+    """Device copy of a bucket's parameter spans with the running block count of an X-element tiling."""
+
+    def __init__(self, spans, x: int, device):
+        starts = [int(s) for s, _e in spans]
+        ends = [int(e) for _s, e in spans]
+        boff, run = [], 0
+        for s, e in zip(starts, ends):
+            boff.append(run)
+            run += (e - s + x - 1) // x
+        self.nblocks, self.nspan, self.x = run, len(starts), int(x)
+        t = lambda v: torch.tensor(v, dtype=torch.int64, device=device)  # noqa: E731
+        self.start, self.end, self.boff = t(starts), t(ends), t(boff + [run])
+
+
+def block_forms(mask, spans, x: int, as_desc: bool, require_whole: bool = False):
+    """Block heads (or packed ``head | tail_len`` descriptors) of the blocks with any selected
+    element, ascending: flags per block, the mask compaction over the flags, heads from the
+    surviving block numbers. ``require_whole`` also returns the number of partly selected blocks."""
+    tab = SpanTable(spans, x, mask.device)
+    if tab.nblocks == 0 or tab.nspan == 0:
+        return torch.empty(0, dtype=torch.int32, device=mask.device), 0
+    flags = torch.empty(tab.nblocks, dtype=torch.uint8, device=mask.device)
+    partial = torch.zeros(1, dtype=torch.int64, device=mask.device)
+    _chk(lib().sga_block_flags(mask.data_ptr(), tab.start.data_ptr(), tab.end.data_ptr(), tab.boff.data_ptr(),
+                               tab.nspan, tab.x, tab.nblocks, flags.data_ptr(), partial.data_ptr(), _st()),
+         "sga_block_flags")
+    ids = torch.empty(tab.nblocks, dtype=torch.int32, device=mask.device)
+    total = torch.zeros(1, dtype=torch.int64, device=mask.device)
+    compact_mask(flags, ids, total)
+    kb = int(total.item())
+    out = torch.empty(kb, dtype=torch.int32, device=mask.device)
+    _chk(lib().sga_block_heads(ids.data_ptr(), kb, tab.start.data_ptr(), tab.end.data_ptr(), tab.boff.data_ptr(),
+                               tab.nspan, tab.x, int(as_desc), out.data_ptr(), _st()), "sga_block_heads")
+    return out, (int(partial.item()) if require_whole else 0)
 
 
 def dir_table(idx, k, n):

@@ -11,6 +11,8 @@ Reference: ``sga/launcher/launcher_ssh.py:30-537``, ``launcher_base.py``.
 """
 from __future__ import annotations
 
+from typing import Optional
+
 import enum
 import os
 import sys
@@ -116,7 +118,25 @@ class SshLauncher(LauncherBase):
             self._tailer.stop()
         return codes
 
-    def query(self) -> JobStatus:
+    def query(self, interval: float = 10.0, timeout: Optional[float] = None, out=print):
+        """Poll the job status every ``interval`` seconds and report it through ``out``; with a
+        ``timeout`` stop after that many seconds, without one keep going until interrupted (Ctrl-C).
+        Blocking; returns the last status seen. ``query_once`` is the non-blocking form.
+        (``sga/launcher/launcher_ssh.py:500-537``.)"""
+        import time
+
+        start, last = time.time(), None
+        try:
+            while timeout is None or time.time() - start < timeout:
+                last = self.query_once()
+                out(f"Job status: {last.name}")
+                time.sleep(max(0.0, float(interval)))
+            out(f"Query timeout reached ({timeout}s)")
+        except KeyboardInterrupt:
+            out("Query interrupted by user")
+        return last
+
+    def query_once(self) -> JobStatus:
         alive = 0
         for rank, h in enumerate(self.hosts):
             pid_file = os.path.join(self.backend.pid_dir, f"host_{rank}_{h['host']}.pid")

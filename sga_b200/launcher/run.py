@@ -62,7 +62,12 @@ class Runner:
             script = open(run_sh).read().replace("nohup ", "").rsplit(" >> ", 1)[0]
             return subprocess.run(["bash", "-c", script]).returncode
         if action == "query":
-            st = self.launcher.query()
+            runner = (self.config.get("experiment", {}) or {}).get("runner", {}) or {}
+            if runner.get("query_timeout") is not None or runner.get("query_interval") is not None:
+                st = self.launcher.query(interval=float(runner.get("query_interval", 10)),
+                                         timeout=runner.get("query_timeout"))
+            else:
+                st = self.launcher.query_once()
             print(f"[launcher] job status: {st.value}")
             return st
         if action == "stop":

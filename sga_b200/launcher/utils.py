@@ -126,10 +126,46 @@ def node_overrides(config: dict, host: str, node_type: Optional[str]) -> dict:
     return out
 
 
+def find_latest_stdout_log(root: str) -> Optional[str]:
+    """The ``stdout.log`` to follow on the console: torchrun (with ``--log-dir`` / ``--redirects``)
+    writes ``<root>/.../<run>/attempt_<N>/<local rank>/stdout.log``. Of the directories that hold
+    attempts the lexicographically last (newest timestamp / run id) wins, inside it the highest
+    attempt number, inside that the highest local rank that has a log. ``None`` when there is none yet.
+    Same choice as ``sga/launcher/utils.py:397-443``."""
+    if not os.path.isdir(root):
+        return None
+    holders = sorted((d for d, subs, _f in os.walk(root) if any(x.startswith("attempt_") for x in subs)),
+                     reverse=True)
+    if not holders:
+        return None
+
+    def number(name: str, prefix: str = "") -> int:
+        tail = name[len(prefix):]
+        return int(tail) if tail.isdigit() else -1
+
+    run = holders[0]
+    attempts = sorted((x for x in os.listdir(run) if x.startswith("attempt_")),
+                      key=lambda x: number(x, "attempt_"), reverse=True)
+    if not attempts:
+        return None
+    attempt = os.path.join(run, attempts[0])
+    try:
+        ranks = sorted((x for x in os.listdir(attempt) if x.isdigit()), key=int, reverse=True)
+    except OSError:
+        return None
+    for r in ranks:
+        log = os.path.join(attempt, r, "stdout.log")
+        if os.path.exists(log):
+            return log
+    return None
+
+
 class LogTailer:
     """Follows a file from its current end and prints new lines (node 0's log)."""
 
-    def __init__(self, path: str, prefix: str = "", poll_s: float = 0.5, out=print):
+    def __init__(self, path, prefix: str = "", poll_s: float = 0.5, out=print):
+        # ``path``: a file name, or a callable returning the current file to follow (or None while
+        # there is none yet), e.g. ``lambda: find_latest_stdout_log(log_dir)``
         self.path, self.prefix, self.poll_s, self.out = path, prefix, poll_s, out
         self._stop = threading.Event()
         self._t = None
@@ -140,10 +176,16 @@ class LogTailer:
         return self
 
     def _run(self):
-        pos = 0
+        pos, current = 0, None
         while not self._stop.is_set():
+            path = self.path() if callable(self.path) else self.path
+            if path != current:
+                pos, current = 0, path  # a new attempt's log: start at its beginning
+            if path is None:
+                time.sleep(self.poll_s)
+                continue
             try:
-                with open(self.path) as fh:
+                with open(path) as fh:
                     fh.seek(pos)
                     for line in fh:
                         self.out(self.prefix + line.rstrip("\n"))

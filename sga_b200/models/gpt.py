@@ -73,6 +73,9 @@ PRESETS = {
     "llama_tiny": GPTConfig("llama_tiny", 4, 512, 2048, 8, 2, 64, 32000, 512, 500000.0, 1e-5, False, False),
     "test_tiny": GPTConfig("test_tiny", 2, 128, 256, 4, 2, 32, 512, 32, 10000.0, 1e-5, False, True),
     "test_tiny_qk": GPTConfig("test_tiny_qk", 2, 128, 256, 4, 2, 32, 512, 32, 10000.0, 1e-6, True, False),
+    # small models whose head dimensions take the native attention kernels (64 and 128; grouped queries)
+    "test_hd64": GPTConfig("test_hd64", 2, 256, 512, 4, 2, 64, 512, 320, 500000.0, 1e-5, False, True),
+    "test_hd128_qk": GPTConfig("test_hd128_qk", 2, 256, 512, 4, 2, 128, 512, 320, 1e6, 1e-6, True, False),
 }
 
 

@@ -46,8 +46,22 @@ def native_available(qkv, hd: int = 64) -> bool:
         return False
 
 
-def attn_fwd(qkv, B, S, nq, nkv, hd):
+def _whole_sequences_only(cp_group) -> None:
+    """``cp_group`` is the extension point for context parallelism (sequence shards exchanging key /
+    value blocks around a ring): the entry points take it so that callers can already thread a group
+    through, but every sequence must live whole on one rank for now."""
+    if cp_group is None:
+        return
+    import torch.distributed as dist
+
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(cp_group) > 1:
+        raise NotImplementedError("context-parallel attention (cp_group with more than one rank) is not built: "
+                                  "the attention kernels take whole sequences")
+
+
+def attn_fwd(qkv, B, S, nq, nkv, hd, cp_group=None):
     """Returns ``(ctx [T, nq*hd] bf16, saved)``."""
+    _whole_sequences_only(cp_group)
     scale = 1.0 / math.sqrt(hd)
     if native_available(qkv, hd):
         from . import attention_native as AN
@@ -74,8 +88,9 @@ def attn_fwd(qkv, B, S, nq, nkv, hd):
     return ctx, ("cpu", p, scale)
 
 
-def attn_bwd(dctx, qkv, saved, B, S, nq, nkv, hd, dqkv=None):
+def attn_bwd(dctx, qkv, saved, B, S, nq, nkv, hd, dqkv=None, cp_group=None):
     """``dctx``: ``[T, nq*hd]``. Returns ``dqkv`` ``[T, (nq+2nkv)*hd]`` bf16."""
+    _whole_sequences_only(cp_group)
     if dqkv is None:
         dqkv = torch.empty_like(qkv)
     kind = saved[0]

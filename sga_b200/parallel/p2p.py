@@ -83,13 +83,16 @@ def _ptrs(bufs_or_buf, offset_bytes=0):
 
 def allreduce_(ch: PeerChannel, buf: SymmBuffer, offset_bytes: int, n: int, *, scale: float = 1.0, grad=None,
                idx=None, factor: float = 1.0, pack=False, zero_after_pack=False, scatter=False, rs_only=False,
-               sumsq_out=None, accumulate=False, max_ctas: int = 0) -> None:
+               sumsq_out=None, accumulate=False, max_ctas: int = 0, block_x: int = 0) -> None:
     """In-place two-shot all-reduce of ``n`` fp32 values at ``offset_bytes`` of a
     symmetric buffer, optionally fused with the pack of ``grad[idx]`` before
-    and the scatter back after."""
+    and the scatter back after. With ``block_x`` > 0, ``idx`` holds packed
+    ``head | tail_len`` descriptors of ``block_x``-element runs and ``n`` is
+    ``len(idx) * block_x``: whole runs are gathered and scattered 16 bytes at a time."""
     d = ch.next_desc()
     rc = lib().sga_p2p_allreduce(ctypes.byref(d), _ptrs(buf, offset_bytes), int(n), float(scale), _p(grad), _p(idx),
-                                 float(factor), int(pack), int(zero_after_pack), int(scatter), int(rs_only),
+                                 float(factor), int(pack), int(zero_after_pack), int(scatter), int(block_x),
+                                 int(rs_only),
                                  ch.norm_slots(), ch.cta_partials.data_ptr(), _p(sumsq_out), int(accumulate),
                                  max_ctas, _st())
     _chk(rc, "sga_p2p_allreduce")

@@ -34,7 +34,6 @@ class _SgaAdamBase:
         get_score_spec(self.emit_score)  # unknown names fail here
         self.residual_mean = bool(args.sga_optimizer_residual_mean)
         self.inactive_lr_scale = float(args.sga_optimizer_full_sync_inactive_lr_scale)
-        self.compact_search = args.sga_optimizer_compact_search
 
     # state lives in the arena; nothing to allocate per parameter
     def ensure_state(self, bucket_states) -> None:

@@ -132,6 +132,38 @@ class Supervisor:
                 log.close()
 
 
+def worker_pid_file(spec_path: str, node_rank: int, phase: str) -> str:
+    """Where a node worker records its process-group id: beside the job description, which every
+    node sees at the same path."""
+    return f"{spec_path}.{phase}.node{node_rank}.pgid"
+
+
+def render_sweep_argv(host: str, pid_file: str, ssh_key: Optional[str] = None) -> list:
+    """ssh command that ends exactly the process group a node worker recorded (and nothing else),
+    then removes the record; harmless when the file or the group is already gone."""
+    remote = (f"if [ -f {shlex.quote(pid_file)} ]; then kill -TERM -- -$(cat {shlex.quote(pid_file)}) 2>/dev/null; "
+              f"rm -f {shlex.quote(pid_file)}; fi; true")
+    return render_ssh_argv(host, remote, ssh_key)
+
+
+def sweep_node_workers(hosts, spec_path: str, phase: str, ssh_key, executor: str) -> None:
+    """Best-effort, out-of-band clean-up after a failed or interrupted launch. The supervisor's kill
+    took the ssh clients down and a remote worker normally dies with its channel; should one have
+    missed the hang-up, its GPUs would stay pinned, so every node is asked once more to end the
+    process group its worker recorded at start. Never raises. Skipped for the local executor, where
+    the supervisor's own kill of the child process groups is authoritative.
+    Counterpart of ``sga/replay_launch.py:480-501`` (which sweeps by command-line pattern; a recorded
+    process group cannot hit a stranger's process)."""
+    if executor == "local":
+        return
+    for i, h in enumerate(hosts):
+        try:
+            subprocess.run(render_sweep_argv(h, worker_pid_file(spec_path, i, phase), ssh_key), capture_output=True,
+                           timeout=30)
+        except (OSError, subprocess.TimeoutExpired):
+            pass
+
+
 def _free_port() -> int:
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
@@ -177,7 +209,11 @@ def run_fused_branch_multinode(ns, t0, cfgs, horizons, scores, ratios, executor:
             wc = render_worker_cmd(spec_path, i, nnodes, spn, master, port, phase)
             cmds.append(wc if executor == "local" else render_ssh_argv(h, " ".join(shlex.quote(x) for x in wc),
                                                                        ns.ssh_key))
-        sup.run(cmds, [f"{phase}_node{i}" for i in range(nnodes)], deadline_s=deadline, what=phase)
+        try:
+            sup.run(cmds, [f"{phase}_node{i}" for i in range(nnodes)], deadline_s=deadline, what=phase)
+        except (LaunchError, KeyboardInterrupt):
+            sweep_node_workers(hosts, spec_path, phase, ns.ssh_key, executor)
+            raise
     return torch.load(out_path, weights_only=False)
 
 
@@ -218,6 +254,26 @@ def node_worker(ns) -> int:
 
     spec = torch.load(ns.spec, weights_only=False)
     world = ns.nnodes * ns.shards_per_node
+    # own process group, recorded for the launcher's out-of-band sweep; the shards spawned below join it
+    pid_file = worker_pid_file(ns.spec, ns.node_rank, ns.phase)
+    try:
+        if os.getpgrp() != os.getpid():
+            os.setpgid(0, 0)
+        with open(pid_file, "w") as fh:
+            fh.write(str(os.getpgrp()))
+    except OSError:
+        pid_file = None
+    try:
+        return _run_shards(mp, ns, spec, world)
+    finally:
+        if pid_file:
+            try:
+                os.remove(pid_file)
+            except OSError:
+                pass
+
+
+def _run_shards(mp, ns, spec, world) -> int:
     mp.spawn(_child, args=(ns.node_rank, ns.shards_per_node, world, ns.master_addr, ns.master_port, spec, ns.phase),
              nprocs=ns.shards_per_node, join=True)
     return 0

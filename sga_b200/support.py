@@ -82,9 +82,21 @@ def _span_blocks(mask_u8, spans, x):
         yield start, end, nb, seg_any.any(dim=1), seg_all.all(dim=1)
 
 
+def _check_spans(spans):
+    prev_end = 0
+    for start, end in spans:
+        assert start >= prev_end, f"spans must be ascending and non-overlapping ({start} after {prev_end})"
+        prev_end = end
+
+
 def block_idx_from_mask(mask_u8: torch.Tensor, spans, x: int) -> torch.Tensor:
     """Block heads derived from the mask with the ANY rule, per parameter span."""
     assert mask_u8.numel() < 2 ** 31
+    if mask_u8.is_cuda:
+        from . import kernels as K
+
+        _check_spans(spans)
+        return K.block_forms(mask_u8, [(s, e) for s, e in spans if e > s], x, as_desc=False)[0]
     outs = []
     for start, _end, _nb, any_sel, _all in _span_blocks(mask_u8, spans, x):
         heads = torch.nonzero(any_sel, as_tuple=False).view(-1)
@@ -99,6 +111,17 @@ def block_desc_from_mask(mask_u8: torch.Tensor, spans, x: int) -> torch.Tensor:
     """Packed ``head | tail_len`` descriptors; requires x a power of two >= 4,
     x-aligned span starts, and whole-run selection of every listed block."""
     assert x >= 4 and x & (x - 1) == 0, f"block_desc: block_size must be a power of two >= 4, got {x}"
+    if mask_u8.is_cuda:
+        from . import kernels as K
+
+        _check_spans(spans)
+        for start, _end in spans:
+            assert start % x == 0, f"block_desc: span start {start} is not {x}-aligned"
+        desc, partial = K.block_forms(mask_u8, [(s, e) for s, e in spans if e > s], x, as_desc=True,
+                                      require_whole=True)
+        assert partial == 0, (f"block_desc: {partial} partially selected {x}-block(s); descriptors transfer "
+                              "whole runs")
+        return desc
     outs = []
     for start, end, nb, any_sel, all_sel in _span_blocks(mask_u8, spans, x):
         assert start % x == 0, f"block_desc: span start {start} is not {x}-aligned"

@@ -254,3 +254,68 @@ def test_singleton_and_config_attrs():
     attrs = C.sga_config_attrs(ns)
     assert "sga_backend_timer" not in attrs and attrs["sga_score"] == "abs_g"
     assert all(k.startswith("sga_") for k in attrs)
+
+
+def test_arguments_module_only_declares():
+    """``config/arguments.py`` holds declarations: imports, constants, the two value-type helpers,
+    group functions whose bodies are ``add_argument_group`` / ``add_argument`` calls, and the entry
+    that calls them. No rule, no cross-flag logic, no I/O (those belong to ``validation.py``)."""
+    import ast
+    import inspect
+
+    from sga_b200.config import arguments as A
+
+    tree = ast.parse(inspect.getsource(A))
+    types = {"sga_bool", "sga_int_or_null"}
+    for node in tree.body:
+        if isinstance(node, (ast.Import, ast.ImportFrom)):
+            continue
+        if isinstance(node, ast.Expr) and isinstance(node.value, ast.Constant):  # docstring
+            continue
+        if isinstance(node, ast.Assign):
+            assert all(isinstance(t, ast.Name) and t.id.isupper() for t in node.targets), ast.dump(node)
+            continue
+        assert isinstance(node, ast.FunctionDef), f"unexpected top-level statement: {ast.dump(node)[:80]}"
+        if node.name in types:
+            continue
+        for stmt in node.body:
+            if isinstance(stmt, ast.Expr) and isinstance(stmt.value, ast.Constant):
+                continue
+            if isinstance(stmt, ast.Return):
+                continue
+            call = stmt.value if isinstance(stmt, (ast.Expr, ast.Assign)) else None
+            if isinstance(stmt, ast.For):  # the entry point: for group in (...): group(parser)
+                assert all(isinstance(x, ast.Expr) and isinstance(x.value, ast.Call) for x in stmt.body)
+                continue
+            assert isinstance(call, ast.Call), f"{node.name}: only calls are allowed, found {ast.dump(stmt)[:80]}"
+            fn = call.func
+            name = fn.attr if isinstance(fn, ast.Attribute) else getattr(fn, "id", "")
+            assert name in {"add_argument", "add_argument_group"} or name.startswith("_"), f"{node.name}: call to {name}"
+
+
+def test_every_flag_has_a_consumer():
+    """Every declared ``sga_*`` destination is read somewhere outside its declaration, so a flag can
+    never silently do nothing. The flags that select nothing in this framework are listed here with
+    the reason, and nothing may read them (or they must leave the list)."""
+    import os
+    import re
+
+    no_effect = {
+        # chooses between two bracket searches of the reference's compact merge-join kernel; here the
+        # reduced values are read from the dense bucket, so there is no search. Accepted, part of the
+        # saved configuration identity, selects nothing.
+        "sga_optimizer_compact_search",
+    }
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "sga_b200")
+    text = {}
+    for d, _s, files in os.walk(root):
+        for f in files:
+            if f.endswith(".py") and not (d.endswith("config") and f == "arguments.py"):
+                text[os.path.join(d, f)] = open(os.path.join(d, f)).read()
+    blob = "\n".join(text.values())
+    dests = sorted(C.sga_defaults())
+    assert len(dests) >= 44
+    unread = [k for k in dests if not re.search(rf"\b{k}\b", blob)]
+    assert sorted(unread) == sorted(no_effect), f"flags nobody reads: {sorted(set(unread) - no_effect)}; " \
+                                                f"listed as without effect but read: {sorted(no_effect - set(unread))}"
+

@@ -245,6 +245,36 @@ def test_pack_scatter_blocks():
     assert torch.allclose(brm, KT.block_reduce(g, x, False), rtol=1e-5, atol=1e-7)
 
 
+@pytest.mark.parametrize("x", [4, 8, 64, 3])
+def test_block_forms_on_device_match_cpu(x):
+    """Block heads and packed descriptors derived on the device against the per-span PyTorch path."""
+    from sga_b200.support import block_desc_from_mask, block_idx_from_mask
+
+    torch.manual_seed(x)
+    al = x if x & (x - 1) == 0 else 1
+    spans, off = [], 0
+    for ln in (1000, 4096, 7, 333, 65536 + 5, 12):
+        spans.append((off, off + ln))
+        off = (off + ln + al - 1) // al * al + (al * 3)  # gaps between spans, starts aligned to the block size
+    n = off
+    mask = (torch.rand(n) < 0.05).to(torch.uint8)
+    for s, e in zip([0] + [b for _a, b in spans], [a for a, _b in spans] + [n]):
+        mask[s:e] = 0  # nothing selected in the gaps
+    ref = block_idx_from_mask(mask, spans, x)
+    got = block_idx_from_mask(mask.to(DEV), spans, x)
+    assert torch.equal(got.cpu(), ref)
+    if x >= 4 and x & (x - 1) == 0:
+        whole = torch.zeros(n, dtype=torch.uint8)
+        for h in ref.tolist()[::3]:
+            sp = next((a, b) for a, b in spans if a <= h < b)
+            whole[h:min(h + x, sp[1])] = 1
+        rd = block_desc_from_mask(whole, spans, x)
+        gd = block_desc_from_mask(whole.to(DEV), spans, x)
+        assert torch.equal(gd.cpu(), rd) and rd.numel() > 0
+        with pytest.raises(AssertionError, match="partially selected"):
+            block_desc_from_mask(mask.to(DEV), spans, x)
+
+
 # ---------------------------------------------- fused peer kernels, 1 rank
 def _channel():
     from sga_b200.parallel.p2p import PeerChannel
@@ -401,6 +431,31 @@ def test_p2p_allreduce_and_mask_union_single_rank():
         exp = g0.clone()
         exp[idx.long()] = g0[idx.long()] * 0.25
         assert torch.equal(grad, exp)
+        # descriptor wire form: whole runs of x elements (the last run of a span shorter), 16 bytes at a time
+        from sga_b200.backends.nccl_pipelined_index import expand_descriptors
+        from sga_b200.support import block_desc_from_mask
+
+        for xb in (4, 16, 64):
+            spans = [(0, 50000 + 3), (50048, 200000 + 1), (200064, 4 * n - 7)]
+            whole = torch.zeros(4 * n, dtype=torch.uint8, device=DEV)
+            for s0, e0 in spans:
+                heads = torch.arange(s0, e0, xb, device=DEV)
+                pick = heads[torch.rand(heads.numel(), device=DEV) < 0.02]
+                pick = torch.cat([pick, heads[-1:]])  # always the span's last (short) run
+                for h in pick.tolist()[:400]:
+                    whole[h:min(h + xb, e0)] = 1
+            desc = block_desc_from_mask(whole, spans, xb)
+            assert desc.numel() * xb <= n
+            grad.copy_(g0)
+            p2p.allreduce_(ch, buf, 0, desc.numel() * xb, scale=1.0, grad=grad, idx=desc, factor=0.5, pack=True,
+                           scatter=True, block_x=xb, sumsq_out=sq)
+            ch.check()
+            eidx = expand_descriptors(desc, xb).long()
+            assert torch.equal(eidx, torch.nonzero(whole).view(-1))
+            exp = g0.clone()
+            exp[eidx] = g0[eidx] * 0.5
+            assert torch.equal(grad, exp), f"descriptor form, x={xb}"
+            assert abs(sq.item() - (exp[eidx].double() ** 2).sum().item()) <= 1e-4 * sq.item()
         # mask union (one rank: union == own mask, values scaled in place)
         gb = pool.alloc(4 * n)
         bb = pool.alloc(4 * ((n + 31) // 32))

@@ -109,7 +109,10 @@ def test_golden_command_line_and_script_skeleton(tmp_path):
     assert f"--tensorboard-dir {tmp_path}/tensorboard" in last
     stop = open(stop_sh).read()
     assert "kill" in stop and f"host_0_{host}.pid" in stop
-    assert r.launcher.query() == JobStatus.COMPLETED_OR_IDLE
+    assert r.launcher.query_once() == JobStatus.COMPLETED_OR_IDLE
+    said = []
+    assert r.launcher.query(interval=0.01, timeout=0.05, out=said.append) == JobStatus.COMPLETED_OR_IDLE
+    assert said[0] == "Job status: COMPLETED_OR_IDLE" and said[-1].startswith("Query timeout reached")
     assert r.launcher.run(dryrun=True, tail=False) == [0]
 
 
@@ -281,3 +284,30 @@ def test_audit_tool(tmp_path, capsys):
     assert audit.main(["check", str(tmp_path / "bad.yaml")]) == 1
     text = capsys.readouterr().out
     assert "REFUSED" in text and "--no-such-flag" in text
+
+
+def test_find_latest_stdout_log_and_tailer_follow_new_attempts(tmp_path):
+    import time
+
+    from sga_b200.launcher.utils import LogTailer, find_latest_stdout_log
+
+    assert find_latest_stdout_log(str(tmp_path / "missing")) is None
+    assert find_latest_stdout_log(str(tmp_path)) is None
+    base = tmp_path / "host_0_a"
+    for run, attempt, rank in (("2024_01", 0, 0), ("2024_02", 0, 0), ("2024_02", 1, 0), ("2024_02", 1, 3)):
+        d = base / run / "rid" / f"attempt_{attempt}" / str(rank)
+        d.mkdir(parents=True, exist_ok=True)
+        (d / "stdout.log").write_text(f"{run} {attempt} {rank}\n")
+    (base / "2024_02" / "rid" / "attempt_1" / "7").mkdir()  # a rank directory without a log yet
+    want = str(base / "2024_02" / "rid" / "attempt_1" / "3" / "stdout.log")
+    assert find_latest_stdout_log(str(tmp_path)) == want
+    got = []
+    t = LogTailer(lambda: find_latest_stdout_log(str(tmp_path)), poll_s=0.02, out=got.append).start()
+    time.sleep(0.2)
+    d = base / "2024_03" / "rid" / "attempt_0" / "0"
+    d.mkdir(parents=True)
+    (d / "stdout.log").write_text("fresh attempt\n")
+    time.sleep(0.3)
+    t.stop()
+    assert got[0] == "2024_02 1 3" and got[-1] == "fresh attempt"
+

@@ -55,8 +55,26 @@ def _autograd_reference(model, tokens, targets):
     return loss.detach(), {k: v.grad for k, v in P.items()}
 
 
-def _check(device, name, tol):
+def _check(device, name, tol, expect_native_attention=False):
     cfg = get_config(name)
+    if expect_native_attention:
+        from sga_b200.ops import attention as A
+
+        paths = []
+        inner = A.attn_fwd
+
+        def spy(*args, **kw):
+            out = inner(*args, **kw)
+            paths.append(out[1][0])
+            return out
+
+        A.attn_fwd = spy
+        try:
+            _check(device, name, tol)
+        finally:
+            A.attn_fwd = inner
+        assert paths and all(p == "native" for p in paths), f"attention did not take the native kernels: {paths}"
+        return
     model = GPT(cfg, device=device, bucket_elems=20000, seed=3)
     # make the norm weights non-trivial
     g = torch.Generator().manual_seed(1)
@@ -91,3 +109,12 @@ def test_model_matches_autograd_cpu(name):
 @pytest.mark.parametrize("name", ["test_tiny", "test_tiny_qk"])
 def test_model_matches_autograd_gpu(name):
     _check("cuda:0", name, 0.08)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", ["test_hd64", "test_hd128_qk"])
+def test_model_with_native_attention_matches_autograd_gpu(name):
+    """The whole model on its production path (CTA-pair tcgen05 GEMMs, native attention at head
+    dimension 64 and 128, QK-norm, sequence length not a multiple of the attention tile) against autograd."""
+    _check("cuda:0", name, 0.08, expect_native_attention=True)
+

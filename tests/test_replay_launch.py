@@ -154,3 +154,24 @@ def test_multinode_smoke_script_local_executor(tmp_path):
                           str(tmp_path / "work")], env=dict(os.environ, SGA_LAUNCH_EXECUTOR="local"),
                          capture_output=True, text=True, timeout=800)
     assert res.returncode == 0 and "SMOKE PASS" in res.stdout, (res.stdout[-1500:], res.stderr[-1500:])
+
+
+def test_sweep_is_rendered_by_recorded_process_group_and_skipped_locally(tmp_path, monkeypatch):
+    """The out-of-band sweep after a failed launch: one ssh per node that ends the process group the
+    node worker recorded (never a pattern match), nothing at all for the local executor."""
+    from sga_b200.replay import launch as L
+
+    pf = L.worker_pid_file("/work/job_t5.pt", 2, "run")
+    assert pf == "/work/job_t5.pt.run.node2.pgid"
+    argv = L.render_sweep_argv("node7", pf, ssh_key="/k/id")
+    assert argv[0] == "ssh" and "node7" in argv
+    remote = argv[-1]
+    assert "kill -TERM -- -$(cat /work/job_t5.pt.run.node2.pgid)" in remote and "pkill" not in remote
+    assert remote.rstrip().endswith("true")
+    ran = []
+    monkeypatch.setattr(L.subprocess, "run", lambda a, **k: ran.append(a))
+    L.sweep_node_workers(["a", "b"], "/work/job.pt", "run", None, "local")
+    assert ran == []
+    L.sweep_node_workers(["a", "b"], "/work/job.pt", "preflight", None, "ssh")
+    assert len(ran) == 2 and "/work/job.pt.preflight.node1.pgid" in ran[1][-1]
+
