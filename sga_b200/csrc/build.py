@@ -31,7 +31,7 @@ NVCC_FLAGS = [
 ]
 # Files whose numerics must follow IEEE fp32 op for op (no fast-math, no
 # implicit FMA contraction): the optimizer tails and the replay kernels.
-STRICT_FP = {"optim.cu", "replay.cu", "dense_sync.cu", "index_sync.cu"}
+STRICT_FP = {"optim.cu", "replay.cu", "replay_select.cu", "dense_sync.cu", "index_sync.cu"}
 
 
 def _nvcc() -> str:

@@ -62,6 +62,11 @@ register_sigs({
     "sga_replay_blocks": [],
     "sga_replay_pass1": [_P, _I, _F, _P, _P, _P, _I, _L, _P, _P, _P],
     "sga_replay_pass3": [_P, _I, _F, _P, _P, _P, _P, _P, _P, _P, _P, _I, _L, _F, _F, _F, _F, _F, _P, _P, _P],
+    "sga_replay_score": [_P, _I, _F, _P, _P, _P, _P, _P, _P, _P, _I, _D, _D, _D, _D, _D, _L, _P, _P],
+    "sga_replay_find_bin": [_P, _I, _P, _I, _I, _P],
+    "sga_replay_hist_low16": [_P, _L, _P, _P, _P],
+    "sga_replay_mask": [_P, _L, _P, _P, _P, _P],
+    "sga_replay_tie_fill": [_P, _L, _P, _P, _P, _I, _I, _I, _P, _P],
     "sga_attn_fwd": [_P, _P, _P, _I, _I, _I, _I, _I, _L, _L, _F, _P, _P],
     "sga_attn_bwd": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _L, _L, _F, _P, _P],
 })

@@ -3,10 +3,18 @@
 
 Writes a synthetic trace (the generator of ``synth.py``: heavy-tailed bf16
 gradient dumps plus an AdamW snapshot), replays the 18-config grid of the
-headline replay workload (scores |g + residual| and |m| x ratios {0.1, 1, 5} % x cycle lengths
+headline replay workload (scores |g| and |g + residual| x ratios {0.1, 1, 5} % x cycle lengths
 {1, 4, 16}) in one fused pass over ``--shards`` GPUs with exact distributed
-top-k, and prints one JSON line: wall seconds of the replay, milliseconds per
-trace step, and replayed element-configs per second.
+top-k, and prints one JSON line: wall seconds of the replay, the engine's own
+seconds (what the shards spend after their process group is up: set-up, dense
+arm, front block, stream), milliseconds per trace step, and replayed
+element-configs per second.
+
+``--generate`` replaces the files by the on-device generator of
+``synth.SyntheticSource`` (same distribution, produced block by block from the
+seed wherever a pass needs a step), which is how the full-size workload
+(``--elems 1240000000 --steps 64``: 159 GB of dumps) runs without writing them.
+``--state-budget-mb`` bounds the per-shard state of a configuration group.
 
 ``--impl reference`` runs the unmodified reference replay (``python -m
 sga.replay`` from ``baseline/_ref``, its public CLI and stock code path) on the
@@ -36,18 +44,31 @@ def main(argv=None) -> int:
     ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
     ap.add_argument("--trace-dir", default=None)
     ap.add_argument("--impl", default="ours", choices=("ours", "reference", "both"))
+    ap.add_argument("--generate", action="store_true", help="generate the trace on the replay device, no files")
+    ap.add_argument("--state-budget-mb", type=float, default=0.0)
+    ap.add_argument("--scores", default=None,
+                    help="comma list (default abs_g_step,abs_g: |g| and |g + residual|; with the reference arm "
+                         "abs_g,abs_m, since abs_g_step exists only in this framework's replay)")
     ns = ap.parse_args(argv)
+    if ns.scores is None:
+        ns.scores = "abs_g_step,abs_g" if ns.impl == "ours" else "abs_g,abs_m"
     from . import core as RC
     from . import fused as RF
-    from .synth import make_synthetic_trace
+    from .synth import SyntheticSource, make_synthetic_trace
 
-    tdir = ns.trace_dir or tempfile.mkdtemp(prefix="sga_replay_bench_")
-    third = ns.elems // 3
     t_gen = time.perf_counter()
-    make_synthetic_trace(tdir, sizes=(third, third, ns.elems - 2 * third), steps=ns.steps, g_dtype="bf16", seed=0)
+    if ns.generate:
+        if ns.impl != "ours":
+            ap.error("--generate has no files for the reference arm to read")
+        tdir = SyntheticSource(ns.elems, steps=ns.steps, seed=0)
+    else:
+        tdir = ns.trace_dir or tempfile.mkdtemp(prefix="sga_replay_bench_")
+        third = ns.elems // 3
+        make_synthetic_trace(tdir, sizes=(third, third, ns.elems - 2 * third), steps=ns.steps, g_dtype="bf16", seed=0)
     t_gen = time.perf_counter() - t_gen
-    # the replay scores the accumulated gradient q = g + residual: "abs_g" is |g + residual| here
-    scores, ratios, Ts = ["abs_g", "abs_m"], [0.1, 1.0, 5.0], [1, 4, 16]
+    # the replay scores the accumulated gradient q = g + residual: "abs_g" is |g + residual| here, and
+    # "abs_g_step" the step's own |g|
+    scores, ratios, Ts = [x for x in ns.scores.split(",") if x], [0.1, 1.0, 5.0], [1, 4, 16]
     cfgs = [RC.CycleConfig(score=s, ratio_percent=r, cycle_len=T) for s in scores for r in ratios for T in Ts]
     ref = None
     if ns.impl in ("reference", "both"):
@@ -57,10 +78,17 @@ def main(argv=None) -> int:
             return 0
     t0 = time.perf_counter()
     frag = RF.run_fused_branch(tdir, 0, cfgs, ns.steps, [ns.steps], world=ns.shards, device=ns.device,
-                               max_configs=len(cfgs), score_names=scores, ratios=ratios, semantics="topk")
+                               max_configs=len(cfgs), state_budget_mb=ns.state_budget_mb, score_names=scores,
+                               ratios=ratios, semantics="topk")
     wall = time.perf_counter() - t0
+    prof = frag.get("profile") or [{}]
+    engine_s = sum((prof[0].get("phases_s") or {}).values())
+    stream_s = (prof[0].get("phases_s") or {}).get("stream")
     rec = {"bench": "fused replay", "elems": ns.elems, "steps": ns.steps, "configs": len(cfgs), "shards": ns.shards,
-           "device": ns.device, "trace_gen_s": round(t_gen, 2), "replay_wall_s": round(wall, 3),
+           "device": ns.device, "scores": scores, "source": "generated on the device" if ns.generate else "trace files",
+           "trace_gen_s": round(t_gen, 2), "replay_wall_s": round(wall, 3), "engine_s": round(engine_s, 3),
+           "stream_s": stream_s, "host_syncs_per_step": round(sum(p.get("host_syncs", 0) for p in prof) /
+                                                             max(ns.steps * len(prof), 1), 2),
            "ms_per_step": round(1e3 * wall / ns.steps, 2),
            "elem_configs_per_s": round(ns.elems * len(cfgs) * ns.steps / wall / 1e9, 3),
            "unit": "1e9 element-configs/s (wall clock, includes trace reads and process start)",

@@ -143,8 +143,9 @@ def build_configs(ns):
 
     scores = [s for s in str(ns.score_names).split(",") if s]
     for s in scores:
-        if s not in score_names():
-            raise ValueError(f"unknown score '{s}' (registered: {score_names()})")
+        if s not in score_names() and s not in RC.REPLAY_ONLY_SCORES:
+            raise ValueError(f"unknown score '{s}' (registered: {score_names()}; replay only: "
+                             f"{list(RC.REPLAY_ONLY_SCORES)})")
     ratios = _floats(ns.ratios)
     if ns.cycle_len is not None and ns.cycle_lens:
         raise ValueError("give --cycle-len or --cycle-lens, not both")

@@ -232,8 +232,19 @@ def coef_dense_for(gmeta: dict):
     return min(clip / (norm + 1.0e-6), 1.0), None
 
 
-def replay_score(name, w, m, v, q, hp: Hyper, count, optimizer="adamw"):
-    """Registry score on the pre-commit state in fp64, stored as fp32."""
+REPLAY_ONLY_SCORES = ("abs_g_step",)
+
+
+def replay_score(name, w, m, v, q, hp: Hyper, count, optimizer="adamw", g_step=None):
+    """Registry score on the pre-commit state in fp64, stored as fp32. ``abs_g_step`` exists only
+    in the replay: ``|g|`` of the step's own gradient, without the residual a boundary adds to it
+    (``g_step``; at the branch point, where there is no residual yet, it equals ``abs_g``)."""
+    if name == "abs_g_step":
+        return (q if g_step is None else g_step).abs().float()
+    if name == "abs_g":   # the two magnitude scores need no fp64 copies of the whole state
+        return q.abs().float()
+    if name == "abs_m":
+        return m.abs().float()
     adams = optimizer == "adams"
     bc1 = 1.0 if adams else 1.0 - hp.beta1 ** count
     bc2 = 1.0 if adams else 1.0 - hp.beta2 ** count
@@ -306,7 +317,7 @@ def reference_cycle(w0, m0, v0, logged, grad_norms, lrs, hp: Hyper, t0, cfg: Cyc
             q = q_pre * coef if coef != 1.0 else q_pre
             out_sel = sel
             if reselect and 0 < si < W - 1:
-                sel = select_topk_flat(replay_score(cfg.score, w, m, v, q, hp, count, cfg.optimizer), k)
+                sel = select_topk_flat(replay_score(cfg.score, w, m, v, q, hp, count, cfg.optimizer, g_step=g), k)
             res = torch.zeros_like(res)
         else:
             zero = torch.zeros_like(g)

@@ -254,6 +254,10 @@ class GPrefetcher:
         return item
 
 
+# score codes of csrc/replay_select.cu: the registry's, plus the replay-only |step gradient|
+_SCORE_CODES = {"update": 0, "abs_g": 1, "abs_m": 2, "coi": 3, "abs_g_step": 4}
+
+
 class _CfgStruct(ctypes.Structure):
     _fields_ = [("boundary", ctypes.c_int), ("fold", ctypes.c_int), ("dual", ctypes.c_int), ("adams", ctypes.c_int),
                 ("horizon", ctypes.c_int), ("fold_div", ctypes.c_float), ("coef", ctypes.c_float),
@@ -305,8 +309,94 @@ class FusedGroup:
             if key not in cache:
                 sc = RC.replay_score(c.score, self.W[r], self.M[r], self.V[r], g, self._hp_dev(), self.t0 + 1,
                                      c.optimizer)
-                cache[key] = self._select(sc, self.k[r])
+                if self._device_select:
+                    cache[key] = self._device_topk([sc.contiguous()], [self.k[r]])[0].clone()
+                else:
+                    cache[key] = self._select(sc, self.k[r])
             self.SEL[r] = cache[key].to(torch.uint8)
+
+    @property
+    def _device_select(self) -> bool:
+        """Exact top-k selections run wholly on the device (``csrc/replay_select.cu``) when the
+        step kernels do; the balanced-histogram rule keeps its host-driven form."""
+        return self.use_kernel and self.semantics == "topk"
+
+    def _select_scratch(self, rows: int):
+        if getattr(self, "_sel_rows", 0) < rows:
+            dev, n = self.device, self.n
+            nblk = (n + 4095) // 4096
+            self._h1 = torch.zeros(rows, 32769, dtype=torch.int64, device=dev)
+            self._h2 = torch.zeros(rows, 65536, dtype=torch.int64, device=dev)
+            self._state = torch.zeros(rows, 8, dtype=torch.int64, device=dev)
+            self._blockcnt = torch.zeros(rows, max(nblk, 1), dtype=torch.int32, device=dev)
+            self._newsel = torch.zeros(rows, n, dtype=torch.uint8, device=dev)
+            self._totals = torch.zeros(self.comms.world * rows, dtype=torch.int64, device=dev)
+            self._sel_rows = rows
+
+    def _device_topk(self, scores, ks):
+        """Exact distributed top-``ks[j]`` of ``|scores[j]|`` for every row at once, ties in global
+        index order: two radix digits whose histograms are summed over the shards (one collective
+        per digit for all rows), one gathered tie count, every decision in between taken by kernels.
+        Returns uint8 masks (views of a scratch buffer that the next call overwrites)."""
+        from .. import kernels as K
+        from ..csrc import lib
+
+        L = lib()
+        rows, n = len(scores), self.n
+        self._select_scratch(rows)
+        st = torch.cuda.current_stream().cuda_stream
+        h1, h2, state = self._h1[:rows], self._h2[:rows], self._state[:rows]
+        h1.zero_()
+        h2.zero_()
+        state.zero_()
+        state[:, 7] = torch.tensor([int(k) for k in ks], dtype=torch.int64).to(self.device, non_blocking=True)
+        for j, sc in enumerate(scores):
+            if n:
+                K.hist_top(sc, 16, 1, 32769, h1[j])
+        self.comms.sum_(h1)
+        assert L.sga_replay_find_bin(h1.data_ptr(), 32769, state.data_ptr(), 0, rows, st) == 0
+        for j, sc in enumerate(scores):
+            assert L.sga_replay_hist_low16(sc.data_ptr(), n, state[j].data_ptr(), h2[j].data_ptr(), st) == 0
+        self.comms.sum_(h2)
+        assert L.sga_replay_find_bin(h2.data_ptr(), 65536, state.data_ptr(), 1, rows, st) == 0
+        for j, sc in enumerate(scores):
+            assert L.sga_replay_mask(sc.data_ptr(), n, state[j].data_ptr(), self._newsel[j].data_ptr(),
+                                     self._blockcnt[j].data_ptr(), st) == 0
+        W = self.comms.world
+        totals = self._totals[:W * rows]
+        mine = state[:, 6].contiguous()
+        if W > 1:
+            self.comms.ops += 1
+            dist.all_gather_into_tensor(totals, mine, group=self.comms.group)
+        else:
+            totals.copy_(mine)
+        for j, sc in enumerate(scores):
+            assert L.sga_replay_tie_fill(sc.data_ptr(), n, state[j].data_ptr(), self._blockcnt[j].data_ptr(),
+                                         totals.data_ptr(), self.comms.rank, rows, j, self._newsel[j].data_ptr(),
+                                         st) == 0
+        return [self._newsel[j] for j in range(rows)]
+
+    def _boundary_select_device(self, rs, plan, g_dev, coef_dense, count):
+        """Scores of the configurations ``rs`` on their pre-commit state (one kernel each), then the
+        batched exact top-k."""
+        from ..csrc import lib
+
+        L = lib()
+        st = torch.cuda.current_stream().cuda_stream
+        self._upload(plan)
+        if getattr(self, "_sc", None) is None or self._sc.shape[0] < len(rs):
+            self._sc = torch.empty(len(rs), self.n, dtype=torch.float32, device=self.device)
+        stride = ctypes.sizeof(_CfgStruct)
+        for j, r in enumerate(rs):
+            p = plan[r]
+            rc = L.sga_replay_score(g_dev.data_ptr(), int(g_dev.dtype == torch.bfloat16), coef_dense,
+                                    self.W[r].data_ptr(), self.M[r].data_ptr(), self.V[r].data_ptr(),
+                                    self.RES[r].data_ptr(), self.SEL[r].data_ptr(), self.wd.data_ptr(),
+                                    self._cfg_dev.data_ptr() + r * stride, _SCORE_CODES[self.cfgs[r].score],
+                                    float(self.hp.beta1), float(self.hp.beta2), float(self.hp.eps),
+                                    float(p["bc1"]), float(p["bc2"]), self.n, self._sc[j].data_ptr(), st)
+            assert rc == 0, rc
+        return self._device_topk([self._sc[j] for j in range(len(rs))], [self.k[r] for r in rs])
 
     def _select(self, sc, k):
         """The trajectory-driving selection: exact top-k, or the online balanced-histogram rule."""
@@ -383,7 +473,12 @@ class FusedGroup:
         # ---- pass 2: boundary reselection on the pre-commit state (the outgoing support stays for pass 3)
         t0 = time.perf_counter()
         new_sel = {}
-        if any(p["boundary"] and 0 < si < self.Wlen - 1 for p in plan):
+        reselect = [r for r, p in enumerate(plan) if p["boundary"] and 0 < si < self.Wlen - 1]
+        if reselect and self._device_select:
+            masks = self._boundary_select_device(reselect, plan, g_dev, coef_dense, count)
+            new_sel = dict(zip(reselect, masks))
+            self.stats["selects"] += len(reselect)
+        elif reselect:
             if g is None:
                 g = RC._div(g_dev.float(), coef_dense)
             cache = {}
@@ -391,7 +486,8 @@ class FusedGroup:
                 if not (p["boundary"] and 0 < si < self.Wlen - 1):
                     continue
                 q = self._q_pre(p, g, r) * p["coef"]
-                sc = RC.replay_score(c.score, self.W[r], self.M[r], self.V[r], q, self._hp_dev(), count, c.optimizer)
+                sc = RC.replay_score(c.score, self.W[r], self.M[r], self.V[r], q, self._hp_dev(), count, c.optimizer,
+                                     g_step=g)
                 new_sel[r] = self._select(sc, self.k[r]).to(torch.uint8)
                 self.stats["selects"] += 1
         self.stats["select_s"] += time.perf_counter() - t0
@@ -473,25 +569,35 @@ def run_shard(rank, world, trace_dir, t0, configs, window, horizons, device, den
                                 (ENV_FRONT_SORT, ("auto", "cpu"), "auto"), (ENV_P1_READ, ("mmap", "load"), "mmap"),
                                 (ENV_S0_PROFILE, ("0", "1"), "0")):
         _switch(name, allowed, dflt)
-    info = RC.discover_trace(trace_dir)
+    from .synth import SyntheticSource
+
+    synth = trace_dir if isinstance(trace_dir, SyntheticSource) else None
+    info = synth if synth is not None else RC.discover_trace(trace_dir)
     dev = torch.device(device)
     comms = Comms(rank, world, group, dev)
     lo, hi = shard_bounds(info.numel, world, rank)
-    meta, payload = RC.load_state(info, t0)
     steps = info.window(t0, window)
     W = len(steps)
     if W == 0:
         raise ValueError(f"no gradient files at branch point {t0}")
     horizons = sorted(h for h in horizons if h <= W) or [W]
+    if synth is not None:
+        # generated on the replay device: nothing is read from disk and nothing crosses PCIe
+        meta = synth.meta(t0)
+        wd_vec = torch.full((hi - lo,), float(meta["param_groups"][0]["weight_decay"]), device=dev)
+        w0, m0, v0 = (synth.slice(k_, t0, lo, hi, dev) for k_ in ("w", "m", "v"))
+        g0 = synth.slice("g", t0, lo, hi, dev)
+    else:
+        meta, payload = RC.load_state(info, t0)
+        wd_vec = RC.group_vector(info, [g["weight_decay"] for g in meta["param_groups"]], lo, hi)
+        w0 = RC.flatten(payload["w"], info, torch.float32, lo, hi)
+        m0 = RC.flatten(payload["m"], info, torch.float32, lo, hi)
+        v0 = RC.flatten(payload["v"], info, torch.float32, lo, hi)
+        g0 = RC.flatten(payload["g"], info, torch.float32, lo, hi)
+        del payload
     groups_hp = meta["param_groups"]
     hp = RC.Hyper(wd=None, beta1=groups_hp[0]["adam_beta1"], beta2=groups_hp[0]["adam_beta2"],
                   eps=groups_hp[0]["adam_eps"], clip=meta["clip_grad"])
-    wd_vec = RC.group_vector(info, [g["weight_decay"] for g in groups_hp], lo, hi)
-    w0 = RC.flatten(payload["w"], info, torch.float32, lo, hi)
-    m0 = RC.flatten(payload["m"], info, torch.float32, lo, hi)
-    v0 = RC.flatten(payload["v"], info, torch.float32, lo, hi)
-    g0 = RC.flatten(payload["g"], info, torch.float32, lo, hi)
-    del payload
     use_kernel = dev.type == "cuda" and _switch(ENV_KERNEL, ("on", "off"), "on") == "on"
     gdtype = torch.bfloat16 if info.g_dtype == "bf16" else torch.float32
     # ---- dense arm (element-wise: every shard replays its own slice; cached per shard)
@@ -504,16 +610,19 @@ def run_shard(rank, world, trace_dir, t0, configs, window, horizons, device, den
     lap("setup")
     cache_hit = {}
     for opt in optimizers:
-        ident = RC.cache_ident(trace_dir, t0, W, horizons, "fp32", info.g_dtype, f"fused-v3-{world}-{rank}", opt)
+        ident = RC.cache_ident(str(trace_dir), t0, W, horizons, "fp32", info.g_dtype, f"fused-v3-{world}-{rank}", opt)
         blob = RC.load_cache(dense_cache, ident) if dense_cache else None
         cache_hit[opt] = blob is not None
-        if blob is None:
+        if blob is None and synth is not None:
+            logged, metas = synth.gradients(steps, lo, hi, dev), [synth.meta(t) for t in steps]
+        elif blob is None:
             pf = GPrefetcher(info, steps, lo, hi, gdtype, pin=dev.type == "cuda")
             logged, metas = [], []
             for _ in steps:
                 _t, gm, flat = pf.get()
                 logged.append(flat)
                 metas.append(gm)
+        if blob is None:
             # the dense arm runs where the sparse arms run (same arithmetic on both sides of the distortion)
             hp_d = RC.Hyper(wd=wd_vec.to(dev), beta1=hp.beta1, beta2=hp.beta2, eps=hp.eps, clip=hp.clip)
             label = torch.zeros_like(w0, device=dev)
@@ -526,7 +635,7 @@ def run_shard(rank, world, trace_dir, t0, configs, window, horizons, device, den
             if dense_cache:
                 RC.save_cache(dense_cache, ident, {"snap_d": {h: t.cpu() for h, t in snaps.items()}, "metas": metas,
                                                    "label": label.cpu(), "recon2": recon})
-            if window_g is None and sum(t.numel() * t.element_size() for t in logged) <= keep_bytes:
+            if synth is None and window_g is None and sum(t.numel() * t.element_size() for t in logged) <= keep_bytes:
                 window_g = list(zip(steps, metas, logged))
             del logged
         dense[opt] = blob["snap_d"]
@@ -602,9 +711,14 @@ def run_shard(rank, world, trace_dir, t0, configs, window, horizons, device, den
                         dense[grp[0].optimizer],
                         use_kernel, semantics=semantics, entries=entries)
         fg.initial_select(g0)
-        pf = None if window_g is not None else GPrefetcher(info, steps, lo, hi, gdtype, pin=dev.type == "cuda")
+        lazy = synth.gradients(steps, lo, hi, dev) if synth is not None else None
+        pf = None if (window_g is not None or lazy is not None) else GPrefetcher(info, steps, lo, hi, gdtype,
+                                                                                 pin=dev.type == "cuda")
         for si in range(W):
-            _t, gm, flat = window_g[si] if pf is None else pf.get()
+            if lazy is not None:
+                _t, gm, flat = steps[si], synth.meta(steps[si]), lazy[si]
+            else:
+                _t, gm, flat = window_g[si] if pf is None else pf.get()
             fg.step(StepInput(si, flat, float(gm["grad_norm"]), float(gm["lr"][0])))
         for r, c in enumerate(grp):
             results[c] = {h: math.sqrt(fg.numer[h][r]) / math.sqrt(den[c.optimizer][hi_])

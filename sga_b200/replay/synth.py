@@ -58,3 +58,74 @@ def make_synthetic_trace(out_dir: str, sizes=(400000, 300000, 170000), steps: in
             torch.save({"meta": m, "payload": state}, os.path.join(out_dir, f"step_{step:06d}_state.pt"))
         torch.save({"meta": meta(step, norm), "payload": gq}, os.path.join(out_dir, f"step_{step:06d}_g.pt"))
     return out_dir
+
+
+class SyntheticSource:
+    """The synthetic trace at full size without files: state snapshot and per-step gradients of a
+    flat ``numel``-element vector generated on the replay device, block by block, from a seed.
+
+    A dump of the 1.24 B-element vector is 2.5 GB per step in bf16 (159 GB for 64 steps), more than a
+    benchmark box should be asked to write and read back; generated values are the same distribution
+    (``sigma_t = 1e-3 * (1 + 0.5 * sin(t / 8))``, 1 % of the coordinates x20, state ``m ~ N(0, 1e-6^2)``,
+    ``v = |N(0, 1e-6^2)|``, ``w ~ N(0, 0.02^2)``). Every 4 Mi-element block has its own generator seeded
+    by (seed, array, step, block), so any sharding of the vector sees the same numbers and a step can be
+    produced again whenever a pass needs it. Gradients are logged unclipped (``clip_grad`` 0)."""
+
+    BLOCK = 1 << 22
+
+    def __init__(self, numel: int, steps: int = 64, seed: int = 0, lr: float = 3e-4, g_dtype: str = "bf16"):
+        self.numel, self.steps, self.seed, self.lr, self.g_dtype = int(numel), int(steps), int(seed), float(lr), g_dtype
+        self.offsets, self.shapes = [0], [(int(numel),)]
+
+    def __repr__(self):
+        return f"synthetic(numel={self.numel}, steps={self.steps}, seed={self.seed}, g={self.g_dtype})"
+
+    # ---- the parts of a trace the fused engine reads
+    def window(self, t0: int, want: int) -> list:
+        return list(range(t0, min(t0 + want, self.steps)))
+
+    def meta(self, step: int) -> dict:
+        pg = [{"lr": self.lr, "weight_decay": 0.1, "adam_beta1": 0.9, "adam_beta2": 0.95, "adam_eps": 1e-8}]
+        return {"step": step, "phase": "shadow", "lr": [self.lr], "grad_norm": float("nan"), "clip_grad": 0.0,
+                "weight_decay": 0.1, "adam_beta1": 0.9, "adam_beta2": 0.95, "adam_eps": 1e-8, "param_groups": pg,
+                "state_absent": False}
+
+    def _block(self, what: int, step: int, b: int, device) -> torch.Tensor:
+        gen = torch.Generator(device=device)
+        gen.manual_seed((self.seed * 1000003 + what * 7919 + step * 104729 + b * 15485863) % (2 ** 63 - 1))
+        x = torch.randn(self.BLOCK, generator=gen, device=device)
+        if what == 0:   # gradient of `step`
+            sigma = 1e-3 * (1 + 0.5 * math.sin(step / 8.0))
+            heavy = torch.rand(self.BLOCK, generator=gen, device=device) < 0.01
+            return torch.where(heavy, x * (20.0 * sigma), x * sigma)
+        if what == 1:
+            return x * 0.02
+        if what == 2:
+            return x * 1e-6
+        return (x * 1e-6).abs()
+
+    def slice(self, what: str, step: int, lo: int, hi: int, device, dtype=torch.float32) -> torch.Tensor:
+        """Elements ``[lo, hi)`` of array ``what`` ('g' of ``step``, or the snapshot's 'w' / 'm' / 'v')."""
+        code = {"g": 0, "w": 1, "m": 2, "v": 3}[what]
+        out = torch.empty(hi - lo, dtype=dtype, device=device)
+        for b in range(lo // self.BLOCK, (hi + self.BLOCK - 1) // self.BLOCK if hi > lo else 0):
+            b0 = b * self.BLOCK
+            a, e = max(lo, b0), min(hi, b0 + self.BLOCK)
+            out[a - lo:e - lo] = self._block(code, step if code == 0 else 0, b, device)[a - b0:e - b0].to(dtype)
+        return out
+
+    def gradients(self, steps, lo: int, hi: int, device):
+        """Lazy sequence of this shard's logged gradients: element ``i`` is generated when it is read."""
+        src, dt = self, (torch.bfloat16 if self.g_dtype == "bf16" else torch.float32)
+
+        class _Lazy:
+            def __len__(self):
+                return len(steps)
+
+            def __getitem__(self, i):
+                return src.slice("g", steps[i], lo, hi, device, dt)
+
+            def __iter__(self):
+                return (self[i] for i in range(len(steps)))
+
+        return _Lazy()

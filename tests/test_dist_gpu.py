@@ -43,3 +43,29 @@ def test_pipeline_parallel_two_gpus():
         pytest.skip("needs at least 2 GPUs")
     res = _run(2, worker="pp_gpu_worker.py", port=29745)
     assert res.returncode == 0 and "PP_GPU_OK" in res.stdout, res.stdout[-3000:] + "\n" + res.stderr[-6000:]
+
+
+@pytest.mark.timeout(900)
+def test_fused_replay_two_shards_on_gpus(tmp_path):
+    """Two replay shards on two GPUs (NCCL collectives between the device-side selection passes)
+    against one shard: discrete quantities exact, sums inside the reordering band."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least 2 GPUs")
+    from sga_b200.replay import core as RC
+    from sga_b200.replay import fused as RF
+    from sga_b200.replay.synth import make_synthetic_trace
+
+    trace = make_synthetic_trace(str(tmp_path / "trace"), sizes=(400000, 300000, 170000), steps=12, g_dtype="bf16",
+                                 seed=3)
+    cfgs = [RC.CycleConfig(score=s, ratio_percent=r, cycle_len=t) for s in ("abs_g", "update") for r in (1.0, 5.0)
+            for t in (1, 4)]
+    kw = dict(score_names=["abs_g", "update"], ratios=[1.0, 5.0], semantics="topk")
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    one = RF.run_fused_branch(trace, 0, cfgs, 12, [6, 12], world=1, device="cuda", **kw)
+    two = RF.run_fused_branch(trace, 0, cfgs, 12, [6, 12], world=2, device="cuda", **kw)
+    for c in cfgs:
+        for h in (6, 12):
+            assert two["results"][c][h] == pytest.approx(one["results"][c][h], rel=1e-6), (c, h)
+    for key, m in one["front"].items():
+        assert two["front"][key]["recall_at_k"] == m["recall_at_k"]
+

@@ -504,7 +504,7 @@ def test_peer_wait_times_out_cleanly():
         bufs[1] = bufs[0]
         ns = ch.norm_slots()
         ns[1] = ns[0]
-        rc = lib().sga_p2p_allreduce(ctypes.byref(d), bufs, n, 1.0, None, None, 1.0, 0, 0, 0, 0, ns,
+        rc = lib().sga_p2p_allreduce(ctypes.byref(d), bufs, n, 1.0, None, None, 1.0, 0, 0, 0, 0, 0, ns,
                                      ch.cta_partials.data_ptr(), None, 0, 0, torch.cuda.current_stream().cuda_stream)
         assert rc == 0
         torch.cuda.synchronize()
