@@ -90,6 +90,7 @@ class TorchPipelinedIndexBackend:
         self._payload_off: dict = {}
         self._slots = {}           # rank-local receive slots per channel
         self._scratch = None
+        self._deferred = []        # tokens of buckets whose receive side is still to run this step
         self._touched = None
         self.sumsq = None          # device scalar: norm^2 of the payloads reduced this step
 
@@ -273,16 +274,20 @@ class TorchPipelinedIndexBackend:
         return None
 
     # ---------------------------------------------------------- rank local
-    def sync_rank_local(self, bucket_state, k: int, comm_view, comm_group, world: int, score=None) -> None:
+    def sync_rank_local(self, bucket_state, k: int, comm_view, comm_group, world: int, score=None,
+                        defer_reduce: bool = False) -> None:
         """Exact per-bucket top-``k`` of the score (``None``: ``|grad + residual|``; otherwise a
         ``ScoreInputs`` with the bucket's weights, moments and Adam scalars) on this rank, exchange of
         (int32 index, fp32 value) pairs, rank-ordered sum / world into ``comm_view``; the selected
-        coordinates of the bucket are zeroed. Coordinates with a zero score are never selected."""
+        coordinates of the bucket are zeroed. Coordinates with a zero score are never selected.
+        ``defer_reduce`` (peer-memory transport): only select and push now; the receive side of every
+        deferred bucket runs in ``flush_rank_local``, which the caller invokes once all buckets have
+        been launched -- by then no rank has to wait for a slower peer's pairs."""
         with backend_timer.region("sparse", backend=self.name, emission="rank_local", layout="er", block_size=1,
                                   bucket=bucket_state.bucket_id, k=k):
-            self._rank_local_impl(bucket_state, k, comm_view, comm_group, world, score)
+            self._rank_local_impl(bucket_state, k, comm_view, comm_group, world, score, defer_reduce)
 
-    def _rank_local_impl(self, bs, k, comm_view, comm_group, world, score=None):
+    def _rank_local_impl(self, bs, k, comm_view, comm_group, world, score=None, defer_reduce=False):
         grad = bs.grad_data
         n = grad.numel()
         if self.transport == "p2p" or (grad.is_cuda and world == 1 and self.ddp is not None and self.ddp.channels):
@@ -295,9 +300,12 @@ class TorchPipelinedIndexBackend:
                 self._slots[ci] = p2p.IndexSyncSlots(ddp.pool, self._kcap, self._max_bucket)
             if self._scratch is None:
                 self._scratch = p2p.IndexSyncScratch(ddp.device, self._max_bucket)
-            p2p.bucket_index_sync_(ch, self._scratch, grad, k, slots=self._slots[ci], comm=comm_view,
-                                   scale=1.0 / ddp.world, sumsq_out=self.sumsq, accumulate=True,
-                                   score=score, max_ctas=ddp.ddp_config.comm_max_ctas)
+            token = p2p.bucket_index_sync_(ch, self._scratch, grad, k, slots=self._slots[ci], comm=comm_view,
+                                           scale=1.0 / ddp.world, sumsq_out=self.sumsq, accumulate=True,
+                                           score=score, max_ctas=ddp.ddp_config.comm_max_ctas,
+                                           defer_reduce=defer_reduce and not _DEBUG_SYNC)
+            if token is not None:
+                self._deferred.append(token)
             if _DEBUG_SYNC:
                 # debugging aid (SGA_ISYNC_DEBUG=1): stop at the first bucket whose chain reports an error
                 torch.cuda.synchronize()
@@ -321,6 +329,14 @@ class TorchPipelinedIndexBackend:
             all_idx, all_val = [idx], [vals]
         for ri, rv in zip(all_idx, all_val):
             comm_view.index_add_(0, ri.long(), rv * scale)
+
+    def flush_rank_local(self) -> None:
+        """Receive side of every bucket whose push was deferred, in launch order."""
+        from ..parallel import p2p
+
+        pending, self._deferred = self._deferred, []
+        for token in pending:
+            p2p.bucket_index_reduce_(token)
 
     def configure_rank_local(self, max_bucket_elems: int, max_k: int) -> None:
         """Sizes of the largest bucket and payload; the receive areas of both channels and the work

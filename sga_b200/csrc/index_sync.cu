@@ -100,6 +100,8 @@ struct ISyncArgs {
   int zero_selected;
   unsigned* bits;        // select-only mode: bit mask of the selection (zeroed by the host)
   unsigned* result;      // [4]: threshold key, ties taken, keys above the threshold, pairs produced
+  unsigned* reduce_ticket;  // the reduce kernel's own ticket word (zero between launches): the reduce may run
+                            // long after its bucket's chain, when the shared state block belongs to another bucket
 };
 
 // Programmatic dependent launch: every kernel of the chain first lets the next one be scheduled
@@ -804,7 +806,7 @@ __global__ void __launch_bounds__(IS_THREADS) isync_reduce_kernel(const ISyncArg
     if (threadIdx.x == 0) a.partials[range] = bs;
     __syncthreads();
   }
-  if (!last_cta<true>(a.state + ST_TICKET0 + 6)) return;
+  if (!last_cta<true>(a.reduce_ticket)) return;
   float t = 0.f;
   for (int i = threadIdx.x; i < nranges; i += IS_THREADS) t = t + __ldcg(a.partials + i);
   const float tot = block_sum(t, red);
@@ -835,6 +837,8 @@ struct SgaISyncDesc {
   int seg_capacity;          // entries of segcnt / segsel (roff holds one more)
   int partials_capacity;
   int accumulate, zero_selected, mode, max_ctas;
+  int phase;                 // 0: whole chain. 1: up to the push (no reduce). 2: the reduce alone
+  void* reduce_ticket;       // one zeroed word per channel
 };
 
 // Launch one kernel of the chain; `dependent` lets it be scheduled while its predecessor (the
@@ -871,8 +875,10 @@ SGA_API int sga_index_sync(const SgaPeerDesc* d, const SgaISyncDesc* s, void* st
   const int nseg = (int)((s->n + IS_SEG - 1) / IS_SEG);
   if ((long long)nseg * IS_SEG > s->cand_capacity || nseg > s->seg_capacity) return -7;
   const int nranges = (nseg + IS_SEG_PER_RANGE - 1) / IS_SEG_PER_RANGE;
+  if (s->phase < 0 || s->phase > 2 || (s->phase != 0 && s->mode != 0)) return -6;
   if (s->mode == 0) {
     if (s->k > s->kcap || nseg + 1 > s->hstride || nranges > s->partials_capacity || !s->comm) return -7;
+    if (!s->reduce_ticket) return -6;
   } else if (!s->bits) {
     return -6;
   }
@@ -913,6 +919,7 @@ SGA_API int sga_index_sync(const SgaPeerDesc* d, const SgaISyncDesc* s, void* st
   a.accumulate = s->accumulate; a.zero_selected = s->zero_selected;
   a.bits = reinterpret_cast<unsigned*>(s->bits);
   a.result = reinterpret_cast<unsigned*>(s->result);
+  a.reduce_ticket = reinterpret_cast<unsigned*>(s->reduce_ticket);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int cap = s->max_ctas > 0 ? s->max_ctas : 148 * 8;
   const int wpc = IS_THREADS / 32;
@@ -924,6 +931,10 @@ SGA_API int sga_index_sync(const SgaPeerDesc* d, const SgaISyncDesc* s, void* st
   if (grid_sample < 1) grid_sample = 1;
   int grid_range = nranges < cap ? nranges : cap;
   static const bool pdl = [] { const char* e = getenv("SGA_ISYNC_PDL"); return !(e && e[0] == '0'); }();
+  if (s->phase == 2) {  // the deferred reduce of a bucket whose pairs were pushed by an earlier call
+    launch_chain(isync_reduce_kernel, grid_range, st, a, false);
+    return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  }
   cudaMemsetAsync(a.state, 0, 64 * sizeof(unsigned), st);
   if (s->mode == 1) cudaMemsetAsync(a.bits, 0, (size_t)((s->n + 31) / 32) * 4, st);
   switch (s->score) {
@@ -938,7 +949,7 @@ SGA_API int sga_index_sync(const SgaPeerDesc* d, const SgaISyncDesc* s, void* st
     launch_chain(isync_mask_kernel, grid_seg, st, a, pdl);
   } else {
     launch_chain(isync_emit_kernel, grid_seg, st, a, pdl);
-    launch_chain(isync_reduce_kernel, grid_range, st, a, pdl);
+    if (s->phase == 0) launch_chain(isync_reduce_kernel, grid_range, st, a, pdl);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

@@ -135,7 +135,7 @@ class ISyncDesc(ctypes.Structure):
                 ("cand_capacity", ctypes.c_longlong), ("seg_capacity", ctypes.c_int),
                 ("partials_capacity", ctypes.c_int),
                 ("accumulate", ctypes.c_int), ("zero_selected", ctypes.c_int), ("mode", ctypes.c_int),
-                ("max_ctas", ctypes.c_int)]
+                ("max_ctas", ctypes.c_int), ("phase", ctypes.c_int), ("reduce_ticket", ctypes.c_void_p)]
 
 
 def _nseg(n: int) -> int:
@@ -182,6 +182,7 @@ class IndexSyncSlots:
         self.pairs_bytes = (8 * self.kcap * pool.world + 255) // 256 * 256
         self.buf: SymmBuffer = pool.alloc(self.pairs_bytes + 4 * self.hstride * pool.world)
         self.world = pool.world
+        self.ticket = torch.zeros(1, dtype=torch.int32, device=pool.device)  # the reduce kernel's last-CTA ticket
 
     def pairs(self, src_rank: int, count: int) -> torch.Tensor:
         """``[count, 2]`` int32 view of what rank ``src_rank`` pushed here (index, value bits)."""
@@ -205,11 +206,15 @@ class ScoreInputs:
 def bucket_index_sync_(ch: PeerChannel, scratch: IndexSyncScratch, acc: torch.Tensor, k: int, *,
                        slots: IndexSyncSlots | None = None, comm=None, bits: torch.Tensor | None = None,
                        scale: float = 1.0, sumsq_out=None, accumulate=False, select_only=False, zero_selected=True,
-                       score: ScoreInputs | None = None, max_ctas: int = 0) -> None:
+                       score: ScoreInputs | None = None, max_ctas: int = 0, defer_reduce: bool = False):
     """Exact top-``k`` of the score over ``acc`` (default ``|acc|``), exchange of the selected
     (index, value) pairs with every rank of the channel and rank-ordered scatter-add of all ranks'
     pairs, times ``scale``, into ``comm``; the selected coordinates of ``acc`` are zeroed. With
-    ``select_only`` nothing is exchanged and the selection's bit mask is written to ``bits``."""
+    ``select_only`` nothing is exchanged and the selection's bit mask is written to ``bits``.
+
+    ``defer_reduce`` stops after the push and returns a token for :func:`bucket_index_reduce_`: the
+    receive side then runs later (e.g. once every bucket has pushed, when no rank has to wait for a
+    slower peer's payload any more). The channel and its slots must not be used in between."""
     n = acc.numel()
     scratch.ensure(n)
     d = ch.peek_desc() if select_only else ch.next_desc()
@@ -246,8 +251,19 @@ def bucket_index_sync_(ch: PeerChannel, scratch: IndexSyncScratch, acc: torch.Te
         s.bits = bits.data_ptr()
     s.sumsq_out = _p(sumsq_out)
     s.accumulate, s.zero_selected, s.mode, s.max_ctas = int(accumulate), int(zero_selected), int(select_only), max_ctas
+    s.phase = 1 if (defer_reduce and not select_only) else 0
+    s.reduce_ticket = slots.ticket.data_ptr() if slots is not None else None
     rc = lib().sga_index_sync(ctypes.byref(d), ctypes.byref(s), _st())
     _chk(rc, "sga_index_sync")
+    return (d, s, (acc, comm, slots, scratch, sumsq_out)) if s.phase == 1 else None
+
+
+def bucket_index_reduce_(token) -> None:
+    """The receive side of a :func:`bucket_index_sync_` call that was made with ``defer_reduce``."""
+    d, s, _keep = token
+    s.phase = 2
+    rc = lib().sga_index_sync(ctypes.byref(d), ctypes.byref(s), _st())
+    _chk(rc, "sga_index_sync (reduce)")
 
 
 def dense_adamw_ag_(ch: PeerChannel, w, g, m, v, model: SymmBuffer, bucket_start, bucket_len, table, group_lr,

@@ -68,11 +68,15 @@ class DataParallel:
         if transport == "p2p":
             from ..parallel.p2p import PeerChannel
 
-            self.channels = [PeerChannel(pool), PeerChannel(pool)]
+            # one channel (flag words, receive slots of the backends) per bucket: a bucket's exchange can
+            # then stay open until the end of the backward pass without blocking the next bucket's
+            self.channels = [PeerChannel(pool) for _ in range(max(2, len(self.arena.buckets)))]
         # per-step overlap state
         self._pending = {}
         self._synced = set()
         self.bucket_sync_fn: Optional[Callable[[Bucket], None]] = None
+        self.after_last_bucket: Optional[Callable[[], None]] = None  # runs on the comm stream once every bucket
+        #                                                              of the step has been launched (deferred work)
         self._armed = False
         self._slot_bucket = {id(s): s.bucket for s in self.arena.slots}
         self._bucket_nparams = [len(b.slots) for b in self.arena.buckets]
@@ -158,8 +162,23 @@ class DataParallel:
         for b in self.arena.buckets:
             if b.index not in self._synced:
                 self._launch_bucket(b)
+        self._run_deferred()
         self.join()
         self._armed = False
+
+    def _run_deferred(self) -> None:
+        fn, self.after_last_bucket = self.after_last_bucket, None
+        if fn is None or self.null_sync:
+            return
+        timed = getattr(self, "time_syncs", False) and self.device.type == "cuda"
+        if self.comm_stream is not None:
+            with torch.cuda.stream(self.comm_stream):
+                pair = self._timed_pair() if timed else None
+                fn()
+                if pair is not None:
+                    pair[1].record()
+        else:
+            fn()
 
     def join(self) -> None:
         if self.comm_stream is not None:
@@ -193,6 +212,7 @@ class DataParallel:
         self._armed = False
 
     def begin_step(self) -> None:
+        self.after_last_bucket = None
         self._synced = set()
         self._pending = {}
         self._armed = False

@@ -353,8 +353,14 @@ class SGAEngine:
         if self.rank_local:
             k = self._k_for_bucket(bucket.numel)
             if self.backend.consumes == "idx":
+                # peer-memory transport, a bucket per channel: push now, add the ranks' pairs once every
+                # bucket is out (no rank then waits for a slower peer in the middle of its backward pass)
+                defer = (getattr(ddp, "transport", None) == "p2p" and len(getattr(ddp, "channels", ())) >= len(arena.buckets)
+                         and callable(getattr(self.backend, "flush_rank_local", None)))
                 self.backend.sync_rank_local(bs, k, arena.comm[bucket.start:bucket.end], ddp.group, ddp.world,
-                                             score=self._rank_local_score(bs, bucket))
+                                             score=self._rank_local_score(bs, bucket), defer_reduce=defer)
+                if defer:
+                    ddp.after_last_bucket = self.backend.flush_rank_local
             else:
                 self.backend.sync_rank_local(bs, k, self._active_mask_arena()[bucket.start:bucket.end], ddp.group,
                                              ddp.world)

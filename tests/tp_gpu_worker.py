@@ -78,7 +78,10 @@ def check_rs(tp, dev, M, N, Kd, b_mn, with_res):
 
 
 def check_model(tp, dev):
-    cfg = get_config("test_tiny", seq_len=256)
+    # heads and FFN columns divide over the ranks; B * S rows are a multiple of 256 per rank
+    W_ = tp.world
+    cfg = get_config("test_tiny", seq_len=128 * W_, n_heads=max(4, W_), n_kv_heads=max(2, W_),
+                     hidden=32 * max(4, W_), ffn=256 * max(1, W_ // 2))
     model = GPT(cfg, device=dev, seed=5, tp=tp)
     full = GPT(cfg, device=dev, seed=5)
     g = torch.Generator().manual_seed(21)
@@ -161,13 +164,15 @@ def main():
     rank = dist.get_rank()
     torch.manual_seed(7 + rank)
     tp = TPContext(device=dev, transport="fused")
+    # the fused kernels work on CTA-pair tiles of 256 rows per rank's chunk: M is a multiple of 256 * ranks
+    unit = 256 * tp.world
     for b_mn in (False, True):
-        check_ag(tp, dev, 1024, 384, 256, b_mn)
-        check_ag(tp, dev, 2048, 1024, 160, b_mn)
+        check_ag(tp, dev, 2 * unit, 384, 256, b_mn)
+        check_ag(tp, dev, 4 * unit, 1024, 160, b_mn)
     for b_mn in (False, True):
         for with_res in (False, True):
-            check_rs(tp, dev, 1024, 384, 320, b_mn, with_res)
-    check_rs(tp, dev, 2048, 128, 1024, False, True)
+            check_rs(tp, dev, 2 * unit, 384, 320, b_mn, with_res)
+    check_rs(tp, dev, 4 * unit, 128, 1024, False, True)
     losses = check_model(tp, dev)
     dist.barrier()
     if rank == 0:
