@@ -236,6 +236,12 @@ def main() -> int:
     # ---- gradient synchronisation: device time of the per-bucket sync launches, outside the timed regions
     grad_sync = None
     if tr.tp_size == 1 and tr.pp_size == 1:
+        # the index backend's exchange kernels count the time they stand waiting for peers' flags
+        scratch = getattr(getattr(tr.engine, "backend", None), "_scratch", None) if tr.engine is not None else None
+        wait_ctr = getattr(scratch, "wait_ns", None)
+        if wait_ctr is not None:
+            torch.cuda.synchronize(dev)
+            wait_ctr.zero_()
         tr.ddp.time_syncs = True
         for i in range(2):
             tr.train_step(tr.host_batch(step_id + K + i))
@@ -244,14 +250,24 @@ def main() -> int:
             local_ms = tr.ddp.sync_device_ms() / 2
         except Exception:  # a rank without a reading still joins the reduction below
             local_ms = 0.0
-        sync_ms = torch.tensor([local_ms], dtype=torch.float64, device=dev)
+        wait_ms = float(wait_ctr.item()) / 2e6 if wait_ctr is not None else 0.0
+        # max over ranks of the whole time, and of the time not spent waiting for peers
+        sync_ms = torch.tensor([local_ms, max(local_ms - wait_ms, 0.0), wait_ms], dtype=torch.float64, device=dev)
         if world > 1:
             dist.all_reduce(sync_ms, op=dist.ReduceOp.MAX)
+        busy_ms, peer_wait_ms = float(sync_ms[1].item()), float(sync_ms[2].item())
+        sync_ms = sync_ms[:1]
         if float(sync_ms.item()) > 0.0:
             grad_sync = {"ms_per_step": float(sync_ms.item()), "buckets": len(tr.model.arena.buckets),
                          "what": "sum over buckets of the device time of each bucket's sync launch on the "
                                  "communication stream (event pairs), mean of 2 untimed steps, max over ranks; "
                                  "runs under the backward pass"}
+            if wait_ctr is not None:
+                grad_sync["peer_wait_ms_per_step"] = peer_wait_ms
+                grad_sync["busy_ms_per_step"] = busy_ms
+                grad_sync["busy_what"] = ("ms_per_step minus the time this rank's exchange kernels stood waiting for "
+                                          "peers' flags (device timer around the wait, max over ranks): ranks reach "
+                                          "the end of a step milliseconds apart, and whoever is first waits")
     if grad_sync is not None and ns.mode == "sga" and ns.sga_backend == "index":
         try:
             hbm = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"]) * 1e9
@@ -266,6 +282,8 @@ def main() -> int:
             bound += max(3 * 4.0 * n / hbm, (world - 1) * k * 8.0 / 770e9)
         grad_sync["roofline_ms"] = bound * 1e3
         grad_sync["frac_of_roofline"] = bound * 1e3 / max(grad_sync["ms_per_step"], 1e-9)
+        if "busy_ms_per_step" in grad_sync:
+            grad_sync["frac_of_roofline_excluding_peer_wait"] = bound * 1e3 / max(grad_sync["busy_ms_per_step"], 1e-9)
         grad_sync["roofline"] = "per bucket max(3 x 4 B x n / measured HBM, (W-1) x k x 8 B / 770 GB/s)"
 
     # ---- exposed synchronisation: step time minus the same step with every bucket's sync skipped.

@@ -70,11 +70,18 @@ __global__ void __launch_bounds__(256) dense_adamw_ag_kernel(const DenseAdamArgs
       const float lr = a.group_lr[grp], wd = a.group_wd[grp];
       const int lim = (int)min((long long)4, start + n - i);
       float wv[4], mv[4], vv[4], gv[4];
-      for (int j = 0; j < lim; ++j) {
-        wv[j] = a.w[i + j];
-        gv[j] = a.g[i + j];
-        mv[j] = a.m[i + j];
-        vv[j] = a.v[i + j];
+      if (lim == 4) {  // bucket starts and the slice cut are 16-byte aligned: one 128-bit access per array
+        *reinterpret_cast<float4*>(wv) = *reinterpret_cast<const float4*>(a.w + i);
+        *reinterpret_cast<float4*>(gv) = *reinterpret_cast<const float4*>(a.g + i);
+        *reinterpret_cast<float4*>(mv) = *reinterpret_cast<const float4*>(a.m + i);
+        *reinterpret_cast<float4*>(vv) = *reinterpret_cast<const float4*>(a.v + i);
+      } else {
+        for (int j = 0; j < lim; ++j) {
+          wv[j] = a.w[i + j];
+          gv[j] = a.g[i + j];
+          mv[j] = a.m[i + j];
+          vv[j] = a.v[i + j];
+        }
       }
       __nv_bfloat16 bo[4];
       for (int j = 0; j < lim; ++j) {
@@ -84,10 +91,16 @@ __global__ void __launch_bounds__(256) dense_adamw_ag_kernel(const DenseAdamArgs
         wv[j] = wv[j] - lr * upd;
         bo[j] = __float2bfloat16_rn(wv[j]);
       }
-      for (int j = 0; j < lim; ++j) {
-        a.w[i + j] = wv[j];
-        a.m[i + j] = mv[j];
-        a.v[i + j] = vv[j];
+      if (lim == 4) {
+        *reinterpret_cast<float4*>(a.w + i) = *reinterpret_cast<float4*>(wv);
+        *reinterpret_cast<float4*>(a.m + i) = *reinterpret_cast<float4*>(mv);
+        *reinterpret_cast<float4*>(a.v + i) = *reinterpret_cast<float4*>(vv);
+      } else {
+        for (int j = 0; j < lim; ++j) {
+          a.w[i + j] = wv[j];
+          a.m[i + j] = mv[j];
+          a.v[i + j] = vv[j];
+        }
       }
       if (lim == 4) {
 #pragma unroll

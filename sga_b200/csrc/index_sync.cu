@@ -100,6 +100,7 @@ struct ISyncArgs {
   int zero_selected;
   unsigned* bits;        // select-only mode: bit mask of the selection (zeroed by the host)
   unsigned* result;      // [4]: threshold key, ties taken, keys above the threshold, pairs produced
+  unsigned long long* wait_ns;  // nullable: nanoseconds CTA 0 spent waiting on peers' flags are added here
   unsigned* reduce_ticket;  // the reduce kernel's own ticket word (zero between launches): the reduce may run
                             // long after its bucket's chain, when the shared state block belongs to another bucket
 };
@@ -110,6 +111,21 @@ struct ISyncArgs {
 __device__ __forceinline__ void chain_enter() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+// peer_wait with the time CTA 0 spent in it added to *wait_ns: how long this rank stood still for
+// slower peers, as opposed to working (the step's synchronisation time is reported with and without it).
+__device__ __forceinline__ void timed_peer_wait(const PeerCtx& c, int slot, int target, unsigned long long* wait_ns) {
+  const bool timing = wait_ns != nullptr && blockIdx.x == 0 && threadIdx.x == 0;
+  const unsigned long long t0 = timing ? global_ns() : 0ULL;
+  peer_wait(c, slot, target);
+  if (timing) atomicAdd(wait_ns, global_ns() - t0);
 }
 
 __device__ __forceinline__ unsigned key_bits(float x) { return __float_as_uint(x) & 0x7FFFFFFFu; }
@@ -692,7 +708,7 @@ __global__ void __launch_bounds__(IS_THREADS) isync_count_kernel(const ISyncArgs
 __global__ void __launch_bounds__(IS_THREADS) isync_emit_kernel(const ISyncArgs a) {
   chain_enter();
   const PeerCtx& c = a.c;
-  if (c.prev_seq > 0) peer_wait(c, 1, c.prev_seq);  // peers are done reading my previous payload
+  if (c.prev_seq > 0) timed_peer_wait(c, 1, c.prev_seq, a.wait_ns);  // peers are done reading my previous payload
   const unsigned T = ldv(a.state + ST_T), icut = ldv(a.state + ST_ICUT);
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
   const unsigned lt = (1u << lane) - 1u;
@@ -763,7 +779,7 @@ __global__ void __launch_bounds__(IS_THREADS) isync_reduce_kernel(const ISyncArg
   __shared__ unsigned sh_bm[IS_SEG_PER_RANGE * IS_SEG / 32];
   __shared__ float red[IS_THREADS];
   const PeerCtx& c = a.c;
-  peer_wait(c, 0, c.seq);
+  timed_peer_wait(c, 0, c.seq, a.wait_ns);
   const int nranges = (a.nseg + IS_SEG_PER_RANGE - 1) / IS_SEG_PER_RANGE;
   const int2* my_slots = a.slots[c.rank];
   const int* my_hdr = a.hdr[c.rank];
@@ -839,6 +855,7 @@ struct SgaISyncDesc {
   int accumulate, zero_selected, mode, max_ctas;
   int phase;                 // 0: whole chain. 1: up to the push (no reduce). 2: the reduce alone
   void* reduce_ticket;       // one zeroed word per channel
+  void* wait_ns;             // nullable uint64 counter: time spent waiting for peers
 };
 
 // Launch one kernel of the chain; `dependent` lets it be scheduled while its predecessor (the
@@ -920,6 +937,7 @@ SGA_API int sga_index_sync(const SgaPeerDesc* d, const SgaISyncDesc* s, void* st
   a.bits = reinterpret_cast<unsigned*>(s->bits);
   a.result = reinterpret_cast<unsigned*>(s->result);
   a.reduce_ticket = reinterpret_cast<unsigned*>(s->reduce_ticket);
+  a.wait_ns = reinterpret_cast<unsigned long long*>(s->wait_ns);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int cap = s->max_ctas > 0 ? s->max_ctas : 148 * 8;
   const int wpc = IS_THREADS / 32;

@@ -188,32 +188,55 @@ __global__ void __launch_bounds__(512) p2p_mask_union_kernel(const MaskUnionArgs
   const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
   float sq = 0.f;
   long long cnt = 0;
-  for (long long w = w0 + warp; w < w1; w += nwarps) {
+  // A warp takes 32 mask words per trip: each lane loads (and ORs over the ranks) one word, coalesced,
+  // and stores the union back; the words are then visited four at a time, lane l owning bit l of each,
+  // with every rank's value of the four words in flight before any is reduced and written back.
+  for (long long wb = w0 + warp * 32; wb < w1; wb += nwarps * 32) {
+    const long long myw = wb + lane;
     uint32_t u = 0;
-#pragma unroll
-    for (int r = 0; r < MAXW; ++r)
-      if (r < c.W) u |= a.bits[r][w];
-    const long long i = w * 32 + lane;
-    if (((u >> lane) & 1u) && i < a.n) {
-      float v[MAXW];
+    if (myw < w1) {
 #pragma unroll
       for (int r = 0; r < MAXW; ++r)
-        if (r < c.W) v[r] = a.grad[r][i];
-      float acc = v[0];
-#pragma unroll
-      for (int r = 1; r < MAXW; ++r)
-        if (r < c.W) acc += v[r];
-      acc *= a.scale;
-      sq += acc * acc;
-      ++cnt;
+        if (r < c.W) u |= a.bits[r][myw];
 #pragma unroll
       for (int r = 0; r < MAXW; ++r)
-        if (r < c.W) a.grad[r][i] = acc;
+        if (r < c.W) a.ubits[r][myw] = u;
     }
-    if (lane == 0) {
+    if (__ballot_sync(0xffffffffu, u != 0u) == 0u) continue;
+    for (int j0 = 0; j0 < 32; j0 += 4) {
+      bool on[4];
+      long long idx[4];
+      uint32_t any = 0;
 #pragma unroll
-      for (int r = 0; r < MAXW; ++r)
-        if (r < c.W) a.ubits[r][w] = u;
+      for (int t = 0; t < 4; ++t) {
+        const uint32_t uj = __shfl_sync(0xffffffffu, u, j0 + t);
+        any |= uj;
+        idx[t] = (wb + j0 + t) * 32 + lane;
+        on[t] = ((uj >> lane) & 1u) && idx[t] < a.n;
+      }
+      if (any == 0u) continue;
+      float v[4][MAXW];
+#pragma unroll
+      for (int t = 0; t < 4; ++t)
+        if (on[t]) {
+#pragma unroll
+          for (int r = 0; r < MAXW; ++r)
+            if (r < c.W) v[t][r] = a.grad[r][idx[t]];
+        }
+#pragma unroll
+      for (int t = 0; t < 4; ++t)
+        if (on[t]) {
+          float acc = v[t][0];
+#pragma unroll
+          for (int r = 1; r < MAXW; ++r)
+            if (r < c.W) acc += v[t][r];
+          acc *= a.scale;
+          sq += acc * acc;
+          ++cnt;
+#pragma unroll
+          for (int r = 0; r < MAXW; ++r)
+            if (r < c.W) a.grad[r][idx[t]] = acc;
+        }
     }
   }
   if (a.count_out) {
@@ -288,7 +311,7 @@ SGA_API int sga_p2p_allreduce(const SgaPeerDesc* d, void* const* bufs, long long
   a.cta_partials = cta_partials; a.sumsq_out = sumsq_out; a.accumulate = accumulate;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   cudaMemsetAsync(a.c.grid_counter, 0, sizeof(int), st);
-  int grid = num_sms();
+  int grid = num_sms();  // one CTA per SM: the grid must be co-resident, beside the backward pass's GEMM CTAs
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   long long need = (n + 2047) / 2048;
   if (need < 1) need = 1;

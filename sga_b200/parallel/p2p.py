@@ -135,7 +135,8 @@ class ISyncDesc(ctypes.Structure):
                 ("cand_capacity", ctypes.c_longlong), ("seg_capacity", ctypes.c_int),
                 ("partials_capacity", ctypes.c_int),
                 ("accumulate", ctypes.c_int), ("zero_selected", ctypes.c_int), ("mode", ctypes.c_int),
-                ("max_ctas", ctypes.c_int), ("phase", ctypes.c_int), ("reduce_ticket", ctypes.c_void_p)]
+                ("max_ctas", ctypes.c_int), ("phase", ctypes.c_int), ("reduce_ticket", ctypes.c_void_p),
+                ("wait_ns", ctypes.c_void_p)]
 
 
 def _nseg(n: int) -> int:
@@ -166,6 +167,9 @@ class IndexSyncScratch:
         self.nranges = (self.nseg + IS_SEG_PER_RANGE - 1) // IS_SEG_PER_RANGE
         self.partials = torch.zeros(self.nranges, dtype=torch.float32, device=device)
         self.result = torch.zeros(4, dtype=torch.int32, device=device)
+        # nanoseconds this rank's exchange kernels stood waiting for peers' flags (accumulates; read and
+        # zero it around the steps of interest)
+        self.wait_ns = torch.zeros(1, dtype=torch.int64, device=device)
 
     def ensure(self, n: int) -> None:
         if _nseg(n) > self.nseg:
@@ -253,6 +257,7 @@ def bucket_index_sync_(ch: PeerChannel, scratch: IndexSyncScratch, acc: torch.Te
     s.accumulate, s.zero_selected, s.mode, s.max_ctas = int(accumulate), int(zero_selected), int(select_only), max_ctas
     s.phase = 1 if (defer_reduce and not select_only) else 0
     s.reduce_ticket = slots.ticket.data_ptr() if slots is not None else None
+    s.wait_ns = scratch.wait_ns.data_ptr()
     rc = lib().sga_index_sync(ctypes.byref(d), ctypes.byref(s), _st())
     _chk(rc, "sga_index_sync")
     return (d, s, (acc, comm, slots, scratch, sumsq_out)) if s.phase == 1 else None

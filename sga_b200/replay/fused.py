@@ -705,8 +705,12 @@ def run_shard(rank, world, trace_dir, t0, configs, window, horizons, device, den
     # ---- stream: groups of configurations, one pass over the window per group
     n_loc = hi - lo
     results, prof = {}, []
+    fg = last = None
     for grp in group_configs(configs, max_configs, state_budget_mb, n_loc):
-        by_opt = {}
+        # one group's state at a time: the previous group is released before the next one is built
+        fg = last = None
+        if dev.type == "cuda":
+            torch.cuda.empty_cache()
         fg = FusedGroup(grp, n_loc, info.numel, dev, comms, hp, wd_vec, w0, m0, v0, t0, W, horizons,
                         dense[grp[0].optimizer],
                         use_kernel, semantics=semantics, entries=entries)
@@ -773,6 +777,12 @@ def _worker(rank, world, port, kwargs, out_path):
         kwargs = dict(kwargs, device=f"cuda:{rank % torch.cuda.device_count()}")
     dist.init_process_group("nccl" if cuda else "gloo", rank=rank, world_size=world)
     try:
+        # the first collective builds the communicator (seconds for NCCL): do it here, so that the
+        # engine's phase times, which start in run_shard, are the engine's own
+        warm = torch.zeros(1, device=kwargs["device"] if cuda else "cpu")
+        dist.all_reduce(warm)
+        if cuda:
+            torch.cuda.synchronize()
         frag = run_shard(rank, world, **kwargs)
         if rank == 0:
             torch.save(frag, out_path)

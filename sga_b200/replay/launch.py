@@ -238,6 +238,7 @@ def _child(local_rank, node_rank, spn, world, master_addr, master_port, spec, ph
         if phase == "preflight":
             dist.barrier()
             return
+        dist.all_reduce(torch.zeros(1, device=device if cuda else "cpu"))  # communicator set-up outside the engine's timers
         kw = {k: v for k, v in spec.items() if k != "out_path"}
         kw["device"] = device
         frag = RF.run_shard(rank, world, **kw)

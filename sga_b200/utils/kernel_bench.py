@@ -175,7 +175,54 @@ def bench_elementwise(small):
         V = 128256
         z = torch.randn(T, V, device=dev, dtype=torch.bfloat16)
         tgt = torch.randint(0, V, (T,), device=dev)
-        emit("ce_fwd_bwd_kernel", f"T={T} V={V}", timed(lambda: F.cross_entropy_(z, tgt, 1.0 / T), 5), bytes_=T * V * 8.0)
+        # the logits are read once (a row's second visit comes from L2 / shared memory) and overwritten with
+        # their gradient in place: 2 B read + 2 B written per element
+        emit("ce_fwd_bwd_kernel", f"T={T} V={V}", timed(lambda: F.cross_entropy_(z, tgt, 1.0 / T), 5, flush=flush),
+             bytes_=T * V * 4.0)
+
+
+def bench_peer(small):
+    """The fused peer-memory kernels on one rank (peer = self): their local work without the link.
+    Reduce-scatter form of the all-reduce, mask-union reduce, sharded AdamW + bf16 parameter push."""
+    from .. import kernels as K
+    from ..parallel import p2p
+    from ..parallel.symm import SymmPool
+
+    dev = "cuda"
+    n = (16 if small else 64) * 1024 * 1024
+    pool = SymmPool(device="cuda:0")
+    ch = p2p.PeerChannel(pool)
+    it = 2 if small else 10
+    buf = pool.alloc(4 * n)
+    buf.view(torch.float32, 0, n).normal_()
+    sq = torch.zeros(1, device=dev)
+    ms = timed(lambda: p2p.allreduce_(ch, buf, 0, n, scale=0.5, rs_only=True, sumsq_out=sq), it, warmup=1)
+    emit("p2p_allreduce_kernel (rs_only)", f"n={n} fp32 (1 rank: read, scale, write back, norm)", ms, bytes_=n * 8.0)
+    nw = (n + 31) // 32
+    grad, bits, ubits = pool.alloc(4 * n), pool.alloc(4 * nw), pool.alloc(4 * nw)
+    grad.view(torch.float32, 0, n).normal_()
+    sel = (torch.rand(nw, 32, device=dev) < 0.0625).to(torch.int64)
+    words = (sel << torch.arange(32, device=dev)).sum(1)
+    bits.view(torch.int32, 0, nw).copy_((words - (words >= 2 ** 31).to(torch.int64) * 2 ** 32).to(torch.int32))
+    del sel, words
+    mu8 = torch.empty(n, dtype=torch.uint8, device=dev)
+    ms = timed(lambda: p2p.mask_union_reduce_(ch, grad, 0, bits, 0, ubits, 0, n, scale=0.5, mask_u8=mu8, sumsq_out=sq),
+               it, warmup=1)
+    # mask words read and written, 1/16 of the entries read and written back (32-byte sectors: about
+    # 40 % of the bucket's sectors are touched), the byte mask written
+    emit("p2p_mask_union_kernel", f"n={n} fp32, 6 % of the entries in the union (1 rank)", ms,
+         bytes_=n * (2 / 8.0 + 1.0 + 0.4 * 8.0))
+    w, g, m, v = (torch.randn(n, device=dev) * 1e-3 for _ in range(4))
+    v.abs_()
+    model = pool.alloc(2 * n)
+    table = K.SegmentTable([0], [0], n, dev)
+    bs = torch.tensor([0], dtype=torch.int64, device=dev)
+    bl = torch.tensor([n], dtype=torch.int64, device=dev)
+    ms = timed(lambda: p2p.dense_adamw_ag_(ch, w, g, m, v, model, bs, bl, table, [3e-4], [0.1], beta1=0.9, beta2=0.95,
+                                           eps=1e-8, step=3), it, warmup=1)
+    emit("dense_adamw_ag_kernel", f"n={n} (1 rank: read w,g,m,v; write w,m,v and the bf16 copy)", ms, bytes_=n * 30.0)
+    ch.check()
+    pool.close()
 
 
 def bench_replay(small):
@@ -249,7 +296,7 @@ def bench_mask_stats(small):
 
 
 CASES = {"mask_stats": bench_mask_stats, "attention": bench_attention, "gemm": bench_gemm, "adam": bench_adam, "index_sync": bench_index_sync, "elementwise": bench_elementwise,
-         "replay": bench_replay}
+         "replay": bench_replay, "peer": bench_peer}
 
 
 def main(argv=None) -> int:
