@@ -131,16 +131,21 @@ __device__ __forceinline__ void timed_peer_wait(const PeerCtx& c, int slot, int 
 __device__ __forceinline__ unsigned key_bits(float x) { return __float_as_uint(x) & 0x7FFFFFFFu; }
 __device__ __forceinline__ unsigned ldv(const unsigned* p) { return *reinterpret_cast<const volatile unsigned*>(p); }
 
-// The CTA that takes the last ticket of a grid sees every other CTA's writes.
+// The CTA that takes the last ticket of a grid sees every other CTA's writes. The block barrier
+// orders the CTA's writes before thread 0's fence, and the fence is cumulative, so one thread per
+// CTA fences (at system scope when the writes went to peers' memory) instead of all 256.
 template <bool SYSTEM = false>
 __device__ __forceinline__ bool last_cta(unsigned* ticket) {
   __shared__ int s_last;
-  if (SYSTEM) __threadfence_system(); else __threadfence();
   __syncthreads();
   if (threadIdx.x == 0) {
+    if (SYSTEM) __threadfence_system(); else __threadfence();
     const unsigned t = atomicAdd(ticket, 1u);
     s_last = (t == gridDim.x - 1);
-    if (s_last) *ticket = 0;
+    if (s_last) {
+      *ticket = 0;
+      __threadfence();
+    }
   }
   __syncthreads();
   if (s_last) __threadfence();
@@ -197,6 +202,43 @@ __device__ __forceinline__ bool find_suffix_bin(const unsigned* hist, int nb, in
     __syncthreads();
     if (s_res[0] != 0xFFFFFFFFu) break;
     run += total;
+  }
+  __syncthreads();
+  bin = s_res[0];
+  above = s_res[1];
+  __syncthreads();
+  return bin != 0xFFFFFFFFu;
+}
+
+// The same over all `NB` bins in one round: thread t owns bins NB-1 - t*PER .. NB - (t+1)*PER
+// (descending), with every replica's load in flight at once, then one block scan and a walk over
+// the owner's own bins. One CTA of 256 threads; result uniform over its threads.
+template <int NB>
+__device__ __forceinline__ bool find_suffix_bin_all(const unsigned* hist, int rep, unsigned want, unsigned* sh,
+                                                    unsigned& bin, unsigned& above) {
+  constexpr int PER = NB / IS_THREADS;
+  static_assert(NB % IS_THREADS == 0, "bins must divide over the CTA");
+  __shared__ unsigned s_res[2];
+  if (threadIdx.x == 0) { s_res[0] = 0xFFFFFFFFu; s_res[1] = 0; }
+  unsigned h[PER];
+  const int hi = NB - 1 - (int)threadIdx.x * PER;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) h[j] = 0;
+  for (int r = 0; r < rep; ++r)
+#pragma unroll
+    for (int j = 0; j < PER; ++j) h[j] += __ldcg(hist + r * NB + hi - j);
+  unsigned mine = 0;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) mine += h[j];
+  unsigned total;
+  const unsigned before = block_excl_scan256(mine, sh, total);  // barriers inside order the reset of s_res
+  if (before < want && before + mine >= want) {
+    unsigned run = before;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      if (run < want && run + h[j] >= want) { s_res[0] = (unsigned)(hi - j); s_res[1] = run; }
+      run += h[j];
+    }
   }
   __syncthreads();
   bin = s_res[0];
@@ -548,7 +590,7 @@ __global__ void __launch_bounds__(IS_THREADS) isync_digit_kernel(const ISyncArgs
   if (!last_cta(a.state + ST_TICKET0 + 3)) return;
   const unsigned k = (unsigned)a.k, aboveA = ldv(a.state + ST_ABOVE);
   unsigned bB, aboveB;
-  if (!find_suffix_bin(a.histB, IS_BBINS, IS_REP, k - aboveA, IS_BBINS - 1, 0, sh_scan, bB, aboveB)) {
+  if (!find_suffix_bin_all<IS_BBINS>(a.histB, IS_REP, k - aboveA, sh_scan, bB, aboveB)) {
     if (threadIdx.x == 0) atomicOr(a.c.err, SGA_ERR_BOUNDS);
     bB = 0; aboveB = 0;
   }

@@ -112,7 +112,8 @@ def bench_index_sync(small):
 
     pool = SymmPool(device="cuda:0")
     ch = p2p.PeerChannel(pool)
-    for mi in ((32,) if small else (8, 16, 32, 64)):
+    # up to the bucket size the training step uses for this mode (1.24 G parameters in 7 buckets of about 176 M)
+    for mi in ((32,) if small else (8, 16, 32, 64, 128, 168)):
         _index_sync_case(pool, ch, p2p, mi * 1024 * 1024, small)
     pool.close()
 
