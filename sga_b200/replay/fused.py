@@ -40,7 +40,8 @@ from . import core as RC
 ENV_KERNEL = "REPLAY_FUSED_KERNEL"      # on | off  (off: PyTorch ops even on CUDA)
 ENV_SELECT = "REPLAY_FUSED_SELECT"      # auto | cpu  (cpu: the front block's selections run on host tensors)
 ENV_FRONT_SORT = "REPLAY_FUSED_FRONT_SORT"  # auto | cpu  (cpu: the front block's ranking sorts run on the host)
-ENV_P1_READ = "REPLAY_FUSED_P1_READ"    # mmap | load  (mmap: a shard touches only its slice of every gradient file)
+ENV_FRONT_RANK_BG = "REPLAY_FUSED_FRONT_RANK_BG"  # on | off  (on: rank 0 ranks the front block on a worker thread)
+ENV_P1_READ = "REPLAY_FUSED_P1_READ"    # mmap | load | pread  (mmap and pread: a shard touches only its slice of every gradient file)
 ENV_S0_PROFILE = "REPLAY_S0_PROFILE"    # 0 | 1  (1: rank 0 prints per-group counters and the phase times)
 ENV_WINDOW_HOST_GIB = "REPLAY_FUSED_WINDOW_HOST_GIB"  # host bytes (GiB, default 8) a shard may spend keeping the
 #                                          window's gradients between the dense arm and the stream
@@ -209,6 +210,105 @@ def shard_select_balanced(score_loc: torch.Tensor, k: int, comms: Comms, entries
     return (sel, _key_float(int(b) << shift)) if return_threshold else sel  # threshold: the bin's lower edge
 
 
+def front_metrics(got_s, got_l, ideal, k: int, threshold, stats, sort_on_host: bool) -> dict:
+    """Ranking metrics of one (score, ratio, optimizer) cell from the gathered selections: the
+    score's own top-k (``got_s`` scores with their labels ``got_l``) against the label's top-k
+    (``ideal``). Pure function of its arguments; runs on whichever device the tensors live on."""
+    if sort_on_host:
+        got_s, got_l, ideal = got_s.cpu(), got_l.cpu(), ideal.cpu()
+    disc = 1.0 / torch.log2(torch.arange(2, k + 2, dtype=torch.float64, device=got_s.device))
+    order = torch.argsort(got_s, descending=True, stable=True)
+    idl = torch.sort(ideal.double(), descending=True).values
+    idcg = float((idl * disc[:idl.numel()]).sum())
+    ndcg = float((got_l.double()[order] * disc[:order.numel()]).sum()) / idcg if idcg > 0 else 0.0
+    return {"k": k, "threshold": threshold, "ndcg_at_k": ndcg, "recall_at_k": stats[0] / max(k, 1),
+            "missed_label_mass": stats[1] / stats[2] if stats[2] > 0 else 0.0,
+            "missed_score_mass": stats[3] / stats[4] if stats[4] > 0 else 0.0}
+
+
+class RankLane:
+    """One worker thread that turns gathered selections into ranking metrics while the main thread
+    goes on to the next cell's collectives. Work items are closed over plain tensors and numbers:
+    the worker never sees a process group and never issues a collective, so every collective stays
+    on the main thread, and cells are ranked in submission order by the single writer of
+    ``results``, which makes the report identical to the inline path.
+
+    A failure in the worker is kept, not swallowed: ``submit`` refuses to queue behind a dead
+    worker (a bounded queue with no consumer would block the main thread for ever) and ``finish``
+    re-raises it before the results are used. With ``enabled=False`` the same calls run inline."""
+
+    _STOP = object()
+
+    def __init__(self, enabled: bool, device: torch.device, depth: int = 4):
+        self.enabled, self.device = bool(enabled), device
+        self.results: dict = {}
+        self.rank_s = 0.0      # time spent ranking (worker or inline)
+        self.wait_s = 0.0      # time the main thread stood in submit / finish
+        self.error: Optional[BaseException] = None
+        self.current = "start-up"
+        self.thread = None
+        if self.enabled:
+            self.q = queue.Queue(maxsize=depth)
+            self.thread = threading.Thread(target=self._work, name="sga-replay-front-rank", daemon=True)
+            self.thread.start()
+
+    def _rank(self, key, args) -> None:
+        t0 = time.perf_counter()
+        self.current = repr(key)
+        self.results[key] = front_metrics(*args)
+        self.rank_s += time.perf_counter() - t0
+
+    def _work(self):
+        try:
+            if self.device.type == "cuda":
+                torch.cuda.set_device(self.device)  # the current device is per thread
+            while True:
+                item = self.q.get()
+                if item is self._STOP:
+                    return
+                self._rank(*item)
+        except BaseException as e:  # kept for the main thread
+            self.error = e
+
+    def _fail(self):
+        raise RuntimeError(f"front ranking failed at {self.current}") from self.error
+
+    def submit(self, key, *args) -> None:
+        if not self.enabled:
+            self._rank(key, args)
+            return
+        t0 = time.perf_counter()
+        try:
+            while True:
+                if self.error is not None:
+                    self._fail()
+                try:
+                    self.q.put((key, args), timeout=0.5)
+                    return
+                except queue.Full:
+                    if not self.thread.is_alive() and self.error is None:
+                        raise RuntimeError("front ranking worker exited without a recorded error")
+        finally:
+            self.wait_s += time.perf_counter() - t0
+
+    def finish(self) -> dict:
+        """Drains the lane and returns the results; re-raises a worker failure."""
+        if self.enabled and self.thread is not None:
+            t0 = time.perf_counter()
+            while self.thread.is_alive():
+                try:
+                    self.q.put(self._STOP, timeout=0.5)
+                    break
+                except queue.Full:
+                    continue
+            self.thread.join()
+            self.thread = None
+            self.wait_s += time.perf_counter() - t0
+        if self.error is not None:
+            self._fail()
+        return self.results
+
+
 @dataclass
 class StepInput:
     si: int
@@ -217,21 +317,41 @@ class StepInput:
     lr: float
 
 
-class GPrefetcher:
-    """Background reader: loads each step's gradient file, slices this shard
-    out of it in catalog order and stages it (pinned when the consumer is a
-    GPU). Depth-bounded; the first failure is latched and re-raised by ``get``."""
+READ_ARMS = ("mmap", "load", "pread")
 
-    def __init__(self, info: RC.TraceInfo, steps, lo, hi, dtype, pin: bool, depth: int = 2):
+
+class GPrefetcher:
+    """Background reader: produces, step by step, this shard's slice of the logged gradient in
+    catalog order, staged in pinned memory when the consumer is a GPU. Depth-bounded; the first
+    failure of any of its threads is latched and re-raised by ``get``.
+
+    Read arms (``REPLAY_FUSED_P1_READ``): ``mmap`` maps the step file and copies the slice out of
+    the mapping, ``load`` reads the whole file, ``pread`` never opens the file as an archive at
+    all: one thread copies the slice's bytes out of the stored zip records with positional reads
+    (``ptfile.PtIndex``) while a second thread converts and pins the previous step's bytes, so the
+    conversion never sits between two read calls. The pread arm holds up to ``depth`` raw slices
+    beside the ``depth`` converted ones. ``index_cache`` (path -> PtIndex) lets several
+    prefetchers over the same window parse each file's directory once."""
+
+    def __init__(self, info: RC.TraceInfo, steps, lo, hi, dtype, pin: bool, depth: int = 2, index_cache=None):
         self.info, self.steps, self.lo, self.hi, self.dtype, self.pin = info, list(steps), lo, hi, dtype, pin
+        self.mode = _switch(ENV_P1_READ, READ_ARMS, "mmap")
         self.q = queue.Queue(maxsize=depth)
         self.exc: Optional[BaseException] = None
         self.read_s = 0.0
-        self.t = threading.Thread(target=self._run, name="sga-replay-prefetch", daemon=True)
-        self.t.start()
+        self.convert_s = 0.0
+        self.index_cache = {} if index_cache is None else index_cache
+        if self.mode == "pread":
+            self.raw_q = queue.Queue(maxsize=depth)
+            self.threads = [threading.Thread(target=self._run_pread, name="sga-replay-pread", daemon=True),
+                            threading.Thread(target=self._run_convert, name="sga-replay-convert", daemon=True)]
+        else:
+            self.threads = [threading.Thread(target=self._run, name="sga-replay-prefetch", daemon=True)]
+        for t in self.threads:
+            t.start()
 
     def _load(self, t):
-        return RC.load_g(self.info, t, mmap=_switch(ENV_P1_READ, ("mmap", "load"), "mmap") == "mmap")
+        return RC.load_g(self.info, t, mmap=self.mode == "mmap")
 
     def _run(self):
         try:
@@ -242,6 +362,58 @@ class GPrefetcher:
                 if self.pin:
                     flat = flat.pin_memory()
                 self.read_s += time.perf_counter() - t0
+                self.q.put((t, meta, flat))
+        except BaseException as e:
+            self.exc = e
+            self.q.put(None)
+
+    def _run_pread(self):
+        from .ptfile import PtIndex
+
+        try:
+            for t in self.steps:
+                t0 = time.perf_counter()
+                path = os.path.join(self.info.dir, f"step_{t:06d}_g.pt")
+                idx = self.index_cache.get(path)
+                if idx is None:
+                    idx = self.index_cache[path] = PtIndex(path)
+                meta, stubs = idx.tree["meta"], idx.tree["payload"]
+                pieces = []
+                fd = os.open(path, os.O_RDONLY)
+                try:
+                    for name, off, sh in zip(self.info.names, self.info.offsets, self.info.shapes):
+                        n = int(math.prod(sh)) if sh else 1
+                        a, b = max(off, self.lo), min(off + n, self.hi)
+                        if a >= b:
+                            continue
+                        if name not in stubs:
+                            raise KeyError(f"{path}: no gradient for {name}")
+                        if stubs[name].numel() != n:
+                            raise ValueError(f"{path}: {name} holds {stubs[name].numel()} elements, the catalog says {n}")
+                        pieces.append((a - self.lo, idx.read_slice(fd, stubs[name], a - off, b - a)))
+                finally:
+                    os.close(fd)
+                self.read_s += time.perf_counter() - t0
+                self.raw_q.put((t, meta, pieces))
+            self.raw_q.put(None)
+        except BaseException as e:
+            self.exc = e
+            self.raw_q.put(None)
+
+    def _run_convert(self):
+        try:
+            while True:
+                item = self.raw_q.get()
+                if item is None:
+                    if self.exc is not None:
+                        self.q.put(None)
+                    return
+                t, meta, pieces = item
+                t0 = time.perf_counter()
+                flat = torch.empty(self.hi - self.lo, dtype=self.dtype, pin_memory=self.pin)
+                for dst, piece in pieces:
+                    flat[dst:dst + piece.numel()].copy_(piece)
+                self.convert_s += time.perf_counter() - t0
                 self.q.put((t, meta, flat))
         except BaseException as e:
             self.exc = e
@@ -566,7 +738,7 @@ def run_shard(rank, world, trace_dir, t0, configs, window, horizons, device, den
 
     # every A/B switch is read once, before any work: an unknown value refuses the run by name
     for name, allowed, dflt in ((ENV_KERNEL, ("on", "off"), "on"), (ENV_SELECT, ("auto", "cpu"), "auto"),
-                                (ENV_FRONT_SORT, ("auto", "cpu"), "auto"), (ENV_P1_READ, ("mmap", "load"), "mmap"),
+                                (ENV_FRONT_SORT, ("auto", "cpu"), "auto"), (ENV_P1_READ, READ_ARMS, "mmap"), (ENV_FRONT_RANK_BG, ("on", "off"), "on"),
                                 (ENV_S0_PROFILE, ("0", "1"), "0")):
         _switch(name, allowed, dflt)
     from .synth import SyntheticSource
@@ -607,6 +779,7 @@ def run_shard(rank, world, trace_dir, t0, configs, window, horizons, device, den
     # the window's gradients, read once for the dense arm, serve the stream below too while they fit the budget
     window_g = None
     keep_bytes = int(float(os.environ.get(ENV_WINDOW_HOST_GIB, "8")) * (1 << 30))
+    pt_index = {}  # step file -> parsed archive directory, shared by every prefetcher of this shard (pread arm)
     lap("setup")
     cache_hit = {}
     for opt in optimizers:
@@ -616,7 +789,7 @@ def run_shard(rank, world, trace_dir, t0, configs, window, horizons, device, den
         if blob is None and synth is not None:
             logged, metas = synth.gradients(steps, lo, hi, dev), [synth.meta(t) for t in steps]
         elif blob is None:
-            pf = GPrefetcher(info, steps, lo, hi, gdtype, pin=dev.type == "cuda")
+            pf = GPrefetcher(info, steps, lo, hi, gdtype, pin=dev.type == "cuda", index_cache=pt_index)
             logged, metas = [], []
             for _ in steps:
                 _t, gm, flat = pf.get()
@@ -650,7 +823,6 @@ def run_shard(rank, world, trace_dir, t0, configs, window, horizons, device, den
     del w0_dev
     lap("dense_arm")
     # ---- front: branch scores ranked against the label, the window's summed squared gradient-driven step
-    front = {}
     # A/B arms of the front block (unknown values raise): selections and / or ranking sorts on host tensors.
     # Radix selection is integer arithmetic and the sorts are stable, so both arms give the same report.
     front_sel = _switch(ENV_SELECT, ("auto", "cpu"), "auto")
@@ -664,6 +836,7 @@ def run_shard(rank, world, trace_dir, t0, configs, window, horizons, device, den
     hp_dev = RC.Hyper(wd=wd_vec.to(fdev), beta1=hp.beta1, beta2=hp.beta2, eps=hp.eps, clip=hp.clip)
     score_stats, thresholds, label_stats = {}, {}, {}
     entries = shard_entries(info, lo, hi)
+    lane = RankLane(rank == 0 and _switch(ENV_FRONT_RANK_BG, ("on", "off"), "on") == "on", fdev)
     for opt in optimizers:
         label_sel = {}
         label_loc = labels[opt].to(fdev)
@@ -688,18 +861,8 @@ def run_shard(rank, world, trace_dir, t0, configs, window, horizons, device, den
                 got_l = fcomms.gather_to_root(label_loc[sel_s].float())
                 ideal = fcomms.gather_to_root(label_loc[sel_l].float())
                 if rank == 0:
-                    if front_sort == "cpu":
-                        got_s, got_l, ideal = got_s.cpu(), got_l.cpu(), ideal.cpu()
-                    disc = 1.0 / torch.log2(torch.arange(2, k + 2, dtype=torch.float64, device=got_s.device))
-                    order = torch.argsort(got_s, descending=True, stable=True)
-                    idl = torch.sort(ideal.double(), descending=True).values
-                    idcg = float((idl * disc[:idl.numel()]).sum())
-                    ndcg = float((got_l.double()[order] * disc[:order.numel()]).sum()) / idcg if idcg > 0 else 0.0
-                    s = stats.tolist()
-                    front[(name, ratio, opt)] = {"k": k, "threshold": th, "ndcg_at_k": ndcg,
-                                                 "recall_at_k": s[0] / max(k, 1),
-                                                 "missed_label_mass": s[1] / s[2] if s[2] > 0 else 0.0,
-                                                 "missed_score_mass": s[3] / s[4] if s[4] > 0 else 0.0}
+                    lane.submit((name, ratio, opt), got_s, got_l, ideal, k, th, stats.tolist(), front_sort == "cpu")
+    front = lane.finish()
     del label_sel
     lap("front")
     # ---- stream: groups of configurations, one pass over the window per group
@@ -716,8 +879,8 @@ def run_shard(rank, world, trace_dir, t0, configs, window, horizons, device, den
                         use_kernel, semantics=semantics, entries=entries)
         fg.initial_select(g0)
         lazy = synth.gradients(steps, lo, hi, dev) if synth is not None else None
-        pf = None if (window_g is not None or lazy is not None) else GPrefetcher(info, steps, lo, hi, gdtype,
-                                                                                 pin=dev.type == "cuda")
+        pf = None if (window_g is not None or lazy is not None) else GPrefetcher(
+            info, steps, lo, hi, gdtype, pin=dev.type == "cuda", index_cache=pt_index)
         for si in range(W):
             if lazy is not None:
                 _t, gm, flat = steps[si], synth.meta(steps[si]), lazy[si]
@@ -735,7 +898,9 @@ def run_shard(rank, world, trace_dir, t0, configs, window, horizons, device, den
     if prof:
         prof[0]["phases_s"] = phases
         prof[0]["arms"] = {"front_sel": front_sel, "front_sort": front_sort, "kernel": "cuda" if use_kernel else "torch",
-                           "g_read": _switch(ENV_P1_READ, ("mmap", "load"), "mmap")}
+                           "g_read": _switch(ENV_P1_READ, READ_ARMS, "mmap"),
+                           "front_rank_bg": "on" if lane.enabled else "off",
+                           "front_rank_s": round(lane.rank_s, 4), "front_rank_wait_s": round(lane.wait_s, 4)}
     if _switch(ENV_S0_PROFILE, ("0", "1"), "0") == "1" and rank == 0:
         for gi, pr in enumerate(prof):
             busy = pr["pass1_s"] + pr["select_s"] + pr["pass3_s"]

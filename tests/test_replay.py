@@ -299,3 +299,104 @@ def test_front_block_arms_and_profile_switches(trace, monkeypatch, capsys):
     assert arms["front_sel"] == "cpu" and arms["front_sort"] == "cpu" and arms["g_read"] == "load"
     out = capsys.readouterr().out
     assert "[fused] S0PROFILE group 0: configs=2" in out and "host_syncs=" in out and "S0PROFILE phases" in out
+
+
+# ---------------------------------------------------------------- pread arm, background front ranking
+def test_pt_index_reads_slices_without_loading(tmp_path):
+    from sga_b200.replay.ptfile import PtIndex
+
+    torch.manual_seed(0)
+    base = torch.randn(50)
+    blob = {"meta": {"step": 3, "lr": [1e-3], "nested": {"a": (1, 2.5, "x")}},
+            "payload": {"a": torch.randn(7, 5), "b": torch.randn(11).to(torch.bfloat16), "view": base[10:30],
+                        "scalar": torch.tensor(2.0)}}
+    path = str(tmp_path / "step.pt")
+    torch.save(blob, path)
+    idx = PtIndex(path)
+    assert idx.tree["meta"] == blob["meta"]
+    fd = os.open(path, os.O_RDONLY)
+    try:
+        for name, t in blob["payload"].items():
+            stub = idx.tree["payload"][name]
+            assert stub.dtype == t.dtype and stub.numel() == t.numel()
+            flat = t.reshape(-1)
+            for first, count in ((0, t.numel()), (t.numel() // 3, t.numel() - t.numel() // 3), (0, 0)):
+                got = idx.read_slice(fd, stub, first, count)
+                assert got.dtype == t.dtype and torch.equal(got, flat[first:first + count])
+        with pytest.raises(ValueError, match="outside"):
+            idx.read_slice(fd, idx.tree["payload"]["a"], 30, 10)
+        # a storage record shorter than its tensor claims must fail before any read
+        stub = idx.tree["payload"]["a"]
+        idx.records[stub.key] = (idx.records[stub.key][0], 16)
+        with pytest.raises(ValueError, match="too short"):
+            idx.read_slice(fd, stub, 0, 4)
+    finally:
+        os.close(fd)
+    with pytest.raises(ValueError, match="not a torch.save archive"):
+        import zipfile
+        bad = str(tmp_path / "bad.pt")
+        with zipfile.ZipFile(bad, "w") as z:
+            z.writestr("readme.txt", "no pickle here")
+        PtIndex(bad)
+
+
+@pytest.mark.parametrize("g_dtype", ["fp32", "bf16"])
+def test_pread_arm_equals_mmap_arm(tmp_path, monkeypatch, g_dtype):
+    d = make_synthetic_trace(str(tmp_path / "t"), sizes=SIZES, steps=5, g_dtype=g_dtype, seed=11)
+    info = RC.discover_trace(d)
+    steps = info.window(0, 5)
+    for lo, hi in ((0, info.numel), (3500, 7200), (4000, 4001)):   # whole vector, a shard across parameters, one element
+        for dtype in (torch.float32, torch.bfloat16):
+            outs = {}
+            for arm in ("mmap", "pread"):
+                monkeypatch.setenv(RF.ENV_P1_READ, arm)
+                cache = {}
+                pf = RF.GPrefetcher(info, steps, lo, hi, dtype, pin=False, index_cache=cache)
+                outs[arm] = [pf.get() for _ in steps]
+                if arm == "pread":
+                    assert len(cache) == len(steps) and pf.mode == "pread"
+            for (ta, ma, fa), (tb, mb, fb) in zip(outs["mmap"], outs["pread"]):
+                assert ta == tb and ma == mb and fa.dtype == fb.dtype and torch.equal(fa, fb)
+
+
+def test_pread_arm_failure_is_latched_and_report_is_unchanged(trace, monkeypatch):
+    info = RC.discover_trace(trace)
+    monkeypatch.setenv(RF.ENV_P1_READ, "pread")
+    pf = RF.GPrefetcher(info, [0, 1, 99], 0, info.numel, torch.float32, pin=False)   # step 99 does not exist
+    pf.get()
+    pf.get()
+    with pytest.raises(RuntimeError, match="prefetch failed"):
+        pf.get()
+    cfgs = CONFIGS[:2]
+    got = RF.run_fused_branch(trace, 0, cfgs, 12, [12], score_names=["abs_g"], ratios=[5.0])
+    assert got["profile"][0]["arms"]["g_read"] == "pread"
+    monkeypatch.delenv(RF.ENV_P1_READ)
+    base = RF.run_fused_branch(trace, 0, cfgs, 12, [12], score_names=["abs_g"], ratios=[5.0])
+    assert got["front"] == base["front"] and got["results"] == base["results"]
+
+
+def test_front_rank_lane_background_equals_inline_and_keeps_failures(trace, monkeypatch):
+    cfgs = CONFIGS[:2]
+    monkeypatch.setenv(RF.ENV_FRONT_RANK_BG, "bogus")
+    with pytest.raises(ValueError, match=RF.ENV_FRONT_RANK_BG):
+        RF.run_fused_branch(trace, 0, cfgs, 12, [12], score_names=["abs_g"], ratios=[5.0])
+    reports = {}
+    for arm in ("on", "off"):
+        monkeypatch.setenv(RF.ENV_FRONT_RANK_BG, arm)
+        reports[arm] = RF.run_fused_branch(trace, 0, cfgs, 12, [12], score_names=["abs_g", "update"], ratios=[2.0, 5.0])
+        assert reports[arm]["profile"][0]["arms"]["front_rank_bg"] == arm
+    assert reports["on"]["front"] == reports["off"]["front"] and len(reports["on"]["front"]) == 4
+    assert reports["on"]["results"] == reports["off"]["results"]
+
+    # the lane by itself: order of submission, a worker failure surfaces in submit or finish, never as a hang
+    lane = RF.RankLane(True, torch.device("cpu"), depth=1)
+    s = torch.tensor([3.0, 1.0, 2.0])
+    for i in range(5):
+        lane.submit(("cell", i), s, s.clone(), s.clone(), 3, 0.5, [3.0, 0.0, 6.0, 0.0, 6.0], False)
+    res = lane.finish()
+    assert list(res) == [("cell", i) for i in range(5)] and res[("cell", 0)]["ndcg_at_k"] == pytest.approx(1.0)
+    bad = RF.RankLane(True, torch.device("cpu"), depth=1)
+    with pytest.raises(RuntimeError, match="front ranking failed"):
+        for i in range(8):   # the first item kills the worker; a later submit or the finish must report it
+            bad.submit(("cell", i), "not a tensor", s, s, 3, 0.5, [0.0] * 5, False)
+        bad.finish()
