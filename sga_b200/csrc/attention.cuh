@@ -67,6 +67,16 @@ __device__ __forceinline__ void store_p32(uint8_t* tile, int r, int col, const f
   }
 }
 
+// The same from 16 already packed bf16 pairs (pair i = columns col + 2i, col + 2i + 1).
+__device__ __forceinline__ void store_pk32(uint8_t* tile, int r, int col, const uint32_t (&pk)[16]) {
+  uint8_t* slab = tile + (col >> 6) * (128 * 128) + r * 128;
+  const int k0 = (col & 63) >> 3;
+#pragma unroll
+  for (int v = 0; v < 4; ++v)
+    *reinterpret_cast<uint4*>(slab + (((k0 + v) ^ (r & 7)) << 4)) =
+        make_uint4(pk[4 * v], pk[4 * v + 1], pk[4 * v + 2], pk[4 * v + 3]);
+}
+
 // The same for 16 values, columns [col, col + 16).
 __device__ __forceinline__ void store_p16(uint8_t* tile, int r, int col, const float (&p)[16]) {
   uint8_t* slab = tile + (col >> 6) * (128 * 128) + r * 128;

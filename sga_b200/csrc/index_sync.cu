@@ -54,6 +54,7 @@ constexpr int IS_ABINS = 4096;        // first digit, also the sample's histogra
 constexpr int IS_BBINS = 2048;        // second digit: bits 18..8
 constexpr int IS_FBINS = 1 << 19;     // fine histogram of the low 19 bits inside the crossing first-digit bin
 constexpr int IS_REP = 8;             // replicas of the two coarse global histograms
+constexpr int IS_CU = 4;             // candidate trips (of 32, or of 256 in the reduce) whose loads are issued together
 constexpr int IS_WBINS = 1024;        // the filter's shared-memory window of first-digit bins (4 KB: its CTAs fit beside a GEMM CTA)
 
 // Word offsets inside the state block (unsigned[64], zeroed by the host before each bucket).
@@ -570,19 +571,27 @@ __global__ void __launch_bounds__(IS_THREADS) isync_digit_kernel(const ISyncArgs
        seg += (long long)gridDim.x * (IS_THREADS / 32)) {
     const long long s0 = seg * IS_SEG;
     const int cnt = a.segcnt[seg];
-    for (int j0 = 0; j0 < cnt; j0 += 32) {
-      const int j = j0 + lane;
-      unsigned key = 0;
-      if (j < cnt) key = a.cand_key[s0 + j];
-      const bool valid = j < cnt && (key >> 19) == bA;
-      const unsigned act = __ballot_sync(0xffffffffu, valid);
-      if (valid) {
-        const unsigned low = key & 0x7FFFFu;
-        const unsigned peers = __match_any_sync(act, low);
-        if (lane == __ffs(peers) - 1) {
-          const unsigned c = (unsigned)__popc(peers);
-          atomicAdd(&fine[low], c);
-          atomicAdd(&coarse[low >> 8], c);
+    // IS_CU trips of 32 candidates are loaded before the first is used: a segment holds about 120
+    // candidates, so its keys arrive in one round trip instead of four dependent ones
+    for (int j0 = 0; j0 < cnt; j0 += 32 * IS_CU) {
+      unsigned key[IS_CU];
+#pragma unroll
+      for (int t = 0; t < IS_CU; ++t) {
+        const int j = j0 + t * 32 + lane;
+        key[t] = j < cnt ? a.cand_key[s0 + j] : 0u;
+      }
+#pragma unroll
+      for (int t = 0; t < IS_CU; ++t) {
+        const bool valid = j0 + t * 32 + lane < cnt && (key[t] >> 19) == bA;
+        const unsigned act = __ballot_sync(0xffffffffu, valid);
+        if (valid) {
+          const unsigned low = key[t] & 0x7FFFFu;
+          const unsigned peers = __match_any_sync(act, low);
+          if (lane == __ffs(peers) - 1) {
+            const unsigned c = (unsigned)__popc(peers);
+            atomicAdd(&fine[low], c);
+            atomicAdd(&coarse[low >> 8], c);
+          }
         }
       }
     }
@@ -634,10 +643,19 @@ __global__ void __launch_bounds__(IS_THREADS) isync_count_kernel(const ISyncArgs
     const long long s0 = seg * IS_SEG;
     const int cnt = a.segcnt[seg];
     int g = 0, e = 0;
-    for (int j = lane; j < cnt; j += 32) {
-      const unsigned key = a.cand_key[s0 + j];
-      g += key > T;
-      e += key == T;
+    for (int j0 = 0; j0 < cnt; j0 += 32 * IS_CU) {
+      unsigned key[IS_CU];
+#pragma unroll
+      for (int t = 0; t < IS_CU; ++t) {
+        const int j = j0 + t * 32 + lane;
+        key[t] = j < cnt ? a.cand_key[s0 + j] : 0u;
+      }
+#pragma unroll
+      for (int t = 0; t < IS_CU; ++t) {
+        const bool have = j0 + t * 32 + lane < cnt;
+        g += have && key[t] > T;
+        e += have && key[t] == T;
+      }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -759,26 +777,35 @@ __global__ void __launch_bounds__(IS_THREADS) isync_emit_kernel(const ISyncArgs 
     const long long s0 = seg * IS_SEG;
     const int cnt = a.segcnt[seg];
     int pos0 = a.roff[seg];
-    for (int j0 = 0; j0 < cnt; j0 += 32) {
-      const int j = j0 + lane;
-      bool sel = false;
-      int2 pr = make_int2(0, 0);
-      if (j < cnt) {
-        pr.x = a.cand_idx[s0 + j];
-        pr.y = __float_as_int(a.cand_val[s0 + j]);
-        sel = is_selected(a.cand_key[s0 + j], pr.x, T, icut);
-      }
-      const unsigned bal = __ballot_sync(0xffffffffu, sel);
-      if (sel) {
-        const int pos = pos0 + __popc(bal & lt);
-        if (pos < a.kcap) {
+    for (int j0 = 0; j0 < cnt; j0 += 32 * IS_CU) {
+      int2 pr[IS_CU];
+      unsigned key[IS_CU];
 #pragma unroll
-          for (int r = 0; r < MAXW; ++r)
-            if (r < c.W) a.slots[r][(long long)c.rank * a.kcap + pos] = pr;
+      for (int t = 0; t < IS_CU; ++t) {
+        const int j = j0 + t * 32 + lane;
+        pr[t] = make_int2(0, 0);
+        key[t] = 0u;
+        if (j < cnt) {
+          pr[t].x = a.cand_idx[s0 + j];
+          pr[t].y = __float_as_int(a.cand_val[s0 + j]);
+          key[t] = a.cand_key[s0 + j];
         }
-        if (a.zero_selected) a.acc[pr.x] = 0.f;
       }
-      pos0 += __popc(bal);
+#pragma unroll
+      for (int t = 0; t < IS_CU; ++t) {
+        const bool sel = j0 + t * 32 + lane < cnt && is_selected(key[t], pr[t].x, T, icut);
+        const unsigned bal = __ballot_sync(0xffffffffu, sel);
+        if (sel) {
+          const int pos = pos0 + __popc(bal & lt);
+          if (pos < a.kcap) {
+#pragma unroll
+            for (int r = 0; r < MAXW; ++r)
+              if (r < c.W) a.slots[r][(long long)c.rank * a.kcap + pos] = pr[t];
+          }
+          if (a.zero_selected) a.acc[pr[t].x] = 0.f;
+        }
+        pos0 += __popc(bal);
+      }
     }
   }
   for (long long i = (long long)blockIdx.x * IS_THREADS + threadIdx.x; i <= a.nseg;
@@ -804,9 +831,19 @@ __global__ void __launch_bounds__(IS_THREADS) isync_mask_kernel(const ISyncArgs 
        seg += (long long)gridDim.x * (IS_THREADS / 32)) {
     const long long s0 = seg * IS_SEG;
     const int cnt = a.segcnt[seg];
-    for (int j = lane; j < cnt; j += 32) {
-      const int idx = a.cand_idx[s0 + j];
-      if (is_selected(a.cand_key[s0 + j], idx, T, icut)) atomicOr(&a.bits[idx >> 5], 1u << (idx & 31));
+    for (int j0 = 0; j0 < cnt; j0 += 32 * IS_CU) {
+      int idx[IS_CU];
+      unsigned key[IS_CU];
+#pragma unroll
+      for (int t = 0; t < IS_CU; ++t) {
+        const int j = j0 + t * 32 + lane;
+        idx[t] = j < cnt ? a.cand_idx[s0 + j] : 0;
+        key[t] = j < cnt ? a.cand_key[s0 + j] : 0u;
+      }
+#pragma unroll
+      for (int t = 0; t < IS_CU; ++t)
+        if (j0 + t * 32 + lane < cnt && is_selected(key[t], idx[t], T, icut))
+          atomicOr(&a.bits[idx[t] >> 5], 1u << (idx[t] & 31));
     }
   }
 }
@@ -837,14 +874,32 @@ __global__ void __launch_bounds__(IS_THREADS) isync_reduce_kernel(const ISyncArg
         if (threadIdx.x == 0) atomicOr(c.err, SGA_ERR_BOUNDS);
       } else {
         const int2* list = my_slots + (long long)r * a.kcap;
-        for (int j = lo + threadIdx.x; j < hi; j += IS_THREADS) {
-          const int2 pr = __ldcg(list + j);
-          const long long p = pr.x;
-          if (p >= r0 && p < r1) {
-            a.comm[p] = a.comm[p] + __int_as_float(pr.y) * a.scale;
-            atomicOr(&sh_bm[(p - r0) >> 5], 1u << ((p - r0) & 31));
-          } else {
-            atomicOr(c.err, SGA_ERR_BOUNDS);
+        // a rank lists a coordinate at most once, so the IS_CU pairs a thread holds touch different
+        // entries: their loads of the staging buffer are issued together, then the stores
+        for (int j = lo + threadIdx.x; j < hi; j += IS_THREADS * IS_CU) {
+          int2 pr[IS_CU];
+          float cur[IS_CU];
+          bool in[IS_CU];
+#pragma unroll
+          for (int u = 0; u < IS_CU; ++u) {
+            const int jj = j + u * IS_THREADS;
+            pr[u] = jj < hi ? __ldcg(list + jj) : make_int2(-1, 0);
+          }
+#pragma unroll
+          for (int u = 0; u < IS_CU; ++u) {
+            const long long p = pr[u].x;
+            in[u] = j + u * IS_THREADS < hi && p >= r0 && p < r1;
+            cur[u] = in[u] ? a.comm[p] : 0.f;
+          }
+#pragma unroll
+          for (int u = 0; u < IS_CU; ++u) {
+            if (in[u]) {
+              const long long p = pr[u].x;
+              a.comm[p] = cur[u] + __int_as_float(pr[u].y) * a.scale;
+              atomicOr(&sh_bm[(p - r0) >> 5], 1u << ((p - r0) & 31));
+            } else if (j + u * IS_THREADS < hi) {
+              atomicOr(c.err, SGA_ERR_BOUNDS);
+            }
           }
         }
       }
