@@ -35,6 +35,7 @@ struct FwdParams {
   __nv_bfloat16* ctx; // [T, nq * hd]
   float* lse;         // [B, nq, S], natural log
   int* err;
+  int warp_arrive;    // 1: one lane per warp signals "tile written" after a warp barrier; 0: every thread does
 };
 
 template <int HD>
@@ -333,7 +334,7 @@ __global__ void __launch_bounds__(F_THREADS, 1) attn_fwd_acc_kernel(const __grid
     }
     for (int w = 0; w < 2; ++w) {
       mbar_init(&s_full[w], 1);
-      mbar_init(&p_full[w], 128);
+      mbar_init(&p_full[w], p.warp_arrive ? 4 : 128);
       mbar_init(&o_full[w], 1);
     }
     mbar_fence_init();
@@ -496,7 +497,13 @@ __global__ void __launch_bounds__(F_THREADS, 1) attn_fwd_acc_kernel(const __grid
       for (int c = 0; c < BN; c += 32) store_pk32(myP, r, c, *reinterpret_cast<const uint32_t(*)[16]>(&pk[c >> 1]));
       tc_fence_before();
       fence_proxy_async_smem();
-      mbar_arrive(&p_full[w]);
+      if (p.warp_arrive) {
+        // every writer has fenced its own stores; the warp barrier orders them before the one arrival
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_full[w]);
+      } else {
+        mbar_arrive(&p_full[w]);
+      }
     }
     if (ok && nw[w] > 0) {
       ok = __all_sync(0xffffffffu, mbar_wait(&o_full[w], (nw[w] - 1) & 1, p.err));
@@ -588,6 +595,7 @@ SGA_API int sga_attn_fwd(const void* qkv, void* ctx, float* lse, int B, int S, i
   p.ctx = reinterpret_cast<__nv_bfloat16*>(ctx);
   p.lse = lse;
   p.err = err;
+  p.warp_arrive = attn_warp_arrive();
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   return hd == 64 ? launch_fwd<64>(tm, p, st) : launch_fwd<128>(tm, p, st);
 }

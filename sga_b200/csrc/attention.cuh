@@ -7,9 +7,21 @@
 // MN-major operand (contraction over the rows), only the descriptor differs.
 #pragma once
 #include "gemm_common.cuh"
+#include <stdlib.h>
 
 namespace sga {
 namespace attn {
+
+// How the softmax threads tell the MMA thread that an operand tile is in shared memory. Default: every
+// thread fences its own stores, the warp synchronises, one lane arrives (4 to 16 arrivals on the barrier
+// per tile instead of 128 to 512 serialised ones). SGA_ATTN_ARRIVE=thread restores one arrival per thread.
+static inline int attn_warp_arrive() {
+  static const int v = [] {
+    const char* e = getenv("SGA_ATTN_ARRIVE");
+    return (e && e[0] == 't') ? 0 : 1;
+  }();
+  return v;
+}
 
 // [rows x hd] tile of the fused QKV (or dO) matrix -> shared memory, 64 x 64 boxes.
 __device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int col0, int row0,

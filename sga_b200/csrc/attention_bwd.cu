@@ -29,6 +29,7 @@ struct BwdParams {
   const float* delta;     // [B, nq, S]
   __nv_bfloat16* dqkv;    // [T, (nq + 2 nkv) * hd]
   int* err;
+  int warp_arrive;        // see attn_warp_arrive()
 };
 
 // ------------------------------------------------------------------ delta
@@ -121,7 +122,7 @@ __global__ void __launch_bounds__(DQ_THREADS, 1) attn_dq_kernel(const __grid_con
     }
     for (int w = 0; w < 2; ++w) {
       mbar_init(&sd_full[w], 1);
-      mbar_init(&ds_full[w], 256);
+      mbar_init(&ds_full[w], p.warp_arrive ? 8 : 256);
       mbar_init(&dq_done[w], 1);
     }
     mbar_fence_init();
@@ -247,7 +248,12 @@ __global__ void __launch_bounds__(DQ_THREADS, 1) attn_dq_kernel(const __grid_con
       }
       tc_fence_before();
       fence_proxy_async_smem();
-      mbar_arrive(&ds_full[w]);
+      if (p.warp_arrive) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ds_full[w]);
+      } else {
+        mbar_arrive(&ds_full[w]);
+      }
     }
     if (ok && nw[w] > 0) {
       ok = __all_sync(0xffffffffu, mbar_wait(&dq_done[w], (nw[w] - 1) & 1, p.err));
@@ -338,7 +344,7 @@ __global__ void __launch_bounds__(DKV_THREADS, 1) attn_dkv_kernel(const __grid_c
     }
     for (int u = 0; u < 2; ++u) {
       mbar_init(&st_full[u], 1);
-      mbar_init(&pt_full[u], 512);
+      mbar_init(&pt_full[u], p.warp_arrive ? 16 : 512);
       mbar_init(&acc_done[u], 1);
     }
     mbar_fence_init();
@@ -481,7 +487,12 @@ __global__ void __launch_bounds__(DKV_THREADS, 1) attn_dkv_kernel(const __grid_c
           store_p16(sDS + u * C::PT_BYTES, r, c, ds);
           tc_fence_before();
           fence_proxy_async_smem();
-          mbar_arrive(&pt_full[u]);
+          if (p.warp_arrive) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&pt_full[u]);
+          } else {
+            mbar_arrive(&pt_full[u]);
+          }
         }
       }
       if (threadIdx.x < 128) sStat[(u ^ 1) * 128 + threadIdx.x] = nxt;
@@ -591,5 +602,6 @@ SGA_API int sga_attn_bwd(const void* dctx, const void* qkv, const void* ctx, con
   p.delta = delta;
   p.dqkv = reinterpret_cast<__nv_bfloat16*>(dqkv);
   p.err = err;
+  p.warp_arrive = attn_warp_arrive();
   return hd == 64 ? launch_bwd<64>(tq, td, p, st) : launch_bwd<128>(tq, td, p, st);
 }
