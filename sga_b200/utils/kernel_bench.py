@@ -173,13 +173,23 @@ def bench_elementwise(small):
     emit("rope_kernel", f"T={T} heads=40 hd=64", timed(lambda: F.rope_(qkv, cs, sn, 2048, 40, 64, 0, 1.0), it,
                                                        flush=flush), bytes_=T * 2560 * 4.0)
     if not small:
-        V = 128256
-        z = torch.randn(T, V, device=dev, dtype=torch.bfloat16)
-        tgt = torch.randint(0, V, (T,), device=dev)
-        # the logits are read once (a row's second visit comes from L2 / shared memory) and overwritten with
-        # their gradient in place: 2 B read + 2 B written per element
-        emit("ce_fwd_bwd_kernel", f"T={T} V={V}", timed(lambda: F.cross_entropy_(z, tgt, 1.0 / T), 5, flush=flush),
-             bytes_=T * V * 4.0)
+        bench_ce(False)
+
+
+def bench_ce(small):
+    """Fused cross-entropy forward + backward over bf16 logits, in place (2.1 GB of logits at the Llama-3
+    vocabulary: larger than L2 by itself)."""
+    from ..ops import functional as F
+
+    dev = "cuda"
+    T, V = (4096 if small else 8192), 128256
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    z = torch.randn(T, V, device=dev, dtype=torch.bfloat16)
+    tgt = torch.randint(0, V, (T,), device=dev)
+    # the logits are read once (a row's second visit comes from L2 / shared memory) and overwritten with
+    # their gradient in place: 2 B read + 2 B written per element
+    emit("ce_fwd_bwd_kernel", f"T={T} V={V}", timed(lambda: F.cross_entropy_(z, tgt, 1.0 / T), 2 if small else 5,
+                                                     warmup=1 if small else 3, flush=flush), bytes_=T * V * 4.0)
 
 
 def bench_peer(small):
@@ -190,7 +200,7 @@ def bench_peer(small):
     from ..parallel.symm import SymmPool
 
     dev = "cuda"
-    n = (16 if small else 64) * 1024 * 1024
+    n = (48 if small else 64) * 1024 * 1024   # 192 MB of fp32 even in the small case: larger than L2
     pool = SymmPool(device="cuda:0")
     ch = p2p.PeerChannel(pool)
     it = 2 if small else 10
@@ -297,7 +307,7 @@ def bench_mask_stats(small):
 
 
 CASES = {"mask_stats": bench_mask_stats, "attention": bench_attention, "gemm": bench_gemm, "adam": bench_adam, "index_sync": bench_index_sync, "elementwise": bench_elementwise,
-         "replay": bench_replay, "peer": bench_peer}
+         "replay": bench_replay, "peer": bench_peer, "ce": bench_ce}
 
 
 def main(argv=None) -> int:
@@ -306,7 +316,7 @@ def main(argv=None) -> int:
     ap.add_argument("--small", action="store_true")
     ns = ap.parse_args(argv)
     for name, fn in CASES.items():
-        if ns.kernel in ("all", name):
+        if ns.kernel == name or (ns.kernel == "all" and name != "ce"):  # "elementwise" already runs the CE case
             fn(ns.small)
     return 0
 
