@@ -247,6 +247,11 @@ class RankLane:
         self.error: Optional[BaseException] = None
         self.current = "start-up"
         self.thread = None
+        # the worker thread starts on the process's default device: give it the creator's one by number
+        # (a bare "cuda" device carries no index)
+        self.cuda_index = None
+        if self.enabled and device.type == "cuda":
+            self.cuda_index = device.index if device.index is not None else torch.cuda.current_device()
         if self.enabled:
             self.q = queue.Queue(maxsize=depth)
             self.thread = threading.Thread(target=self._work, name="sga-replay-front-rank", daemon=True)
@@ -260,8 +265,8 @@ class RankLane:
 
     def _work(self):
         try:
-            if self.device.type == "cuda":
-                torch.cuda.set_device(self.device)  # the current device is per thread
+            if self.cuda_index is not None:
+                torch.cuda.set_device(self.cuda_index)  # the current device is per thread
             while True:
                 item = self.q.get()
                 if item is self._STOP:

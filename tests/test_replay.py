@@ -187,6 +187,24 @@ def test_fused_gpu_kernels_match_per_config_and_cpu(trace):
 
 
 @pytest.mark.gpu
+def test_fused_gpu_front_block_on_a_bare_cuda_device_with_and_without_the_rank_lane(trace, monkeypatch):
+    """device="cuda" carries no index: the ranking worker thread has to be given the creator's device
+    by number. Both arms of the background switch give the same front block as the CPU run."""
+    cfgs = CONFIGS[:2]
+    kw = dict(score_names=["abs_g", "update"], ratios=[5.0])
+    cpu = RF.run_fused_branch(trace, 0, cfgs, 12, [12], device="cpu", **kw)
+    got = {}
+    for arm in ("on", "off"):
+        monkeypatch.setenv(RF.ENV_FRONT_RANK_BG, arm)
+        got[arm] = RF.run_fused_branch(trace, 0, cfgs, 12, [12], device="cuda", **kw)
+        assert got[arm]["profile"][0]["arms"]["front_rank_bg"] == arm
+    assert got["on"]["front"] == got["off"]["front"] and got["on"]["results"] == got["off"]["results"]
+    for key, m in cpu["front"].items():   # device and host arithmetic may differ in the last bit of a score
+        assert got["on"]["front"][key]["recall_at_k"] == pytest.approx(m["recall_at_k"], abs=3.0 / m["k"])
+        assert got["on"]["front"][key]["ndcg_at_k"] == pytest.approx(m["ndcg_at_k"], rel=1e-3)
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("g_dtype", [torch.float32, torch.bfloat16])
 def test_replay_vector_kernels_equal_scalar_kernels(g_dtype):
     """The four-elements-per-thread kernels (row length a multiple of 4) against the scalar ones (any
