@@ -188,9 +188,13 @@ __global__ void __launch_bounds__(512) p2p_mask_union_kernel(const MaskUnionArgs
   const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
   float sq = 0.f;
   long long cnt = 0;
-  // A warp takes 32 mask words per trip: each lane loads (and ORs over the ranks) one word, coalesced,
-  // and stores the union back; the words are then visited four at a time, lane l owning bit l of each,
-  // with every rank's value of the four words in flight before any is reduced and written back.
+  // A warp takes 32 mask words (1024 coordinates) per trip: each lane loads one word, ORs it over the ranks,
+  // coalesced, and stores the union back. The set positions of the trip are then compacted into a list in
+  // shared memory (a warp scan of the words' bit counts gives every lane its slot), so that every lane holds
+  // a coordinate of the union whatever its density: two coordinates per lane and every rank's value of both
+  // are in flight before either is reduced, in rank order, and written back to every rank.
+  __shared__ uint16_t s_list[16][1024];
+  uint16_t* list = s_list[threadIdx.x >> 5];
   for (long long wb = w0 + warp * 32; wb < w1; wb += nwarps * 32) {
     const long long myw = wb + lane;
     uint32_t u = 0;
@@ -201,30 +205,45 @@ __global__ void __launch_bounds__(512) p2p_mask_union_kernel(const MaskUnionArgs
 #pragma unroll
       for (int r = 0; r < MAXW; ++r)
         if (r < c.W) a.ubits[r][myw] = u;
+      const long long left = a.n - myw * 32;   // coordinates of this word that exist
+      if (left < 32) u &= left > 0 ? ((1u << left) - 1u) : 0u;
     }
     if (__ballot_sync(0xffffffffu, u != 0u) == 0u) continue;
-    for (int j0 = 0; j0 < 32; j0 += 4) {
-      bool on[4];
-      long long idx[4];
-      uint32_t any = 0;
+    const int mine = __popc(u);
+    int incl = mine;
 #pragma unroll
-      for (int t = 0; t < 4; ++t) {
-        const uint32_t uj = __shfl_sync(0xffffffffu, u, j0 + t);
-        any |= uj;
-        idx[t] = (wb + j0 + t) * 32 + lane;
-        on[t] = ((uj >> lane) & 1u) && idx[t] < a.n;
+    for (int o = 1; o < 32; o <<= 1) {
+      const int y = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += y;
+    }
+    const int total = __shfl_sync(0xffffffffu, incl, 31);
+    {
+      int pos = incl - mine;
+      uint32_t bits = u;
+      while (bits) {
+        const int b = __ffs(bits) - 1;
+        bits &= bits - 1;
+        list[pos++] = (uint16_t)(lane * 32 + b);
       }
-      if (any == 0u) continue;
-      float v[4][MAXW];
+    }
+    __syncwarp();
+    for (int e0 = 0; e0 < total; e0 += 64) {
+      long long idx[2];
+      bool on[2];
+      float v[2][MAXW];
 #pragma unroll
-      for (int t = 0; t < 4; ++t)
+      for (int t = 0; t < 2; ++t) {
+        const int e = e0 + t * 32 + lane;
+        on[t] = e < total;
+        idx[t] = wb * 32 + (on[t] ? (int)list[e] : 0);
         if (on[t]) {
 #pragma unroll
           for (int r = 0; r < MAXW; ++r)
             if (r < c.W) v[t][r] = a.grad[r][idx[t]];
         }
+      }
 #pragma unroll
-      for (int t = 0; t < 4; ++t)
+      for (int t = 0; t < 2; ++t)
         if (on[t]) {
           float acc = v[t][0];
 #pragma unroll
@@ -238,6 +257,7 @@ __global__ void __launch_bounds__(512) p2p_mask_union_kernel(const MaskUnionArgs
             if (r < c.W) a.grad[r][idx[t]] = acc;
         }
     }
+    __syncwarp();  // the list is rewritten by the next trip
   }
   if (a.count_out) {
     for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);

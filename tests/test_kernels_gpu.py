@@ -461,20 +461,23 @@ def test_p2p_allreduce_and_mask_union_single_rank():
         bb = pool.alloc(4 * ((n + 31) // 32))
         ub = pool.alloc(4 * ((n + 31) // 32))
         g = gb.view(torch.float32, 0, n)
-        g.copy_(x)
-        m = (torch.rand(n, device=DEV) < 0.05)
         import numpy as np
 
-        packed = np.packbits(m.cpu().numpy().astype("uint8"), bitorder="little")
-        packed = np.concatenate([packed, np.zeros((-len(packed)) % 4, dtype="uint8")]).view("int32")
-        bb.view(torch.int32, 0, packed.size).copy_(torch.from_numpy(packed.copy()))
-        mu8 = torch.empty(n, dtype=torch.uint8, device=DEV)
-        cnt = torch.zeros(1, dtype=torch.int64, device=DEV)
-        p2p.mask_union_reduce_(ch, gb, 0, bb, 0, ub, 0, n, scale=0.5, mask_u8=mu8, sumsq_out=sq, count_out=cnt)
-        ch.check()
-        assert torch.equal(mu8.bool(), m)
-        assert torch.equal(g, torch.where(m, x * 0.5, x))
-        assert cnt.item() == int(m.sum())
+        for density in (0.05, 0.6, 1.0):   # sparse words, words with most bits set, every coordinate
+            g.copy_(x)
+            m = (torch.rand(n, device=DEV) < density)
+            packed = np.packbits(m.cpu().numpy().astype("uint8"), bitorder="little")
+            packed = np.concatenate([packed, np.zeros((-len(packed)) % 4, dtype="uint8")]).view("int32")
+            bb.view(torch.int32, 0, packed.size).copy_(torch.from_numpy(packed.copy()))
+            mu8 = torch.empty(n, dtype=torch.uint8, device=DEV)
+            cnt = torch.zeros(1, dtype=torch.int64, device=DEV)
+            p2p.mask_union_reduce_(ch, gb, 0, bb, 0, ub, 0, n, scale=0.5, mask_u8=mu8, sumsq_out=sq, count_out=cnt)
+            ch.check()
+            assert torch.equal(mu8.bool(), m), density
+            assert torch.equal(g, torch.where(m, x * 0.5, x)), density
+            assert cnt.item() == int(m.sum()), density
+            want = (torch.where(m, x * 0.5, torch.zeros_like(x)).double() ** 2).sum().item()
+            assert abs(sq.item() - want) <= 1e-4 * max(want, 1e-12), density
     finally:
         pool.close()
 
