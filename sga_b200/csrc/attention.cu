@@ -833,22 +833,25 @@ __global__ void __launch_bounds__(FS_THREADS, 1) attn_fwd_split_kernel(const __g
 
 static TmaEncoder g_enc;
 
-// SGA_ATTN_FWD selects the forward kernel: "accumulate" (default: output accumulated in TMEM, one read of
-// the scores per block), "split" (the same with a query row split over two threads) or "fold" (output folded
-// into registers after every block).
-static int fwd_mode() {
-  static const int mode = [] {
+// The forward kernel. By default the measured faster form per head dimension: at 64 the row split over two
+// threads (key blocks of 128: the per-thread walk is the limiter), at 128 the one-thread-per-row kernel with
+// the TMEM accumulator (key blocks of 64). SGA_ATTN_FWD = accumulate | split | fold forces one form
+// ("fold": output folded into registers after every block).
+static int fwd_mode(int hd) {
+  static const int forced = [] {
     const char* e = getenv("SGA_ATTN_FWD");
     if (e && e[0] == 'f') return 0;
+    if (e && e[0] == 'a') return 1;
     if (e && e[0] == 's') return 2;
-    return 1;
+    return -1;
   }();
-  return mode;
+  if (forced >= 0) return forced;
+  return hd == 64 ? 2 : 1;
 }
 
 template <int HD>
 static int launch_fwd(const CUtensorMap& tm, const FwdParams& p, cudaStream_t st) {
-  const int mode = fwd_mode();
+  const int mode = fwd_mode(HD);
   auto kern = mode == 2 ? attn_fwd_split_kernel<HD> : (mode == 1 ? attn_fwd_acc_kernel<HD> : attn_fwd_kernel<HD>);
   const int smem = mode == 2 ? FwdCfg<HD>::SMEM_SPLIT : FwdCfg<HD>::SMEM;
   static bool attr[3][64] = {};
