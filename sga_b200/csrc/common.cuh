@@ -70,15 +70,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 __device__ __forceinline__ bool sga_aborted(const int* err) {
   return err != nullptr && *reinterpret_cast<const volatile int*>(err) != 0;
 }
+// The status word lives in global memory: reading it costs a trip to L2, during which a barrier that
+// completes goes unnoticed. It is therefore looked at on every sixteenth failed poll only; the cycle
+// limit (a register read) is checked on every one.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err) {
   if (mbar_try_wait(bar, parity)) return true;
   long long t0 = clock64();
+  unsigned polls = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if (sga_aborted(err)) return false;
     if (clock64() - t0 > SGA_WAIT_CYCLES) {
       if (err) atomicOr(err, SGA_ERR_MBAR_TIMEOUT);
       return false;
     }
+    if ((++polls & 15u) == 0u && sga_aborted(err)) return false;
   }
   return true;
 }
@@ -267,12 +271,13 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t pa
 __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, int* err) {
   if (mbar_try_wait_cluster(bar, parity)) return true;
   long long t0 = clock64();
+  unsigned polls = 0;
   while (!mbar_try_wait_cluster(bar, parity)) {
-    if (sga_aborted(err)) return false;
     if (clock64() - t0 > SGA_WAIT_CYCLES) {
       if (err) atomicOr(err, SGA_ERR_MBAR_TIMEOUT);
       return false;
     }
+    if ((++polls & 15u) == 0u && sga_aborted(err)) return false;
   }
   return true;
 }
