@@ -184,8 +184,6 @@ class GPT:
         self.tp = tp if (tp is not None and tp.world > 1) else None
         self.tp_size = self.tp.world if self.tp is not None else 1
         self.pp_size, self.pp_rank = pp_size, pp_rank
-        if pp_size > 1 and self.tp is not None:
-            raise NotImplementedError("pipeline stages combined with tensor parallelism are not built")
         self.first_stage, self.last_stage = pp_rank == 0, pp_rank == pp_size - 1
         self.layer_ids = stage_layers(cfg.num_layers, pp_size, pp_rank)
         self.arena = arena if arena is not None else FlatArena(
@@ -358,12 +356,15 @@ class GPT:
     # column-parallel linears (QKV, gate|up) gather their input rows inside the GEMM
     # kernel, the row-parallel ones (output, down) reduce-scatter their output rows
     # inside it. The gathered inputs are kept for the weight gradients.
-    def _layer_fwd_tp(self, i, L, x, B, S):
+    def _layer_fwd_tp(self, i, L, x, B, S, inflight=0):
+        # The gathered inputs of the two column-parallel linears stay in per-layer symmetric buffers for
+        # the backward pass. A pipeline stage holds several micro-batches between their forward and their
+        # backward, so the buffers are also keyed by the micro-batch's in-flight slot.
         c, tp = self.cfg, self.tp
         T = B * S
         cs, sn = self._rope_tables()
         nq, nkv, hd = c.n_heads // tp.world, c.n_kv_heads // tp.world, c.head_dim
-        g1 = tp.slot(("h1", i), T, c.hidden)
+        g1 = tp.slot(("h1", i, inflight), T, c.hidden)
         _, rstd1 = F.rmsnorm_fwd(x, L["ln1"].model, c.norm_eps, out=g1.local)
         qkv = tp.ag_linear(g1, L["qkv"].model)
         qk_saved = None
@@ -376,7 +377,7 @@ class GPT:
         F.rope_(qkv, cs, sn, S, nq + nkv, hd, 0, +1.0)
         ctx, att_saved = A.attn_fwd(qkv, B, S, nq, nkv, hd)
         x_mid = tp.linear_rs(ctx, L["proj"].model, residual=x)
-        g2 = tp.slot(("h2", i), T, c.hidden)
+        g2 = tp.slot(("h2", i, inflight), T, c.hidden)
         _, rstd2 = F.rmsnorm_fwd(x_mid, L["ln2"].model, c.norm_eps, out=g2.local)
         gu = tp.ag_linear(g2, L["fc1"].model)
         s = F.swiglu_fwd(gu)
@@ -432,11 +433,41 @@ class GPT:
         self.launches += 7
 
     def _forward_backward_tp(self, tokens, targets, loss_scale, on_param_done, backward, reduce_replicated):
+        loss, ctx = self._stage_forward_tp(tokens, targets, None, loss_scale, backward, 0)
+        if backward:
+            self._stage_backward_tp(ctx, None, on_param_done, reduce_replicated)
+        return loss
+
+    # One micro-batch through this stage's layers under tensor parallelism. Activations are sharded by rows
+    # (sequence parallel), so what travels between stages is this rank's [T / tp, hidden] block: rank t of a
+    # stage talks to rank t of its neighbours.
+    def _stage_forward_tp(self, tokens, targets, x_in, loss_scale, write_grad, inflight):
         c, tp = self.cfg, self.tp
         B, S = tokens.shape
         T = B * S
         Tl = T // tp.world
         lo = tp.rank * Tl
+        ids = tokens.reshape(-1)[lo:lo + Tl] if self.first_stage else None
+        x = F.embed_fwd(ids, self.emb.model) if self.first_stage else x_in
+        saved = []
+        for i, L in enumerate(self.layers):
+            x, sv = self._layer_fwd_tp(i, L, x, B, S, inflight)
+            saved.append(sv)
+        self.launches += 1
+        if not self.last_stage:
+            return x, dict(B=B, S=S, ids=ids, saved=saved)
+        tgt = targets.reshape(-1)[lo:lo + Tl]
+        hf, rstd_f = F.rmsnorm_fwd(x, self.final_norm.model, c.norm_eps)
+        logits = self._linear(hf, self.head)
+        self.launches += 2
+        loss_tok = F.cross_entropy_(logits, tgt, grad_scale=loss_scale / T, write_grad=write_grad)
+        loss = tp.allreduce_scalar(loss_tok.sum() / T)
+        return loss, dict(B=B, S=S, ids=ids, saved=saved, x=x, hf=hf, rstd_f=rstd_f, dlogits=logits)
+
+    def _stage_backward_tp(self, ctx, dx_out, on_param_done, reduce_replicated):
+        c, tp = self.cfg, self.tp
+        B, S, saved = ctx["B"], ctx["S"], ctx["saved"]
+        T = B * S
         user_done = on_param_done if on_param_done is not None else (lambda slot: None)
 
         def done(slot):
@@ -450,37 +481,30 @@ class GPT:
                 st.zero_()
             user_done(slot)
 
-        ids = tokens.reshape(-1)[lo:lo + Tl]
-        tgt = targets.reshape(-1)[lo:lo + Tl]
-        x = F.embed_fwd(ids, self.emb.model)
-        saved = []
-        for i, L in enumerate(self.layers):
-            x, sv = self._layer_fwd_tp(i, L, x, B, S)
-            saved.append(sv)
-        hf, rstd_f = F.rmsnorm_fwd(x, self.final_norm.model, c.norm_eps)
-        logits = self._linear(hf, self.head)
-        self.launches += 3
-        loss_tok = F.cross_entropy_(logits, tgt, grad_scale=loss_scale / T, write_grad=backward)
-        loss = tp.allreduce_scalar(loss_tok.sum() / T)
-        if not backward:
-            return loss
-        dlogits = logits
-        self._wgrad(dlogits, hf, self.head)
-        if not c.tied_embeddings:
-            done(self.head)
-        dhf = self._dgrad(dlogits, self.head)
-        del logits, dlogits, hf
         gdx = tp.slot("dx", T, c.hidden)
-        F.rmsnorm_bwd(x, self.final_norm.model, dhf, rstd_f, dw_out=self._gbuf(self.final_norm), dx_out=gdx.local)
-        done(self.final_norm)
-        del dhf
+        if self.last_stage:
+            dlogits, hf = ctx.pop("dlogits"), ctx.pop("hf")
+            self._wgrad(dlogits, hf, self.head)
+            if not c.tied_embeddings:
+                done(self.head)
+            dhf = self._dgrad(dlogits, self.head)
+            del dlogits, hf
+            F.rmsnorm_bwd(ctx.pop("x"), self.final_norm.model, dhf, ctx.pop("rstd_f"),
+                          dw_out=self._gbuf(self.final_norm), dx_out=gdx.local)
+            done(self.final_norm)
+            del dhf
+            self.launches += 3
+        else:
+            gdx.local.copy_(dx_out)
         for L, sv in zip(reversed(self.layers), reversed(saved)):
             self._layer_bwd_tp(L, sv, gdx, B, S, done)
         saved.clear()
-        F.embed_bwd(ids, gdx.local, self._gbuf(self.emb))
-        done(self.emb)
-        self.launches += 4
-        return loss
+        if self.first_stage:
+            F.embed_bwd(ctx["ids"], gdx.local, self._gbuf(self.emb))
+            done(self.emb)
+            self.launches += 1
+            return None
+        return gdx.local.clone()  # the buffer is the next backward pass's too
 
     def forward_backward(self, tokens: torch.Tensor, targets: torch.Tensor, *, loss_scale: float = 1.0,
                          on_param_done: Optional[Callable] = None, backward: bool = True,
@@ -503,7 +527,12 @@ class GPT:
     # One micro-batch through this stage's layers. The first stage embeds ``tokens``; later stages take
     # the previous stage's activation ``x_in`` ``[T, hidden]``. The last stage computes the loss (and,
     # in the same kernel, the logit gradient); earlier stages return the activation to send on.
-    def stage_forward(self, tokens, targets, x_in, *, loss_scale: float = 1.0, write_grad: bool = True):
+    def stage_forward(self, tokens, targets, x_in, *, loss_scale: float = 1.0, write_grad: bool = True,
+                      inflight: int = 0):
+        """``inflight``: which of the stage's in-flight micro-batch slots this pass uses (only tensor
+        parallelism keeps per-slot buffers between a forward and its backward)."""
+        if self.tp is not None:
+            return self._stage_forward_tp(tokens, targets, x_in, loss_scale, write_grad, inflight)
         c = self.cfg
         B, S = tokens.shape
         T = B * S
@@ -526,7 +555,10 @@ class GPT:
     def stage_backward(self, ctx, dx_out, on_param_done: Optional[Callable] = None):
         """Backward of one micro-batch through this stage. ``dx_out`` is the gradient of the stage's
         output received from the next stage (``None`` on the last stage); returns the gradient of the
-        stage's input (``None`` on the first stage)."""
+        stage's input (``None`` on the first stage). Under tensor parallelism the pass that is given
+        ``on_param_done`` (the step's last) also sums the replicated parameters' gradients over the group."""
+        if self.tp is not None:
+            return self._stage_backward_tp(ctx, dx_out, on_param_done, on_param_done is not None)
         c = self.cfg
         done = on_param_done if on_param_done is not None else (lambda slot: None)
         B, S, saved = ctx["B"], ctx["S"], ctx["saved"]

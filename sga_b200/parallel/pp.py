@@ -16,7 +16,8 @@ The reference leaves pipeline stages to its external training stack and only
 tolerates them (untied embeddings, no always-sync layers:
 ``sga/runtime.py:71-76``, ``sga/config/validation.py:332-341``); the
 data-parallel gradient machinery of each stage runs unchanged on the stage's
-own parameters.
+own parameters. Combined with tensor parallelism every tensor-parallel rank of a
+stage runs this schedule with the same-index rank of the neighbouring stages.
 """
 from __future__ import annotations
 
@@ -66,16 +67,19 @@ class Pipeline:
         m = len(micro_batches)
         model = self.model
         B, S = micro_batches[0][0].shape
-        act_shape = (B * S, model.cfg.hidden)
+        # under tensor parallelism the activations are sharded by rows: a rank exchanges its own block
+        # with the rank of the same tensor-parallel index in the neighbouring stages
+        act_shape = (B * S // getattr(model, "tp_size", 1), model.cfg.hidden)
         warm = min(self.pp_size - self.pp_rank - 1, m)
         steady = m - warm
+        depth = warm + 1  # micro-batches this stage holds between their forward and their backward
         ctxs, losses = [], []
         f = b = 0
 
         def forward(x_in):
             nonlocal f
             tokens, targets = micro_batches[f]
-            out, ctx = model.stage_forward(tokens, targets, x_in, loss_scale=loss_scale)
+            out, ctx = model.stage_forward(tokens, targets, x_in, loss_scale=loss_scale, inflight=f % depth)
             ctxs.append(ctx)
             f += 1
             if self.last:

@@ -283,8 +283,6 @@ class Trainer:
                              "head dimension, hidden and FFN sizes must be multiples of 8")
         self.tp_size = max(1, int(args.tensor_model_parallel_size))
         self.pp_size = max(1, int(args.pipeline_model_parallel_size or 1))
-        if self.pp_size > 1 and self.tp_size > 1:
-            raise NotImplementedError("pipeline stages combined with tensor parallelism are not built")
         if self.pp_size > 1 and int(getattr(args, "eval_interval", 0) or 0) > 0:
             raise NotImplementedError("--eval-interval with pipeline stages: the validation pass has no "
                                       "forward-only pipeline schedule; run validation without pipeline parallelism")
@@ -293,32 +291,35 @@ class Trainer:
         self.dp_world = self.world // mp
         # rank = (pp_rank * dp + dp_rank) * tp + tp_rank: adjacent ranks form a tensor-parallel group,
         # data-parallel groups stride over them inside a pipeline stage, stages are the outermost axis
-        self.tp_rank = self.rank % self.tp_size
-        self.dp_rank = (self.rank // self.tp_size) % self.dp_world
-        self.pp_rank = self.rank // (self.tp_size * self.dp_world)
+        tp, dp, pp = self.tp_size, self.dp_world, self.pp_size
+        self.tp_rank = self.rank % tp
+        self.dp_rank = (self.rank // tp) % dp
+        self.pp_rank = self.rank // (tp * dp)
         self.tp_group = self.dp_group = self.pp_group = None
-        if self.tp_size > 1:
-            for d in range(self.dp_world):
-                ranks = list(range(d * self.tp_size, (d + 1) * self.tp_size))
-                grp = dist.new_group(ranks=ranks)
-                if d == self.dp_rank:
-                    self.tp_group = grp
-            for t in range(self.tp_size):
-                ranks = list(range(t, self.world, self.tp_size))
-                grp = dist.new_group(ranks=ranks)
-                if t == self.tp_rank:
-                    self.dp_group = grp
-        if self.pp_size > 1:
-            for pstage in range(self.pp_size):
-                ranks = list(range(pstage * self.dp_world, (pstage + 1) * self.dp_world))
-                grp = dist.new_group(ranks=ranks)
-                if pstage == self.pp_rank:
-                    self.dp_group = grp
-            for d in range(self.dp_world):
-                ranks = [d + pstage * self.dp_world for pstage in range(self.pp_size)]
-                grp = dist.new_group(ranks=ranks)
-                if d == self.dp_rank:
-                    self.pp_group = grp
+
+        def rank_of(p, d, t):
+            return (p * dp + d) * tp + t
+
+        # every rank creates every group, in the same order (a requirement of new_group)
+        if tp > 1:
+            for p in range(pp):
+                for d in range(dp):
+                    grp = dist.new_group(ranks=[rank_of(p, d, t) for t in range(tp)])
+                    if (p, d) == (self.pp_rank, self.dp_rank):
+                        self.tp_group = grp
+        if tp > 1 or pp > 1:
+            for p in range(pp):
+                for t in range(tp):
+                    grp = dist.new_group(ranks=[rank_of(p, d, t) for d in range(dp)])
+                    if (p, t) == (self.pp_rank, self.tp_rank):
+                        self.dp_group = grp
+        if pp > 1:
+            for d in range(dp):
+                for t in range(tp):
+                    grp = dist.new_group(ranks=[rank_of(p, d, t) for p in range(pp)])
+                    if (d, t) == (self.dp_rank, self.tp_rank):
+                        self.pp_group = grp
+        self._last_stage_peer = rank_of(pp - 1, self.dp_rank, self.tp_rank)
         assert args.global_batch_size % (args.micro_batch_size * self.dp_world) == 0, (
             "global batch must be a multiple of micro_batch * data-parallel size")
         self.num_micro = args.global_batch_size // (args.micro_batch_size * self.dp_world)
@@ -365,8 +366,9 @@ class Trainer:
             from ..parallel.pp import Pipeline
 
             self.pipeline = Pipeline(self.model, pp_rank=self.pp_rank, pp_size=self.pp_size,
-                                     prev_rank=self.rank - self.dp_world if self.pp_rank > 0 else None,
-                                     next_rank=self.rank + self.dp_world if self.pp_rank < self.pp_size - 1 else None)
+                                     prev_rank=self.rank - self.dp_world * self.tp_size if self.pp_rank > 0 else None,
+                                     next_rank=(self.rank + self.dp_world * self.tp_size
+                                                if self.pp_rank < self.pp_size - 1 else None))
         ddp_cfg = DDPConfig(average_in_collective=True, overlap_grad_reduce=bool(args.overlap_grad_reduce),
                             comm_max_ctas=args.comm_max_ctas)
         if getattr(args, "sga_backend_timer", None):
@@ -581,7 +583,7 @@ class Trainer:
             # the loss lives on the last stage: hand it to every stage of the replica
             t = torch.stack(losses).mean() if losses else torch.zeros((), dtype=torch.float32, device=self.device)
             t = t.reshape(1).clone()
-            dist.broadcast(t, src=self.rank % self.dp_world + (self.pp_size - 1) * self.dp_world, group=self.pp_group)
+            dist.broadcast(t, src=self._last_stage_peer, group=self.pp_group)
             return t[0]
         return torch.stack(losses).mean()
 
