@@ -96,7 +96,8 @@ def stage_layers(num_layers: int, pp_size: int, pp_rank: int) -> range:
     return range(lo, lo + base + (1 if pp_rank < extra else 0))
 
 
-def param_specs(cfg: GPTConfig, tp_size: int = 1, tp_rank: int = 0, pp_size: int = 1, pp_rank: int = 0) -> list:
+def param_specs(cfg: GPTConfig, tp_size: int = 1, tp_rank: int = 0, pp_size: int = 1, pp_rank: int = 0,
+                vocab_parallel: bool = False) -> list:
     """Parameter specs in the order their gradients become final in the backward pass.
 
     With ``pp_size > 1`` only the parameters of stage ``pp_rank`` are returned:
@@ -108,7 +109,8 @@ def param_specs(cfg: GPTConfig, tp_size: int = 1, tp_rank: int = 0, pp_size: int
     output and down projections by input columns) and carry the slices of the
     full tensor they are cut from; norm weights, the embedding and the output
     layer are replicated (activations are sharded by rows, so each rank embeds
-    and scores its own tokens against the full vocabulary)."""
+    and scores its own tokens against the full vocabulary). ``vocab_parallel``
+    shards those two by vocabulary rows instead (``vocab % tp_size == 0``)."""
     std = cfg.init_std
     tp = tp_size
     nq, nkv, hd, F_, H = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, cfg.ffn, cfg.hidden
@@ -126,9 +128,19 @@ def param_specs(cfg: GPTConfig, tp_size: int = 1, tp_rank: int = 0, pp_size: int
         shape[dim] = sum(hi - lo for _, lo, hi in pieces)
         return ParamSpec(name, tuple(shape), 0, "normal", std, tp_full_shape=tuple(full_shape), tp_pieces=pieces)
 
+    vp = vocab_parallel and tp > 1
+    if vp:
+        assert cfg.vocab % tp == 0, "the vocabulary must divide over the tensor-parallel ranks"
+    Vl = cfg.vocab // tp
+
+    def vocab_rows(name):
+        if vp:
+            return sharded(name, (cfg.vocab, H), _rows((r * Vl, (r + 1) * Vl)))
+        return ParamSpec(name, (cfg.vocab, H), 0, "normal", std, tp_duplicate=dup)
+
     specs = []
     if not cfg.tied_embeddings:
-        specs.append(ParamSpec("output_layer.weight", (cfg.vocab, H), 0, "normal", std, tp_duplicate=dup))
+        specs.append(vocab_rows("output_layer.weight"))
     specs.append(ParamSpec("decoder.final_layernorm.weight", (H,), 1, "ones", tp_duplicate=True))
     for i in reversed(range(cfg.num_layers)):
         p = f"decoder.layers.{i}."
@@ -146,7 +158,7 @@ def param_specs(cfg: GPTConfig, tp_size: int = 1, tp_rank: int = 0, pp_size: int
                              _rows((r * nql * hd, (r + 1) * nql * hd), (ko + r * nkvl * hd, ko + (r + 1) * nkvl * hd),
                                    (vo + r * nkvl * hd, vo + (r + 1) * nkvl * hd))))
         specs.append(ParamSpec(p + "input_layernorm.weight", (H,), 1, "ones", tp_duplicate=True))
-    specs.append(ParamSpec("embedding.word_embeddings.weight", (cfg.vocab, H), 0, "normal", std, tp_duplicate=dup))
+    specs.append(vocab_rows("embedding.word_embeddings.weight"))
     if tp > 1 or pp_size > 1:
         for i, s in enumerate(specs):
             s.init_order = i  # every parameter keeps the random stream it has in the whole model
@@ -174,7 +186,8 @@ def param_specs(cfg: GPTConfig, tp_size: int = 1, tp_rank: int = 0, pp_size: int
 class GPT:
     def __init__(self, cfg: GPTConfig, *, device="cpu", pool=None, bucket_elems: int = 16 * 1024 * 1024,
                  seed: int = 0, need_comm_staging: bool = False, arena: Optional[FlatArena] = None, tp=None,
-                 init_on_device: bool = False, pp_size: int = 1, pp_rank: int = 0, recompute: bool = False):
+                 init_on_device: bool = False, pp_size: int = 1, pp_rank: int = 0, recompute: bool = False,
+                 vocab_parallel: bool = False):
         self.cfg = cfg
         # False: the normalised inputs of the two column-parallel linears and the SwiGLU output are kept
         # for the backward pass (about 0.2 GB per layer at 8192 tokens; HBM is not the scarce resource);
@@ -186,8 +199,13 @@ class GPT:
         self.pp_size, self.pp_rank = pp_size, pp_rank
         self.first_stage, self.last_stage = pp_rank == 0, pp_rank == pp_size - 1
         self.layer_ids = stage_layers(cfg.num_layers, pp_size, pp_rank)
+        # Under tensor parallelism the embedding and the output layer are replicated by default (each rank
+        # embeds and scores its own rows); vocab_parallel shards both by vocabulary rows: 1 / tp of their
+        # parameters, gradients and optimizer state per rank, for two library collectives per micro-batch.
+        self.vocab_parallel = bool(vocab_parallel) and self.tp is not None
         self.arena = arena if arena is not None else FlatArena(
-            param_specs(cfg, self.tp_size, self.tp.rank if self.tp is not None else 0, pp_size, pp_rank),
+            param_specs(cfg, self.tp_size, self.tp.rank if self.tp is not None else 0, pp_size, pp_rank,
+                        vocab_parallel=self.vocab_parallel),
             bucket_elems=bucket_elems, device=device, pool=pool, need_comm_staging=need_comm_staging,
             split_on_tp_duplicate=self.tp_size > 1)
         if arena is None:
@@ -447,22 +465,76 @@ class GPT:
         T = B * S
         Tl = T // tp.world
         lo = tp.rank * Tl
-        ids = tokens.reshape(-1)[lo:lo + Tl] if self.first_stage else None
-        x = F.embed_fwd(ids, self.emb.model) if self.first_stage else x_in
+        ids = vp_rows = None
+        if self.first_stage and self.vocab_parallel:
+            # every rank looks up the tokens of the whole micro-batch that fall into its vocabulary rows
+            # (zeros elsewhere); the sum over the ranks, scattered by rows, is the sequence-parallel input
+            Vl = c.vocab // tp.world
+            all_ids = tokens.reshape(-1)
+            mine = (all_ids >= tp.rank * Vl) & (all_ids < (tp.rank + 1) * Vl)
+            vp_rows = torch.nonzero(mine).view(-1)
+            ids = all_ids[vp_rows] - tp.rank * Vl
+            part = torch.zeros(T, c.hidden, dtype=torch.bfloat16, device=self.device)
+            if vp_rows.numel():
+                part[vp_rows] = F.embed_fwd(ids, self.emb.model)
+            x = tp.reduce_scatter_rows(part)
+            del part
+        elif self.first_stage:
+            ids = tokens.reshape(-1)[lo:lo + Tl]
+            x = F.embed_fwd(ids, self.emb.model)
+        else:
+            x = x_in
         saved = []
         for i, L in enumerate(self.layers):
             x, sv = self._layer_fwd_tp(i, L, x, B, S, inflight)
             saved.append(sv)
         self.launches += 1
         if not self.last_stage:
-            return x, dict(B=B, S=S, ids=ids, saved=saved)
-        tgt = targets.reshape(-1)[lo:lo + Tl]
-        hf, rstd_f = F.rmsnorm_fwd(x, self.final_norm.model, c.norm_eps)
-        logits = self._linear(hf, self.head)
-        self.launches += 2
-        loss_tok = F.cross_entropy_(logits, tgt, grad_scale=loss_scale / T, write_grad=write_grad)
-        loss = tp.allreduce_scalar(loss_tok.sum() / T)
-        return loss, dict(B=B, S=S, ids=ids, saved=saved, x=x, hf=hf, rstd_f=rstd_f, dlogits=logits)
+            return x, dict(B=B, S=S, ids=ids, vp_rows=vp_rows, saved=saved)
+        if self.vocab_parallel:
+            # the output layer holds 1 / tp of the vocabulary: gather the normalised rows, score every token
+            # against the local rows, and combine the softmax statistics over the ranks
+            gh = tp.slot(("hf", inflight), T, c.hidden)
+            _, rstd_f = F.rmsnorm_fwd(x, self.final_norm.model, c.norm_eps, out=gh.local)
+            hf = tp.gather(gh)
+            logits = self._linear(hf, self.head)
+            self.launches += 2
+            loss_tok = self._vocab_parallel_ce_(logits, targets.reshape(-1), loss_scale / T, write_grad)
+            loss = loss_tok.sum() / T   # every rank holds every token's loss
+        else:
+            tgt = targets.reshape(-1)[lo:lo + Tl]
+            hf, rstd_f = F.rmsnorm_fwd(x, self.final_norm.model, c.norm_eps)
+            logits = self._linear(hf, self.head)
+            self.launches += 2
+            loss_tok = F.cross_entropy_(logits, tgt, grad_scale=loss_scale / T, write_grad=write_grad)
+            loss = tp.allreduce_scalar(loss_tok.sum() / T)
+        return loss, dict(B=B, S=S, ids=ids, vp_rows=vp_rows, saved=saved, x=x, hf=hf, rstd_f=rstd_f, dlogits=logits)
+
+    def _vocab_parallel_ce_(self, logits, targets, grad_scale, write_grad):
+        """Cross-entropy over a vocabulary whose columns are sharded over the tensor-parallel ranks:
+        ``logits`` is ``[T, vocab / tp]`` for all ``T`` tokens. Row maximum, sum of exponentials and the
+        target's logit are combined over the ranks; ``logits`` is overwritten by its gradient. Returns the
+        per-token loss (fp32, the same on every rank)."""
+        tp = self.tp
+        Vl = logits.shape[1]
+        lo = tp.rank * Vl
+        z = logits.float()
+        m = z.max(1).values
+        tp.allreduce_(m, torch.distributed.ReduceOp.MAX)
+        e = torch.exp(z - m[:, None])
+        ssum = e.sum(1)
+        tp.allreduce_(ssum)
+        local = (targets >= lo) & (targets < lo + Vl)
+        col = (targets - lo).clamp(0, Vl - 1)
+        zt = torch.where(local, z.gather(1, col[:, None]).squeeze(1), torch.zeros_like(m))
+        tp.allreduce_(zt)
+        loss = torch.log(ssum) + m - zt
+        if write_grad:
+            e /= ssum[:, None]
+            rows = torch.nonzero(local).view(-1)
+            e[rows, col[rows]] -= 1.0
+            logits.copy_((e * grad_scale).to(logits.dtype))
+        return loss
 
     def _stage_backward_tp(self, ctx, dx_out, on_param_done, reduce_replicated):
         c, tp = self.cfg, self.tp
@@ -489,6 +561,8 @@ class GPT:
                 done(self.head)
             dhf = self._dgrad(dlogits, self.head)
             del dlogits, hf
+            if self.vocab_parallel:
+                dhf = tp.reduce_scatter_rows(dhf)  # every rank's vocabulary rows contribute to every token
             F.rmsnorm_bwd(ctx.pop("x"), self.final_norm.model, dhf, ctx.pop("rstd_f"),
                           dw_out=self._gbuf(self.final_norm), dx_out=gdx.local)
             done(self.final_norm)
@@ -500,7 +574,14 @@ class GPT:
             self._layer_bwd_tp(L, sv, gdx, B, S, done)
         saved.clear()
         if self.first_stage:
-            F.embed_bwd(ctx["ids"], gdx.local, self._gbuf(self.emb))
+            if self.vocab_parallel:
+                rows = ctx["vp_rows"]
+                if rows.numel():
+                    F.embed_bwd(ctx["ids"], tp.gather(gdx)[rows].contiguous(), self._gbuf(self.emb))
+                else:
+                    tp.gather(gdx)  # the collective is the group's
+            else:
+                F.embed_bwd(ctx["ids"], gdx.local, self._gbuf(self.emb))
             done(self.emb)
             self.launches += 1
             return None

@@ -218,6 +218,26 @@ class TPContext:
             dist.all_reduce(t, group=self.group)
         return t
 
+    def allreduce_(self, t: torch.Tensor, op=None) -> torch.Tensor:
+        """In-place all-reduce over the group (sum by default)."""
+        if self.world > 1:
+            dist.all_reduce(t, op=op if op is not None else dist.ReduceOp.SUM, group=self.group)
+        return t
+
+    def reduce_scatter_rows(self, full: torch.Tensor) -> torch.Tensor:
+        """Sum of ``full`` ``[rows, cols]`` over the group; this rank keeps its row chunk. Library
+        collective (the vocabulary-parallel embedding and output layer use it twice per micro-batch)."""
+        if self.world == 1:
+            return full
+        rows = full.shape[0] // self.world
+        if full.is_cuda:
+            out = torch.empty(rows, full.shape[1], dtype=full.dtype, device=full.device)
+            dist.reduce_scatter_tensor(out, full.contiguous(), group=self.group)
+            return out
+        acc = full.float()   # gloo: no reduce-scatter, and sums in fp32
+        dist.all_reduce(acc, group=self.group)
+        return acc[self.rank * rows:(self.rank + 1) * rows].to(full.dtype)
+
     def check(self) -> None:
         for ch, what in ((self.ag_channel, "all-gather GEMM"), (self.rs_channel, "GEMM reduce-scatter")):
             if ch is not None:

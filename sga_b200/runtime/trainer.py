@@ -101,6 +101,9 @@ def add_trainer_args(p: argparse.ArgumentParser) -> argparse.ArgumentParser:
                    help="draw the initial weights with the device generator (large models)")
     g.add_argument("--tp-comm", type=str, default="auto", choices=("auto", "fused", "library"),
                    help="tensor-parallel linears: collective fused into the GEMM kernel, or library collectives")
+    g.add_argument("--vocab-parallel-embedding", action="store_true",
+                   help="under tensor parallelism shard the embedding and the output layer by vocabulary rows "
+                        "instead of replicating them (two library collectives per micro-batch)")
     g.add_argument("--pipeline-model-parallel-size", type=int, default=1)
     g.add_argument("--sequence-parallel", action="store_true")
     g.add_argument("--untie-embeddings-and-output-weights", action="store_true")
@@ -360,7 +363,8 @@ class Trainer:
                          need_comm_staging=need_comm, tp=self.tp,
                          init_on_device=bool(getattr(args, "init_on_device", False)),
                          pp_size=self.pp_size, pp_rank=self.pp_rank,
-                         recompute=bool(getattr(args, "recompute_activations", False)))
+                         recompute=bool(getattr(args, "recompute_activations", False)),
+                         vocab_parallel=bool(getattr(args, "vocab_parallel_embedding", False)))
         self.pipeline = None
         if self.pp_size > 1:
             from ..parallel.pp import Pipeline

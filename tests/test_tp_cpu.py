@@ -29,14 +29,17 @@ def _shard_of(full: torch.Tensor, spec) -> torch.Tensor:
     return torch.cat([full.narrow(dim, lo, hi - lo) for _, lo, hi in spec.tp_pieces], dim)
 
 
-def _worker(rank, world, port, preset, out):
+def _worker(rank, world, port, preset, out, vocab_parallel=False):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         cfg = get_config(preset)
         tp = TPContext(device="cpu")
-        model = GPT(cfg, device="cpu", seed=3, tp=tp)
+        model = GPT(cfg, device="cpu", seed=3, tp=tp, vocab_parallel=vocab_parallel)
         full = GPT(cfg, device="cpu", seed=3)
+        emb = model.arena.by_name["embedding.word_embeddings.weight"]
+        assert emb.main.shape[0] == (cfg.vocab // world if vocab_parallel else cfg.vocab)
+        assert emb.spec.tp_duplicate != vocab_parallel
         # same seed -> the shard is cut from the same full tensors
         for slot in model.arena.slots:
             ref = _shard_of(full.arena.by_name[slot.name].main, slot.spec)
@@ -67,10 +70,20 @@ def test_tp2_matches_unsharded_model(tmp_path, preset):
     assert torch.load(out)["worst"] < 0.06
 
 
-def test_tp_specs_cover_the_full_tensors():
+@pytest.mark.parametrize("preset", ["test_tiny", "test_tiny_qk"])   # tied and untied embeddings
+def test_tp2_vocab_parallel_matches_unsharded_model(tmp_path, preset):
+    """The embedding and the output layer sharded by vocabulary rows: same loss, and every rank's
+    rows of their gradients equal the unsharded model's."""
+    out = str(tmp_path / "r.pt")
+    mp.spawn(_worker, args=(2, _free_port(), preset, out, True), nprocs=2, join=True)
+    assert torch.load(out)["worst"] < 0.06
+
+
+@pytest.mark.parametrize("vocab_parallel", [False, True])
+def test_tp_specs_cover_the_full_tensors(vocab_parallel):
     cfg = get_config("test_tiny")
     full = {s.name: s for s in param_specs(cfg)}
-    shards = [param_specs(cfg, 2, r) for r in range(2)]
+    shards = [param_specs(cfg, 2, r, vocab_parallel=vocab_parallel) for r in range(2)]
     for name, fs in full.items():
         parts = [next(s for s in sh if s.name == name) for sh in shards]
         if parts[0].tp_pieces is None:
@@ -86,13 +99,13 @@ def test_tp_specs_cover_the_full_tensors():
         assert pos == fs.shape[dim]
 
 
-def _trainer_worker(rank, world, port, tp_size, sga, out):
+def _trainer_worker(rank, world, port, tp_size, sga, out, vocab_parallel=False):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       LOCAL_RANK=str(rank))
     from sga_b200.runtime.trainer import Trainer, default_args
 
     kw = dict(model="test_tiny", micro_batch_size=2, global_batch_size=8, device="cpu", lr=1e-3, clip_grad=1.0,
-              tensor_model_parallel_size=tp_size, log_interval=0)
+              tensor_model_parallel_size=tp_size, log_interval=0, vocab_parallel_embedding=vocab_parallel)
     if sga:
         kw.update(sga_enabled=True, sga_score="abs_g", sga_selection_method="exact", sga_selection_ratio_percent=5.0,
                   sga_backend="torch_pipelined_index", sga_selection_locality="rank_local", sga_cycle_period=3)
@@ -112,7 +125,8 @@ def _trainer_worker(rank, world, port, tp_size, sga, out):
     if rank == 0:
         torch.save({"losses": losses, "norms": norms}, out)
     tr.close()
-    dist.destroy_process_group()
+    if dist.is_initialized():
+        dist.destroy_process_group()
 
 
 @pytest.mark.parametrize("sga", [False, True])
@@ -130,3 +144,16 @@ def test_tp2_dp2_trainer_tracks_dp2(tmp_path, sga):
         assert abs(x - y) < ltol, (ra, rb)
     for x, y in zip(ra["norms"], rb["norms"]):
         assert abs(x - y) < ntol * max(y, 1e-3), (ra, rb)
+
+
+def test_tp2_vocab_parallel_trainer_tracks_single_rank(tmp_path):
+    """Two tensor-parallel ranks with the vocabulary-parallel embedding follow the single-rank SGA trainer."""
+    a, b = str(tmp_path / "vp.pt"), str(tmp_path / "one.pt")
+    mp.spawn(_trainer_worker, args=(2, _free_port(), 2, True, a, True), nprocs=2, join=True)
+    mp.spawn(_trainer_worker, args=(1, _free_port(), 1, True, b), nprocs=1, join=True)
+    ra, rb = torch.load(a), torch.load(b)
+    assert abs(ra["losses"][0] - rb["losses"][0]) < 2e-2
+    for x, y in zip(ra["losses"], rb["losses"]):
+        assert abs(x - y) < 5e-2, (ra, rb)
+    for x, y in zip(ra["norms"], rb["norms"]):
+        assert abs(x - y) < 0.25 * max(y, 1e-3), (ra, rb)

@@ -30,7 +30,7 @@ def _shard_of(full: torch.Tensor, spec) -> torch.Tensor:
     return torch.cat([full.narrow(dim, lo, hi - lo) for _, lo, hi in spec.tp_pieces], dim)
 
 
-def _worker(rank, world, port, n_micro, out):
+def _worker(rank, world, port, n_micro, vocab_parallel, out):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
@@ -40,7 +40,7 @@ def _worker(rank, world, port, n_micro, out):
         cfg = get_config("test_tiny_qk", num_layers=3)
         tp = TPContext(group=groups[pp_rank], device="cpu")
         assert tp.rank == tp_rank and tp.world == tp_size
-        stage = GPT(cfg, device="cpu", seed=9, tp=tp, pp_size=pp_size, pp_rank=pp_rank)
+        stage = GPT(cfg, device="cpu", seed=9, tp=tp, pp_size=pp_size, pp_rank=pp_rank, vocab_parallel=vocab_parallel)
         full = GPT(cfg, device="cpu", seed=9)
         for slot in stage.arena.slots:
             assert torch.equal(slot.main, _shard_of(full.arena.by_name[slot.name].main, slot.spec)), slot.name
@@ -74,10 +74,10 @@ def _worker(rank, world, port, n_micro, out):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("n_micro", [1, 4])
-def test_tp2_pp2_matches_unsplit_model(tmp_path, n_micro):
+@pytest.mark.parametrize("n_micro,vocab_parallel", [(1, False), (4, False), (4, True)])
+def test_tp2_pp2_matches_unsplit_model(tmp_path, n_micro, vocab_parallel):
     out = str(tmp_path / "r.pt")
-    mp.spawn(_worker, args=(4, _free_port(), n_micro, out), nprocs=4, join=True)
+    mp.spawn(_worker, args=(4, _free_port(), n_micro, vocab_parallel, out), nprocs=4, join=True)
     assert torch.load(out)["ok"]
 
 
