@@ -131,7 +131,10 @@ def main() -> int:
                     help="gradient bucket size in elements (default: 128 Mi for the rank-local index mode, whose "
                          "per-bucket chain of kernels has a fixed cost; the trainer's 16 Mi otherwise)")
     ap.add_argument("--sga-score", type=str, default="abs_g", choices=("abs_g", "abs_m", "update", "coi"))
-    ap.add_argument("--sga-checks", action="store_true", help="leave the engine's cross-rank checks at their defaults")
+    ap.add_argument("--sga-checks", action="store_true",
+                    help="accepted for older command lines: the engine's cross-rank checks are at their defaults (on) anyway")
+    ap.add_argument("--no-sga-checks", action="store_true",
+                    help="switch every cross-rank consistency check of the engine off (the engine prints its escape-hatch warning)")
     ap.add_argument("--no-exposed", action="store_true", help="skip the exposed-synchronisation measurement")
     ns = ap.parse_args()
     if ns.impl == "reference":
@@ -162,7 +165,7 @@ def main() -> int:
                     sga_optimizer="adamw", sga_selection_locality="rank_local",
                     sga_cycle_period=ns.cycle_period or 0, sga_cycle_start_iter=0,
                     sga_bucket_elems=ns.bucket_elems or (128 << 20))
-        if not ns.sga_checks:
+        if ns.no_sga_checks:
             over.update(sga_checks=False)
     elif ns.mode == "sga":
         over.update(sga_enabled=True, sga_score="abs_g", sga_selection="topk", sga_selection_method="histogram",
@@ -336,6 +339,8 @@ def main() -> int:
                             % (ns.ratio_percent, ns.cycle_period or 4))) if ns.mode == "sga" else None,
                    "transport": tr.ddp.transport, "bucket_elems": int(getattr(args, "sga_bucket_elems", 0)),
                    "sharded_optimizer_step": bool(tr.sharded_state),
+                   "engine_checks": ("defaults (on)" if bool(getattr(args, "sga_checks", True)) else "off")
+                   if ns.mode == "sga" else None,
                    "l2": "inputs larger than L2 (weights %.1f GB, grads %.1f GB per rank)" % (
                        2e-9 * tr.model.arena.numel, 4e-9 * tr.model.arena.numel),
                    "params": tr.cfg.num_params()},
