@@ -304,7 +304,7 @@ def main() -> int:
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
             return float(t.item())
 
-        n_exp = 2
+        n_exp = 2 if K < 10 else 1  # long runs (many timed steps) keep this side measurement short
         with_sync = _timed_steps(n_exp, step_id + K + 2)
         tr.ddp.null_sync = True
         without = _timed_steps(n_exp, step_id + K + 4)
