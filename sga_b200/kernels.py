@@ -54,6 +54,7 @@ register_sigs({
     "sga_ipc_close": [_P],
     "sga_p2p_allreduce": [_P, _P, _L, _F, _P, _P, _F, _I, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P],
     "sga_p2p_mask_union": [_P, _P, _P, _P, _L, _F, _P, _P, _P, _P, _I, _P, _I, _P],
+    "sga_nvls_allreduce": [_P, _P, _P, _L, _F, _I, _P, _P, _P, _I, _I, _P],
     "sga_index_sync": [_P, _P, _P],
     "sga_dense_adamw_ag": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _P, _P, _I, _P, _F, _F, _F, _F, _F, _F, _F,
                            _I, _I, _P],

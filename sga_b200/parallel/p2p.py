@@ -98,6 +98,23 @@ def allreduce_(ch: PeerChannel, buf: SymmBuffer, offset_bytes: int, n: int, *, s
     _chk(rc, "sga_p2p_allreduce")
 
 
+def nvls_allreduce_(ch: PeerChannel, buf: SymmBuffer, offset_bytes: int, n: int, *, scale: float = 1.0,
+                    rs_only=False, sumsq_out=None, accumulate=False, max_ctas: int = 0) -> bool:
+    """The dense all-reduce (or its reduce-scatter form) through the NVSwitch's in-switch reduction, for a
+    buffer bound to a multicast object (``buf.mc_ptr``). Returns False, having launched nothing, when the
+    buffer has no multicast mapping or the range is not a whole number of 16-byte groups: the caller then
+    takes :func:`allreduce_`."""
+    if not getattr(buf, "mc_ptr", 0) or n % 4 or offset_bytes % 16:
+        return False
+    d = ch.next_desc()
+    rc = lib().sga_nvls_allreduce(ctypes.byref(d), ctypes.c_void_p(buf.local_ptr + offset_bytes),
+                                  ctypes.c_void_p(buf.mc_ptr + offset_bytes), int(n), float(scale), int(rs_only),
+                                  ch.norm_slots(), ch.cta_partials.data_ptr(), _p(sumsq_out), int(accumulate),
+                                  max_ctas, _st())
+    _chk(rc, "sga_nvls_allreduce")
+    return True
+
+
 def mask_union_reduce_(ch: PeerChannel, grad: SymmBuffer, grad_off: int, bits: SymmBuffer, bits_off: int,
                        ubits: SymmBuffer, ubits_off: int, n: int, *, scale: float = 1.0, mask_u8=None,
                        sumsq_out=None, accumulate=False, count_out=None, max_ctas: int = 0) -> None:

@@ -49,6 +49,8 @@ class SymmBuffer:
     world: int
     rank: int
     _opened: list = field(default_factory=list)
+    mc_ptr: int = 0            # the buffer through an NVLink multicast mapping (0: not bound to one)
+    _keep: object = None       # what owns the memory when it did not come from sga_symm_alloc
 
     def view(self, dtype, offset_bytes: int = 0, numel: int | None = None) -> torch.Tensor:
         sz = _DT_SIZE[dtype]
@@ -129,3 +131,53 @@ class SymmPool:
         for b in self.buffers:
             L.sga_symm_free(b.local_ptr)
         self.buffers = []
+
+
+class McastPool(SymmPool):
+    """Symmetric buffers that are also bound to an NVLink multicast object, so that a kernel can reduce
+    a buffer inside the NVSwitch (``multimem.ld_reduce``) and broadcast through it (``multimem.st``).
+    Allocation, the exchange of the handles and the multicast binding are ``torch.distributed``'s
+    symmetric memory; this class only adapts its handles to :class:`SymmBuffer`. A buffer whose
+    ``mc_ptr`` is 0 (no multicast support on this system) still has its peer pointers and serves the
+    peer-load kernels unchanged.
+
+    Gated: nothing takes this pool unless the trainer is started with ``--nvls-dense``. A rank that
+    dies while its memory is bound to a multicast object can raise NVLink faults on the other ranks'
+    GPUs, so failure tests must not run with it."""
+
+    def __init__(self, group=None, device=None):
+        super().__init__(group=group, device=device)
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self._symm_mem = symm_mem
+        self._handles = []
+
+    def alloc(self, nbytes: int) -> SymmBuffer:
+        nbytes = (int(nbytes) + 255) // 256 * 256
+        if self.world == 1:
+            return super().alloc(nbytes)
+        sm = self._symm_mem
+        with torch.cuda.device(self.device):
+            t = sm.empty(nbytes, dtype=torch.uint8, device=self.device)
+            t.zero_()
+            torch.cuda.synchronize(self.device)
+            group = self.group if self.group is not None else dist.group.WORLD
+            hdl = sm.rendezvous(t, group=group)
+        peers = [int(p) for p in hdl.buffer_ptrs]
+        if len(peers) != self.world or peers[self.rank] != t.data_ptr():
+            raise RuntimeError("symmetric-memory rendezvous returned an unexpected pointer table")
+        mc = int(getattr(hdl, "multicast_ptr", 0) or 0)
+        buf = SymmBuffer(nbytes, t.data_ptr(), peers, t, self.world, self.rank, [], mc_ptr=mc, _keep=(t, hdl))
+        self.buffers.append(buf)
+        self._handles.append(hdl)
+        dist.barrier(group=self.group)
+        return buf
+
+    def close(self) -> None:
+        torch.cuda.synchronize(self.device)
+        if self.world > 1 and dist.is_initialized():
+            dist.barrier(group=self.group)
+        own = [b for b in self.buffers if b._keep is None]
+        self.buffers = own          # buffers of the framework's allocator are released with their tensors
+        self._handles = []
+        super().close()

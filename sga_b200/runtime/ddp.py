@@ -31,6 +31,9 @@ class DDPConfig:
         self.overlap_grad_reduce = overlap_grad_reduce
         self.comm_max_ctas = comm_max_ctas
         self.use_distributed_optimizer = False
+        # dense all-reduce through the NVSwitch's in-switch reduction where the gradient buffer is bound to
+        # a multicast object (parallel.symm.McastPool); off unless asked for
+        self.nvls_dense = False
 
 
 class DataParallel:
@@ -190,8 +193,12 @@ class DataParallel:
         if self.transport == "p2p":
             from ..parallel import p2p
 
-            p2p.allreduce_(self.channel_for(bucket), self.arena.symm_grad, 4 * bucket.start, bucket.numel,
-                           scale=self.gradient_scaling_factor, max_ctas=self.ddp_config.comm_max_ctas)
+            ch, buf = self.channel_for(bucket), self.arena.symm_grad
+            if not (self.ddp_config.nvls_dense and p2p.nvls_allreduce_(
+                    ch, buf, 4 * bucket.start, bucket.numel, scale=self.gradient_scaling_factor,
+                    max_ctas=self.ddp_config.comm_max_ctas)):
+                p2p.allreduce_(ch, buf, 4 * bucket.start, bucket.numel, scale=self.gradient_scaling_factor,
+                               max_ctas=self.ddp_config.comm_max_ctas)
         elif self.transport in ("nccl", "gloo"):
             if self.ddp_config.average_in_collective and self.transport == "nccl":
                 dist.all_reduce(g, op=dist.ReduceOp.AVG, group=self.group)

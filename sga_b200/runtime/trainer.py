@@ -101,6 +101,10 @@ def add_trainer_args(p: argparse.ArgumentParser) -> argparse.ArgumentParser:
                    help="draw the initial weights with the device generator (large models)")
     g.add_argument("--tp-comm", type=str, default="auto", choices=("auto", "fused", "library"),
                    help="tensor-parallel linears: collective fused into the GEMM kernel, or library collectives")
+    g.add_argument("--nvls-dense", action="store_true",
+                   help="dense gradient all-reduce through the NVSwitch's in-switch reduction (multimem): the "
+                        "gradient arena is allocated as torch.distributed symmetric memory bound to a multicast "
+                        "object; buffers without multicast support keep the peer-load kernels")
     g.add_argument("--vocab-parallel-embedding", action="store_true",
                    help="under tensor parallelism shard the embedding and the output layer by vocabulary rows "
                         "instead of replicating them (two library collectives per micro-batch)")
@@ -339,9 +343,10 @@ class Trainer:
                 print("[train] the data-parallel group spans hosts (or more than 8 ranks): transport nccl, "
                       "dense steps by all-reduce", flush=True)
         if cuda and transport in ("auto", "p2p"):
-            from ..parallel.symm import SymmPool
+            from ..parallel.symm import McastPool, SymmPool
 
-            self.pool = SymmPool(group=self.dp_group, device=self.device)
+            pool_cls = McastPool if getattr(args, "nvls_dense", False) else SymmPool
+            self.pool = pool_cls(group=self.dp_group, device=self.device)
         self.tp = None
         if self.tp_size > 1:
             from ..parallel.tp import TPContext
@@ -375,6 +380,7 @@ class Trainer:
                                                 if self.pp_rank < self.pp_size - 1 else None))
         ddp_cfg = DDPConfig(average_in_collective=True, overlap_grad_reduce=bool(args.overlap_grad_reduce),
                             comm_max_ctas=args.comm_max_ctas)
+        ddp_cfg.nvls_dense = bool(getattr(args, "nvls_dense", False))
         if getattr(args, "sga_backend_timer", None):
             ddp_cfg.overlap_grad_reduce = False
         if self.tp is not None:
@@ -607,9 +613,11 @@ class Trainer:
     def _rs_bucket_sync(self, bucket) -> None:
         from ..parallel import p2p
 
-        p2p.allreduce_(self.ddp.channel_for(bucket), self.model.arena.symm_grad, 4 * bucket.start, bucket.numel,
-                       scale=self.ddp.gradient_scaling_factor, rs_only=True, sumsq_out=self._dev_sumsq,
-                       accumulate=True, max_ctas=self.ddp.ddp_config.comm_max_ctas)
+        ch, buf = self.ddp.channel_for(bucket), self.model.arena.symm_grad
+        kw = dict(scale=self.ddp.gradient_scaling_factor, rs_only=True, sumsq_out=self._dev_sumsq, accumulate=True,
+                  max_ctas=self.ddp.ddp_config.comm_max_ctas)
+        if not (self.ddp.ddp_config.nvls_dense and p2p.nvls_allreduce_(ch, buf, 4 * bucket.start, bucket.numel, **kw)):
+            p2p.allreduce_(ch, buf, 4 * bucket.start, bucket.numel, **kw)
 
     def _dense_step(self) -> None:
         arena = self.model.arena
