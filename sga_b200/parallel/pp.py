@@ -57,6 +57,29 @@ class Pipeline:
         for r in reqs:
             r.wait()
 
+    # ----------------------------------------------------------- validation
+    def run_forward(self, micro_batches):
+        """Forward passes only (the validation pass): every micro-batch goes down the stages once, nothing is
+        kept for a backward pass and no gradient is written. Returns the micro-batch losses on the last
+        stage, an empty list elsewhere."""
+        model = self.model
+        B, S = micro_batches[0][0].shape
+        act_shape = (B * S // getattr(model, "tp_size", 1), model.cfg.hidden)
+        losses = []
+        for tokens, targets in micro_batches:
+            x_in = None
+            if not self.first:
+                reqs, x_in = self._post(None, None, act_shape, self.prev_rank)
+                self._wait(reqs)
+            out, ctx = model.stage_forward(tokens, targets, x_in, loss_scale=1.0, write_grad=False)
+            ctx.clear()
+            if self.last:
+                losses.append(out)
+            else:
+                reqs, _ = self._post(out, self.next_rank, None, None)
+                self._wait(reqs)
+        return losses
+
     # ------------------------------------------------------------- schedule
     def run(self, micro_batches, *, loss_scale: float, on_param_done_last: Optional[Callable] = None,
             before_last_backward: Optional[Callable] = None):

@@ -290,9 +290,6 @@ class Trainer:
                              "head dimension, hidden and FFN sizes must be multiples of 8")
         self.tp_size = max(1, int(args.tensor_model_parallel_size))
         self.pp_size = max(1, int(args.pipeline_model_parallel_size or 1))
-        if self.pp_size > 1 and int(getattr(args, "eval_interval", 0) or 0) > 0:
-            raise NotImplementedError("--eval-interval with pipeline stages: the validation pass has no "
-                                      "forward-only pipeline schedule; run validation without pipeline parallelism")
         mp = self.tp_size * self.pp_size
         assert self.world % mp == 0, "world size must be a multiple of tensor-parallel x pipeline-parallel size"
         self.dp_world = self.world // mp
@@ -468,8 +465,6 @@ class Trainer:
     def evaluate(self, iters: int) -> float:
         """Mean token loss over ``iters`` global batches of the validation stream, forward passes only,
         averaged over the data-parallel ranks. Touches neither gradients nor optimizer state."""
-        if self.pp_size > 1:
-            raise NotImplementedError("validation under pipeline parallelism is not implemented")
         if getattr(self, "_eval_data", None) is None:
             a, cuda = self.args, self.device.type == "cuda"
             path = getattr(a, "eval_data_path", None) or getattr(a, "data_path", None)
@@ -484,11 +479,22 @@ class Trainer:
         total = torch.zeros((), dtype=torch.float32, device=self.device)
         for step in range(iters):
             batch = self._eval_data.batch(step, self.dp_rank * per_rank, per_rank).to(self.device, non_blocking=True)
+            if self.pipeline is not None:
+                mbs = [(batch[i * mb:(i + 1) * mb][:, :-1], batch[i * mb:(i + 1) * mb][:, 1:])
+                       for i in range(self.num_micro)]
+                for loss in self.pipeline.run_forward(mbs):   # the last stage holds the losses
+                    total += loss
+                continue
             for i in range(self.num_micro):
                 chunk = batch[i * mb:(i + 1) * mb]
                 total += self.model.forward_backward(chunk[:, :-1], chunk[:, 1:], backward=False,
                                                      reduce_replicated=False)
         total /= max(iters * self.num_micro, 1)
+        if self.pipeline is not None:
+            # hand the last stage's mean to every stage of the replica
+            t = total.reshape(1).clone()
+            dist.broadcast(t, src=self._last_stage_peer, group=self.pp_group)
+            total = t[0]
         if self.dp_world > 1:
             dist.all_reduce(total, group=self.dp_group)
             total /= self.dp_world

@@ -88,13 +88,14 @@ def _trainer_worker(rank, world, port, pp, sga, out):
                   sga_backend="torch_pipelined_index", sga_selection_locality="rank_local", sga_cycle_period=3,
                   untie_embeddings_and_output_weights=True)
     tr = Trainer(default_args(**kw), quiet=True)
+    ev0 = tr.evaluate(1)   # forward-only schedule over the stages, before any update: same weights in both layouts
     losses, norms = [], []
     for s in range(4):
         losses.append(float(tr.train_step(tr.host_batch(s))))
         gn = tr.last_grad_norm
         norms.append(float(gn.item()) if hasattr(gn, "item") else float(gn))
     if rank == 0:
-        torch.save({"losses": losses, "norms": norms}, out)
+        torch.save({"losses": losses, "norms": norms, "eval0": ev0}, out)
     tr.close()
     dist.destroy_process_group()
 
@@ -106,6 +107,7 @@ def test_pp2_dp2_trainer_tracks_dp2(tmp_path, sga):
     mp.spawn(_trainer_worker, args=(2, _free_port(), 1, sga, b), nprocs=2, join=True)
     ra, rb = torch.load(a), torch.load(b)
     ltol, ntol = (5e-2, 0.25) if sga else (2e-2, 0.05)
+    assert abs(ra["eval0"] - rb["eval0"]) < 2e-3 * max(1.0, abs(rb["eval0"])), (ra["eval0"], rb["eval0"])
     assert abs(ra["losses"][0] - rb["losses"][0]) < 2e-2
     for x, y in zip(ra["losses"], rb["losses"]):
         assert abs(x - y) < ltol, (ra, rb)

@@ -95,6 +95,7 @@ def _trainer_worker(rank, world, port, tp_size, pp_size, sga, out):
     tr = Trainer(default_args(**kw), quiet=True)
     assert (tr.tp_rank, tr.pp_rank, tr.dp_rank) == (rank % tp_size, rank // (tp_size * tr.dp_world),
                                                     (rank // tp_size) % tr.dp_world)
+    ev0 = tr.evaluate(1)
     losses, norms = [], []
     for s in range(4):
         losses.append(float(tr.train_step(tr.host_batch(s))))
@@ -107,7 +108,7 @@ def _trainer_worker(rank, world, port, tp_size, pp_size, sga, out):
                 dist.all_gather(parts, slot.main.contiguous(), group=tr.tp_group)
                 assert all(torch.equal(parts[0], p) for p in parts), slot.name
     if rank == 0:
-        torch.save({"losses": losses, "norms": norms}, out)
+        torch.save({"losses": losses, "norms": norms, "eval0": ev0}, out)
     tr.close()
     if dist.is_initialized():
         dist.destroy_process_group()
@@ -121,6 +122,7 @@ def test_tp2_pp2_trainer_tracks_single_rank(tmp_path, sga):
     ra, rb = torch.load(a), torch.load(b)
     # sparse steps select per bucket, and the sharded, staged model has other buckets: close, not equal
     ltol, ntol = (5e-2, 0.25) if sga else (2e-2, 0.05)
+    assert abs(ra["eval0"] - rb["eval0"]) < 2e-3 * max(1.0, abs(rb["eval0"])), (ra["eval0"], rb["eval0"])
     assert abs(ra["losses"][0] - rb["losses"][0]) < 2e-2
     for x, y in zip(ra["losses"], rb["losses"]):
         assert abs(x - y) < ltol, (ra, rb)
