@@ -352,14 +352,14 @@ class Trainer:
             if tp_comm == "auto":
                 tp_comm = "fused" if (cuda and transport in ("auto", "p2p")) else "library"
             self.tp = TPContext(group=self.tp_group, device=self.device, transport=tp_comm)
-        self.sga = bool(args.sga_enabled)
+        self.sga = bool(getattr(args, "sga_enabled", False))  # the one gate: nothing else of sga_* is read when it is off
         if self.sga and self.tp_size > 1 and getattr(args, "sga_selection_locality", "shared") != "rank_local":
             raise NotImplementedError(
                 "SGA under tensor parallelism needs --sga-selection-locality rank_local: a shared support's "
                 "threshold is global over the model, so it would differ between tensor-parallel ranks and "
                 "select different coordinates of the parameters they replicate")
         need_comm = (self.sga and getattr(args, "sga_selection_locality", "shared") == "rank_local"
-                     and args.sga_backend != "torch_pipelined_mask")
+                     and getattr(args, "sga_backend", None) != "torch_pipelined_mask")
         self.model = GPT(self.cfg, device=self.device, pool=self.pool,
                          bucket_elems=getattr(args, "sga_bucket_elems", 16 << 20), seed=args.seed,
                          need_comm_staging=need_comm, tp=self.tp,
