@@ -8,7 +8,6 @@ external training stack are inert without the flag).
 """
 import argparse
 
-import pytest
 import torch
 
 import sga_b200.runtime.trainer as T
